@@ -1,0 +1,870 @@
+// C-ABI layer: table life cycle, option checks, the stream-ordered group lock
+// and one thin function per operation of include/hkv_b200.h.
+//
+// Host logic follows the reference's HashTable methods
+// (include/merlin_hashtable.cuh: init 984-1089, check_evict_strategy 3832-3861,
+// export clamp 3206-3212, size 3424-3451) and create_table
+// (include/merlin/core_kernels.cuh:327-381).
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/hkv_b200.h"
+#include "hkv_device.cuh"
+#include "hkv_internal.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+struct HkvError {
+  int code;
+  std::string msg;
+};
+
+#define HKV_CUDA(call)                                                                   \
+  do {                                                                                   \
+    cudaError_t e_ = (call);                                                             \
+    if (e_ != cudaSuccess) {                                                             \
+      throw HkvError{HKV_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_)};  \
+    }                                                                                    \
+  } while (0)
+
+#define HKV_CHECK(cond, msg)                               \
+  do {                                                     \
+    if (!(cond)) throw HkvError{HKV_ERR_MERLIN, (msg)};    \
+  } while (0)
+
+// ---- stream-ordered group lock ----------------------------------------------
+//
+// The reference serialises readers / updaters / inserters with a host+device
+// mutex: every acquire launches a one-thread kernel and synchronises a side
+// stream, every release is another one-thread kernel
+// (include/merlin/group_lock.cuh:57-337, core_kernels/group_lock_kernels.cuh).
+// Here the same exclusion (readers share, updaters share, inserters are alone)
+// is expressed as stream dependencies: an operation makes ITS stream wait on
+// the completion events of the incompatible operations enqueued before it on
+// OTHER streams, and leaves an event behind for later ones.  Nothing blocks on
+// the host and no extra kernel runs; operations on one stream are ordered by
+// the stream itself.
+enum Group : int { kReader = 0, kUpdater = 1, kInserter = 2 };
+
+class StreamGroupLock {
+ public:
+  ~StreamGroupLock() {
+    for (auto& e : entries_) cudaEventDestroy(e.event);
+  }
+
+  // Held from acquire() to release() by the enqueueing host thread.
+  void acquire(Group g, cudaStream_t stream) {
+    mu_.lock();
+    for (auto& e : entries_) {
+      if (!e.pending || e.stream == stream) continue;
+      const bool compatible = (e.group == g) && g != kInserter;
+      if (compatible) continue;
+      if (cudaEventQuery(e.event) == cudaSuccess) {
+        e.pending = false;
+        continue;
+      }
+      cudaStreamWaitEvent(stream, e.event, 0);
+    }
+    if (g == kInserter) {
+      // everything enqueued before is now ordered before this operation
+      for (auto& e : entries_) {
+        if (e.stream != stream) e.pending = false;
+      }
+    }
+  }
+
+  void release(Group g, cudaStream_t stream) {
+    Entry* slot = nullptr;
+    for (auto& e : entries_) {
+      if (e.stream == stream && e.group == g) {
+        slot = &e;
+        break;
+      }
+    }
+    if (slot == nullptr) {
+      for (auto& e : entries_) {
+        if (!e.pending) {
+          slot = &e;
+          break;
+        }
+      }
+    }
+    if (slot == nullptr) {
+      Entry e{};
+      if (cudaEventCreateWithFlags(&e.event, cudaEventDisableTiming) != cudaSuccess) {
+        mu_.unlock();
+        throw HkvError{HKV_ERR_CUDA, "cudaEventCreateWithFlags failed in the group lock"};
+      }
+      entries_.push_back(e);
+      slot = &entries_.back();
+    }
+    slot->stream = stream;
+    slot->group = g;
+    slot->pending = true;
+    cudaEventRecord(slot->event, stream);
+    mu_.unlock();
+  }
+
+  void abandon() { mu_.unlock(); }
+
+ private:
+  struct Entry {
+    cudaEvent_t event;
+    cudaStream_t stream;
+    Group group;
+    bool pending;
+  };
+  std::mutex mu_;
+  std::vector<Entry> entries_;
+};
+
+}  // namespace
+
+struct hkv_table {
+  hkv_options opt{};
+  hkv::TableView view{};
+  hkv_allocator alloc{};
+  bool own_allocator = true;
+  std::atomic<uint64_t> global_epoch{hkv::kIgnoredEpoch};
+  unsigned long long* d_scratch = nullptr;  // counters for size / count overloads
+  StreamGroupLock lock;
+  int device = 0;
+  void* meta_block = nullptr;  // digests + keys + scores + sizes + status
+  void* host_rows = nullptr;   // host address of the pinned value rows
+};
+
+namespace {
+
+int default_alloc(void*, int type, void** ptr, size_t size, unsigned int flags) {
+  switch (type) {
+    case HKV_MEM_DEVICE: return cudaMalloc(ptr, size);
+    case HKV_MEM_PINNED: return cudaHostAlloc(ptr, size, flags);
+    default:
+      *ptr = std::malloc(size);
+      return *ptr ? 0 : int(cudaErrorMemoryAllocation);
+  }
+}
+
+int default_free(void*, int type, void* ptr) {
+  switch (type) {
+    case HKV_MEM_DEVICE: return cudaFree(ptr);
+    case HKV_MEM_PINNED: return cudaFreeHost(ptr);
+    default: std::free(ptr); return 0;
+  }
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+    else prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+struct LockScope {
+  hkv_table* t;
+  Group g;
+  cudaStream_t s;
+  bool held;
+  LockScope(hkv_table* table, Group group, cudaStream_t stream)
+      : t(table), g(group), s(stream), held(table->opt.api_lock != 0) {
+    if (held) t->lock.acquire(g, s);
+  }
+  // Called after the kernels were enqueued.
+  void done() {
+    if (held) {
+      held = false;
+      t->lock.release(g, s);
+    }
+  }
+  ~LockScope() {
+    if (held) t->lock.abandon();
+  }
+};
+
+template <class F>
+int guarded(F&& f) {
+  try {
+    f();
+    return HKV_OK;
+  } catch (const HkvError& e) {
+    g_last_error = e.msg;
+    return e.code;
+  } catch (const std::bad_alloc&) {
+    g_last_error = "out of host memory";
+    return HKV_ERR_RUNTIME;
+  } catch (const std::exception& e) {
+    g_last_error = e.what();
+    return HKV_ERR_RUNTIME;
+  }
+}
+
+void check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    throw HkvError{HKV_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(e)};
+  }
+}
+
+uint32_t widest_vec(uint64_t row_bytes) {
+  for (uint32_t v = 16; v > 1; v >>= 1) {
+    if (row_bytes % v == 0) return v;
+  }
+  return 1;
+}
+
+// View whose row access width also respects the alignment of the caller's
+// batch buffers.
+hkv::TableView view_for(const hkv_table* t, const void* a, const void* b = nullptr) {
+  hkv::TableView v = t->view;
+  uint32_t vec = v.vec_bytes;
+  auto lower = [&](const void* p) {
+    if (p == nullptr) return;
+    while (vec > 1 && (reinterpret_cast<uintptr_t>(p) % vec) != 0) vec >>= 1;
+  };
+  lower(a);
+  lower(b);
+  if (vec != v.vec_bytes) {
+    v.vec_bytes = vec;
+    v.chunks_per_row = v.row_bytes / vec;
+    int shift = -1;
+    if ((v.chunks_per_row & (v.chunks_per_row - 1)) == 0) {
+      shift = 0;
+      while ((1u << shift) < v.chunks_per_row) ++shift;
+    }
+    v.chunks_per_row_shift = shift;
+  }
+  return v;
+}
+
+// check_evict_strategy, include/merlin_hashtable.cuh:3832-3861
+void check_strategy(const hkv_table* t, int strategy, const uint64_t* scores) {
+  if (strategy == HKV_LRU || strategy == HKV_EPOCH_LRU) {
+    HKV_CHECK(scores == nullptr,
+              "the scores should not be specified when running on LRU or Epoch LRU mode.");
+  }
+  if (strategy == HKV_LFU || strategy == HKV_EPOCH_LFU) {
+    HKV_CHECK(scores != nullptr,
+              "the scores should be specified when running on LFU or Epoch LFU mode.");
+  }
+  if (strategy == HKV_CUSTOMIZED) {
+    HKV_CHECK(scores != nullptr, "the scores should be specified when running on customized mode.");
+  }
+  if (strategy == HKV_EPOCH_LRU || strategy == HKV_EPOCH_LFU) {
+    HKV_CHECK(t->global_epoch.load() != hkv::kIgnoredEpoch,
+              "the global_epoch is invalid and should be assigned by calling `set_global_epoch` "
+              "when running on Epoch LRU or Epoch LFU mode.");
+  }
+}
+
+hkv::MutateArgs base_args(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
+                          const uint64_t* scores, bool ignore_strategy) {
+  hkv::MutateArgs a;
+  a.keys = keys;
+  a.n = n;
+  a.values = static_cast<uint8_t*>(const_cast<void*>(values));
+  a.scores = scores;
+  // ignore_evict_strategy re-dispatches as kCustomized with the epoch ignored
+  // (include/merlin_hashtable.cuh:1131-1133)
+  a.strategy = ignore_strategy ? int(HKV_CUSTOMIZED) : t->opt.evict_strategy;
+  a.epoch = t->global_epoch.load();
+  return a;
+}
+
+void mutate(hkv_table* t, int op, hkv::MutateArgs& args, const hkv::TableView& v, Group g,
+            bool unique_key, cudaStream_t stream) {
+  DeviceGuard dg(t->device);
+  LockScope ls(t, g, stream);
+  hkv::launch_mutate(op, v, args, unique_key, stream);
+  ls.done();
+  check_launch();
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* hkv_last_error(void) { return g_last_error.c_str(); }
+
+int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator, hkv_table** out) {
+  return guarded([&] {
+    if (options == nullptr || out == nullptr) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "options and out must not be null"};
+    }
+    const hkv_options& o = *options;
+    HKV_CHECK(o.table_mode == 0,
+              "[MEMORY_MODE] dual-bucket tables are not part of this library.");
+    HKV_CHECK(o.reserved_key_start_bit >= 0 && o.reserved_key_start_bit <= 62,
+              "options.reserved_key_start_bit should >= 0 and <= 62.");
+    HKV_CHECK(o.max_bucket_size != 0 && (o.max_bucket_size & (o.max_bucket_size - 1)) == 0,
+              "Bucket size should be the pow of 2");
+    HKV_CHECK(o.max_bucket_size == hkv::kBucketSlots,
+              "only max_bucket_size == 128 is supported by this library.");
+    HKV_CHECK(o.num_of_buckets_per_alloc != 0 &&
+                  (o.num_of_buckets_per_alloc & (o.num_of_buckets_per_alloc - 1)) == 0,
+              "Then `num_of_buckets_per_alloc` should be the pow of 2");
+    HKV_CHECK(o.init_capacity >= o.num_of_buckets_per_alloc * o.max_bucket_size,
+              "Then `num_of_buckets_per_alloc` must be equal or less than initial required "
+              "buckets number");
+    HKV_CHECK(!(o.io_by_cpu && o.max_hbm_for_vectors != 0),
+              "[HierarchicalKV] `io_by_cpu` should not be true when `max_hbm_for_vectors` is "
+              "not 0!");
+    HKV_CHECK(!o.io_by_cpu, "`io_by_cpu` is not part of this library.");
+    HKV_CHECK(o.score_size == 8, "only 64-bit scores are supported by this library.");
+    HKV_CHECK(o.evict_strategy >= HKV_LRU && o.evict_strategy <= HKV_CUSTOMIZED,
+              "unknown evict strategy");
+    HKV_CHECK(o.dim > 0 && o.value_size > 0, "dim and value_size must be positive");
+
+    auto* t = new hkv_table();
+    try {
+      t->opt = o;
+      if (allocator != nullptr) {
+        t->alloc = *allocator;
+        t->own_allocator = false;
+      } else {
+        t->alloc = hkv_allocator{nullptr, default_alloc, default_free};
+      }
+      if (o.device_id >= 0) {
+        HKV_CUDA(cudaSetDevice(o.device_id));
+        t->device = o.device_id;
+      } else {
+        HKV_CUDA(cudaGetDevice(&t->device));
+        t->opt.device_id = t->device;
+      }
+
+      // create_table, include/merlin/core_kernels.cuh:336-356
+      const uint64_t max_size = o.init_capacity > o.max_capacity ? o.init_capacity : o.max_capacity;
+      uint64_t buckets;
+      if (o.init_capacity * 2 > max_size) {
+        buckets = 1 + (max_size - 1) / hkv::kBucketSlots;
+      } else {
+        buckets = 1;
+        while (buckets * hkv::kBucketSlots < o.init_capacity) buckets *= 2;
+      }
+      const uint64_t capacity = buckets * hkv::kBucketSlots;
+      HKV_CHECK(capacity <= (1ull << 31), "capacity above 2^31 slots is not supported.");
+      const uint64_t row_bytes = o.dim * uint64_t(o.value_size);
+      HKV_CHECK(row_bytes < (1ull << 24), "value rows above 16 MiB are not supported.");
+
+      hkv::TableView& v = t->view;
+      v.buckets = buckets;
+      v.capacity = capacity;
+      v.row_bytes = uint32_t(row_bytes);
+      v.vec_bytes = widest_vec(row_bytes);
+      v.chunks_per_row = uint32_t(row_bytes / v.vec_bytes);
+      v.chunks_per_row_shift = -1;
+      if ((v.chunks_per_row & (v.chunks_per_row - 1)) == 0) {
+        int s = 0;
+        while ((1u << s) < v.chunks_per_row) ++s;
+        v.chunks_per_row_shift = s;
+      }
+      v.capacity_pow2 = (capacity & (capacity - 1)) == 0 ? 1u : 0u;
+
+      // reserved keys, include/merlin/types.cuh:80-109
+      const int bit = o.reserved_key_start_bit;
+      if (bit == 0) {
+        v.empty_key = 0xFFFFFFFFFFFFFFFFull;
+        v.reclaim_key = 0xFFFFFFFFFFFFFFFEull;
+        v.locked_key = 0xFFFFFFFFFFFFFFFDull;
+        v.reserved_mask = 0xFFFFFFFFFFFFFFFCull;
+        v.reserved_value = 0xFFFFFFFFFFFFFFFCull;
+      } else {
+        const uint64_t m1 = ~(3ull << bit);
+        const uint64_t m2 = m1 & ~1ull;
+        v.reserved_mask = m1;
+        v.reserved_value = m2;
+        v.empty_key = m2 | (3ull << bit);
+        v.reclaim_key = (~(1ull << bit)) & ~1ull;
+        v.locked_key = v.empty_key & ~(2ull << bit);
+      }
+      const uint32_t ed = uint32_t(hkv::fmix64(v.empty_key) >> 32) & 0xFFu;
+      v.empty_digest4 = ed * 0x01010101u;
+      v.reclaim_digest = uint32_t(hkv::fmix64(v.reclaim_key) >> 32) & 0xFFu;
+
+      // one metadata block: digests | keys | scores | bucket sizes | status
+      auto align256 = [](uint64_t x) { return (x + 255) & ~255ull; };
+      const uint64_t off_digests = 0;
+      const uint64_t off_keys = align256(off_digests + capacity);
+      const uint64_t off_scores = align256(off_keys + capacity * 8);
+      const uint64_t off_sizes = align256(off_scores + capacity * 8);
+      const uint64_t off_status = align256(off_sizes + buckets * 4);
+      const uint64_t meta_bytes = off_status + 256;
+      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &t->meta_block, meta_bytes, 0) != 0 ||
+          t->meta_block == nullptr) {
+        cudaGetLastError();
+        throw HkvError{HKV_ERR_CUDA, "device allocation of the table metadata failed"};
+      }
+      uint8_t* mb = static_cast<uint8_t*>(t->meta_block);
+      v.digests = mb + off_digests;
+      v.keys = reinterpret_cast<uint64_t*>(mb + off_keys);
+      v.scores = reinterpret_cast<uint64_t*>(mb + off_scores);
+      v.bucket_sizes = reinterpret_cast<int32_t*>(mb + off_sizes);
+      v.status = reinterpret_cast<uint32_t*>(mb + off_status);
+      t->d_scratch = reinterpret_cast<unsigned long long*>(mb + off_status + 64);
+      HKV_CUDA(cudaMemset(mb + off_status, 0, 256));
+
+      // value rows: whole buckets in HBM while max_hbm_for_vectors lasts, the
+      // rest in mapped pinned host memory (static split by bucket index, as
+      // include/merlin/core_kernels.cuh:204-232 does per slice)
+      uint64_t hbm_buckets = o.max_hbm_for_vectors / (row_bytes * hkv::kBucketSlots);
+      if (hbm_buckets > buckets) hbm_buckets = buckets;
+      v.hbm_slots = hbm_buckets * hkv::kBucketSlots;
+      v.values_hbm = nullptr;
+      v.values_host = nullptr;
+      if (v.hbm_slots > 0) {
+        void* p = nullptr;
+        if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &p, v.hbm_slots * row_bytes, 0) != 0 ||
+            p == nullptr) {
+          cudaGetLastError();
+          throw HkvError{HKV_ERR_CUDA, "device allocation of the value rows failed"};
+        }
+        v.values_hbm = static_cast<uint8_t*>(p);
+      }
+      if (v.hbm_slots < capacity) {
+        void* p = nullptr;
+        const uint64_t bytes = (capacity - v.hbm_slots) * row_bytes;
+        if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_PINNED, &p, bytes,
+                           cudaHostAllocMapped | cudaHostAllocPortable) != 0 ||
+            p == nullptr) {
+          cudaGetLastError();
+          throw HkvError{HKV_ERR_CUDA, "pinned host allocation of the value rows failed"};
+        }
+        t->host_rows = p;
+        void* dp = nullptr;
+        HKV_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
+        v.values_host = static_cast<uint8_t*>(dp);
+      }
+      hkv::launch_clear(v, nullptr);
+      check_launch();
+      HKV_CUDA(cudaDeviceSynchronize());
+    } catch (...) {
+      hkv_table_destroy(t);
+      throw;
+    }
+    *out = t;
+  });
+}
+
+int hkv_table_destroy(hkv_table* t) {
+  if (t == nullptr) return HKV_OK;
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaDeviceSynchronize();
+    if (t->meta_block) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->meta_block);
+    if (t->view.values_hbm) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->view.values_hbm);
+    if (t->host_rows) t->alloc.free(t->alloc.ctx, HKV_MEM_PINNED, t->host_rows);
+    delete t;
+  });
+}
+
+int hkv_insert_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
+                         const uint64_t* scores, hkv_stream stream, int unique_key,
+                         int ignore_evict_strategy) {
+  return guarded([&] {
+    if (n == 0) return;
+    if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
+    if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
+    mutate(t, hkv::kOpInsertOrAssign, a, view_for(t, values), kInserter, unique_key != 0,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_insert_and_evict(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
+                         const uint64_t* scores, uint64_t* evicted_keys, void* evicted_values,
+                         uint64_t* evicted_scores, uint64_t* d_evicted_counter, hkv_stream stream,
+                         int unique_key, int ignore_evict_strategy) {
+  return guarded([&] {
+    if (n == 0) return;
+    if (t->view.hbm_slots < t->view.capacity) {
+      // include/merlin_hashtable.cuh:1384-1386
+      throw HkvError{HKV_ERR_RUNTIME, "Only allow insert_and_evict in pure HBM mode."};
+    }
+    if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
+    if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
+    a.evicted_keys = evicted_keys;
+    a.evicted_values = static_cast<uint8_t*>(evicted_values);
+    a.evicted_scores = evicted_scores;
+    a.evicted_counter = reinterpret_cast<unsigned long long*>(d_evicted_counter);
+    mutate(t, hkv::kOpInsertAndEvict, a, view_for(t, values, evicted_values), kInserter,
+           unique_key != 0, static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_insert_and_evict_count(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
+                               const uint64_t* scores, uint64_t* evicted_keys,
+                               void* evicted_values, uint64_t* evicted_scores, hkv_stream stream,
+                               int unique_key, int ignore_evict_strategy,
+                               uint64_t* evicted_count) {
+  return guarded([&] {
+    *evicted_count = 0;
+    if (n == 0) return;
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned long long* ctr = t->d_scratch + 1;
+    HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
+    int rc = hkv_insert_and_evict(t, n, keys, values, scores, evicted_keys, evicted_values,
+                                  evicted_scores, reinterpret_cast<uint64_t*>(ctr), stream,
+                                  unique_key, ignore_evict_strategy);
+    if (rc != HKV_OK) throw HkvError{rc, g_last_error};
+    unsigned long long h = 0;
+    HKV_CUDA(cudaMemcpyAsync(&h, ctr, sizeof(h), cudaMemcpyDeviceToHost, s));
+    HKV_CUDA(cudaStreamSynchronize(s));
+    *evicted_count = h;
+  });
+}
+
+int hkv_accum_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys,
+                        const void* value_or_deltas, const bool* accum_or_assigns,
+                        const uint64_t* scores, hkv_stream stream, int ignore_evict_strategy) {
+  return guarded([&] {
+    if (n == 0) return;
+    HKV_CHECK(t->opt.value_size == 4, "accum_or_assign adds float32 elements only.");
+    if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores, ignore_evict_strategy != 0);
+    if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
+    a.accum_flags = accum_or_assigns;
+    // the reference has no unique_key argument here and always runs its
+    // duplicate-tolerant tile kernel (include/merlin_hashtable.cuh:1618-1631)
+    mutate(t, hkv::kOpAccumOrAssign, a, view_for(t, value_or_deltas), kInserter, false,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_find_or_insert(hkv_table* t, uint64_t n, const uint64_t* keys, void* values,
+                       uint64_t* scores, hkv_stream stream, int unique_key,
+                       int ignore_evict_strategy) {
+  return guarded([&] {
+    if (n == 0) return;
+    if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
+    if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
+    mutate(t, hkv::kOpFindOrInsert, a, view_for(t, values), kInserter, unique_key != 0,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_find_or_insert_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void** values,
+                           bool* founds, uint64_t* scores, hkv_stream stream, int unique_key,
+                           int ignore_evict_strategy, uint64_t** locked_key_ptrs) {
+  return guarded([&] {
+    if (n == 0) return;
+    if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, ignore_evict_strategy != 0);
+    if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
+    a.ptrs = values;
+    a.founds = founds;
+    a.locked_key_ptrs = locked_key_ptrs;
+    mutate(t, hkv::kOpFindOrInsertPtr, a, t->view, kInserter, unique_key != 0,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_lock_keys(hkv_table* t, uint64_t n, const uint64_t* keys, uint64_t** locked_key_ptrs,
+                  bool* success, hkv_stream stream, const uint64_t* scores) {
+  return guarded([&] {
+    if (n == 0) return;
+    if (locked_key_ptrs == nullptr) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "locked_key_ptrs must not be null"};
+    }
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
+    a.founds = success;
+    a.locked_key_ptrs = locked_key_ptrs;
+    mutate(t, hkv::kOpLockKeys, a, t->view, kInserter, true, static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_unlock_keys(hkv_table* t, uint64_t n, uint64_t** locked_key_ptrs, const uint64_t* keys,
+                    bool* success, hkv_stream stream) {
+  return guarded([&] {
+    if (n == 0) return;
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LockScope ls(t, kInserter, s);
+    hkv::launch_unlock_keys(t->view, n, locked_key_ptrs, keys, success, s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
+               const uint64_t* scores, hkv_stream stream, int unique_key) {
+  return guarded([&] {
+    if (n == 0) return;
+    check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores, false);
+    mutate(t, hkv::kOpAssign, a, view_for(t, values), kUpdater, unique_key != 0,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_assign_scores(hkv_table* t, uint64_t n, const uint64_t* keys, const uint64_t* scores,
+                      hkv_stream stream, int unique_key) {
+  return guarded([&] {
+    if (n == 0) return;
+    check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
+    mutate(t, hkv::kOpAssignScores, a, t->view, kUpdater, unique_key != 0,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_assign_values(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
+                      hkv_stream stream, int unique_key) {
+  return guarded([&] {
+    if (n == 0) return;
+    hkv::MutateArgs a = base_args(t, n, keys, values, nullptr, false);
+    mutate(t, hkv::kOpAssignValues, a, view_for(t, values), kUpdater, unique_key != 0,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_find(hkv_table* t, uint64_t n, const uint64_t* keys, void* values, bool* founds,
+             uint64_t* scores, hkv_stream stream) {
+  return guarded([&] {
+    if (n == 0) return;
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LockScope ls(t, kReader, s);
+    hkv::launch_find(view_for(t, values), n, keys, values, founds, scores, s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_find_missed(hkv_table* t, uint64_t n, const uint64_t* keys, void* values,
+                    uint64_t* missed_keys, int* missed_indices, int* missed_size, uint64_t* scores,
+                    hkv_stream stream) {
+  return guarded([&] {
+    if (n == 0) return;
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    HKV_CUDA(cudaMemsetAsync(missed_size, 0, sizeof(int), s));
+    LockScope ls(t, kReader, s);
+    hkv::launch_find_missed(view_for(t, values), n, keys, values, missed_keys, missed_indices,
+                            missed_size, scores, s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_find_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void** values, bool* founds,
+                 uint64_t* scores, hkv_stream stream, int /*unique_key*/) {
+  return guarded([&] {
+    if (n == 0) return;
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LockScope ls(t, kReader, s);
+    hkv::launch_find_ptr(t->view, n, keys, values, founds, scores, s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_find_and_update(hkv_table* t, uint64_t n, const uint64_t* keys, void** values,
+                        bool* founds, uint64_t* scores, hkv_stream stream, int unique_key) {
+  return guarded([&] {
+    if (n == 0) return;
+    // scores are an input here for the strategies that take them and are
+    // overwritten with the stored score
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
+    a.scores_out = scores;
+    a.ptrs = values;
+    a.founds = founds;
+    mutate(t, hkv::kOpFindAndUpdate, a, t->view, kUpdater, unique_key != 0,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_contains(hkv_table* t, uint64_t n, const uint64_t* keys, bool* founds, hkv_stream stream) {
+  return guarded([&] {
+    if (n == 0) return;
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LockScope ls(t, kReader, s);
+    hkv::launch_contains(t->view, n, keys, founds, s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_erase(hkv_table* t, uint64_t n, const uint64_t* keys, hkv_stream stream) {
+  return guarded([&] {
+    if (n == 0) return;
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LockScope ls(t, kInserter, s);
+    hkv::launch_erase(t->view, n, keys, s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_clear(hkv_table* t, hkv_stream stream) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LockScope ls(t, kInserter, s);
+    hkv::launch_clear(t->view, s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_export_batch_if(hkv_table* t, int predicate, uint64_t pattern, uint64_t threshold,
+                        uint64_t n, uint64_t offset, uint64_t* d_counter, uint64_t* keys,
+                        void* values, uint64_t* scores, hkv_stream stream) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (predicate < HKV_PRED_ALL || predicate > HKV_PRED_SCORE_LESS_EQ) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "unknown predicate"};
+    }
+    LockScope ls(t, kReader, s);
+    HKV_CUDA(cudaMemsetAsync(d_counter, 0, sizeof(uint64_t), s));
+    if (offset < t->view.capacity) {
+      const uint64_t left = t->view.capacity - offset;
+      if (n > left) n = left;
+      hkv::launch_export(view_for(t, values), predicate, pattern, threshold, n, offset,
+                         reinterpret_cast<unsigned long long*>(d_counter), keys, values, scores,
+                         s);
+    }
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_export_batch(hkv_table* t, uint64_t n, uint64_t offset, uint64_t* d_counter,
+                     uint64_t* keys, void* values, uint64_t* scores, hkv_stream stream) {
+  return hkv_export_batch_if(t, HKV_PRED_ALL, 0, 0, n, offset, d_counter, keys, values, scores,
+                             stream);
+}
+
+int hkv_export_batch_count(hkv_table* t, uint64_t n, uint64_t offset, uint64_t* keys,
+                           void* values, uint64_t* scores, hkv_stream stream, uint64_t* count) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned long long* ctr = t->d_scratch + 2;
+    int rc = hkv_export_batch(t, n, offset, reinterpret_cast<uint64_t*>(ctr), keys, values,
+                              scores, stream);
+    if (rc != HKV_OK) throw HkvError{rc, g_last_error};
+    unsigned long long h = 0;
+    HKV_CUDA(cudaMemcpyAsync(&h, ctr, sizeof(h), cudaMemcpyDeviceToHost, s));
+    HKV_CUDA(cudaStreamSynchronize(s));
+    *count = h;
+  });
+}
+
+int hkv_size_if(hkv_table* t, int predicate, uint64_t pattern, uint64_t threshold,
+                uint64_t* d_counter, hkv_stream stream) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (predicate < HKV_PRED_ALL || predicate > HKV_PRED_SCORE_LESS_EQ) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "unknown predicate"};
+    }
+    LockScope ls(t, kReader, s);
+    HKV_CUDA(cudaMemsetAsync(d_counter, 0, sizeof(uint64_t), s));
+    hkv::launch_size_if(t->view, predicate, pattern, threshold,
+                        reinterpret_cast<unsigned long long*>(d_counter), s);
+    ls.done();
+    check_launch();
+  });
+}
+
+int hkv_size(hkv_table* t, hkv_stream stream, uint64_t* size) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned long long* ctr = t->d_scratch;
+    {
+      LockScope ls(t, kReader, s);
+      HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
+      hkv::launch_sum_sizes(t->view, ctr, s);
+      ls.done();
+    }
+    check_launch();
+    unsigned long long h = 0;
+    HKV_CUDA(cudaMemcpyAsync(&h, ctr, sizeof(h), cudaMemcpyDeviceToHost, s));
+    HKV_CUDA(cudaStreamSynchronize(s));
+    *size = h;
+  });
+}
+
+int hkv_load_factor(hkv_table* t, hkv_stream stream, float* load_factor) {
+  uint64_t sz = 0;
+  int rc = hkv_size(t, stream, &sz);
+  if (rc != HKV_OK) return rc;
+  *load_factor = static_cast<float>((sz * 1.0) / (t->view.capacity * 1.0));
+  return HKV_OK;
+}
+
+uint64_t hkv_capacity(const hkv_table* t) { return t->view.capacity; }
+uint64_t hkv_bucket_count(const hkv_table* t) { return t->view.buckets; }
+uint64_t hkv_dim(const hkv_table* t) { return t->opt.dim; }
+uint64_t hkv_max_bucket_size(const hkv_table* t) { return t->opt.max_bucket_size; }
+
+int hkv_set_global_epoch(hkv_table* t, uint64_t epoch) {
+  t->global_epoch.store(epoch);
+  return HKV_OK;
+}
+
+int hkv_reserve(hkv_table* t, uint64_t new_capacity, hkv_stream) {
+  return guarded([&] {
+    if (new_capacity > t->view.capacity) {
+      throw HkvError{HKV_ERR_UNSUPPORTED,
+                     "reserve beyond the current capacity: rehash is not part of this library"};
+    }
+  });
+}
+
+int hkv_get_view(const hkv_table* t, hkv_table_view* view) {
+  return guarded([&] {
+    const hkv::TableView& v = t->view;
+    view->digests = v.digests;
+    view->keys = v.keys;
+    view->scores = v.scores;
+    view->values_hbm = v.values_hbm;
+    view->values_host = v.values_host;
+    view->bucket_sizes = v.bucket_sizes;
+    view->buckets = v.buckets;
+    view->capacity = v.capacity;
+    view->hbm_slots = v.hbm_slots;
+    view->row_bytes = v.row_bytes;
+    view->empty_key = v.empty_key;
+    view->reclaim_key = v.reclaim_key;
+    view->locked_key = v.locked_key;
+    view->reserved_mask = v.reserved_mask;
+    view->reserved_value = v.reserved_value;
+  });
+}
+
+int hkv_device_status(hkv_table* t, hkv_stream stream, uint32_t* status) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint32_t h = 0;
+    HKV_CUDA(cudaMemcpyAsync(&h, t->view.status, sizeof(h), cudaMemcpyDeviceToHost, s));
+    HKV_CUDA(cudaMemsetAsync(t->view.status, 0, sizeof(uint32_t), s));
+    HKV_CUDA(cudaStreamSynchronize(s));
+    *status = h;
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,345 @@
+// Device-side building blocks shared by every kernel of the table:
+// addressing, reserved keys, slot atomics, the 8-lane bucket probe and the
+// warp-cooperative row copy.
+//
+// Storage is flat structure-of-arrays (one allocation per plane):
+//   digests      [buckets][128]  u8    one 128-byte line per bucket
+//   keys         [buckets][128]  u64   the key doubles as the slot lock
+//   scores       [buckets][128]  u64
+//   values       [buckets*128][row_bytes]   HBM part, then pinned-host part
+//   bucket_sizes [buckets]       i32
+//
+// Semantics follow the reference (NVIDIA-Merlin/HierarchicalKV):
+//   hash / bucket / start / digest  include/merlin/utils.cuh:137-145,
+//                                   include/merlin/core_kernels/kernel_utils.cuh:72-103,638-643
+//   reserved keys                   include/merlin/types.cuh:47-109
+//   key-as-lock slot protocol       include/merlin/core_kernels/upsert.cuh:89-110,199-232
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hkv {
+
+constexpr int kBucketSlots = 128;        // slots per bucket (one digest line)
+constexpr int kGroupLanes = 8;           // lanes that probe one bucket
+constexpr int kKeysPerPass = 4;          // buckets probed per warp instruction
+constexpr int kPasses = 8;               // passes to cover a warp's 32 keys
+constexpr uint32_t kNoSlot = 0xFFFFFFFFu;
+constexpr uint64_t kMaxScore = 0xFFFFFFFFFFFFFFFFull;
+constexpr uint64_t kIgnoredEpoch = 0xFFFFFFFFFFFFFFFFull;
+constexpr uint32_t kSpinLimit = 1u << 16;  // bound of every device-side wait
+
+// Bits of the per-table device status word.
+constexpr uint32_t kStatusLockTimeout = 1u;   // a bounded slot wait ran out
+constexpr uint32_t kStatusRetryExhausted = 2u;  // eviction retries ran out
+
+enum Strategy : int {
+  kLru = 0,
+  kLfu = 1,
+  kEpochLru = 2,
+  kEpochLfu = 3,
+  kCustomized = 4,
+};
+
+// Kernel-parameter view of a table.  Reserved keys travel with the view (not
+// in __constant__ memory) so tables with different reserved_key_start_bit can
+// live side by side in one process.
+struct TableView {
+  uint8_t* digests;
+  uint64_t* keys;
+  uint64_t* scores;
+  uint8_t* values_hbm;    // rows of slots [0, hbm_slots)
+  uint8_t* values_host;   // rows of slots [hbm_slots, capacity), pinned+mapped
+  int32_t* bucket_sizes;
+  uint32_t* status;       // device status word (kStatus* bits)
+  uint64_t buckets;
+  uint64_t capacity;      // buckets * 128
+  uint64_t hbm_slots;
+  uint32_t row_bytes;     // dim * sizeof(V)
+  uint32_t vec_bytes;     // widest power-of-two access usable on a row
+  uint32_t chunks_per_row;        // row_bytes / vec_bytes
+  int32_t chunks_per_row_shift;   // log2(chunks_per_row) or -1
+  uint32_t capacity_pow2;         // 1 when capacity is a power of two
+  uint64_t empty_key;
+  uint64_t reclaim_key;
+  uint64_t locked_key;
+  uint64_t reserved_mask;   // (key & reserved_mask) == reserved_value
+  uint64_t reserved_value;
+  uint32_t empty_digest4;   // empty digest replicated in 4 bytes
+  uint32_t reclaim_digest;
+};
+
+__host__ __device__ __forceinline__ uint64_t fmix64(uint64_t k) {
+  k ^= k >> 33;
+  k *= 0xff51afd7ed558ccdull;
+  k ^= k >> 33;
+  k *= 0xc4ceb9fe1a85ec53ull;
+  k ^= k >> 33;
+  return k;
+}
+
+__device__ __forceinline__ bool is_reserved(const TableView& t, uint64_t key) {
+  return (key & t.reserved_mask) == t.reserved_value;
+}
+
+__device__ __forceinline__ uint64_t global_nano() {
+  uint64_t v;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+  return v;
+}
+
+struct Address {
+  uint64_t bucket;
+  uint32_t start;   // probe start slot inside the bucket
+  uint32_t digest;  // 8-bit digest
+};
+
+__device__ __forceinline__ Address locate(const TableView& t, uint64_t key) {
+  const uint64_t h = fmix64(key);
+  const uint64_t g = t.capacity_pow2 ? (h & (t.capacity - 1)) : (h % t.capacity);
+  Address a;
+  a.bucket = g >> 7;
+  a.start = static_cast<uint32_t>(g) & (kBucketSlots - 1);
+  a.digest = static_cast<uint32_t>(h >> 32) & 0xFFu;
+  return a;
+}
+
+__device__ __forceinline__ uint8_t* row_ptr(const TableView& t, uint64_t slot) {
+  return slot < t.hbm_slots
+             ? t.values_hbm + slot * t.row_bytes
+             : t.values_host + (slot - t.hbm_slots) * t.row_bytes;
+}
+
+// ---- slot atomics (64-bit keys and scores, device scope) -------------------
+
+__device__ __forceinline__ uint64_t ld_relaxed(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint64_t ld_acquire(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_relaxed(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ void st_release(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Returns the value observed; the swap happened iff it equals `expected`.
+__device__ __forceinline__ uint64_t cas_acquire(uint64_t* p, uint64_t expected,
+                                                uint64_t desired) {
+  uint64_t old;
+  asm volatile("atom.acquire.gpu.global.cas.b64 %0, [%1], %2, %3;"
+               : "=l"(old)
+               : "l"(p), "l"(expected), "l"(desired)
+               : "memory");
+  return old;
+}
+
+__device__ __forceinline__ void st_u8_cg(uint8_t* p, uint32_t v) {
+  asm volatile("st.global.cg.u8 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Loads with an L2 cache policy.  Digest lines and key lines are reused by
+// later batches and are asked to stay in L2 (evict_last); value rows are
+// touched once per batch and stream through (__ldcs / __stcs, evict_first).
+__device__ __forceinline__ uint64_t policy_keep() {
+  uint64_t p;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+__device__ __forceinline__ uint4 ld_meta_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy_keep())
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint64_t ld_meta_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.global.L1::no_allocate.L2::cache_hint.u64 %0, [%1], %2;"
+               : "=l"(v)
+               : "l"(p), "l"(policy_keep())
+               : "memory");
+  return v;
+}
+
+template <int VEC>
+struct VecType;
+template <>
+struct VecType<16> { using type = uint4; };
+template <>
+struct VecType<8> { using type = uint2; };
+template <>
+struct VecType<4> { using type = uint32_t; };
+template <>
+struct VecType<2> { using type = uint16_t; };
+template <>
+struct VecType<1> { using type = uint8_t; };
+
+template <class T>
+__device__ __forceinline__ T ld_stream(const T* p) {
+  return __ldcs(p);
+}
+template <class T>
+__device__ __forceinline__ void st_stream(T* p, const T& v) {
+  __stcs(p, v);
+}
+// __ldcs/__stcs have no 1- and 2-byte unsigned overloads for every toolkit;
+// narrow rows are rare, plain accesses are enough for them.
+template <>
+__device__ __forceinline__ uint16_t ld_stream<uint16_t>(const uint16_t* p) {
+  return *p;
+}
+template <>
+__device__ __forceinline__ void st_stream<uint16_t>(uint16_t* p, const uint16_t& v) {
+  *p = v;
+}
+template <>
+__device__ __forceinline__ uint8_t ld_stream<uint8_t>(const uint8_t* p) {
+  return *p;
+}
+template <>
+__device__ __forceinline__ void st_stream<uint8_t>(uint8_t* p, const uint8_t& v) {
+  *p = v;
+}
+
+// ---- digest matching -------------------------------------------------------
+
+// 4-bit mask, bit i set when byte i of `word` equals the byte replicated in
+// `pattern4`.
+__device__ __forceinline__ uint32_t match4(uint32_t word, uint32_t pattern4) {
+  const uint32_t eq = __vcmpeq4(word, pattern4) & 0x01010101u;
+  return (eq * 0x01020408u) >> 24;
+}
+
+// 16-bit mask over the 16 digests a lane holds.
+__device__ __forceinline__ uint32_t match16(const uint4& d, uint32_t pattern4) {
+  return match4(d.x, pattern4) | (match4(d.y, pattern4) << 4) |
+         (match4(d.z, pattern4) << 8) | (match4(d.w, pattern4) << 12);
+}
+
+__device__ __forceinline__ uint32_t replicate4(uint32_t byte) {
+  return byte * 0x01010101u;
+}
+
+// ---- warp-cooperative row copy --------------------------------------------
+//
+// A warp owns up to 32 consecutive rows of a batch buffer (`batch_rows` points
+// at the first).  Lane r holds in `slot` the table slot paired with batch row
+// r, or kNoSlot when that row takes no part.  All 32 lanes move 16-byte (or
+// narrower) chunks: chunk c belongs to row c / chunks_per_row, so the batch
+// side is one contiguous, fully coalesced stream and the table side is one
+// contiguous segment per row.
+//
+// MODE 0: table -> batch (gather)   MODE 1: batch -> table (scatter)
+// MODE 2: table += batch (fp32 accumulate; needs VEC % 4 == 0)
+template <int VEC, int MODE>
+__device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* batch_rows,
+                                                   uint32_t slot, uint32_t lane) {
+  using T = typename VecType<VEC>::type;
+  constexpr int U = (VEC == 16) ? 8 : 4;  // chunks in flight per lane
+  const uint32_t cpr = t.chunks_per_row;
+  const int32_t shift = t.chunks_per_row_shift;
+  const uint32_t total = cpr * 32u;
+  for (uint32_t base = 0; base < total; base += 32u * U) {
+    T regs[U];
+    uint8_t* tab[U];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t c = base + u * 32u + lane;
+      const uint32_t r = shift >= 0 ? (c >> shift) : (c / cpr);
+      const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r & 31u);
+      ok[u] = (c < total) && (s != kNoSlot);
+      const uint32_t off = (c - r * cpr) * VEC;
+      tab[u] = ok[u] ? row_ptr(t, s) + off : nullptr;
+      if (ok[u]) {
+        if (MODE == 0) {
+          regs[u] = ld_stream(reinterpret_cast<const T*>(tab[u]));
+        } else {
+          regs[u] = ld_stream(reinterpret_cast<const T*>(batch_rows + size_t(c) * VEC));
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t c = base + u * 32u + lane;
+      if (ok[u]) {
+        if (MODE == 0) {
+          st_stream(reinterpret_cast<T*>(batch_rows + size_t(c) * VEC), regs[u]);
+        } else if (MODE == 1) {
+          st_stream(reinterpret_cast<T*>(tab[u]), regs[u]);
+        } else {
+          if constexpr (VEC % 4 == 0) {
+            T cur = *reinterpret_cast<const T*>(tab[u]);
+            float* a = reinterpret_cast<float*>(&cur);
+            const float* b = reinterpret_cast<const float*>(&regs[u]);
+#pragma unroll
+            for (int e = 0; e < VEC / 4; ++e) a[e] += b[e];
+            *reinterpret_cast<T*>(tab[u]) = cur;
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int MODE>
+__device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
+                                               uint32_t slot, uint32_t lane) {
+  // vec_bytes is warp-uniform; the host lowers it when a batch pointer is
+  // less aligned than the rows.
+  switch (t.vec_bytes) {
+    case 16: warp_move_rows_vec<16, MODE>(t, batch_rows, slot, lane); break;
+    case 8: warp_move_rows_vec<8, MODE>(t, batch_rows, slot, lane); break;
+    case 4: warp_move_rows_vec<4, MODE>(t, batch_rows, slot, lane); break;
+    case 2: warp_move_rows_vec<2, MODE>(t, batch_rows, slot, lane); break;
+    default: warp_move_rows_vec<1, MODE>(t, batch_rows, slot, lane); break;
+  }
+}
+
+// ---- the 8-lane bucket probe ----------------------------------------------
+//
+// One warp serves 32 keys.  Lane l owns key l.  The probe runs in 8 passes; in
+// pass j the four 8-lane groups g = lane >> 3 look at keys 4j + g.  A group
+// loads its bucket's 128-byte digest line as 8 x 16 bytes (one fully used
+// cache line per group, four lines per warp instruction), so a lane holds 16
+// digests of slots [16*sub, 16*sub + 16), sub = lane & 7.
+
+struct ProbeLane {
+  uint32_t sub;    // lane & 7
+  uint32_t group;  // lane >> 3
+  uint32_t lane;
+};
+
+__device__ __forceinline__ ProbeLane probe_lane() {
+  ProbeLane p;
+  p.lane = threadIdx.x & 31u;
+  p.sub = p.lane & 7u;
+  p.group = p.lane >> 3;
+  return p;
+}
+
+// Owner lane of the key a group looks at in pass j.
+__device__ __forceinline__ uint32_t pass_owner(uint32_t j, uint32_t group) {
+  return j * kKeysPerPass + group;
+}
+
+// Mask of the 8 lanes of this lane's group.
+__device__ __forceinline__ uint32_t group_mask(uint32_t group) {
+  return 0xFFu << (group * 8u);
+}
+
+}  // namespace hkv

@@ -1,0 +1,175 @@
+// Read-only lookups: find (values / pointers / missed-keys form) and contains.
+//
+// Replaces the reference's lookup kernels
+//   include/merlin/core_kernels/lookup.cuh:119-378   (pipeline find)
+//   include/merlin/core_kernels/lookup.cuh:873-925   (tile find)
+//   include/merlin/core_kernels/lookup_ptr.cuh:26-152 (find*)
+//   include/merlin/core_kernels/contains.cuh:46-214  (contains)
+// with one warp kernel: 8-lane digest probe of 32 keys with every digest line
+// and every first-candidate key load in flight at once, then a
+// warp-cooperative streaming gather of the hit rows.
+#include "hkv_device.cuh"
+#include "hkv_internal.h"
+
+namespace hkv {
+
+namespace {
+
+constexpr int kFindBlock = 128;
+
+// Probes the 32 keys of a warp.  Returns in the owner lane the global slot of
+// its key, or kNoSlot.
+__device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, const ProbeLane& pl,
+                                                        uint64_t key, bool valid,
+                                                        const Address& a) {
+  const uint32_t full = 0xFFFFFFFFu;
+  const uint32_t my_bucket = static_cast<uint32_t>(a.bucket);
+  uint4 dg[kPasses];
+  uint32_t bkt[kPasses];
+  bool act[kPasses];
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    const uint32_t owner = pass_owner(j, pl.group);
+    bkt[j] = __shfl_sync(full, my_bucket, owner);
+    act[j] = __shfl_sync(full, valid ? 1u : 0u, owner) != 0u;
+    dg[j] = make_uint4(0, 0, 0, 0);
+    if (act[j]) {
+      dg[j] = ld_meta_v4(t.digests + (uint64_t(bkt[j]) << 7) + pl.sub * 16u);
+    }
+  }
+  uint32_t cand[kPasses];
+  uint64_t first_key[kPasses];
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    const uint32_t owner = pass_owner(j, pl.group);
+    const uint32_t tgt = __shfl_sync(full, a.digest, owner);
+    cand[j] = act[j] ? match16(dg[j], replicate4(tgt)) : 0u;
+    first_key[j] = 0;
+    if (cand[j]) {
+      const uint32_t pos = pl.sub * 16u + (__ffs(cand[j]) - 1);
+      first_key[j] = ld_meta_u64(t.keys + (uint64_t(bkt[j]) << 7) + pos);
+    }
+  }
+  uint32_t my_slot = kNoSlot;
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    const uint32_t owner = pass_owner(j, pl.group);
+    const uint64_t want = __shfl_sync(full, key, owner);
+    uint32_t hit_slot = kNoSlot;
+    if (cand[j]) {
+      uint32_t m = cand[j];
+      uint32_t pos = pl.sub * 16u + (__ffs(m) - 1);
+      if (first_key[j] == want) {
+        hit_slot = (bkt[j] << 7) + pos;
+      } else {
+        m &= m - 1;
+        while (m) {
+          pos = pl.sub * 16u + (__ffs(m) - 1);
+          m &= m - 1;
+          if (ld_meta_u64(t.keys + (uint64_t(bkt[j]) << 7) + pos) == want) {
+            hit_slot = (bkt[j] << 7) + pos;
+            break;
+          }
+        }
+      }
+    }
+    const uint32_t votes = (__ballot_sync(full, hit_slot != kNoSlot) >> (pl.group * 8u)) & 0xFFu;
+    const uint32_t src = votes ? (pl.group * 8u + (__ffs(votes) - 1)) : pl.lane;
+    const uint32_t group_slot = __shfl_sync(full, hit_slot, src);
+    // hand the result to the owner lane: owner of (j, g) is lane 4j + g
+    const uint32_t got = __shfl_sync(full, group_slot, (pl.lane & 3u) * 8u);
+    if ((pl.lane >> 2) == uint32_t(j)) my_slot = got;
+  }
+  return my_slot;
+}
+
+// FORM 0: values + founds (+scores)       (HashTable::find, merlin_hashtable.cuh:2464)
+// FORM 1: value pointers + founds (+scores) (find*, merlin_hashtable.cuh:2729)
+// FORM 2: values + missed keys/indices/size (merlin_hashtable.cuh:2600)
+// FORM 3: founds only                     (contains, merlin_hashtable.cuh:2856)
+template <int FORM>
+__global__ void __launch_bounds__(kFindBlock)
+    find_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
+                uint8_t* __restrict__ values, void** __restrict__ ptrs, bool* __restrict__ founds,
+                uint64_t* __restrict__ scores, uint64_t* __restrict__ missed_keys,
+                int* __restrict__ missed_indices, int* __restrict__ missed_size) {
+  const ProbeLane pl = probe_lane();
+  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t base = warp * 32u;
+  if (base >= n) return;
+  const uint64_t i = base + pl.lane;
+  uint64_t key = 0;
+  bool valid = false;
+  if (i < n) {
+    key = keys[i];
+    valid = !is_reserved(t, key);
+  }
+  Address a{0, 0, 0};
+  if (valid) a = locate(t, key);
+
+  const uint32_t slot = warp_probe_readonly(t, pl, key, valid, a);
+  const bool found = slot != kNoSlot;
+
+  if (i < n) {
+    if (FORM != 2) founds[i] = found;
+    if (FORM == 1) ptrs[i] = found ? row_ptr(t, slot) : nullptr;
+    if (FORM != 3 && scores != nullptr && found) scores[i] = t.scores[slot];
+  }
+  if (FORM == 2) {
+    const bool missed = (i < n) && !found;
+    const uint32_t mm = __ballot_sync(0xFFFFFFFFu, missed);
+    if (mm) {
+      int at = 0;
+      if (pl.lane == 0) at = atomicAdd(missed_size, __popc(mm));
+      at = __shfl_sync(0xFFFFFFFFu, at, 0);
+      if (missed) {
+        const int mine = at + __popc(mm & ((1u << pl.lane) - 1u));
+        missed_keys[mine] = key;
+        missed_indices[mine] = static_cast<int>(i);
+      }
+    }
+  }
+  if (FORM == 0 || FORM == 2) {
+    if (values != nullptr) {
+      warp_move_rows<0>(t, values + base * t.row_bytes, slot, pl.lane);
+    }
+  }
+}
+
+template <int FORM>
+void launch_form(const TableView& t, uint64_t n, const uint64_t* keys, void* values, void** ptrs,
+                 bool* founds, uint64_t* scores, uint64_t* missed_keys, int* missed_indices,
+                 int* missed_size, cudaStream_t stream) {
+  if (n == 0) return;
+  const uint64_t warps = (n + 31) / 32;
+  const uint64_t blocks = (warps * 32 + kFindBlock - 1) / kFindBlock;
+  find_kernel<FORM><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
+      t, keys, n, static_cast<uint8_t*>(values), ptrs, founds, scores, missed_keys, missed_indices,
+      missed_size);
+}
+
+}  // namespace
+
+void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values, bool* founds,
+                 uint64_t* scores, cudaStream_t stream) {
+  launch_form<0>(t, n, keys, values, nullptr, founds, scores, nullptr, nullptr, nullptr, stream);
+}
+
+void launch_find_ptr(const TableView& t, uint64_t n, const uint64_t* keys, void** ptrs,
+                     bool* founds, uint64_t* scores, cudaStream_t stream) {
+  launch_form<1>(t, n, keys, nullptr, ptrs, founds, scores, nullptr, nullptr, nullptr, stream);
+}
+
+void launch_find_missed(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
+                        uint64_t* missed_keys, int* missed_indices, int* missed_size,
+                        uint64_t* scores, cudaStream_t stream) {
+  launch_form<2>(t, n, keys, values, nullptr, nullptr, scores, missed_keys, missed_indices,
+                 missed_size, stream);
+}
+
+void launch_contains(const TableView& t, uint64_t n, const uint64_t* keys, bool* founds,
+                     cudaStream_t stream) {
+  launch_form<3>(t, n, keys, nullptr, nullptr, founds, nullptr, nullptr, nullptr, nullptr, stream);
+}
+
+}  // namespace hkv

@@ -1,0 +1,81 @@
+// Launchers shared between the kernel translation units and the C-ABI layer.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "hkv_device.cuh"
+
+namespace hkv {
+
+// Operations served by the mutating kernel (hkv_upsert.cu).
+enum MutateOp : int {
+  kOpInsertOrAssign = 0,   // HashTable::insert_or_assign
+  kOpFindOrInsert = 1,     // HashTable::find_or_insert (values in/out)
+  kOpInsertAndEvict = 2,   // HashTable::insert_and_evict
+  kOpFindOrInsertPtr = 3,  // HashTable::find_or_insert (pointer form)
+  kOpAccumOrAssign = 4,    // HashTable::accum_or_assign
+  kOpAssign = 5,           // HashTable::assign (values + scores)
+  kOpAssignScores = 6,     // HashTable::assign_scores
+  kOpAssignValues = 7,     // HashTable::assign_values
+  kOpFindAndUpdate = 8,    // HashTable::find_and_update
+  kOpLockKeys = 9,         // HashTable::lock_keys
+};
+
+struct MutateArgs {
+  const uint64_t* keys = nullptr;
+  uint64_t n = 0;
+  uint8_t* values = nullptr;          // batch rows (read, or read/write)
+  const uint64_t* scores = nullptr;   // input scores, may be null
+  uint64_t* scores_out = nullptr;     // find_and_update: scores returned
+  void** ptrs = nullptr;              // pointer forms: row addresses out
+  bool* founds = nullptr;             // pointer forms: hit flags out
+  uint64_t** locked_key_ptrs = nullptr;  // keys left locked when non-null
+  const bool* accum_flags = nullptr;
+  uint64_t* evicted_keys = nullptr;
+  uint8_t* evicted_values = nullptr;
+  uint64_t* evicted_scores = nullptr;
+  unsigned long long* evicted_counter = nullptr;
+  int strategy = kLru;
+  uint64_t epoch = kIgnoredEpoch;
+};
+
+void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values, bool* founds,
+                 uint64_t* scores, cudaStream_t stream);
+void launch_find_ptr(const TableView& t, uint64_t n, const uint64_t* keys, void** ptrs,
+                     bool* founds, uint64_t* scores, cudaStream_t stream);
+void launch_find_missed(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
+                        uint64_t* missed_keys, int* missed_indices, int* missed_size,
+                        uint64_t* scores, cudaStream_t stream);
+void launch_contains(const TableView& t, uint64_t n, const uint64_t* keys, bool* founds,
+                     cudaStream_t stream);
+
+// unique_key == false selects the serialising kernel that tolerates repeated
+// keys inside one batch.
+void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool unique_key,
+                   cudaStream_t stream);
+
+void launch_unlock_keys(const TableView& t, uint64_t n, uint64_t** locked_key_ptrs,
+                        const uint64_t* keys, bool* success, cudaStream_t stream);
+
+void launch_erase(const TableView& t, uint64_t n, const uint64_t* keys, cudaStream_t stream);
+
+// Predicates of export_batch_if / size_if that cross the C ABI by number.
+enum Predicate : int {
+  kPredAll = 0,             // every live slot (export_batch)
+  kPredScoreLess = 1,       // score <  threshold
+  kPredScoreGreaterEq = 2,  // score >= threshold
+  kPredKeyMaskEq = 3,       // (key & threshold) == pattern
+  kPredScoreGreater = 4,    // score >  threshold
+  kPredScoreLessEq = 5,     // score <= threshold
+};
+
+void launch_export(const TableView& t, int pred, uint64_t pattern, uint64_t threshold, uint64_t n,
+                   uint64_t offset, unsigned long long* d_counter, uint64_t* keys, void* values,
+                   uint64_t* scores, cudaStream_t stream);
+void launch_size_if(const TableView& t, int pred, uint64_t pattern, uint64_t threshold,
+                    unsigned long long* d_counter, cudaStream_t stream);
+void launch_clear(const TableView& t, cudaStream_t stream);
+void launch_sum_sizes(const TableView& t, unsigned long long* d_total, cudaStream_t stream);
+
+}  // namespace hkv

@@ -1,0 +1,167 @@
+// Whole-table scans: export_batch / export_batch_if, size_if, size, clear.
+//
+// Replaces the reference's
+//   include/merlin/core_kernels.cuh:859-912   dump_kernel      (export_batch)
+//   include/merlin/core_kernels.cuh:983-1041  dump_kernel_v2   (export_batch_if)
+//   include/merlin/core_kernels.cuh:1116-1151 size_if_kernel
+//   include/merlin/core_kernels.cuh:657-676   clear_kernel
+//   include/merlin/core_kernels.cuh:1396-1423 SumOp            (size)
+//
+// Export is a compacting scan: a block of 256 threads reads 256 consecutive
+// slots (keys and scores are linear planes, so these are two fully coalesced
+// 2 KiB reads), every warp ballots its survivors, the block takes ONE ticket
+// range from the global counter, and each warp gathers its survivors' rows
+// with the same coalesced row mover the lookups use.
+#include "hkv_device.cuh"
+#include "hkv_internal.h"
+
+namespace hkv {
+
+namespace {
+
+constexpr int kScanBlock = 256;
+constexpr int kScanWarps = kScanBlock / 32;
+
+__device__ __forceinline__ bool keep(const TableView& t, int pred, uint64_t key, uint64_t score,
+                                     uint64_t pattern, uint64_t threshold) {
+  if (is_reserved(t, key)) return false;
+  switch (pred) {
+    case kPredAll: return true;
+    case kPredScoreLess: return score < threshold;
+    case kPredScoreGreaterEq: return score >= threshold;
+    case kPredKeyMaskEq: return (key & threshold) == pattern;
+    case kPredScoreGreater: return score > threshold;
+    case kPredScoreLessEq: return score <= threshold;
+    default: return false;
+  }
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+    export_kernel(const TableView t, const int pred, const uint64_t pattern,
+                  const uint64_t threshold, const uint64_t n, const uint64_t offset,
+                  unsigned long long* __restrict__ d_counter, uint64_t* __restrict__ out_keys,
+                  uint8_t* __restrict__ out_values, uint64_t* __restrict__ out_scores) {
+  __shared__ uint32_t warp_count[kScanWarps];
+  __shared__ unsigned long long block_base;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t wid = threadIdx.x >> 5;
+  const uint64_t tiles = (n + kScanBlock - 1) / kScanBlock;
+  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const uint64_t rel = tile * kScanBlock + threadIdx.x;
+    const uint64_t slot = offset + rel;
+    uint64_t key = t.empty_key;
+    uint64_t score = 0;
+    bool live = false;
+    if (rel < n) {
+      key = __ldcs(t.keys + slot);
+      score = __ldcs(t.scores + slot);
+      live = keep(t, pred, key, score, pattern, threshold);
+    }
+    const uint32_t votes = __ballot_sync(0xFFFFFFFFu, live);
+    if (lane == 0) warp_count[wid] = __popc(votes);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t total = 0;
+#pragma unroll
+      for (int w = 0; w < kScanWarps; ++w) total += warp_count[w];
+      block_base = total ? atomicAdd(d_counter, (unsigned long long)total) : 0ull;
+    }
+    __syncthreads();
+    uint64_t at = block_base;
+    for (uint32_t w = 0; w < wid; ++w) at += warp_count[w];
+    __syncthreads();  // warp_count / block_base are rewritten by the next tile
+    if (votes) {
+      const uint32_t mine = __popc(votes & ((1u << lane) - 1u));
+      if (live) {
+        __stcs(out_keys + at + mine, key);
+        if (out_scores != nullptr) __stcs(out_scores + at + mine, score);
+      }
+      if (out_values != nullptr) {
+        // lane r carries the slot of the r-th survivor
+        const uint32_t src = __fns(votes, 0, lane + 1);
+        const uint32_t s = __shfl_sync(0xFFFFFFFFu, uint32_t(slot), src & 31u);
+        warp_move_rows<0>(t, out_values + at * t.row_bytes, src == 0xFFFFFFFFu ? kNoSlot : s,
+                          lane);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+    size_if_kernel(const TableView t, const int pred, const uint64_t pattern,
+                   const uint64_t threshold, unsigned long long* __restrict__ d_counter) {
+  unsigned long long local = 0;
+  for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < t.capacity;
+       slot += uint64_t(gridDim.x) * blockDim.x) {
+    const uint64_t key = __ldcs(t.keys + slot);
+    const uint64_t score = __ldcs(t.scores + slot);
+    local += keep(t, pred, key, score, pattern, threshold) ? 1 : 0;
+  }
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_down_sync(0xFFFFFFFFu, local, o);
+  if ((threadIdx.x & 31u) == 0 && local) atomicAdd(d_counter, local);
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+    sum_sizes_kernel(const TableView t, unsigned long long* __restrict__ d_total) {
+  unsigned long long local = 0;
+  for (uint64_t b = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < t.buckets;
+       b += uint64_t(gridDim.x) * blockDim.x) {
+    local += static_cast<unsigned long long>(t.bucket_sizes[b]);
+  }
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_down_sync(0xFFFFFFFFu, local, o);
+  if ((threadIdx.x & 31u) == 0 && local) atomicAdd(d_total, local);
+}
+
+__global__ void __launch_bounds__(kScanBlock) clear_kernel(const TableView t) {
+  // one thread per 16 slots: a 16-byte digest store, 8 key and 8 score pairs
+  const uint64_t groups = t.capacity / 16;
+  for (uint64_t g = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < groups;
+       g += uint64_t(gridDim.x) * blockDim.x) {
+    const uint32_t d = t.empty_digest4;
+    reinterpret_cast<uint4*>(t.digests)[g] = make_uint4(d, d, d, d);
+    ulonglong2* k = reinterpret_cast<ulonglong2*>(t.keys + g * 16);
+    ulonglong2* s = reinterpret_cast<ulonglong2*>(t.scores + g * 16);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      k[q] = make_ulonglong2(t.empty_key, t.empty_key);
+      s[q] = make_ulonglong2(0ull, 0ull);
+    }
+    if ((g & 7u) == 0) t.bucket_sizes[g >> 3] = 0;
+  }
+}
+
+unsigned scan_grid(uint64_t items_per_block_pass, uint64_t items) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const uint64_t want = (items + items_per_block_pass - 1) / items_per_block_pass;
+  const uint64_t cap = uint64_t(sms) * 8;  // 8 resident blocks of 256 threads per SM
+  return static_cast<unsigned>(want < cap ? (want ? want : 1) : cap);
+}
+
+}  // namespace
+
+void launch_export(const TableView& t, int pred, uint64_t pattern, uint64_t threshold, uint64_t n,
+                   uint64_t offset, unsigned long long* d_counter, uint64_t* keys, void* values,
+                   uint64_t* scores, cudaStream_t stream) {
+  if (n == 0) return;
+  export_kernel<<<scan_grid(kScanBlock, n), kScanBlock, 0, stream>>>(
+      t, pred, pattern, threshold, n, offset, d_counter, keys, static_cast<uint8_t*>(values),
+      scores);
+}
+
+void launch_size_if(const TableView& t, int pred, uint64_t pattern, uint64_t threshold,
+                    unsigned long long* d_counter, cudaStream_t stream) {
+  size_if_kernel<<<scan_grid(kScanBlock * 4, t.capacity), kScanBlock, 0, stream>>>(
+      t, pred, pattern, threshold, d_counter);
+}
+
+void launch_clear(const TableView& t, cudaStream_t stream) {
+  clear_kernel<<<scan_grid(kScanBlock, t.capacity / 16), kScanBlock, 0, stream>>>(t);
+}
+
+void launch_sum_sizes(const TableView& t, unsigned long long* d_total, cudaStream_t stream) {
+  sum_sizes_kernel<<<scan_grid(kScanBlock * 4, t.buckets), kScanBlock, 0, stream>>>(t, d_total);
+}
+
+}  // namespace hkv

@@ -1,0 +1,868 @@
+// Mutating operations: insert_or_assign, find_or_insert (value and pointer
+// forms), insert_and_evict, accum_or_assign, assign / assign_scores /
+// assign_values, find_and_update, lock_keys.
+//
+// Replaces the reference's
+//   include/merlin/core_kernels/upsert.cuh:27-986            (insert_or_assign)
+//   include/merlin/core_kernels/upsert_and_evict.cuh:27-1099 (insert_and_evict)
+//   include/merlin/core_kernels/find_or_insert.cuh:27-1050   (find_or_insert)
+//   include/merlin/core_kernels/find_ptr_or_insert.cuh:27-260
+//   include/merlin/core_kernels/accum_or_assign.cuh:83-174
+//   include/merlin/core_kernels/update*.cuh                  (assign family)
+// and the score rules of kernel_utils.cuh:267-615.
+//
+// One warp serves 32 keys in four phases:
+//   1. eight 8-lane digest probes, all digest lines and first-candidate key
+//      loads in flight at once; a hit is locked by CAS key -> LOCKED;
+//   2. a miss claims the first EMPTY slot from its start position by CAS;
+//   3. keys whose bucket is full: four at a time, each 8-lane group loads the
+//      bucket's 128 scores (1 KiB, coalesced), reduces the minimum with warp
+//      REDUX and CASes the victim's key.  A slot found LOCKED is skipped, so
+//      no lane ever waits on another lane's lock;
+//   4. digests / scores are written, rows move cooperatively and coalesced,
+//      and the owner lane publishes its key with a release store.
+#include "hkv_device.cuh"
+#include "hkv_internal.h"
+
+namespace hkv {
+
+namespace {
+
+constexpr int kMutateBlock = 128;
+constexpr uint32_t kEvictRetryLimit = 1u << 20;
+
+enum Result : uint32_t {
+  kInitial = 0,
+  kDuplicate = 1,         // key found and locked
+  kOccupiedEmpty = 2,     // claimed an EMPTY slot
+  kOccupiedReclaimed = 3, // claimed a RECLAIM tombstone via the score scan
+  kEvict = 4,             // locked a victim
+  kRefused = 5,           // incoming score below the bucket minimum
+  kNeedEvict = 6,         // bucket has no free slot, goes to phase 3
+  kMiss = 7,              // not found and the operation does not insert
+  kFoundNoLock = 8,       // found, operation leaves the slot alone
+};
+
+constexpr uint32_t kModeValid = 1u;
+constexpr uint32_t kModeLockOnHit = 2u;
+constexpr uint32_t kModeInsertOnMiss = 4u;
+constexpr uint32_t kModeBucketFull = 8u;
+
+__device__ __forceinline__ bool op_inserts(int op) { return op <= kOpAccumOrAssign; }
+
+__device__ __forceinline__ uint64_t epoch_hi(uint64_t e) { return e << 32; }
+__device__ __forceinline__ uint64_t nano_lo() { return (global_nano() >> 20) & 0xFFFFFFFFull; }
+
+// Score an incoming key competes with (kernel_utils.cuh desired_when_missed).
+__device__ __forceinline__ uint64_t desired_score(int strategy, const uint64_t* scores,
+                                                  uint64_t in_score, uint64_t epoch) {
+  switch (strategy) {
+    case kLru: return global_nano();
+    case kLfu: return kMaxScore;
+    case kEpochLru:
+      if (epoch == kIgnoredEpoch && scores != nullptr) return in_score;
+      return epoch_hi(epoch) | nano_lo();
+    case kEpochLfu:
+      if (epoch == kIgnoredEpoch) return in_score;
+      return epoch_hi(epoch) | (in_score & 0xFFFFFFFFull);
+    default: return in_score;
+  }
+}
+
+// Score stored for a newly inserted key (update_with_digest, new_insert=true).
+__device__ __forceinline__ uint64_t inserted_score(int strategy, uint64_t in_score,
+                                                   uint64_t desired) {
+  switch (strategy) {
+    case kLru: return global_nano();
+    case kLfu: return in_score;
+    default: return desired;
+  }
+}
+
+__device__ __forceinline__ uint64_t epoch_lfu_merge(uint64_t old_score, uint64_t add) {
+  const uint64_t lo = old_score & 0xFFFFFFFFull;
+  if (0xFFFFFFFFull - lo > (add & 0xFFFFFFFFull)) return lo + add;
+  return (add & 0xFFFFFFFF00000000ull) | 0xFFFFFFFFull;
+}
+
+// Score stored when an upsert hits an existing key (update_with_digest,
+// new_insert=false).  Returns false when the score is left untouched.
+__device__ __forceinline__ bool hit_score_upsert(int strategy, const uint64_t* scores,
+                                                 uint64_t in_score, uint64_t desired,
+                                                 uint64_t old_score, uint64_t* out) {
+  switch (strategy) {
+    case kLru: *out = global_nano(); return true;
+    case kLfu:
+      if (scores == nullptr) return false;
+      *out = in_score + old_score;
+      return true;
+    case kEpochLfu: *out = epoch_lfu_merge(old_score, desired); return true;
+    default: *out = desired; return true;
+  }
+}
+
+// Score stored by the assign family (update_without_missed).
+__device__ __forceinline__ bool hit_score_assign(int strategy, const uint64_t* scores,
+                                                 uint64_t in_score, uint64_t epoch,
+                                                 uint64_t old_score, uint64_t* out) {
+  switch (strategy) {
+    case kLru: *out = global_nano(); return true;
+    case kLfu:
+      if (scores == nullptr) return false;
+      *out = in_score + old_score;
+      return true;
+    case kEpochLru: *out = epoch_hi(epoch) | nano_lo(); return true;
+    case kEpochLfu:
+      if (scores == nullptr) return false;
+      *out = epoch_lfu_merge(old_score, epoch_hi(epoch) | (in_score & 0xFFFFFFFFull));
+      return true;
+    default:
+      if (scores == nullptr) return false;
+      *out = in_score;
+      return true;
+  }
+}
+
+__device__ __forceinline__ void ld_scores16(const uint64_t* p, uint64_t (&s)[16]) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];"
+                 : "=l"(s[2 * q]), "=l"(s[2 * q + 1])
+                 : "l"(p + 2 * q)
+                 : "memory");
+  }
+}
+
+// Copies one row with the 8 lanes of a group.
+__device__ __forceinline__ void group_copy_row(const TableView& t, uint8_t* dst,
+                                               const uint8_t* src, uint32_t sub) {
+  const uint32_t vec = t.vec_bytes;
+  const uint32_t cpr = t.chunks_per_row;
+  if (vec == 16) {
+    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
+      __stcs(reinterpret_cast<uint4*>(dst) + c, __ldcs(reinterpret_cast<const uint4*>(src) + c));
+  } else if (vec == 8) {
+    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
+      reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
+  } else if (vec == 4) {
+    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
+      reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
+  } else if (vec == 2) {
+    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
+      reinterpret_cast<uint16_t*>(dst)[c] = reinterpret_cast<const uint16_t*>(src)[c];
+  } else {
+    for (uint32_t c = sub; c < cpr; c += kGroupLanes) dst[c] = src[c];
+  }
+}
+
+// Distance, in probe order from `start`, of the first set bit of a lane's
+// 16-slot mask; 255 when the mask is empty.
+__device__ __forceinline__ uint32_t first_from_start(uint32_t mask16, uint32_t sub,
+                                                     uint32_t start) {
+  const int rel = int(start) - int(sub * 16u);
+  uint32_t hi;
+  if (rel <= 0) {
+    hi = mask16;
+  } else if (rel >= 16) {
+    hi = 0;
+  } else {
+    hi = mask16 & (0xFFFFu << rel);
+  }
+  const uint32_t lo = mask16 & ~hi;
+  if (hi) return sub * 16u + (__ffs(hi) - 1) - start;
+  if (lo) return sub * 16u + (__ffs(lo) - 1) + kBucketSlots - start;
+  return 255u;
+}
+
+struct EvictOutcome {
+  uint32_t result;
+  uint32_t slot;
+};
+
+// Phase 3 for one key, run by the 8 lanes of a group (all collectives use the
+// group's mask).  Never waits on a locked slot: the locked minimum is skipped.
+template <int OP>
+__device__ __forceinline__ EvictOutcome group_evict(const TableView& t, const MutateArgs& args,
+                                                    const ProbeLane& pl, uint32_t bucket,
+                                                    uint64_t key, uint32_t digest,
+                                                    uint64_t desired, uint64_t in_score,
+                                                    uint64_t batch_index) {
+  const uint32_t gmask = group_mask(pl.group);
+  const uint64_t slot0 = uint64_t(bucket) << 7;
+  const uint64_t* score_line = t.scores + slot0 + pl.sub * 16u;
+  EvictOutcome out{kInitial, kNoSlot};
+  uint32_t attempts = 0;
+  while (out.result == kInitial) {
+    if (++attempts > kEvictRetryLimit) {
+      if (pl.sub == 0) atomicOr(t.status, kStatusRetryExhausted);
+      out.result = kRefused;
+      break;
+    }
+    uint64_t s[16];
+    ld_scores16(score_line, s);
+    uint32_t excluded = 0;
+    while (true) {
+      uint64_t ms = kMaxScore;
+      uint32_t mp = 255u;
+#pragma unroll
+      for (int b = 0; b < 16; ++b) {
+        const bool usable = ((excluded >> b) & 1u) == 0u;
+        if (usable && (mp == 255u || s[b] < ms)) {
+          ms = s[b];
+          mp = b;
+        }
+      }
+      const uint32_t hi = mp == 255u ? 0xFFFFFFFFu : uint32_t(ms >> 32);
+      const uint32_t ghi = __reduce_min_sync(gmask, hi);
+      const uint32_t lo = (mp != 255u && hi == ghi) ? uint32_t(ms) : 0xFFFFFFFFu;
+      const uint32_t glo = __reduce_min_sync(gmask, lo);
+      const uint32_t cand = (mp != 255u && hi == ghi && lo == glo) ? pl.sub * 16u + mp : 255u;
+      const uint32_t gpos = __reduce_min_sync(gmask, cand);
+      if (gpos == 255u) {
+        // every slot is locked by someone else right now
+        __nanosleep(64);
+        break;
+      }
+      const uint64_t gmin = (uint64_t(ghi) << 32) | glo;
+      const bool refuse = (OP == kOpFindOrInsertPtr) ? (desired <= gmin) : (desired < gmin);
+      if (refuse) {
+        out.result = kRefused;
+        break;
+      }
+      const bool leader = (gpos >> 4) == pl.sub;
+      uint32_t code = 0;  // 1 skip slot, 2 reload, 3 locked a victim, 4 locked a vacant slot
+      uint64_t victim = 0;
+      if (leader) {
+        uint64_t* kp = t.keys + slot0 + gpos;
+        victim = ld_relaxed(kp);
+        if (victim == t.locked_key) {
+          code = 1;
+        } else if (cas_acquire(kp, victim, t.locked_key) != victim) {
+          code = 2;
+        } else {
+          uint64_t* sp = t.scores + slot0 + gpos;
+          if (ld_relaxed(sp) > gmin) {
+            st_release(kp, victim);
+            code = 2;
+          } else {
+            const bool vacant = victim == t.empty_key || victim == t.reclaim_key;
+            code = vacant ? 4 : 3;
+            // the slot now belongs to `key`: new digest and score at once so
+            // later scans of this bucket see them
+            st_u8_cg(t.digests + slot0 + gpos, digest);
+            st_relaxed(sp, inserted_score(args.strategy, in_score, desired));
+          }
+        }
+      }
+      const uint32_t leader_lane = pl.group * 8u + (gpos >> 4);
+      code = __shfl_sync(gmask, code, leader_lane);
+      if (code == 1) {
+        if (leader) excluded |= 1u << (gpos & 15u);
+        continue;
+      }
+      if (code == 2) break;
+      out.slot = uint32_t(slot0 + gpos);
+      out.result = code == 4 ? kOccupiedReclaimed : kEvict;
+      if (OP == kOpInsertAndEvict && code == 3) {
+        unsigned long long ticket = 0;
+        if (leader) {
+          ticket = atomicAdd(args.evicted_counter, 1ull);
+          __stcs(args.evicted_keys + ticket, victim);
+          if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + ticket, gmin);
+        }
+        ticket = __shfl_sync(gmask, ticket, leader_lane);
+        group_copy_row(t, args.evicted_values + ticket * t.row_bytes, row_ptr(t, out.slot),
+                       pl.sub);
+      }
+      break;
+    }
+  }
+  if (OP == kOpInsertAndEvict && out.result == kRefused) {
+    // a refused input leaves through the evicted arrays as well
+    // (upsert_and_evict.cuh:189-194,244-246)
+    unsigned long long ticket = 0;
+    if (pl.sub == 0) {
+      ticket = atomicAdd(args.evicted_counter, 1ull);
+      __stcs(args.evicted_keys + ticket, key);
+      if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + ticket, desired);
+    }
+    ticket = __shfl_sync(gmask, ticket, pl.group * 8u);
+    group_copy_row(t, args.evicted_values + ticket * t.row_bytes,
+                   args.values + batch_index * t.row_bytes, pl.sub);
+  }
+  return out;
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kMutateBlock)
+    mutate_kernel(const TableView t, const MutateArgs args) {
+  const uint32_t full = 0xFFFFFFFFu;
+  const ProbeLane pl = probe_lane();
+  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t base = warp * 32u;
+  const uint64_t n = args.n;
+  if (base >= n) return;
+  const uint64_t i = base + pl.lane;
+  const int strategy = args.strategy;
+
+  // ---- phase 0: own key --------------------------------------------------
+  uint64_t key = 0;
+  uint64_t in_score = 0;
+  uint64_t desired = 0;
+  bool is_accum = false;
+  uint32_t mode = 0;
+  Address a{0, 0, 0};
+  if (i < n) {
+    key = args.keys[i];
+    if (!is_reserved(t, key)) {
+      mode = kModeValid;
+      a = locate(t, key);
+      if (args.scores != nullptr) in_score = args.scores[i];
+      if (op_inserts(OP) || OP == kOpLockKeys) {
+        desired = desired_score(strategy, args.scores, in_score, args.epoch);
+      }
+      if (OP == kOpAccumOrAssign) {
+        is_accum = args.accum_flags[i];
+        mode |= is_accum ? kModeLockOnHit : kModeInsertOnMiss;
+      } else if (op_inserts(OP)) {
+        mode |= kModeLockOnHit | kModeInsertOnMiss;
+      } else {
+        mode |= kModeLockOnHit;
+      }
+      if (op_inserts(OP) && t.bucket_sizes[a.bucket] >= kBucketSlots) mode |= kModeBucketFull;
+    }
+  }
+  const uint32_t my_bucket = uint32_t(a.bucket);
+
+  // ---- phase 1: digest lines and first candidates, all in flight ----------
+  uint4 dg[kPasses];
+  uint32_t bkt[kPasses];
+  uint32_t pmode[kPasses];
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    const uint32_t owner = pass_owner(j, pl.group);
+    bkt[j] = __shfl_sync(full, my_bucket, owner);
+    pmode[j] = __shfl_sync(full, mode, owner);
+    dg[j] = make_uint4(0, 0, 0, 0);
+    if (pmode[j] & kModeValid) {
+      dg[j] = ld_meta_v4(t.digests + (uint64_t(bkt[j]) << 7) + pl.sub * 16u);
+    }
+  }
+  uint32_t cand[kPasses];
+  uint64_t first_key[kPasses];
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    const uint32_t owner = pass_owner(j, pl.group);
+    const uint32_t tgt = __shfl_sync(full, a.digest, owner);
+    cand[j] = (pmode[j] & kModeValid) ? match16(dg[j], replicate4(tgt)) : 0u;
+    first_key[j] = 0;
+    if (cand[j]) {
+      const uint32_t pos = pl.sub * 16u + (__ffs(cand[j]) - 1);
+      first_key[j] = ld_relaxed(t.keys + (uint64_t(bkt[j]) << 7) + pos);
+    }
+  }
+
+  // ---- phase 2: lock hits, claim empty slots ------------------------------
+  uint32_t my_result = kInitial;
+  uint32_t my_slot = kNoSlot;
+#pragma unroll
+  for (int j = 0; j < kPasses; ++j) {
+    const uint32_t gmask = group_mask(pl.group);
+    const uint32_t owner = pass_owner(j, pl.group);
+    const uint64_t want = __shfl_sync(full, key, owner);
+    const uint32_t start = __shfl_sync(full, a.start, owner);
+    const uint64_t slot0 = uint64_t(bkt[j]) << 7;
+    uint32_t result = kInitial;
+    uint32_t slot = kNoSlot;
+    if (pmode[j] & kModeValid) {
+      uint32_t hit_pos = 255u;
+      if (cand[j]) {
+        uint32_t m = cand[j];
+        uint32_t pos = pl.sub * 16u + (__ffs(m) - 1);
+        if (first_key[j] == want) {
+          hit_pos = pos;
+        } else {
+          m &= m - 1;
+          while (m) {
+            pos = pl.sub * 16u + (__ffs(m) - 1);
+            m &= m - 1;
+            if (ld_relaxed(t.keys + slot0 + pos) == want) {
+              hit_pos = pos;
+              break;
+            }
+          }
+        }
+      }
+      const uint32_t votes = __ballot_sync(gmask, hit_pos != 255u);
+      if (votes) {
+        const uint32_t src = __ffs(votes) - 1;
+        uint32_t ok = 1;
+        if (pl.lane == src && (pmode[j] & kModeLockOnHit)) {
+          ok = cas_acquire(t.keys + slot0 + hit_pos, want, t.locked_key) == want ? 1u : 0u;
+        }
+        ok = __shfl_sync(gmask, ok, src);
+        const uint32_t pos = __shfl_sync(gmask, hit_pos, src);
+        if (ok) {
+          result = (pmode[j] & kModeLockOnHit) ? kDuplicate : kFoundNoLock;
+          slot = uint32_t(slot0) + pos;
+        }
+      }
+      if (result == kInitial) {
+        if (!(pmode[j] & kModeInsertOnMiss)) {
+          result = kMiss;
+        } else if (pmode[j] & kModeBucketFull) {
+          result = kNeedEvict;
+        } else {
+          uint32_t em = match16(dg[j], t.empty_digest4);
+          while (true) {
+            const uint32_t d = first_from_start(em, pl.sub, start);
+            const uint32_t gd = __reduce_min_sync(gmask, d);
+            if (gd == 255u) {
+              result = kNeedEvict;
+              break;
+            }
+            const uint32_t pos = (start + gd) & (kBucketSlots - 1);
+            bool won = false;
+            if (d == gd) {
+              won = cas_acquire(t.keys + slot0 + pos, t.empty_key, t.locked_key) == t.empty_key;
+              em &= ~(1u << (pos & 15u));
+            }
+            if (__ballot_sync(gmask, won)) {
+              result = kOccupiedEmpty;
+              slot = uint32_t(slot0) + pos;
+              break;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+    const uint32_t r = __shfl_sync(full, result, (pl.lane & 3u) * 8u);
+    const uint32_t s = __shfl_sync(full, slot, (pl.lane & 3u) * 8u);
+    if ((pl.lane >> 2) == uint32_t(j)) {
+      my_result = r;
+      my_slot = s;
+    }
+  }
+
+  // ---- phase 3: evictions, four keys at a time ----------------------------
+  if (op_inserts(OP)) {
+    uint32_t need = __ballot_sync(full, my_result == kNeedEvict);
+    while (need) {
+      const uint32_t k = __fns(need, 0, pl.group + 1);
+      const bool active = k != 0xFFFFFFFFu;
+      const uint32_t src = active ? k : 0u;
+      const uint64_t e_key = __shfl_sync(full, key, src);
+      const uint64_t e_desired = __shfl_sync(full, desired, src);
+      const uint64_t e_in = __shfl_sync(full, in_score, src);
+      const uint32_t e_bucket = __shfl_sync(full, my_bucket, src);
+      const uint32_t e_digest = __shfl_sync(full, a.digest, src);
+      EvictOutcome eo{kInitial, kNoSlot};
+      if (active) {
+        eo = group_evict<OP>(t, args, pl, e_bucket, e_key, e_digest, e_desired, e_in, base + src);
+      }
+      __syncwarp();
+      const uint32_t rank = __popc(need & ((1u << pl.lane) - 1u));
+      const uint32_t r = __shfl_sync(full, eo.result, (rank & 3u) * 8u);
+      const uint32_t s = __shfl_sync(full, eo.slot, (rank & 3u) * 8u);
+      if (((need >> pl.lane) & 1u) && rank < 4u) {
+        my_result = r;
+        my_slot = s;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) need &= need - 1;  // (0 & -1) stays 0
+    }
+  }
+
+  // ---- phase 4: metadata, rows, publication -------------------------------
+  const bool holds_lock = my_result == kDuplicate || my_result == kOccupiedEmpty ||
+                          my_result == kOccupiedReclaimed || my_result == kEvict;
+  const bool fresh = my_result == kOccupiedEmpty || my_result == kOccupiedReclaimed ||
+                     my_result == kEvict;
+  if (holds_lock) {
+    if (my_result == kOccupiedEmpty) {
+      st_u8_cg(t.digests + my_slot, a.digest);
+      st_relaxed(t.scores + my_slot, inserted_score(strategy, in_score, desired));
+    }
+    if (my_result == kOccupiedEmpty || my_result == kOccupiedReclaimed) {
+      atomicAdd(t.bucket_sizes + a.bucket, 1);
+    }
+    if (my_result == kDuplicate && OP != kOpAssignValues) {
+      const uint64_t old_score = ld_relaxed(t.scores + my_slot);
+      uint64_t ns = 0;
+      bool write;
+      if (op_inserts(OP) || OP == kOpLockKeys) {
+        write = hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns);
+      } else {
+        write = hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
+      }
+      if (write) st_relaxed(t.scores + my_slot, ns);
+      if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
+        args.scores_out[i] = write ? ns : old_score;
+      }
+    }
+  }
+
+  if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
+      OP == kOpAssignValues) {
+    warp_move_rows<1>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
+                      pl.lane);
+  } else if (OP == kOpFindOrInsert) {
+    warp_move_rows<0>(t, args.values + base * t.row_bytes,
+                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
+    warp_move_rows<1>(t, args.values + base * t.row_bytes, fresh ? my_slot : kNoSlot, pl.lane);
+  } else if (OP == kOpAccumOrAssign) {
+    warp_move_rows<2>(t, args.values + base * t.row_bytes,
+                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
+    warp_move_rows<1>(t, args.values + base * t.row_bytes, fresh ? my_slot : kNoSlot, pl.lane);
+  }
+
+  if (OP == kOpFindOrInsertPtr || OP == kOpFindAndUpdate || OP == kOpLockKeys) {
+    if (i < n) {
+      if (args.ptrs != nullptr) args.ptrs[i] = holds_lock ? row_ptr(t, my_slot) : nullptr;
+      if (args.founds != nullptr) args.founds[i] = my_result == kDuplicate;
+      if (args.locked_key_ptrs != nullptr) {
+        args.locked_key_ptrs[i] = holds_lock ? t.keys + my_slot : nullptr;
+      }
+    }
+  }
+
+  __syncwarp();
+  const bool keep_locked =
+      (OP == kOpFindOrInsertPtr || OP == kOpLockKeys) && args.locked_key_ptrs != nullptr;
+  if (holds_lock && !keep_locked) st_release(t.keys + my_slot, key);
+}
+
+// ---- serialising kernel for batches that may repeat a key -------------------
+//
+// One warp walks its 32 keys one after the other and finishes each (lock,
+// write, publish) before the next, reading the bucket's 128 keys directly
+// (4 per lane) as the reference's tile kernels do
+// (kernel_utils.cuh:675-898, upsert.cuh:1233-1305).  A LOCKED slot met during
+// the scan is waited for (bounded), so a second occurrence of a key finds the
+// first one's slot once it is published.
+template <int OP>
+__global__ void __launch_bounds__(kMutateBlock)
+    mutate_serial_kernel(const TableView t, const MutateArgs args) {
+  const uint32_t full = 0xFFFFFFFFu;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t base = warp * 32u;
+  const uint64_t n = args.n;
+  if (base >= n) return;
+  const int strategy = args.strategy;
+  const uint32_t count = uint32_t(min(uint64_t(32), n - base));
+
+  for (uint32_t q = 0; q < count; ++q) {
+    const uint64_t i = base + q;
+    const uint64_t key = args.keys[i];
+    if (is_reserved(t, key)) {
+      if (lane == 0 &&
+          (OP == kOpFindOrInsertPtr || OP == kOpFindAndUpdate || OP == kOpLockKeys)) {
+        if (args.ptrs != nullptr) args.ptrs[i] = nullptr;
+        if (args.founds != nullptr) args.founds[i] = false;
+        if (args.locked_key_ptrs != nullptr) args.locked_key_ptrs[i] = nullptr;
+      }
+      continue;
+    }
+    const Address a = locate(t, key);
+    const uint64_t in_score = args.scores != nullptr ? args.scores[i] : 0;
+    const uint64_t desired = (op_inserts(OP) || OP == kOpLockKeys)
+                                 ? desired_score(strategy, args.scores, in_score, args.epoch)
+                                 : 0;
+    const bool is_accum = OP == kOpAccumOrAssign ? args.accum_flags[i] : false;
+    const bool lock_on_hit = OP == kOpAccumOrAssign ? is_accum : true;
+    const bool insert_on_miss = OP == kOpAccumOrAssign ? !is_accum : op_inserts(OP);
+    const uint64_t slot0 = a.bucket << 7;
+    uint64_t* key_line = t.keys + slot0;
+
+    uint32_t result = kInitial;
+    uint32_t pos = 0;
+    uint64_t victim = 0;
+    uint64_t victim_score = 0;
+    uint32_t attempts = 0;
+    while (result == kInitial) {
+      if (++attempts > kSpinLimit) {
+        if (lane == 0) atomicOr(t.status, kStatusLockTimeout);
+        result = kRefused;
+        break;
+      }
+      // lane l looks at slots l, l+32, l+64, l+96
+      uint64_t k4[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) k4[c] = ld_acquire(key_line + c * 32 + lane);
+      uint32_t eq = 0, locked = 0, empty = 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        eq |= (k4[c] == key) ? (1u << c) : 0u;
+        locked |= (k4[c] == t.locked_key) ? (1u << c) : 0u;
+        empty |= (k4[c] == t.empty_key) ? (1u << c) : 0u;
+      }
+      const uint32_t any_eq = __ballot_sync(full, eq != 0);
+      if (any_eq) {
+        const uint32_t src = __ffs(any_eq) - 1;
+        const uint32_t p = __shfl_sync(full, (__ffs(eq) - 1) * 32 + lane, src);
+        uint32_t ok = 1;
+        if (lock_on_hit) {
+          if (lane == src) ok = cas_acquire(key_line + p, key, t.locked_key) == key ? 1u : 0u;
+          ok = __shfl_sync(full, ok, src);
+        }
+        if (ok) {
+          result = lock_on_hit ? kDuplicate : kFoundNoLock;
+          pos = p;
+        }
+        continue;
+      }
+      if (__ballot_sync(full, locked != 0)) {
+        // somebody is writing a slot of this bucket; it may be this very key
+        __nanosleep(128);
+        continue;
+      }
+      if (!insert_on_miss) {
+        result = kMiss;
+        break;
+      }
+      // first EMPTY slot in probe order from a.start
+      uint32_t best = 255u;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if ((empty >> c) & 1u) {
+          const uint32_t d = (uint32_t(c) * 32u + lane - a.start) & (kBucketSlots - 1);
+          best = min(best, d);
+        }
+      }
+      const uint32_t gbest = __reduce_min_sync(full, best);
+      if (gbest != 255u) {
+        const uint32_t p = (a.start + gbest) & (kBucketSlots - 1);
+        uint32_t ok = 0;
+        if (lane == 0) ok = cas_acquire(key_line + p, t.empty_key, t.locked_key) == t.empty_key;
+        ok = __shfl_sync(full, ok, 0);
+        if (ok) {
+          result = kOccupiedEmpty;
+          pos = p;
+        }
+        continue;
+      }
+      // full bucket: minimum score, first position on ties
+      uint64_t s4[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s4[c] = ld_relaxed(t.scores + slot0 + c * 32 + lane);
+      uint64_t ms = s4[0];
+      uint32_t mp = lane;
+#pragma unroll
+      for (int c = 1; c < 4; ++c) {
+        if (s4[c] < ms) {
+          ms = s4[c];
+          mp = c * 32 + lane;
+        }
+      }
+      const uint32_t hi = uint32_t(ms >> 32);
+      const uint32_t ghi = __reduce_min_sync(full, hi);
+      const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
+      const uint32_t glo = __reduce_min_sync(full, lo);
+      const uint32_t cp = (hi == ghi && lo == glo) ? mp : 255u;
+      const uint32_t gpos = __reduce_min_sync(full, cp);
+      const uint64_t gmin = (uint64_t(ghi) << 32) | glo;
+      const bool refuse = (OP == kOpFindOrInsertPtr) ? (desired <= gmin) : (desired < gmin);
+      if (refuse) {
+        result = kRefused;
+        break;
+      }
+      uint32_t code = 0;
+      if (lane == 0) {
+        uint64_t* kp = key_line + gpos;
+        const uint64_t v = ld_relaxed(kp);
+        if (v != t.locked_key && cas_acquire(kp, v, t.locked_key) == v) {
+          if (ld_relaxed(t.scores + slot0 + gpos) > gmin) {
+            st_release(kp, v);
+          } else {
+            victim = v;
+            code = (v == t.empty_key || v == t.reclaim_key) ? 2 : 1;
+          }
+        }
+      }
+      code = __shfl_sync(full, code, 0);
+      if (code) {
+        result = code == 2 ? kOccupiedReclaimed : kEvict;
+        pos = gpos;
+        victim = __shfl_sync(full, victim, 0);
+        victim_score = gmin;
+      }
+    }
+
+    const uint32_t slot = uint32_t(slot0) + pos;
+    const bool holds_lock = result == kDuplicate || result == kOccupiedEmpty ||
+                            result == kOccupiedReclaimed || result == kEvict;
+    const bool fresh = holds_lock && result != kDuplicate;
+    uint8_t* batch_row = args.values != nullptr ? args.values + i * t.row_bytes : nullptr;
+
+    if (OP == kOpInsertAndEvict && (result == kEvict || result == kRefused)) {
+      unsigned long long ticket = 0;
+      if (lane == 0) {
+        ticket = atomicAdd(args.evicted_counter, 1ull);
+        args.evicted_keys[ticket] = result == kEvict ? victim : key;
+        if (args.evicted_scores != nullptr) {
+          args.evicted_scores[ticket] = result == kEvict ? victim_score : desired;
+        }
+      }
+      ticket = __shfl_sync(full, ticket, 0);
+      const uint8_t* src = result == kEvict ? row_ptr(t, slot) : batch_row;
+      uint8_t* dst = args.evicted_values + ticket * t.row_bytes;
+      for (uint32_t c = lane; c < t.row_bytes / t.vec_bytes; c += 32) {
+        for (uint32_t b = 0; b < t.vec_bytes; ++b) dst[c * t.vec_bytes + b] = src[c * t.vec_bytes + b];
+      }
+      __syncwarp();
+    }
+
+    if (holds_lock) {
+      if (lane == 0) {
+        if (fresh) {
+          st_u8_cg(t.digests + slot, a.digest);
+          st_relaxed(t.scores + slot, inserted_score(strategy, in_score, desired));
+          if (result != kEvict) atomicAdd(t.bucket_sizes + a.bucket, 1);
+        } else if (OP != kOpAssignValues) {
+          const uint64_t old_score = ld_relaxed(t.scores + slot);
+          uint64_t ns = 0;
+          const bool write =
+              (op_inserts(OP) || OP == kOpLockKeys)
+                  ? hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns)
+                  : hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
+          if (write) st_relaxed(t.scores + slot, ns);
+          if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
+            args.scores_out[i] = write ? ns : old_score;
+          }
+        }
+      }
+      uint8_t* row = row_ptr(t, slot);
+      const uint32_t vec = t.vec_bytes;
+      const uint32_t words = t.row_bytes / vec;
+      const bool to_table = OP == kOpInsertOrAssign || OP == kOpInsertAndEvict ||
+                            OP == kOpAssign || OP == kOpAssignValues ||
+                            ((OP == kOpFindOrInsert || OP == kOpAccumOrAssign) && fresh);
+      const bool from_table = OP == kOpFindOrInsert && !fresh;
+      const bool accumulate = OP == kOpAccumOrAssign && !fresh;
+      if (to_table || from_table) {
+        uint8_t* dst = to_table ? row : batch_row;
+        const uint8_t* src = to_table ? batch_row : row;
+        if (vec == 16) {
+          for (uint32_t c = lane; c < words; c += 32)
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+        } else if (vec == 8) {
+          for (uint32_t c = lane; c < words; c += 32)
+            reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
+        } else if (vec == 4) {
+          for (uint32_t c = lane; c < words; c += 32)
+            reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
+        } else {
+          for (uint32_t c = lane; c < t.row_bytes; c += 32) dst[c] = src[c];
+        }
+      } else if (accumulate) {
+        float* dst = reinterpret_cast<float*>(row);
+        const float* src = reinterpret_cast<const float*>(batch_row);
+        for (uint32_t c = lane; c < t.row_bytes / 4; c += 32) dst[c] += src[c];
+      }
+    }
+    if (lane == 0 &&
+        (OP == kOpFindOrInsertPtr || OP == kOpFindAndUpdate || OP == kOpLockKeys)) {
+      if (args.ptrs != nullptr) args.ptrs[i] = holds_lock ? row_ptr(t, slot) : nullptr;
+      if (args.founds != nullptr) args.founds[i] = result == kDuplicate;
+      if (args.locked_key_ptrs != nullptr) {
+        args.locked_key_ptrs[i] = holds_lock ? t.keys + slot : nullptr;
+      }
+    }
+    __syncwarp();
+    const bool keep_locked =
+        (OP == kOpFindOrInsertPtr || OP == kOpLockKeys) && args.locked_key_ptrs != nullptr;
+    if (holds_lock && !keep_locked && lane == 0) {
+      __threadfence();
+      st_release(key_line + pos, key);
+    }
+    __syncwarp();
+  }
+}
+
+__global__ void unlock_keys_kernel(const TableView t, uint64_t n, uint64_t** locked_key_ptrs,
+                                   const uint64_t* keys, bool* success) {
+  const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint64_t* p = locked_key_ptrs[i];
+  bool ok = false;
+  if (p != nullptr) {
+    // only a slot that is still locked is given back its key
+    // (core_kernels.cuh:1181-1204)
+    ok = cas_acquire(p, t.locked_key, keys[i]) == t.locked_key;
+  }
+  if (success != nullptr) success[i] = ok;
+}
+
+// erase: tombstone = RECLAIM key, reclaim digest, score 0, size - 1
+// (core_kernels.cuh:680-734).
+__global__ void __launch_bounds__(kMutateBlock)
+    erase_kernel(const TableView t, uint64_t n, const uint64_t* keys) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (warp >= n) return;
+  const uint64_t key = keys[warp];
+  if (is_reserved(t, key)) return;
+  const Address a = locate(t, key);
+  const uint64_t slot0 = a.bucket << 7;
+  const uint32_t d4 = reinterpret_cast<const uint32_t*>(t.digests + slot0)[lane];
+  uint32_t m = match4(d4, replicate4(a.digest));
+  while (m) {
+    const uint32_t pos = lane * 4 + (__ffs(m) - 1);
+    m &= m - 1;
+    if (cas_acquire(t.keys + slot0 + pos, key, t.locked_key) == key) {
+      st_u8_cg(t.digests + slot0 + pos, t.reclaim_digest);
+      st_relaxed(t.scores + slot0 + pos, 0);
+      atomicSub(t.bucket_sizes + a.bucket, 1);
+      st_release(t.keys + slot0 + pos, t.reclaim_key);
+      break;
+    }
+  }
+}
+
+template <int OP>
+void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cudaStream_t stream) {
+  const uint64_t warps = (args.n + 31) / 32;
+  const uint64_t blocks = (warps * 32 + kMutateBlock - 1) / kMutateBlock;
+  if (unique_key) {
+    mutate_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+  } else {
+    mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+  }
+}
+
+}  // namespace
+
+void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool unique_key,
+                   cudaStream_t stream) {
+  if (args.n == 0) return;
+  switch (op) {
+    case kOpInsertOrAssign: launch_op<kOpInsertOrAssign>(t, args, unique_key, stream); break;
+    case kOpFindOrInsert: launch_op<kOpFindOrInsert>(t, args, unique_key, stream); break;
+    case kOpInsertAndEvict: launch_op<kOpInsertAndEvict>(t, args, unique_key, stream); break;
+    case kOpFindOrInsertPtr: launch_op<kOpFindOrInsertPtr>(t, args, unique_key, stream); break;
+    case kOpAccumOrAssign: launch_op<kOpAccumOrAssign>(t, args, unique_key, stream); break;
+    case kOpAssign: launch_op<kOpAssign>(t, args, unique_key, stream); break;
+    case kOpAssignScores: launch_op<kOpAssignScores>(t, args, unique_key, stream); break;
+    case kOpAssignValues: launch_op<kOpAssignValues>(t, args, unique_key, stream); break;
+    case kOpFindAndUpdate: launch_op<kOpFindAndUpdate>(t, args, unique_key, stream); break;
+    case kOpLockKeys: launch_op<kOpLockKeys>(t, args, unique_key, stream); break;
+    default: break;
+  }
+}
+
+void launch_unlock_keys(const TableView& t, uint64_t n, uint64_t** locked_key_ptrs,
+                        const uint64_t* keys, bool* success, cudaStream_t stream) {
+  if (n == 0) return;
+  unlock_keys_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
+      t, n, locked_key_ptrs, keys, success);
+}
+
+void launch_erase(const TableView& t, uint64_t n, const uint64_t* keys, cudaStream_t stream) {
+  if (n == 0) return;
+  const uint64_t blocks = (n * 32 + kMutateBlock - 1) / kMutateBlock;
+  erase_kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, n, keys);
+}
+
+}  // namespace hkv

@@ -1,0 +1,255 @@
+/*
+ * hkv_b200 -- C ABI of the B200-native HierarchicalKV hash-table hot path.
+ *
+ * Every entry point takes plain pointers and sizes.  Batch buffers (keys,
+ * values, scores, flags, counters) must be GPU-accessible (device memory or
+ * mapped pinned host memory), exactly as the reference requires of its
+ * callers (include/merlin_hashtable.cuh:216-221).  All operations enqueue on
+ * the caller's stream and return without synchronising, except those that
+ * return a count to the host.
+ *
+ * Each declaration names the reference interface it replaces, by the file's
+ * path inside NVIDIA-Merlin/HierarchicalKV.  The drop-in C++ class
+ * nv::merlin::HashTable<K,V,S,Strategy> in include/merlin_hashtable.cuh is a
+ * thin wrapper over these functions.
+ *
+ * Key type: 64-bit (uint64_t or int64_t bit pattern).  Score type: uint64_t.
+ * Value rows are opaque bytes of `dim * value_size` except in
+ * hkv_accum_or_assign, which adds float32 elements.
+ */
+#ifndef HKV_B200_H_
+#define HKV_B200_H_
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HKV_API __attribute__((visibility("default")))
+
+typedef struct hkv_table hkv_table;
+typedef void* hkv_stream; /* cudaStream_t */
+
+/* Return codes.  The C++ wrapper rethrows them as the reference's exception
+ * types (include/merlin/debug.hpp:27-72). */
+typedef enum hkv_status {
+  HKV_OK = 0,
+  HKV_ERR_MERLIN = 1,      /* nv::merlin::MerlinException (MERLIN_CHECK failed) */
+  HKV_ERR_CUDA = 2,        /* nv::merlin::CudaException   (CUDA_CHECK failed)   */
+  HKV_ERR_RUNTIME = 3,     /* std::runtime_error                                 */
+  HKV_ERR_INVALID_ARG = 4, /* std::invalid_argument                              */
+  HKV_ERR_UNSUPPORTED = 5  /* feature of the reference outside this library      */
+} hkv_status;
+
+/* EvictStrategy::EvictStrategyEnum, include/merlin_hashtable.cuh:79-87 */
+typedef enum hkv_evict_strategy {
+  HKV_LRU = 0,
+  HKV_LFU = 1,
+  HKV_EPOCH_LRU = 2,
+  HKV_EPOCH_LFU = 3,
+  HKV_CUSTOMIZED = 4
+} hkv_evict_strategy;
+
+/* MemoryType, include/merlin/allocator.cuh:27-31 */
+typedef enum hkv_memory_type { HKV_MEM_DEVICE = 0, HKV_MEM_PINNED = 1, HKV_MEM_HOST = 2 } hkv_memory_type;
+
+/* BaseAllocator bridged to C, include/merlin/allocator.cuh:37-59.  Borrowed,
+ * never owned.  A null hkv_allocator* selects cudaMalloc / cudaHostAlloc. */
+typedef struct hkv_allocator {
+  void* ctx;
+  int (*alloc)(void* ctx, int memory_type, void** ptr, size_t size, unsigned int pinned_flags);
+  int (*free)(void* ctx, int memory_type, void* ptr);
+} hkv_allocator;
+
+/* HashTableOptions, include/merlin_hashtable.cuh:103-136, field for field,
+ * followed by what the class template carries as template parameters. */
+typedef struct hkv_options {
+  uint64_t init_capacity;
+  uint64_t max_capacity;
+  uint64_t max_hbm_for_vectors; /* bytes; 0 puts every value row in pinned host memory */
+  uint64_t max_bucket_size;     /* only 128 is supported */
+  uint64_t dim;
+  float max_load_factor;
+  int32_t block_size;
+  int32_t io_block_size;
+  int32_t device_id; /* -1: current device */
+  int32_t io_by_cpu; /* must be 0 */
+  int32_t use_constant_memory;
+  int32_t reserved_key_start_bit; /* 0..62 */
+  uint64_t num_of_buckets_per_alloc;
+  int32_t api_lock;
+  int32_t table_mode; /* 0 kThroughput; 1 kMemory is rejected */
+  /* template parameters of HashTable<K,V,S,Strategy> */
+  int32_t evict_strategy; /* hkv_evict_strategy */
+  uint32_t value_size;    /* sizeof(V) */
+  uint32_t score_size;    /* sizeof(S): 8 */
+} hkv_options;
+
+/* Predicates that cross the ABI by number (export_batch_if / size_if /
+ * erase_if with the functors the reference's tests and benchmarks use). */
+typedef enum hkv_predicate {
+  HKV_PRED_ALL = 0,
+  HKV_PRED_SCORE_LESS = 1,       /* score <  threshold */
+  HKV_PRED_SCORE_GREATER_EQ = 2, /* score >= threshold */
+  HKV_PRED_KEY_MASK_EQ = 3,      /* (key & threshold) == pattern */
+  HKV_PRED_SCORE_GREATER = 4,    /* score >  threshold */
+  HKV_PRED_SCORE_LESS_EQ = 5     /* score <= threshold */
+} hkv_predicate;
+
+/* Raw view of the table's planes for header-side kernels that evaluate a
+ * user-templated functor (export_batch_if<PredFunctor>, for_each).  Valid
+ * until the table is destroyed. */
+typedef struct hkv_table_view {
+  uint8_t* digests;      /* [buckets][128] */
+  uint64_t* keys;        /* [buckets][128] */
+  uint64_t* scores;      /* [buckets][128] */
+  uint8_t* values_hbm;   /* rows of slots [0, hbm_slots) */
+  uint8_t* values_host;  /* rows of slots [hbm_slots, capacity), mapped pinned */
+  int32_t* bucket_sizes; /* [buckets] */
+  uint64_t buckets;
+  uint64_t capacity;
+  uint64_t hbm_slots;
+  uint64_t row_bytes;
+  uint64_t empty_key, reclaim_key, locked_key;
+  uint64_t reserved_mask, reserved_value; /* reserved iff (key & mask) == value */
+} hkv_table_view;
+
+/* Message of the last failing call on this thread. */
+HKV_API const char* hkv_last_error(void);
+
+/* HashTable::init, include/merlin_hashtable.cuh:984-1089 (create_table,
+ * include/merlin/core_kernels.cuh:327-381) and ~HashTable 960-970. */
+HKV_API int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
+                             hkv_table** out);
+HKV_API int hkv_table_destroy(hkv_table* table);
+
+/* HashTable::insert_or_assign, include/merlin_hashtable.cuh:1125-1305 */
+HKV_API int hkv_insert_or_assign(hkv_table* table, uint64_t n, const uint64_t* keys,
+                                 const void* values, const uint64_t* scores, hkv_stream stream,
+                                 int unique_key, int ignore_evict_strategy);
+
+/* HashTable::insert_and_evict, include/merlin_hashtable.cuh:1351-1473; the
+ * caller zeroes *d_evicted_counter. */
+HKV_API int hkv_insert_and_evict(hkv_table* table, uint64_t n, const uint64_t* keys,
+                                 const void* values, const uint64_t* scores,
+                                 uint64_t* evicted_keys, void* evicted_values,
+                                 uint64_t* evicted_scores, uint64_t* d_evicted_counter,
+                                 hkv_stream stream, int unique_key, int ignore_evict_strategy);
+/* count-returning overload, include/merlin_hashtable.cuh:1518-1546
+ * (synchronises the stream) */
+HKV_API int hkv_insert_and_evict_count(hkv_table* table, uint64_t n, const uint64_t* keys,
+                                       const void* values, const uint64_t* scores,
+                                       uint64_t* evicted_keys, void* evicted_values,
+                                       uint64_t* evicted_scores, hkv_stream stream, int unique_key,
+                                       int ignore_evict_strategy, uint64_t* evicted_count);
+
+/* HashTable::accum_or_assign, include/merlin_hashtable.cuh:1589-1680
+ * (float32 elements) */
+HKV_API int hkv_accum_or_assign(hkv_table* table, uint64_t n, const uint64_t* keys,
+                                const void* value_or_deltas, const bool* accum_or_assigns,
+                                const uint64_t* scores, hkv_stream stream,
+                                int ignore_evict_strategy);
+
+/* HashTable::find_or_insert (values in/out), include/merlin_hashtable.cuh:1699-1857 */
+HKV_API int hkv_find_or_insert(hkv_table* table, uint64_t n, const uint64_t* keys, void* values,
+                               uint64_t* scores, hkv_stream stream, int unique_key,
+                               int ignore_evict_strategy);
+
+/* HashTable::find_or_insert (pointer form), include/merlin_hashtable.cuh:1883-1965;
+ * with locked_key_ptrs the keys stay locked until hkv_unlock_keys. */
+HKV_API int hkv_find_or_insert_ptr(hkv_table* table, uint64_t n, const uint64_t* keys,
+                                   void** values, bool* founds, uint64_t* scores,
+                                   hkv_stream stream, int unique_key, int ignore_evict_strategy,
+                                   uint64_t** locked_key_ptrs);
+
+/* HashTable::lock_keys / unlock_keys, include/merlin_hashtable.cuh:1982-2044 */
+HKV_API int hkv_lock_keys(hkv_table* table, uint64_t n, const uint64_t* keys,
+                          uint64_t** locked_key_ptrs, bool* success, hkv_stream stream,
+                          const uint64_t* scores);
+HKV_API int hkv_unlock_keys(hkv_table* table, uint64_t n, uint64_t** locked_key_ptrs,
+                            const uint64_t* keys, bool* success, hkv_stream stream);
+
+/* HashTable::assign, include/merlin_hashtable.cuh:2071-2205 */
+HKV_API int hkv_assign(hkv_table* table, uint64_t n, const uint64_t* keys, const void* values,
+                       const uint64_t* scores, hkv_stream stream, int unique_key);
+/* HashTable::assign_scores, include/merlin_hashtable.cuh:2228-2283 */
+HKV_API int hkv_assign_scores(hkv_table* table, uint64_t n, const uint64_t* keys,
+                              const uint64_t* scores, hkv_stream stream, int unique_key);
+/* HashTable::assign_values, include/merlin_hashtable.cuh:2299-2444 */
+HKV_API int hkv_assign_values(hkv_table* table, uint64_t n, const uint64_t* keys,
+                              const void* values, hkv_stream stream, int unique_key);
+
+/* HashTable::find, include/merlin_hashtable.cuh:2464-2577 */
+HKV_API int hkv_find(hkv_table* table, uint64_t n, const uint64_t* keys, void* values,
+                     bool* founds, uint64_t* scores, hkv_stream stream);
+/* HashTable::find (missed-keys form), include/merlin_hashtable.cuh:2600-2705 */
+HKV_API int hkv_find_missed(hkv_table* table, uint64_t n, const uint64_t* keys, void* values,
+                            uint64_t* missed_keys, int* missed_indices, int* missed_size,
+                            uint64_t* scores, hkv_stream stream);
+/* HashTable::find (pointer form, "find*"), include/merlin_hashtable.cuh:2729-2787 */
+HKV_API int hkv_find_ptr(hkv_table* table, uint64_t n, const uint64_t* keys, void** values,
+                         bool* founds, uint64_t* scores, hkv_stream stream, int unique_key);
+/* HashTable::find_and_update, include/merlin_hashtable.cuh:2811-2843 */
+HKV_API int hkv_find_and_update(hkv_table* table, uint64_t n, const uint64_t* keys, void** values,
+                                bool* founds, uint64_t* scores, hkv_stream stream, int unique_key);
+/* HashTable::contains, include/merlin_hashtable.cuh:2856-2894 */
+HKV_API int hkv_contains(hkv_table* table, uint64_t n, const uint64_t* keys, bool* founds,
+                         hkv_stream stream);
+
+/* HashTable::erase, include/merlin_hashtable.cuh:2904-2930 */
+HKV_API int hkv_erase(hkv_table* table, uint64_t n, const uint64_t* keys, hkv_stream stream);
+/* HashTable::clear, include/merlin_hashtable.cuh:3059-3073 */
+HKV_API int hkv_clear(hkv_table* table, hkv_stream stream);
+
+/* HashTable::export_batch, include/merlin_hashtable.cuh:3099-3147; n and
+ * offset count slots; *d_counter is zeroed by the call. */
+HKV_API int hkv_export_batch(hkv_table* table, uint64_t n, uint64_t offset, uint64_t* d_counter,
+                             uint64_t* keys, void* values, uint64_t* scores, hkv_stream stream);
+/* count-returning overload, include/merlin_hashtable.cuh:3131-3147 (synchronises) */
+HKV_API int hkv_export_batch_count(hkv_table* table, uint64_t n, uint64_t offset, uint64_t* keys,
+                                   void* values, uint64_t* scores, hkv_stream stream,
+                                   uint64_t* count);
+/* HashTable::export_batch_if<PredFunctor>, include/merlin_hashtable.cuh:3193-3276,
+ * for the built-in predicates */
+HKV_API int hkv_export_batch_if(hkv_table* table, int predicate, uint64_t pattern,
+                                uint64_t threshold, uint64_t n, uint64_t offset,
+                                uint64_t* d_counter, uint64_t* keys, void* values,
+                                uint64_t* scores, hkv_stream stream);
+/* HashTable::size_if<PredFunctor>, include/merlin_hashtable.cuh:3459-3476 */
+HKV_API int hkv_size_if(hkv_table* table, int predicate, uint64_t pattern, uint64_t threshold,
+                        uint64_t* d_counter, hkv_stream stream);
+
+/* HashTable::size / empty / load_factor / capacity / bucket_count / dim /
+ * max_bucket_size, include/merlin_hashtable.cuh:3416-3451,3487,3551-3553,3586-3602 */
+HKV_API int hkv_size(hkv_table* table, hkv_stream stream, uint64_t* size);
+HKV_API int hkv_load_factor(hkv_table* table, hkv_stream stream, float* load_factor);
+HKV_API uint64_t hkv_capacity(const hkv_table* table);
+HKV_API uint64_t hkv_bucket_count(const hkv_table* table);
+HKV_API uint64_t hkv_dim(const hkv_table* table);
+HKV_API uint64_t hkv_max_bucket_size(const hkv_table* table);
+
+/* HashTable::set_global_epoch, include/merlin_hashtable.cuh:3760 */
+HKV_API int hkv_set_global_epoch(hkv_table* table, uint64_t epoch);
+
+/* HashTable::reserve / set_max_capacity, include/merlin_hashtable.cuh:3503-3579.
+ * Capacity is fixed in this library: reserve succeeds only when the request
+ * fits the current capacity. */
+HKV_API int hkv_reserve(hkv_table* table, uint64_t new_capacity, hkv_stream stream);
+
+/* Planes of the table for header-side functor kernels. */
+HKV_API int hkv_get_view(const hkv_table* table, hkv_table_view* view);
+
+/* Device status word: bit 0 a bounded slot wait ran out, bit 1 eviction
+ * retries ran out.  Reading it synchronises the stream; it is cleared by the
+ * read.  (The reference spins without bound in these places:
+ * include/merlin/core_kernels/kernel_utils.cuh:853-855, upsert.cuh:149.) */
+HKV_API int hkv_device_status(hkv_table* table, hkv_stream stream, uint32_t* status);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HKV_B200_H_ */

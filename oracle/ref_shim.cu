@@ -1,0 +1,278 @@
+// TEST INFRASTRUCTURE ONLY -- never linked into, loaded by or called from the
+// product library.
+//
+// Thin C-ABI shim around the *unmodified* reference headers
+// (include/merlin_hashtable.cuh of NVIDIA-Merlin/HierarchicalKV).  It is
+// compiled from the reference sources where they lie (see oracle/Makefile),
+// one shared object per eviction strategy (-DREF_STRATEGY=0..4), with hidden
+// visibility so that the reference's nv::merlin symbols never meet the
+// product's.  The parity tests and the reference arm of the benchmark drive
+// both libraries with the same seeded batches.
+//
+// K = uint64_t, V = float, S = uint64_t, as in the reference benchmark
+// (benchmark/merlin_hashtable_benchmark.cc.cu:492).
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <exception>
+#include <memory>
+#include <string>
+
+#include "merlin_hashtable.cuh"
+
+#ifndef REF_STRATEGY
+#define REF_STRATEGY 0
+#endif
+
+#define REF_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+using K = uint64_t;
+using V = float;
+using S = uint64_t;
+using Table = nv::merlin::HashTable<K, V, S, REF_STRATEGY>;
+
+thread_local std::string g_err;
+
+template <class K_, class S_>
+struct PredScoreLess {
+  __forceinline__ __device__ bool operator()(const K_& key, S_& score,
+                                             const K_& pattern,
+                                             const S_& threshold) {
+    return score < threshold;
+  }
+};
+
+template <class K_, class S_>
+struct PredScoreGreaterEq {
+  __forceinline__ __device__ bool operator()(const K_& key, S_& score,
+                                             const K_& pattern,
+                                             const S_& threshold) {
+    return score >= threshold;
+  }
+};
+
+template <class K_, class S_>
+struct PredKeyMask {
+  __forceinline__ __device__ bool operator()(const K_& key, S_& score,
+                                             const K_& pattern,
+                                             const S_& threshold) {
+    return (key & static_cast<K_>(threshold)) == pattern;
+  }
+};
+
+template <class F>
+int guarded(F&& f) {
+  try {
+    f();
+    return 0;
+  } catch (const std::exception& e) {
+    g_err = e.what();
+    return 1;
+  } catch (...) {
+    g_err = "unknown exception";
+    return 1;
+  }
+}
+
+}  // namespace
+
+REF_API const char* ref_last_error() { return g_err.c_str(); }
+REF_API int ref_strategy() { return REF_STRATEGY; }
+
+REF_API int ref_create(uint64_t init_capacity, uint64_t max_capacity,
+                       uint64_t max_hbm_for_vectors, uint64_t dim,
+                       uint64_t max_bucket_size, int reserved_key_start_bit,
+                       int api_lock, void** out) {
+  return guarded([&] {
+    nv::merlin::HashTableOptions o;
+    o.init_capacity = init_capacity;
+    o.max_capacity = max_capacity;
+    o.max_hbm_for_vectors = max_hbm_for_vectors;
+    o.dim = dim;
+    o.max_bucket_size = max_bucket_size;
+    o.reserved_key_start_bit = reserved_key_start_bit;
+    o.api_lock = api_lock != 0;
+    // One allocation for all buckets' metadata instead of one per bucket.
+    size_t buckets = 1;
+    while (buckets * 2 * max_bucket_size <= init_capacity) buckets *= 2;
+    o.num_of_buckets_per_alloc = buckets;
+    auto* t = new Table();
+    try {
+      t->init(o);
+    } catch (...) {
+      delete t;
+      throw;
+    }
+    *out = t;
+  });
+}
+
+REF_API int ref_destroy(void* t) {
+  return guarded([&] { delete static_cast<Table*>(t); });
+}
+
+REF_API int ref_set_global_epoch(void* t, uint64_t epoch) {
+  return guarded([&] { static_cast<Table*>(t)->set_global_epoch(epoch); });
+}
+
+REF_API int ref_insert_or_assign(void* t, uint64_t n, const K* keys,
+                                 const V* values, const S* scores,
+                                 cudaStream_t stream, int unique_key) {
+  return guarded([&] {
+    static_cast<Table*>(t)->insert_or_assign(n, keys, values, scores, stream,
+                                             unique_key != 0);
+  });
+}
+
+REF_API int ref_insert_and_evict(void* t, uint64_t n, const K* keys,
+                                 const V* values, const S* scores,
+                                 K* evicted_keys, V* evicted_values,
+                                 S* evicted_scores, uint64_t* d_evicted_counter,
+                                 cudaStream_t stream, int unique_key) {
+  return guarded([&] {
+    static_cast<Table*>(t)->insert_and_evict(
+        n, keys, values, scores, evicted_keys, evicted_values, evicted_scores,
+        reinterpret_cast<size_t*>(d_evicted_counter), stream, unique_key != 0);
+  });
+}
+
+REF_API int ref_accum_or_assign(void* t, uint64_t n, const K* keys,
+                                const V* value_or_deltas,
+                                const bool* accum_or_assigns, const S* scores,
+                                cudaStream_t stream) {
+  return guarded([&] {
+    static_cast<Table*>(t)->accum_or_assign(n, keys, value_or_deltas,
+                                            accum_or_assigns, scores, stream);
+  });
+}
+
+REF_API int ref_find_or_insert(void* t, uint64_t n, const K* keys, V* values,
+                               S* scores, cudaStream_t stream, int unique_key) {
+  return guarded([&] {
+    static_cast<Table*>(t)->find_or_insert(n, keys, values, scores, stream,
+                                           unique_key != 0);
+  });
+}
+
+REF_API int ref_find_or_insert_ptr(void* t, uint64_t n, const K* keys,
+                                   V** values, bool* founds, S* scores,
+                                   cudaStream_t stream, int unique_key) {
+  return guarded([&] {
+    static_cast<Table*>(t)->find_or_insert(n, keys, values, founds, scores,
+                                           stream, unique_key != 0);
+  });
+}
+
+REF_API int ref_assign(void* t, uint64_t n, const K* keys, const V* values,
+                       const S* scores, cudaStream_t stream, int unique_key) {
+  return guarded([&] {
+    static_cast<Table*>(t)->assign(n, keys, values, scores, stream,
+                                   unique_key != 0);
+  });
+}
+
+REF_API int ref_assign_scores(void* t, uint64_t n, const K* keys,
+                              const S* scores, cudaStream_t stream,
+                              int unique_key) {
+  return guarded([&] {
+    static_cast<Table*>(t)->assign_scores(n, keys, scores, stream,
+                                          unique_key != 0);
+  });
+}
+
+REF_API int ref_find(void* t, uint64_t n, const K* keys, V* values,
+                     bool* founds, S* scores, cudaStream_t stream) {
+  return guarded([&] {
+    static_cast<const Table*>(t)->find(n, keys, values, founds, scores, stream);
+  });
+}
+
+REF_API int ref_find_missed(void* t, uint64_t n, const K* keys, V* values,
+                            K* missed_keys, int* missed_indices,
+                            int* missed_size, S* scores, cudaStream_t stream) {
+  return guarded([&] {
+    static_cast<const Table*>(t)->find(n, keys, values, missed_keys,
+                                       missed_indices, missed_size, scores,
+                                       stream);
+  });
+}
+
+REF_API int ref_find_ptr(void* t, uint64_t n, const K* keys, V** values,
+                         bool* founds, S* scores, cudaStream_t stream,
+                         int unique_key) {
+  return guarded([&] {
+    static_cast<const Table*>(t)->find(n, keys, values, founds, scores, stream,
+                                       unique_key != 0);
+  });
+}
+
+REF_API int ref_contains(void* t, uint64_t n, const K* keys, bool* founds,
+                         cudaStream_t stream) {
+  return guarded(
+      [&] { static_cast<const Table*>(t)->contains(n, keys, founds, stream); });
+}
+
+REF_API int ref_erase(void* t, uint64_t n, const K* keys, cudaStream_t stream) {
+  return guarded([&] { static_cast<Table*>(t)->erase(n, keys, stream); });
+}
+
+REF_API int ref_export_batch(void* t, uint64_t n, uint64_t offset,
+                             uint64_t* d_counter, K* keys, V* values, S* scores,
+                             cudaStream_t stream) {
+  return guarded([&] {
+    static_cast<const Table*>(t)->export_batch(
+        n, offset, reinterpret_cast<size_t*>(d_counter), keys, values, scores,
+        stream);
+  });
+}
+
+// pred: 0 = score < threshold, 1 = score >= threshold,
+//       2 = (key & threshold) == pattern.
+REF_API int ref_export_batch_if(void* t, int pred, uint64_t pattern,
+                                uint64_t threshold, uint64_t n, uint64_t offset,
+                                uint64_t* d_counter, K* keys, V* values,
+                                S* scores, cudaStream_t stream) {
+  return guarded([&] {
+    const Table* tb = static_cast<const Table*>(t);
+    size_t* c = reinterpret_cast<size_t*>(d_counter);
+    switch (pred) {
+      case 0:
+        tb->export_batch_if<PredScoreLess>(pattern, threshold, n, offset, c,
+                                           keys, values, scores, stream);
+        break;
+      case 1:
+        tb->export_batch_if<PredScoreGreaterEq>(pattern, threshold, n, offset,
+                                                c, keys, values, scores, stream);
+        break;
+      case 2:
+        tb->export_batch_if<PredKeyMask>(pattern, threshold, n, offset, c, keys,
+                                         values, scores, stream);
+        break;
+      default:
+        throw std::invalid_argument("unknown predicate");
+    }
+  });
+}
+
+REF_API int ref_size(void* t, cudaStream_t stream, uint64_t* out) {
+  return guarded([&] { *out = static_cast<const Table*>(t)->size(stream); });
+}
+
+REF_API int ref_capacity(void* t, uint64_t* out) {
+  return guarded([&] { *out = static_cast<const Table*>(t)->capacity(); });
+}
+
+REF_API int ref_bucket_count(void* t, uint64_t* out) {
+  return guarded([&] { *out = static_cast<const Table*>(t)->bucket_count(); });
+}
+
+REF_API int ref_load_factor(void* t, cudaStream_t stream, float* out) {
+  return guarded(
+      [&] { *out = static_cast<const Table*>(t)->load_factor(stream); });
+}
+
+REF_API int ref_clear(void* t, cudaStream_t stream) {
+  return guarded([&] { static_cast<Table*>(t)->clear(stream); });
+}
