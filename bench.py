@@ -1,0 +1,573 @@
+#!/usr/bin/env python
+"""Benchmark of the hash-table hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl product|reference]
+
+Workload (the reference's pure-HBM throughput table): capacity 64 Mi keys
+(524,288 buckets x 128 slots), uint64 keys, fp32 values of dim 64 (256-byte
+rows), LRU scores, batches of 1,048,576 unique keys, table filled to load
+factor ~1.0.  A step is one `find` of one batch whose keys are all present.
+`value` is find throughput in the reference's unit, n / seconds / 2^30
+("billion-KV/s", benchmark/merlin_hashtable_benchmark.cc.cu:415-417).  The
+other operations of the workload (50 %-hit find, insert_or_assign,
+find_or_insert) are timed after the headline steps and reported under `ops`.
+
+All inputs are synthetic: keys are a seeded bijective mix of a counter (so
+they are unique and uniform), rows are a function of the key.
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BINARY_BILLION = float(1 << 30)
+FIND_HIT_BYTES = lambda row: 2 * row + 145      # key + digest line + key verify + row in + row out + flag
+FIND_MISS_BYTES = 137
+UPSERT_HIT_BYTES = lambda row: 2 * row + 161
+UPSERT_EVICT_BYTES = lambda row: 2 * row + 1193
+
+
+# ---------------------------------------------------------------------------
+# synthetic keys
+# ---------------------------------------------------------------------------
+def _s64(x: int) -> int:
+    x &= (1 << 64) - 1
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+def _lsr(x: torch.Tensor, s: int) -> torch.Tensor:
+    return (x >> s) & ((1 << (64 - s)) - 1)
+
+
+def mixed_keys(start: int, n: int, device) -> torch.Tensor:
+    """splitmix64 finaliser of a counter: a bijection, so keys never repeat."""
+    z = torch.arange(start, start + n, dtype=torch.int64, device=device) + _s64(0x9E3779B97F4A7C15)
+    z = (z ^ _lsr(z, 30)) * _s64(0xBF58476D1CE4E5B9)
+    z = (z ^ _lsr(z, 27)) * _s64(0x94D049BB133111EB)
+    z = z ^ _lsr(z, 31)
+    # the four reserved keys (top 62 bits all set) are remapped to small ones
+    reserved = (z & -4) == -4
+    return torch.where(reserved, z & 0xFFFF, z)
+
+
+def rows_for(keys: torch.Tensor, dim: int) -> torch.Tensor:
+    """Row content is a function of the key: column j holds (key mod 2^20) + j."""
+    base = (keys & 0xFFFFF).to(torch.float32)
+    return (base[:, None] + torch.arange(dim, device=keys.device, dtype=torch.float32)[None, :]).contiguous()
+
+
+# ---------------------------------------------------------------------------
+# the two arms
+# ---------------------------------------------------------------------------
+class ProductArm:
+    name = "product"
+
+    def __init__(self, capacity: int, dim: int, hbm_bytes: int):
+        import hierarchicalkv_b200 as hkv
+        from hierarchicalkv_b200.build import build_library
+
+        build_library()
+        self.t = hkv.HashTable(hkv.EvictStrategy.kLru)
+        self.t.init(hkv.HashTableOptions(init_capacity=capacity, max_capacity=capacity,
+                                         max_hbm_for_vectors=hbm_bytes, dim=dim))
+        self.dim = dim
+
+    def insert_or_assign(self, keys, values):
+        self.t.insert_or_assign(keys.numel(), keys, values)
+
+    def find_or_insert(self, keys, values):
+        self.t.find_or_insert(keys.numel(), keys, values)
+
+    def find(self, keys, values, founds):
+        self.t.find(keys.numel(), keys, values, founds)
+
+    def size(self):
+        return self.t.size()
+
+    def capacity(self):
+        return self.t.capacity()
+
+    def export_keys(self, offset: int, n: int) -> torch.Tensor:
+        k = torch.empty(n, dtype=torch.int64, device="cuda")
+        c = torch.zeros(1, dtype=torch.int64, device="cuda")
+        self.t.export_batch(n, offset, c, k, None, None)
+        torch.cuda.synchronize()
+        return k[: int(c.item())]
+
+    launches_per_find = 1
+
+    def close(self):
+        self.t.close()
+
+
+class ReferenceArm:
+    """The unmodified reference (its own CUDA kernels, compiled for sm_100a
+    behind oracle/ref_shim.cu).  The reference has no CPU implementation of
+    this path, so its arm runs on the same GPU."""
+
+    name = "reference"
+
+    def __init__(self, capacity: int, dim: int, hbm_bytes: int):
+        path = os.path.join(ROOT, "oracle", "_ref", "libhkv_ref_s0.so")
+        if not os.path.exists(path):
+            raise FileNotFoundError(path)
+        self.lib = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
+        self.lib.ref_last_error.restype = ctypes.c_char_p
+        P, U = ctypes.c_void_p, ctypes.c_uint64
+        self.lib.ref_create.argtypes = [U, U, U, U, U, ctypes.c_int, ctypes.c_int,
+                                        ctypes.POINTER(P)]
+        self.lib.ref_insert_or_assign.argtypes = [P, U, P, P, P, P, ctypes.c_int]
+        self.lib.ref_find_or_insert.argtypes = [P, U, P, P, P, P, ctypes.c_int]
+        self.lib.ref_find.argtypes = [P, U, P, P, P, P, P]
+        self.lib.ref_export_batch.argtypes = [P, U, U, P, P, P, P, P]
+        self.lib.ref_size.argtypes = [P, P, ctypes.POINTER(U)]
+        self.lib.ref_capacity.argtypes = [P, ctypes.POINTER(U)]
+        self.lib.ref_destroy.argtypes = [P]
+        self.h = P()
+        self._chk(self.lib.ref_create(capacity, capacity, hbm_bytes, dim, 128, 0, 1,
+                                      ctypes.byref(self.h)))
+        self.dim = dim
+        self._scratch_rows = None
+
+    def _chk(self, rc):
+        if rc:
+            raise RuntimeError("reference: " + (self.lib.ref_last_error() or b"").decode())
+
+    @staticmethod
+    def _s():
+        return torch.cuda.current_stream().cuda_stream or None
+
+    def insert_or_assign(self, keys, values):
+        self._chk(self.lib.ref_insert_or_assign(self.h, keys.numel(), keys.data_ptr(),
+                                                values.data_ptr(), None, self._s(), 1))
+
+    def find_or_insert(self, keys, values):
+        self._chk(self.lib.ref_find_or_insert(self.h, keys.numel(), keys.data_ptr(),
+                                              values.data_ptr(), None, self._s(), 1))
+
+    def find(self, keys, values, founds):
+        self._chk(self.lib.ref_find(self.h, keys.numel(), keys.data_ptr(), values.data_ptr(),
+                                    founds.data_ptr(), None, self._s()))
+
+    def size(self):
+        o = ctypes.c_uint64(0)
+        self._chk(self.lib.ref_size(self.h, self._s(), ctypes.byref(o)))
+        return o.value
+
+    def capacity(self):
+        o = ctypes.c_uint64(0)
+        self._chk(self.lib.ref_capacity(self.h, ctypes.byref(o)))
+        return o.value
+
+    def export_keys(self, offset: int, n: int) -> torch.Tensor:
+        k = torch.empty(n, dtype=torch.int64, device="cuda")
+        if self._scratch_rows is None or self._scratch_rows.shape[0] < n:
+            self._scratch_rows = torch.empty((n, self.dim), dtype=torch.float32, device="cuda")
+        c = torch.zeros(1, dtype=torch.int64, device="cuda")
+        self._chk(self.lib.ref_export_batch(self.h, n, offset, c.data_ptr(), k.data_ptr(),
+                                            self._scratch_rows.data_ptr(), None, self._s()))
+        torch.cuda.synchronize()
+        return k[: int(c.item())]
+
+    # memset of founds + lock kernel + lookup kernel + unlock kernel
+    launches_per_find = 4
+
+    def close(self):
+        if self.h:
+            self.lib.ref_destroy(self.h)
+            self.h = ctypes.c_void_p()
+
+
+# ---------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    """SM clock and throttle-reason samples (NVML, every few ms) taken while
+    the timed region runs."""
+
+    REASONS = {
+        "hw_slowdown": 0x8,
+        "sw_power_cap": 0x4,
+        "hw_thermal_slowdown": 0x40,
+        "sw_thermal_slowdown": 0x20,
+    }
+
+    def __init__(self, gpu_index: int, period_s: float = 0.004):
+        self.gpu_index = gpu_index
+        self.period_s = period_s
+        self.sm: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self.power_w = 0.0
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+
+    def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it is numeric
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            idx = self.gpu_index
+            if vis:
+                parts = [p for p in vis.split(",") if p.strip().isdigit()]
+                if len(parts) > self.gpu_index:
+                    idx = int(parts[self.gpu_index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+            return
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.sm.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for name, bit in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self.power_w = max(self.power_w, nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+            except Exception:
+                pass
+            time.sleep(self.period_s)
+
+    def stop(self) -> dict:
+        if self._nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        self._stop.set()
+        self._thread.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                "sm_max_mhz": self.max_mhz, "samples": len(self.sm),
+                "power_w_max": round(self.power_w, 1), "reasons": sorted(self.reasons)}
+
+
+def fill_table(arm, capacity: int, dim: int, batch: int, target_lf: float, key_base: int):
+    """insert_or_assign of fresh unique keys until the load factor is reached
+    (uniform keys fill some buckets early; they evict under LRU while the
+    others catch up)."""
+    inserted = 0
+    max_batches = int(2.0 * capacity / batch) + 8
+    for b in range(max_batches):
+        keys = mixed_keys(key_base + b * batch, batch, "cuda")
+        arm.insert_or_assign(keys, rows_for(keys, dim))
+        inserted += batch
+        if inserted >= target_lf * capacity and (b % 4 == 3 or inserted >= 1.3 * capacity):
+            if arm.size() >= target_lf * capacity - 0.0005 * capacity:
+                break
+    torch.cuda.synchronize()
+    return inserted
+
+
+def present_batches(arm, capacity: int, batch: int, count: int, seed: int):
+    """`count` query batches of `batch` distinct keys that are in the table."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    chunk = min(capacity, 8 * batch * 2)
+    out = []
+    span = capacity // count
+    for i in range(count):
+        off = (i * span) // 128 * 128
+        ks = arm.export_keys(off, min(chunk, capacity - off))
+        perm = torch.randperm(ks.numel(), generator=g, device="cuda")[:batch]
+        out.append(ks[perm].contiguous())
+    return out
+
+
+def time_steps(fn, steps: int, warmup: int, barrier=None):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(steps):
+        fn(warmup + i)
+    end.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return start.elapsed_time(end)  # ms
+
+
+def cpu_baseline(dim: int, batch: int, seconds_budget: float = 20.0) -> dict:
+    """The CPU restatement (oracle/hkv_oracle.cpp) on all host threads, on a
+    bounded sample: a 1/8-size table filled to the same load factor, then
+    timed all-hit find batches."""
+    import numpy as np
+    from tests.hkv_testlib import OracleTable, load_oracle
+
+    lib = load_oracle()
+    threads = lib.orc_hardware_threads()
+    capacity = 8 << 20
+    t = OracleTable(capacity, dim, strategy=0)
+    fill_batch = 1 << 20
+    t0 = time.time()
+    b = 0
+    while t.size() < 0.97 * capacity and b < 16:
+        keys = mixed_keys(b * fill_batch + (1 << 40), fill_batch, "cpu").numpy().view(np.uint64)
+        vals = np.zeros((fill_batch, dim), dtype=np.float32)
+        t.set_clock((b + 1) << 22)
+        t.insert_or_assign(keys, vals, threads=threads)
+        b += 1
+    fill_s = time.time() - t0
+    ks, _, _ = t.export_batch(n=4 * batch)
+    rng = np.random.default_rng(3)
+    q = np.ascontiguousarray(rng.permutation(ks)[:batch])
+    vals = np.empty((batch, dim), dtype=np.float32)
+    vals.fill(0)  # touch the pages outside the timed region
+    f = np.zeros(batch, dtype=np.bool_)
+    reps, spent = 0, 0.0
+    best = None
+    while spent < max(2.0, seconds_budget - fill_s) and reps < 50:
+        t1 = time.time()
+        lib.orc_find(t.h, q.size, q.ctypes.data, vals.ctypes.data, f.ctypes.data, None, threads)
+        dt = time.time() - t1
+        spent += dt
+        reps += 1
+        best = dt if best is None else min(best, dt)
+    assert f.all()
+    return {"value": q.size / best / BINARY_BILLION, "unit": "B-KV/s (n/s/2^30)",
+            "cores": threads, "kind": "port",
+            "sample": f"find, all hits, {q.size} keys x {reps} reps (best), table of "
+                      f"{capacity} slots (1/8 of the workload) at load factor "
+                      f"{t.size() / capacity:.3f}, dim {dim}"}
+
+
+# ---------------------------------------------------------------------------
+# main
+# ---------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["product", "reference"], default="product")
+    ap.add_argument("--capacity", type=int, default=64 << 20)
+    ap.add_argument("--dim", type=int, default=64)
+    ap.add_argument("--batch", type=int, default=1 << 20)
+    ap.add_argument("--load-factor", type=float, default=1.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ops", action="store_true", help="skip the secondary operations")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        torch.cuda.set_device(0)
+    barrier = (lambda: dist.barrier()) if dist else None
+
+    capacity, dim, batch = args.capacity, args.dim, args.batch
+    row = dim * 4
+    hbm_bytes = capacity * row + (1 << 30)
+
+    if args.impl == "reference":
+        try:
+            arm = ReferenceArm(capacity, dim, hbm_bytes)
+        except (FileNotFoundError, OSError) as e:
+            if rank == 0:
+                print(json.dumps({"impl": "reference",
+                                  "unavailable": f"oracle/_ref/libhkv_ref_s0.so not loadable: {e}"}))
+            return
+    else:
+        arm = ProductArm(capacity, dim, hbm_bytes)
+
+    # Each rank owns one shard of `capacity` slots and serves the batches that
+    # hash to it (weak scaling: per-GPU work is fixed as N grows).
+    key_base = rank << 44
+    inserted = fill_table(arm, capacity, dim, batch, args.load_factor, key_base)
+    size = arm.size()
+    load_factor = size / arm.capacity()
+    n_query_sets = 8
+    queries = present_batches(arm, capacity, batch, n_query_sets, seed=17 + rank)
+    out_vals = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+    founds = torch.empty(batch, dtype=torch.bool, device="cuda")
+
+    def step(i):
+        arm.find(queries[i % n_query_sets], out_vals, founds)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_steps(step, args.steps, args.warmup, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # correctness of what was timed: every key found, rows as generated
+    last = queries[(args.warmup + args.steps - 1) % n_query_sets]
+    assert bool(founds.all()), "timed find missed keys that are in the table"
+    assert torch.equal(out_vals, rows_for(last, dim)), "timed find returned wrong rows"
+
+    if dist:
+        tms = torch.tensor([ms], device="cuda")
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    total_keys = batch * args.steps * world
+    value = total_keys / (ms / 1e3) / BINARY_BILLION
+    ms_per_step = ms / args.steps
+    algo_bytes = FIND_HIT_BYTES(row) * batch
+    achieved_gbs = algo_bytes / (ms_per_step / 1e3) / 1e9
+
+    # ---- end to end: host keys in, host rows + flags out, every step ----------
+    h_keys = [q.cpu().pin_memory() for q in queries]
+    h_vals = torch.empty((batch, dim), dtype=torch.float32).pin_memory()
+    h_founds = torch.empty(batch, dtype=torch.bool).pin_memory()
+    d_keys = torch.empty(batch, dtype=torch.int64, device="cuda")
+
+    def e2e_step(i):
+        d_keys.copy_(h_keys[i % n_query_sets], non_blocking=True)
+        arm.find(d_keys, out_vals, founds)
+        h_vals.copy_(out_vals, non_blocking=True)
+        h_founds.copy_(founds, non_blocking=True)
+
+    e2e_steps = max(5, min(args.steps, 20))
+    e2e_ms = time_steps(e2e_step, e2e_steps, 3, barrier)
+    if dist:
+        tms = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tms.item())
+    assert bool(h_founds.all())
+    e2e_value = batch * e2e_steps * world / (e2e_ms / 1e3) / BINARY_BILLION
+
+    # ---- the other operations of the workload (not part of `value`) -----------
+    ops = {}
+    if not args.no_ops:
+        reps = 10
+
+        def per_kv(ms_total, n_keys):
+            return n_keys / (ms_total / 1e3) / BINARY_BILLION
+
+        # find, 50 % hits
+        half = []
+        for i in range(n_query_sets):
+            fresh = mixed_keys((1 << 50) + key_base + i * batch, batch // 2, "cuda")
+            half.append(torch.cat([queries[i][: batch // 2], fresh])[torch.randperm(batch, device="cuda")].contiguous())
+        t_ms = time_steps(lambda i: arm.find(half[i % n_query_sets], out_vals, founds), reps, 3)
+        ops["find_50pct_hit"] = {"b_kv_s": per_kv(t_ms, batch * reps),
+                                 "achieved_gbs": (FIND_HIT_BYTES(row) + FIND_MISS_BYTES) / 2 * batch * reps / (t_ms / 1e3) / 1e9}
+        # insert_or_assign, all keys present (assign path)
+        vals = [rows_for(q, dim) for q in queries[:2]]
+        t_ms = time_steps(lambda i: arm.insert_or_assign(queries[i % 2], vals[i % 2]), reps, 3)
+        ops["insert_or_assign_all_hit"] = {"b_kv_s": per_kv(t_ms, batch * reps),
+                                           "achieved_gbs": UPSERT_HIT_BYTES(row) * batch * reps / (t_ms / 1e3) / 1e9}
+        # insert_or_assign, all keys new (every insert evicts at load factor 1)
+        newk = [mixed_keys((1 << 52) + key_base + i * batch, batch, "cuda") for i in range(reps + 3)]
+        newv = rows_for(newk[0], dim)
+        t_ms = time_steps(lambda i: arm.insert_or_assign(newk[i], newv), reps, 3)
+        ops["insert_or_assign_all_new"] = {"b_kv_s": per_kv(t_ms, batch * reps),
+                                           "achieved_gbs": UPSERT_EVICT_BYTES(row) * batch * reps / (t_ms / 1e3) / 1e9}
+        # the reference benchmark's mix: 60 % present, 40 % new
+        mixk = []
+        for i in range(reps + 3):
+            cur = arm.export_keys(((i * 7919) % (capacity // 128 - 8 * batch // 128)) * 128, 8 * batch)
+            cur = cur[torch.randperm(cur.numel(), device="cuda")[: int(batch * 0.6)]]
+            fresh = mixed_keys((1 << 54) + key_base + i * batch, batch - cur.numel(), "cuda")
+            mixk.append(torch.cat([cur, fresh]).contiguous())
+        t_ms = time_steps(lambda i: arm.insert_or_assign(mixk[i], newv), reps, 3)
+        ops["insert_or_assign_60_40"] = {"b_kv_s": per_kv(t_ms, batch * reps),
+                                         "achieved_gbs": (0.6 * UPSERT_HIT_BYTES(row) + 0.4 * UPSERT_EVICT_BYTES(row)) * batch * reps / (t_ms / 1e3) / 1e9}
+        newk2 = [mixed_keys((1 << 56) + key_base + i * batch, batch, "cuda") for i in range(reps + 3)]
+        t_ms = time_steps(lambda i: arm.find_or_insert(newk2[i], newv), reps, 3)
+        ops["find_or_insert_all_new"] = {"b_kv_s": per_kv(t_ms, batch * reps),
+                                         "achieved_gbs": UPSERT_EVICT_BYTES(row) * batch * reps / (t_ms / 1e3) / 1e9}
+        for v in ops.values():
+            v["b_kv_s"] = round(v["b_kv_s"], 4)
+            v["achieved_gbs"] = round(v["achieved_gbs"], 1)
+
+    arm.close()
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            peak = float(json.load(f)["hbm_gbs"])
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+
+    line = {
+        "metric": "find B-KV/s at LF=1.0, dim=64 (n/s/2^30), all keys present",
+        "value": round(value, 4),
+        "unit": "B-KV/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 5),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "u64 keys / opaque 256-byte rows (fp32 x 64)",
+        "data": "synthetic",
+        "impl": args.impl,
+        "config": {
+            "workload": "pure-HBM throughput table: capacity %d, dim %d fp32, LRU, batch %d, find with 100%% hits" % (capacity, dim, batch),
+            "load_factor": round(load_factor, 5),
+            "keys_inserted_to_fill": inserted,
+            "l2": "inputs larger than L2: %.1f GiB of rows hit at random, %d rotating query batches, %d MiB output buffer" % (capacity * row / 2**30, n_query_sets, batch * row >> 20),
+            "sharding": "one shard of this size per GPU, batches pre-routed to their shard" if world > 1 else "single table",
+        },
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 4), "unit": "B-KV/s",
+                "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * row + batch,
+                "steps": e2e_steps},
+        "gpu_launches": args.steps * arm.launches_per_find,
+        "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(achieved_gbs / peak, 4),
+                     "traffic": None, "peak_source": peak_src,
+                     "algorithmic_bytes_per_key": FIND_HIT_BYTES(row),
+                     "frac_of_nominal_8000": round(achieved_gbs / 8000.0, 4)},
+        "ops": ops,
+    }
+    if args.impl == "reference":
+        line["cpu_baseline"] = {"value": line["value"], "unit": "B-KV/s", "cores": 0,
+                                "kind": "reference",
+                                "sample": "the reference has no CPU path: its own CUDA kernels "
+                                          "(oracle/_ref, sm_100a build) on the same GPU, same workload"}
+        line["e2e"]["h2d_bytes_per_step"] = batch * 8
+    elif not args.no_cpu_baseline and world == 1:
+        try:
+            line["cpu_baseline"] = cpu_baseline(dim, batch)
+            line["cpu_baseline"]["value"] = round(line["cpu_baseline"]["value"], 5)
+        except Exception as e:  # the baseline is reported, never required
+            line["cpu_baseline"] = {"value": None, "unit": "B-KV/s", "cores": 0, "kind": "port",
+                                    "sample": f"failed: {e}"}
+    print(json.dumps(line))
+    if dist:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -62,6 +62,24 @@ struct PredKeyMask {
   }
 };
 
+// Device-side probes of the reference's own arithmetic, for golden vectors.
+__global__ void probe_constants_kernel(uint64_t* out) {
+  out[0] = nv::merlin::EMPTY_KEY;
+  out[1] = nv::merlin::RECLAIM_KEY;
+  out[2] = nv::merlin::LOCKED_KEY;
+  out[3] = nv::merlin::empty_digest<uint64_t>();
+  out[4] = nv::merlin::reclaim_digest<uint64_t>();
+}
+
+__global__ void probe_keys_kernel(uint64_t n, const uint64_t* keys, uint64_t* hashes,
+                                  uint8_t* digests, bool* reserved) {
+  const uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  hashes[i] = nv::merlin::Murmur3HashDevice(keys[i]);
+  digests[i] = nv::merlin::get_digest<uint64_t>(keys[i]);
+  reserved[i] = nv::merlin::IS_RESERVED_KEY<uint64_t>(keys[i]);
+}
+
 template <class F>
 int guarded(F&& f) {
   try {
@@ -275,4 +293,25 @@ REF_API int ref_load_factor(void* t, cudaStream_t stream, float* out) {
 
 REF_API int ref_clear(void* t, cudaStream_t stream) {
   return guarded([&] { static_cast<Table*>(t)->clear(stream); });
+}
+
+// out[0..4] = EMPTY_KEY, RECLAIM_KEY, LOCKED_KEY, empty digest, reclaim digest
+// as the reference's device code sees them after init_reserved_keys(bit).
+REF_API int ref_probe_reserved(int reserved_key_start_bit, uint64_t* d_out5) {
+  return guarded([&] {
+    // init_reserved_keys leaves the defaults in place for bit 0
+    // (include/merlin/types.cuh:81-85), so a fresh process is assumed there.
+    CUDA_CHECK(nv::merlin::init_reserved_keys(reserved_key_start_bit));
+    probe_constants_kernel<<<1, 1>>>(d_out5);
+    CUDA_CHECK(cudaDeviceSynchronize());
+  });
+}
+
+REF_API int ref_probe_keys(uint64_t n, const uint64_t* d_keys, uint64_t* d_hashes,
+                           uint8_t* d_digests, bool* d_reserved) {
+  return guarded([&] {
+    probe_keys_kernel<<<unsigned((n + 255) / 256), 256>>>(n, d_keys, d_hashes, d_digests,
+                                                          d_reserved);
+    CUDA_CHECK(cudaDeviceSynchronize());
+  });
 }

@@ -177,8 +177,15 @@ class OracleTable:
         self.lib.orc_find(self.h, n, _np(keys), _np(values), _np(founds), _np(scores), threads)
         return values, founds, scores
 
+    def contains(self, keys):
+        founds = np.zeros(keys.size, dtype=np.bool_)
+        self.lib.orc_contains(self.h, keys.size, _np(keys), _np(founds))
+        return founds
+
     def find_or_insert(self, keys, values, scores=None, threads=1):
+        values = np.ascontiguousarray(values).copy()
         self.lib.orc_find_or_insert(self.h, keys.size, _np(keys), _np(values), _np(scores), threads)
+        return values
 
     def find_or_insert_ptr(self, keys, scores=None):
         founds = np.zeros(keys.size, dtype=np.bool_)
@@ -425,10 +432,23 @@ def ref_available(strategy: int = 0) -> bool:
 _ref_libs = {}
 
 
-def load_ref(strategy: int) -> ctypes.CDLL:
-    if strategy in _ref_libs:
+def load_ref(strategy: int, private: bool = False) -> ctypes.CDLL:
+    """private=True loads a fresh copy of the library: the reference keeps its
+    reserved keys in __constant__ memory of the loaded module, so a table with
+    a non-default reserved_key_start_bit changes them for every later table of
+    that module (include/merlin/types.cuh:80-109)."""
+    if strategy in _ref_libs and not private:
         return _ref_libs[strategy]
-    lib = ctypes.CDLL(os.path.join(REF_DIR, f"libhkv_ref_s{strategy}.so"), mode=ctypes.RTLD_LOCAL)
+    path = os.path.join(REF_DIR, f"libhkv_ref_s{strategy}.so")
+    if private:
+        import shutil
+        import tempfile
+
+        tmp = tempfile.NamedTemporaryFile(prefix=f"hkv_ref_s{strategy}_", suffix=".so", delete=False)
+        tmp.close()
+        shutil.copyfile(path, tmp.name)
+        path = tmp.name
+    lib = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
     lib.ref_last_error.restype = ctypes.c_char_p
     sig = {
         "ref_create": [_U64, _U64, _U64, _U64, _U64, _INT, _INT, ctypes.POINTER(_P)],
@@ -454,11 +474,14 @@ def load_ref(strategy: int) -> ctypes.CDLL:
         "ref_load_factor": [_P, _P, ctypes.POINTER(ctypes.c_float)],
         "ref_clear": [_P, _P],
     }
+    sig["ref_probe_reserved"] = [_INT, _P]
+    sig["ref_probe_keys"] = [_U64, _P, _P, _P, _P]
     for name, args in sig.items():
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = _INT
-    _ref_libs[strategy] = lib
+    if not private:
+        _ref_libs[strategy] = lib
     return lib
 
 
@@ -474,7 +497,7 @@ class RefTable:
 
         self.torch = torch
         self.dim = dim
-        self.lib = load_ref(strategy)
+        self.lib = load_ref(strategy, private=reserved_key_start_bit != 0)
         self.h = _P()
         hbm = (16 << 30) if max_hbm_for_vectors is None else max_hbm_for_vectors
         self._chk(self.lib.ref_create(capacity, max_capacity or capacity, hbm, dim, 128,
@@ -575,6 +598,21 @@ class RefTable:
         self._chk(self.lib.ref_assign(self.h, keys.size, self._p(k), self._p(v), self._p(s),
                                       self._s(), 1))
         self.torch.cuda.synchronize()
+
+    def assign_scores(self, keys, scores=None):
+        k = to_dev(keys)
+        s = to_dev(scores) if scores is not None else None
+        self._chk(self.lib.ref_assign_scores(self.h, keys.size, self._p(k), self._p(s), self._s(),
+                                             1))
+        self.torch.cuda.synchronize()
+
+    def contains(self, keys):
+        torch = self.torch
+        k = to_dev(keys)
+        f = torch.zeros(keys.size, dtype=torch.bool, device="cuda")
+        self._chk(self.lib.ref_contains(self.h, keys.size, self._p(k), self._p(f), self._s()))
+        torch.cuda.synchronize()
+        return f.cpu().numpy()
 
     def erase(self, keys):
         k = to_dev(keys)
