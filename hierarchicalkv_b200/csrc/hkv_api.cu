@@ -855,6 +855,24 @@ int hkv_get_view(const hkv_table* t, hkv_table_view* view) {
   });
 }
 
+int hkv_external_begin(hkv_table* t, int group, hkv_stream stream) {
+  return guarded([&] {
+    if (group < kReader || group > kInserter) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "group must be 0 (reader), 1 (updater) or 2 (inserter)"};
+    }
+    if (t->opt.api_lock) t->lock.acquire(static_cast<Group>(group), static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_external_end(hkv_table* t, int group, hkv_stream stream) {
+  return guarded([&] {
+    if (group < kReader || group > kInserter) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "group must be 0 (reader), 1 (updater) or 2 (inserter)"};
+    }
+    if (t->opt.api_lock) t->lock.release(static_cast<Group>(group), static_cast<cudaStream_t>(stream));
+  });
+}
+
 int hkv_device_status(hkv_table* t, hkv_stream stream, uint32_t* status) {
   return guarded([&] {
     DeviceGuard dg(t->device);

@@ -11,16 +11,17 @@
 //   include/merlin/core_kernels/update*.cuh                  (assign family)
 // and the score rules of kernel_utils.cuh:267-615.
 //
-// One warp serves 32 keys in four phases:
-//   1. eight 8-lane digest probes, all digest lines and first-candidate key
-//      loads in flight at once; a hit is locked by CAS key -> LOCKED;
+// One warp serves 32 keys:
+//   1. eight 8-lane digest probes, all digest lines and first-candidate
+//      accesses in flight at once; a hit is locked by CAS key -> LOCKED;
 //   2. a miss claims the first EMPTY slot from its start position by CAS;
-//   3. keys whose bucket is full: four at a time, each 8-lane group loads the
+//   3. digests / scores are written, rows move cooperatively and coalesced,
+//      and the owner lanes publish their keys with a release store;
+//   4. keys whose bucket is full: four at a time, each 8-lane group loads the
 //      bucket's 128 scores (1 KiB, coalesced), reduces the minimum with warp
-//      REDUX and CASes the victim's key.  A slot found LOCKED is skipped, so
-//      no lane ever waits on another lane's lock;
-//   4. digests / scores are written, rows move cooperatively and coalesced,
-//      and the owner lane publishes its key with a release store.
+//      REDUX, CASes the victim's key, writes, copies and publishes.
+// Locks are never held across a wait: phases 1-3 contain no wait at all, and
+// a group of phase 4 waits (bounded) only while it holds nothing.
 #include "hkv_device.cuh"
 #include "hkv_internal.h"
 
@@ -179,8 +180,20 @@ struct EvictOutcome {
   uint32_t slot;
 };
 
-// Phase 3 for one key, run by the 8 lanes of a group (all collectives use the
-// group's mask).  Never waits on a locked slot: the locked minimum is skipped.
+// Does the operation copy the batch row into a freshly claimed slot?
+__device__ __forceinline__ constexpr bool op_writes_row_on_insert(int op) {
+  return op == kOpInsertOrAssign || op == kOpFindOrInsert || op == kOpInsertAndEvict ||
+         op == kOpAccumOrAssign;
+}
+
+// Phase 4 for one key whose bucket is full, run by the 8 lanes of a group (all
+// collectives use the group's mask).  The group holds no lock while it waits:
+// it scans the 128 scores, and when the minimum's slot is LOCKED by somebody
+// else it polls that key (bounded) and scans again -- so the victim is always
+// the true current minimum, as in the reference (upsert.cuh:149-215).  Once the
+// victim is locked the group never waits again: digest and score are written,
+// the old row leaves (insert_and_evict), the new row is copied and the key is
+// published before the function returns.
 template <int OP>
 __device__ __forceinline__ EvictOutcome group_evict(const TableView& t, const MutateArgs& args,
                                                     const ProbeLane& pl, uint32_t bucket,
@@ -200,82 +213,85 @@ __device__ __forceinline__ EvictOutcome group_evict(const TableView& t, const Mu
     }
     uint64_t s[16];
     ld_scores16(score_line, s);
-    uint32_t excluded = 0;
-    while (true) {
-      uint64_t ms = kMaxScore;
-      uint32_t mp = 255u;
+    uint64_t ms = s[0];
+    uint32_t mp = 0;
 #pragma unroll
-      for (int b = 0; b < 16; ++b) {
-        const bool usable = ((excluded >> b) & 1u) == 0u;
-        if (usable && (mp == 255u || s[b] < ms)) {
-          ms = s[b];
-          mp = b;
-        }
+    for (int b = 1; b < 16; ++b) {
+      if (s[b] < ms) {
+        ms = s[b];
+        mp = b;
       }
-      const uint32_t hi = mp == 255u ? 0xFFFFFFFFu : uint32_t(ms >> 32);
-      const uint32_t ghi = __reduce_min_sync(gmask, hi);
-      const uint32_t lo = (mp != 255u && hi == ghi) ? uint32_t(ms) : 0xFFFFFFFFu;
-      const uint32_t glo = __reduce_min_sync(gmask, lo);
-      const uint32_t cand = (mp != 255u && hi == ghi && lo == glo) ? pl.sub * 16u + mp : 255u;
-      const uint32_t gpos = __reduce_min_sync(gmask, cand);
-      if (gpos == 255u) {
-        // every slot is locked by someone else right now
-        __nanosleep(64);
-        break;
-      }
-      const uint64_t gmin = (uint64_t(ghi) << 32) | glo;
-      const bool refuse = (OP == kOpFindOrInsertPtr) ? (desired <= gmin) : (desired < gmin);
-      if (refuse) {
-        out.result = kRefused;
-        break;
-      }
-      const bool leader = (gpos >> 4) == pl.sub;
-      uint32_t code = 0;  // 1 skip slot, 2 reload, 3 locked a victim, 4 locked a vacant slot
-      uint64_t victim = 0;
-      if (leader) {
-        uint64_t* kp = t.keys + slot0 + gpos;
-        victim = ld_relaxed(kp);
-        if (victim == t.locked_key) {
-          code = 1;
-        } else if (cas_acquire(kp, victim, t.locked_key) != victim) {
-          code = 2;
-        } else {
-          uint64_t* sp = t.scores + slot0 + gpos;
-          if (ld_relaxed(sp) > gmin) {
-            st_release(kp, victim);
-            code = 2;
-          } else {
-            const bool vacant = victim == t.empty_key || victim == t.reclaim_key;
-            code = vacant ? 4 : 3;
-            // the slot now belongs to `key`: new digest and score at once so
-            // later scans of this bucket see them
-            st_u8_cg(t.digests + slot0 + gpos, digest);
-            st_relaxed(sp, inserted_score(args.strategy, in_score, desired));
-          }
-        }
-      }
-      const uint32_t leader_lane = pl.group * 8u + (gpos >> 4);
-      code = __shfl_sync(gmask, code, leader_lane);
-      if (code == 1) {
-        if (leader) excluded |= 1u << (gpos & 15u);
-        continue;
-      }
-      if (code == 2) break;
-      out.slot = uint32_t(slot0 + gpos);
-      out.result = code == 4 ? kOccupiedReclaimed : kEvict;
-      if (OP == kOpInsertAndEvict && code == 3) {
-        unsigned long long ticket = 0;
-        if (leader) {
-          ticket = atomicAdd(args.evicted_counter, 1ull);
-          __stcs(args.evicted_keys + ticket, victim);
-          if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + ticket, gmin);
-        }
-        ticket = __shfl_sync(gmask, ticket, leader_lane);
-        group_copy_row(t, args.evicted_values + ticket * t.row_bytes, row_ptr(t, out.slot),
-                       pl.sub);
-      }
+    }
+    const uint32_t hi = uint32_t(ms >> 32);
+    const uint32_t ghi = __reduce_min_sync(gmask, hi);
+    const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
+    const uint32_t glo = __reduce_min_sync(gmask, lo);
+    const uint32_t cand = (hi == ghi && lo == glo) ? pl.sub * 16u + mp : 255u;
+    const uint32_t gpos = __reduce_min_sync(gmask, cand);
+    const uint64_t gmin = (uint64_t(ghi) << 32) | glo;
+    const bool refuse = (OP == kOpFindOrInsertPtr) ? (desired <= gmin) : (desired < gmin);
+    if (refuse) {
+      out.result = kRefused;
       break;
     }
+    const bool leader = (gpos >> 4) == pl.sub;
+    const uint32_t leader_lane = pl.group * 8u + (gpos >> 4);
+    uint32_t code = 0;  // 1 locked by someone: wait, 2 rescan, 3 victim locked, 4 vacant slot locked, 5 gave up
+    uint64_t victim = 0;
+    if (leader) {
+      uint64_t* kp = t.keys + slot0 + gpos;
+      victim = ld_relaxed(kp);
+      if (victim == t.locked_key) {
+        code = 5;
+        for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+          __nanosleep(spin < 64 ? 32 : 256);
+          if (ld_acquire(kp) != t.locked_key) {
+            code = 1;
+            break;
+          }
+        }
+        if (code == 5) atomicOr(t.status, kStatusLockTimeout);
+      } else if (cas_acquire(kp, victim, t.locked_key) != victim) {
+        code = 2;
+      } else {
+        uint64_t* sp = t.scores + slot0 + gpos;
+        if (ld_relaxed(sp) > gmin) {
+          st_release(kp, victim);
+          code = 2;
+        } else {
+          const bool vacant = victim == t.empty_key || victim == t.reclaim_key;
+          code = vacant ? 4 : 3;
+          st_u8_cg(t.digests + slot0 + gpos, digest);
+          st_relaxed(sp, inserted_score(args.strategy, in_score, desired));
+          if (vacant) atomicAdd(t.bucket_sizes + bucket, 1);
+        }
+      }
+    }
+    code = __shfl_sync(gmask, code, leader_lane);
+    if (code == 5) {
+      out.result = kRefused;
+      break;
+    }
+    if (code < 3) continue;
+    out.slot = uint32_t(slot0 + gpos);
+    out.result = code == 4 ? kOccupiedReclaimed : kEvict;
+    uint8_t* row = row_ptr(t, out.slot);
+    if (OP == kOpInsertAndEvict && code == 3) {
+      unsigned long long ticket = 0;
+      if (leader) {
+        ticket = atomicAdd(args.evicted_counter, 1ull);
+        __stcs(args.evicted_keys + ticket, victim);
+        if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + ticket, gmin);
+      }
+      ticket = __shfl_sync(gmask, ticket, leader_lane);
+      group_copy_row(t, args.evicted_values + ticket * t.row_bytes, row, pl.sub);
+    }
+    if (op_writes_row_on_insert(OP)) {
+      group_copy_row(t, row, args.values + batch_index * t.row_bytes, pl.sub);
+    }
+    __syncwarp(gmask);
+    const bool keep_locked = OP == kOpFindOrInsertPtr && args.locked_key_ptrs != nullptr;
+    if (leader && !keep_locked) st_release(t.keys + out.slot, key);
   }
   if (OP == kOpInsertAndEvict && out.result == kRefused) {
     // a refused input leaves through the evicted arrays as well
@@ -293,6 +309,15 @@ __device__ __forceinline__ EvictOutcome group_evict(const TableView& t, const Mu
   return out;
 }
 
+// One warp serves 32 keys.
+//   phase 0  own key: hash, bucket, digest, incoming score, bucket fill
+//   phase 1  all eight digest lines in flight, then all first candidates: a
+//            locking operation CASes key -> LOCKED straight away (a digest
+//            match is the key 255 times out of 256), a non-locking one loads
+//   phase 2  per pass: confirm the hit or claim the first EMPTY slot (CAS)
+//   phase 3  metadata, rows (warp-cooperative, coalesced) and publication of
+//            everything locked so far -- no lock survives into phase 4
+//   phase 4  keys whose bucket is full, four per round (group_evict)
 template <int OP>
 __global__ void __launch_bounds__(kMutateBlock)
     mutate_kernel(const TableView t, const MutateArgs args) {
@@ -305,11 +330,10 @@ __global__ void __launch_bounds__(kMutateBlock)
   const uint64_t i = base + pl.lane;
   const int strategy = args.strategy;
 
-  // ---- phase 0: own key --------------------------------------------------
+  // ---- phase 0 ------------------------------------------------------------
   uint64_t key = 0;
   uint64_t in_score = 0;
   uint64_t desired = 0;
-  bool is_accum = false;
   uint32_t mode = 0;
   Address a{0, 0, 0};
   if (i < n) {
@@ -322,8 +346,7 @@ __global__ void __launch_bounds__(kMutateBlock)
         desired = desired_score(strategy, args.scores, in_score, args.epoch);
       }
       if (OP == kOpAccumOrAssign) {
-        is_accum = args.accum_flags[i];
-        mode |= is_accum ? kModeLockOnHit : kModeInsertOnMiss;
+        mode |= args.accum_flags[i] ? kModeLockOnHit : kModeInsertOnMiss;
       } else if (op_inserts(OP)) {
         mode |= kModeLockOnHit | kModeInsertOnMiss;
       } else {
@@ -334,7 +357,7 @@ __global__ void __launch_bounds__(kMutateBlock)
   }
   const uint32_t my_bucket = uint32_t(a.bucket);
 
-  // ---- phase 1: digest lines and first candidates, all in flight ----------
+  // ---- phase 1 ------------------------------------------------------------
   uint4 dg[kPasses];
   uint32_t bkt[kPasses];
   uint32_t pmode[kPasses];
@@ -349,29 +372,32 @@ __global__ void __launch_bounds__(kMutateBlock)
     }
   }
   uint32_t cand[kPasses];
-  uint64_t first_key[kPasses];
+  uint64_t first_key[kPasses];  // key observed at the first candidate slot
+  uint64_t want[kPasses];
 #pragma unroll
   for (int j = 0; j < kPasses; ++j) {
     const uint32_t owner = pass_owner(j, pl.group);
     const uint32_t tgt = __shfl_sync(full, a.digest, owner);
+    want[j] = __shfl_sync(full, key, owner);
     cand[j] = (pmode[j] & kModeValid) ? match16(dg[j], replicate4(tgt)) : 0u;
-    first_key[j] = 0;
+    first_key[j] = ~want[j];
     if (cand[j]) {
-      const uint32_t pos = pl.sub * 16u + (__ffs(cand[j]) - 1);
-      first_key[j] = ld_relaxed(t.keys + (uint64_t(bkt[j]) << 7) + pos);
+      uint64_t* kp = t.keys + (uint64_t(bkt[j]) << 7) + pl.sub * 16u + (__ffs(cand[j]) - 1);
+      first_key[j] = (pmode[j] & kModeLockOnHit) ? cas_acquire(kp, want[j], t.locked_key)
+                                                 : ld_relaxed(kp);
     }
   }
 
-  // ---- phase 2: lock hits, claim empty slots ------------------------------
+  // ---- phase 2 ------------------------------------------------------------
   uint32_t my_result = kInitial;
   uint32_t my_slot = kNoSlot;
 #pragma unroll
   for (int j = 0; j < kPasses; ++j) {
     const uint32_t gmask = group_mask(pl.group);
     const uint32_t owner = pass_owner(j, pl.group);
-    const uint64_t want = __shfl_sync(full, key, owner);
     const uint32_t start = __shfl_sync(full, a.start, owner);
     const uint64_t slot0 = uint64_t(bkt[j]) << 7;
+    const bool lock_on_hit = (pmode[j] & kModeLockOnHit) != 0;
     uint32_t result = kInitial;
     uint32_t slot = kNoSlot;
     if (pmode[j] & kModeValid) {
@@ -379,14 +405,17 @@ __global__ void __launch_bounds__(kMutateBlock)
       if (cand[j]) {
         uint32_t m = cand[j];
         uint32_t pos = pl.sub * 16u + (__ffs(m) - 1);
-        if (first_key[j] == want) {
+        if (first_key[j] == want[j]) {
           hit_pos = pos;
         } else {
           m &= m - 1;
           while (m) {
             pos = pl.sub * 16u + (__ffs(m) - 1);
             m &= m - 1;
-            if (ld_relaxed(t.keys + slot0 + pos) == want) {
+            uint64_t* kp = t.keys + slot0 + pos;
+            const uint64_t seen =
+                lock_on_hit ? cas_acquire(kp, want[j], t.locked_key) : ld_relaxed(kp);
+            if (seen == want[j]) {
               hit_pos = pos;
               break;
             }
@@ -396,42 +425,32 @@ __global__ void __launch_bounds__(kMutateBlock)
       const uint32_t votes = __ballot_sync(gmask, hit_pos != 255u);
       if (votes) {
         const uint32_t src = __ffs(votes) - 1;
-        uint32_t ok = 1;
-        if (pl.lane == src && (pmode[j] & kModeLockOnHit)) {
-          ok = cas_acquire(t.keys + slot0 + hit_pos, want, t.locked_key) == want ? 1u : 0u;
-        }
-        ok = __shfl_sync(gmask, ok, src);
         const uint32_t pos = __shfl_sync(gmask, hit_pos, src);
-        if (ok) {
-          result = (pmode[j] & kModeLockOnHit) ? kDuplicate : kFoundNoLock;
-          slot = uint32_t(slot0) + pos;
-        }
-      }
-      if (result == kInitial) {
-        if (!(pmode[j] & kModeInsertOnMiss)) {
-          result = kMiss;
-        } else if (pmode[j] & kModeBucketFull) {
-          result = kNeedEvict;
-        } else {
-          uint32_t em = match16(dg[j], t.empty_digest4);
-          while (true) {
-            const uint32_t d = first_from_start(em, pl.sub, start);
-            const uint32_t gd = __reduce_min_sync(gmask, d);
-            if (gd == 255u) {
-              result = kNeedEvict;
-              break;
-            }
-            const uint32_t pos = (start + gd) & (kBucketSlots - 1);
-            bool won = false;
-            if (d == gd) {
-              won = cas_acquire(t.keys + slot0 + pos, t.empty_key, t.locked_key) == t.empty_key;
-              em &= ~(1u << (pos & 15u));
-            }
-            if (__ballot_sync(gmask, won)) {
-              result = kOccupiedEmpty;
-              slot = uint32_t(slot0) + pos;
-              break;
-            }
+        result = lock_on_hit ? kDuplicate : kFoundNoLock;
+        slot = uint32_t(slot0) + pos;
+      } else if (!(pmode[j] & kModeInsertOnMiss)) {
+        result = kMiss;
+      } else if (pmode[j] & kModeBucketFull) {
+        result = kNeedEvict;
+      } else {
+        uint32_t em = match16(dg[j], t.empty_digest4);
+        while (true) {
+          const uint32_t d = first_from_start(em, pl.sub, start);
+          const uint32_t gd = __reduce_min_sync(gmask, d);
+          if (gd == 255u) {
+            result = kNeedEvict;
+            break;
+          }
+          const uint32_t pos = (start + gd) & (kBucketSlots - 1);
+          bool won = false;
+          if (d == gd) {
+            won = cas_acquire(t.keys + slot0 + pos, t.empty_key, t.locked_key) == t.empty_key;
+            em &= ~(1u << (pos & 15u));
+          }
+          if (__ballot_sync(gmask, won)) {
+            result = kOccupiedEmpty;
+            slot = uint32_t(slot0) + pos;
+            break;
           }
         }
       }
@@ -445,7 +464,50 @@ __global__ void __launch_bounds__(kMutateBlock)
     }
   }
 
-  // ---- phase 3: evictions, four keys at a time ----------------------------
+  // ---- phase 3: everything locked so far is written and published ---------------
+  const bool holds_lock = my_result == kDuplicate || my_result == kOccupiedEmpty;
+  const bool keep_locked =
+      (OP == kOpFindOrInsertPtr || OP == kOpLockKeys) && args.locked_key_ptrs != nullptr;
+  if (my_result == kOccupiedEmpty) {
+    st_u8_cg(t.digests + my_slot, a.digest);
+    st_relaxed(t.scores + my_slot, inserted_score(strategy, in_score, desired));
+    atomicAdd(t.bucket_sizes + a.bucket, 1);
+  }
+  if (my_result == kDuplicate && OP != kOpAssignValues) {
+    const bool needs_old = strategy == kLfu || strategy == kEpochLfu ||
+                           (OP == kOpFindAndUpdate && args.scores_out != nullptr);
+    const uint64_t old_score = needs_old ? ld_relaxed(t.scores + my_slot) : 0;
+    uint64_t ns = 0;
+    bool write;
+    if (op_inserts(OP) || OP == kOpLockKeys) {
+      write = hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns);
+    } else {
+      write = hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
+    }
+    if (write) st_relaxed(t.scores + my_slot, ns);
+    if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
+      args.scores_out[i] = write ? ns : old_score;
+    }
+  }
+  if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
+      OP == kOpAssignValues) {
+    warp_move_rows<1>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
+                      pl.lane);
+  } else if (OP == kOpFindOrInsert) {
+    warp_move_rows<0>(t, args.values + base * t.row_bytes,
+                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
+    warp_move_rows<1>(t, args.values + base * t.row_bytes,
+                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
+  } else if (OP == kOpAccumOrAssign) {
+    warp_move_rows<2>(t, args.values + base * t.row_bytes,
+                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
+    warp_move_rows<1>(t, args.values + base * t.row_bytes,
+                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
+  }
+  __syncwarp();
+  if (holds_lock && !keep_locked) st_release(t.keys + my_slot, key);
+
+  // ---- phase 4: full buckets, four keys per round ---------------------------------
   if (op_inserts(OP)) {
     uint32_t need = __ballot_sync(full, my_result == kNeedEvict);
     while (need) {
@@ -474,63 +536,17 @@ __global__ void __launch_bounds__(kMutateBlock)
     }
   }
 
-  // ---- phase 4: metadata, rows, publication -------------------------------
-  const bool holds_lock = my_result == kDuplicate || my_result == kOccupiedEmpty ||
-                          my_result == kOccupiedReclaimed || my_result == kEvict;
-  const bool fresh = my_result == kOccupiedEmpty || my_result == kOccupiedReclaimed ||
-                     my_result == kEvict;
-  if (holds_lock) {
-    if (my_result == kOccupiedEmpty) {
-      st_u8_cg(t.digests + my_slot, a.digest);
-      st_relaxed(t.scores + my_slot, inserted_score(strategy, in_score, desired));
-    }
-    if (my_result == kOccupiedEmpty || my_result == kOccupiedReclaimed) {
-      atomicAdd(t.bucket_sizes + a.bucket, 1);
-    }
-    if (my_result == kDuplicate && OP != kOpAssignValues) {
-      const uint64_t old_score = ld_relaxed(t.scores + my_slot);
-      uint64_t ns = 0;
-      bool write;
-      if (op_inserts(OP) || OP == kOpLockKeys) {
-        write = hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns);
-      } else {
-        write = hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
-      }
-      if (write) st_relaxed(t.scores + my_slot, ns);
-      if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
-        args.scores_out[i] = write ? ns : old_score;
-      }
-    }
-  }
-
-  if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
-      OP == kOpAssignValues) {
-    warp_move_rows<1>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
-                      pl.lane);
-  } else if (OP == kOpFindOrInsert) {
-    warp_move_rows<0>(t, args.values + base * t.row_bytes,
-                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-    warp_move_rows<1>(t, args.values + base * t.row_bytes, fresh ? my_slot : kNoSlot, pl.lane);
-  } else if (OP == kOpAccumOrAssign) {
-    warp_move_rows<2>(t, args.values + base * t.row_bytes,
-                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-    warp_move_rows<1>(t, args.values + base * t.row_bytes, fresh ? my_slot : kNoSlot, pl.lane);
-  }
-
   if (OP == kOpFindOrInsertPtr || OP == kOpFindAndUpdate || OP == kOpLockKeys) {
+    const bool placed = my_result == kDuplicate || my_result == kOccupiedEmpty ||
+                        my_result == kOccupiedReclaimed || my_result == kEvict;
     if (i < n) {
-      if (args.ptrs != nullptr) args.ptrs[i] = holds_lock ? row_ptr(t, my_slot) : nullptr;
+      if (args.ptrs != nullptr) args.ptrs[i] = placed ? row_ptr(t, my_slot) : nullptr;
       if (args.founds != nullptr) args.founds[i] = my_result == kDuplicate;
       if (args.locked_key_ptrs != nullptr) {
-        args.locked_key_ptrs[i] = holds_lock ? t.keys + my_slot : nullptr;
+        args.locked_key_ptrs[i] = placed ? t.keys + my_slot : nullptr;
       }
     }
   }
-
-  __syncwarp();
-  const bool keep_locked =
-      (OP == kOpFindOrInsertPtr || OP == kOpLockKeys) && args.locked_key_ptrs != nullptr;
-  if (holds_lock && !keep_locked) st_release(t.keys + my_slot, key);
 }
 
 // ---- serialising kernel for batches that may repeat a key -------------------

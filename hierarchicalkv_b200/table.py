@@ -161,6 +161,8 @@ _SIGNATURES = {
     "hkv_set_global_epoch": [_P, _U64],
     "hkv_reserve": [_P, _U64, _P],
     "hkv_get_view": [_P, ctypes.POINTER(TableView)],
+    "hkv_external_begin": [_P, _INT, _P],
+    "hkv_external_end": [_P, _INT, _P],
     "hkv_device_status": [_P, _P, ctypes.POINTER(ctypes.c_uint32)],
     "hkv_last_error": [],
 }

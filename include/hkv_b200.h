@@ -239,8 +239,18 @@ HKV_API int hkv_set_global_epoch(hkv_table* table, uint64_t epoch);
  * fits the current capacity. */
 HKV_API int hkv_reserve(hkv_table* table, uint64_t new_capacity, hkv_stream stream);
 
-/* Planes of the table for header-side functor kernels. */
+/* Planes of the table for header-side functor kernels.  No counterpart in
+ * the reference, whose templated kernels live in the class itself. */
 HKV_API int hkv_get_view(const hkv_table* table, hkv_table_view* view);
+
+/* Bracket a kernel the CALLER launches on `stream` over hkv_get_view's planes
+ * so that it takes part in the table's reader (0) / updater (1) / inserter
+ * (2) exclusion, as the reference's lock guards do around its templated
+ * kernels (include/merlin/group_lock.cuh:168-337).  begin orders the stream
+ * after conflicting operations; end must follow the launch on the same host
+ * thread.  Both are no-ops when api_lock is off. */
+HKV_API int hkv_external_begin(hkv_table* table, int group, hkv_stream stream);
+HKV_API int hkv_external_end(hkv_table* table, int group, hkv_stream stream);
 
 /* Device status word: bit 0 a bounded slot wait ran out, bit 1 eviction
  * retries ran out.  Reading it synchronises the stream; it is cleared by the

@@ -1,0 +1,452 @@
+"""Operations and edge cases beyond the shared scenarios, all through the C
+ABI on the GPU: pointer forms, missed-key find, key locking, odd row sizes,
+ragged and empty batches, repeated keys, hybrid HBM + pinned-host values,
+concurrent streams under the API lock, and eviction invariants under score
+ties (LRU at load factor 1.0)."""
+import ctypes
+import threading
+
+import numpy as np
+import pytest
+
+from tests.hkv_testlib import (OracleTable, ProductTable, RefTable, bucket_of, ref_available,
+                               sorted_by_key, to_dev, to_np_u64, unique_keys, values_for)
+
+pytestmark = pytest.mark.gpu
+LRU, LFU, EPOCH_LRU, EPOCH_LFU, CUSTOMIZED = range(5)
+
+
+def read_rows(ptrs: np.ndarray, dim: int):
+    """Rows behind device addresses returned by the pointer forms."""
+    from cuda.bindings import runtime as cudart
+
+    out = np.zeros((ptrs.size, dim), dtype=np.float32)
+    for i, p in enumerate(ptrs):
+        if p:
+            (err,) = cudart.cudaMemcpy(out[i].ctypes.data, int(p), dim * 4,
+                                       cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+            assert int(err) == 0, err
+    return out
+
+
+def test_find_ptr_and_find_missed_and_contains():
+    cap, dim = 128 * 256, 8
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(6000, seed=3)
+    ins, fresh = keys[:4000], keys[4000:]
+    sc = np.arange(1, ins.size + 1, dtype=np.uint64)
+    for x in (t, o):
+        x.insert_or_assign(ins, values_for(ins, dim), sc)
+    q = np.concatenate([ins[:1500], fresh[:777], ins[1500:1511]])
+    ov, of, osc = o.find(q)
+    ptrs, f, s = t.find_ptr(q)
+    np.testing.assert_array_equal(f, of)
+    np.testing.assert_array_equal(s[f], osc[of])
+    assert np.all(ptrs[~f] == 0) and np.all(ptrs[f] != 0)
+    sample = np.flatnonzero(f)[:64]
+    np.testing.assert_array_equal(read_rows(ptrs[sample], dim), ov[sample])
+    # missed-key form: same rows for hits; (key, index) pairs of the misses as a set
+    v, mk, mi = t.find_missed(q)
+    np.testing.assert_array_equal(v[of], ov[of])
+    assert mk.size == (~of).sum()
+    got = sorted(zip(mk.tolist(), mi.tolist()))
+    want = sorted(zip(q[~of].tolist(), np.flatnonzero(~of).tolist()))
+    assert got == want
+    np.testing.assert_array_equal(t.contains(q), of)
+    t.close()
+
+
+def test_find_or_insert_ptr_then_unlock_keys():
+    import torch
+
+    cap, dim = 128 * 64, 4
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(3000, seed=4)
+    sc = np.arange(1, 2001, dtype=np.uint64)
+    for x in (t, o):
+        x.insert_or_assign(keys[:2000], values_for(keys[:2000], dim), sc)
+    q = keys[1000:3000]
+    qs = np.arange(5001, 5001 + q.size, dtype=np.uint64)
+    ptrs, founds = t.find_or_insert_ptr(q, qs)
+    np.testing.assert_array_equal(founds, o.find_or_insert_ptr(q, qs))
+    assert np.all(ptrs != 0)          # nothing refused: the table has room
+    assert t.size() == o.size() == 3000
+    # rows of the hits are the stored rows
+    hits = np.flatnonzero(founds)[:32]
+    np.testing.assert_array_equal(read_rows(ptrs[hits], dim), values_for(q[hits], dim))
+    # same call with locked_key_ptrs: keys stay LOCKED (invisible) until unlock_keys
+    n = 256
+    k = to_dev(keys[:n])
+    p = torch.zeros(n, dtype=torch.int64, device="cuda")
+    f = torch.zeros(n, dtype=torch.bool, device="cuda")
+    lk = torch.zeros(n, dtype=torch.int64, device="cuda")
+    s = to_dev(np.arange(9001, 9001 + n, dtype=np.uint64))
+    t.t.find_or_insert_ptr(n, k, p, f, s, locked_key_ptrs=lk)
+    torch.cuda.synchronize()
+    assert bool(f.all()) and bool((lk != 0).all())
+    assert not t.contains(keys[:n]).any()
+    ok = torch.zeros(n, dtype=torch.bool, device="cuda")
+    t.t.unlock_keys(n, lk, k, ok)
+    torch.cuda.synchronize()
+    assert bool(ok.all())
+    assert t.contains(keys[:n]).all()
+    # lock_keys / unlock_keys round trip; a second unlock reports failure
+    t.t.lock_keys(n, k, lk, ok)
+    torch.cuda.synchronize()
+    assert bool(ok.all()) and not t.contains(keys[:n]).any()
+    t.t.unlock_keys(n, lk, k, ok)
+    t.t.unlock_keys(n, lk, k, f)
+    torch.cuda.synchronize()
+    assert bool(ok.all()) and not bool(f.any())
+    assert t.contains(keys[:n]).all()
+    assert t.t.device_status() == 0
+    t.close()
+
+
+def test_find_and_update_and_assign_values():
+    import torch
+
+    cap, dim = 128 * 32, 4
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(1500, seed=5)
+    t.insert_or_assign(keys[:1000], values_for(keys[:1000], dim), np.arange(1, 1001, dtype=np.uint64))
+    q = keys[500:1500]
+    k = to_dev(q)
+    p = torch.zeros(q.size, dtype=torch.int64, device="cuda")
+    f = torch.zeros(q.size, dtype=torch.bool, device="cuda")
+    s = to_dev(np.arange(7001, 7001 + q.size, dtype=np.uint64))
+    t.t.find_and_update(q.size, k, p, f, s)
+    torch.cuda.synchronize()
+    f = f.cpu().numpy()
+    assert f[:500].all() and not f[500:].any()
+    _, ff, ss = t.find(q)
+    np.testing.assert_array_equal(ss[ff], np.arange(7001, 7501, dtype=np.uint64))
+    newv = values_for(q, dim, seed=9)
+    t.assign_values(q, newv)
+    v, ff, ss = t.find(q)
+    np.testing.assert_array_equal(v[ff], newv[:500])
+    np.testing.assert_array_equal(ss[ff], np.arange(7001, 7501, dtype=np.uint64))  # untouched
+    assert t.size() == 1000
+    t.close()
+
+
+@pytest.mark.parametrize("n", [0, 1, 31, 32, 33, 127, 1000])
+def test_ragged_and_empty_batches(n):
+    cap, dim = 128 * 16, 8
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(max(n, 1) * 2, seed=6)[: 2 * n]
+    a = keys[:n]
+    sc = np.arange(1, n + 1, dtype=np.uint64)
+    for x in (t, o):
+        x.insert_or_assign(a, values_for(a, dim), sc)
+    assert t.size() == o.size() == n
+    pv, pf, ps = t.find(keys)
+    ov, of, os_ = o.find(keys)
+    np.testing.assert_array_equal(pf, of)
+    np.testing.assert_array_equal(pv, ov)
+    np.testing.assert_array_equal(ps[pf], os_[of])
+    t.close()
+
+
+@pytest.mark.parametrize("dim,dtype", [(3, "float32"), (129, "float32"), (5, "int8"), (7, "int16"),
+                                        (224, "float32"), (66, "float64")])
+def test_row_sizes_and_value_types(dim, dtype):
+    """Rows are opaque bytes: any element type and any dim, including rows
+    that are not a multiple of 16 bytes (the reference covers int8..double and
+    dims 3..224, tests/merlin_hashtable_test.cc.cu:3816-3830)."""
+    import torch
+    import hierarchicalkv_b200 as hkv
+
+    tdt = getattr(torch, dtype)
+    cap, n = 128 * 32, 2000
+    t = hkv.HashTable(hkv.EvictStrategy.kCustomized, value_dtype=tdt)
+    t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                dim=dim))
+    keys = unique_keys(2 * n, seed=7)
+    rng = np.random.default_rng(1)
+    raw = rng.integers(-100, 100, size=(n, dim)).astype(dtype)
+    k = to_dev(keys[:n])
+    v = torch.from_numpy(raw).cuda()
+    s = to_dev(np.arange(1, n + 1, dtype=np.uint64))
+    t.insert_or_assign(n, k, v, s)
+    q = to_dev(keys)
+    out = torch.zeros((2 * n, dim), dtype=tdt, device="cuda")
+    f = torch.zeros(2 * n, dtype=torch.bool, device="cuda")
+    t.find(2 * n, q, out, f)
+    torch.cuda.synchronize()
+    fh = f.cpu().numpy()
+    assert fh[:n].all() and not fh[n:].any()
+    np.testing.assert_array_equal(out.cpu().numpy()[:n], raw)
+    assert not out.cpu().numpy()[n:].any()          # misses leave the output untouched
+    # an unaligned batch pointer lowers the access width, not correctness
+    if dim * v.element_size() % 16 == 0:
+        big = torch.zeros(2 * n * dim + 1, dtype=tdt, device="cuda")
+        view = big[1:].view(2 * n, dim)
+        t.find(2 * n, q, view, f)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(view.cpu().numpy()[:n], raw)
+    t.close()
+
+
+def test_repeated_keys_in_one_batch_non_unique():
+    """unique_key=false: a key that occurs several times in a batch ends up in
+    the table once, with one of its rows."""
+    cap, dim = 128 * 8, 4
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    base = unique_keys(300, seed=8)
+    keys = np.concatenate([base, base[:200], base[:100]])
+    rng = np.random.default_rng(2)
+    rng.shuffle(keys)
+    vals = values_for(keys, dim) + np.arange(keys.size, dtype=np.float32)[:, None]
+    sc = np.arange(1, keys.size + 1, dtype=np.uint64)
+    t.insert_or_assign(keys, vals, sc, unique_key=False)
+    assert t.size() == 300
+    ek, ev, es = sorted_by_key(*t.export_batch())
+    np.testing.assert_array_equal(ek, np.sort(base))
+    for k, v, s in zip(ek[:50], ev[:50], es[:50]):
+        cand = np.flatnonzero(keys == k)
+        assert any(np.array_equal(v, vals[c]) for c in cand)
+        assert s in sc[cand]
+    assert t.t.device_status() == 0
+    t.close()
+
+
+def test_same_bucket_contention_unique_batch():
+    """Every key of the batch targets one of two buckets (adversarial for the
+    slot CAS protocol): capacity is respected, nothing is lost or duplicated."""
+    cap, dim = 128 * 8, 4
+    pool = unique_keys(200000, seed=9)
+    b = bucket_of(pool, cap)
+    keys = np.concatenate([pool[b == 1][:400], pool[b == 5][:100]])
+    sc = np.arange(1, keys.size + 1, dtype=np.uint64)
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    for x in (t, o):
+        x.insert_or_assign(keys, values_for(keys, dim), sc)
+    assert t.size() == o.size() == 128 + 100
+    pk, pv, ps = sorted_by_key(*t.export_batch())
+    ok_, ov, os_ = sorted_by_key(*o.export_batch())
+    # distinct increasing scores: the survivors are the 128 highest of bucket 1
+    np.testing.assert_array_equal(pk, ok_)
+    np.testing.assert_array_equal(ps, os_)
+    np.testing.assert_array_equal(pv, ov)
+    assert t.t.device_status() == 0
+    t.close()
+
+
+@pytest.mark.parametrize("hbm_fraction", [0.0, 0.5])
+def test_hybrid_hbm_and_pinned_host_values(hbm_fraction):
+    """max_hbm_for_vectors below the table size puts the rows of the higher
+    buckets in mapped pinned host memory; results are identical."""
+    cap, dim = 128 * 64, 16
+    hbm = int(cap * dim * 4 * hbm_fraction)
+    t = ProductTable(cap, dim, CUSTOMIZED, max_hbm_for_vectors=hbm)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    view = t.t.view()
+    assert view.hbm_slots == (hbm // (128 * dim * 4)) * 128
+    keys = unique_keys(12000, seed=10)
+    for r in range(3):                      # overfills: evictions happen in both halves
+        k = keys[r * 4000:(r + 1) * 4000]
+        s = np.arange(1 + r * 10000, 1 + r * 10000 + k.size, dtype=np.uint64)
+        for x in (t, o):
+            x.insert_or_assign(k, values_for(k, dim, seed=r), s)
+    assert t.size() == o.size()
+    for a, b in zip(sorted_by_key(*t.export_batch()), sorted_by_key(*o.export_batch())):
+        np.testing.assert_array_equal(a, b)
+    pv, pf, ps = t.find(keys)
+    ov, of, os_ = o.find(keys)
+    np.testing.assert_array_equal(pf, of)
+    np.testing.assert_array_equal(pv, ov)
+    with pytest.raises(RuntimeError):       # insert_and_evict is pure-HBM only, as in the reference
+        t.insert_and_evict(keys[:32], values_for(keys[:32], dim), np.arange(1, 33, dtype=np.uint64))
+    t.close()
+
+
+def test_lru_eviction_invariants_under_score_ties():
+    """LRU at load factor 1.0: thousands of keys written by one kernel share a
+    timer value, so the victim among equal minima is not unique.  Checked:
+    conservation, capacity, every evicted score <= the smallest score kept in
+    its bucket, and the evicted tuples carry their own rows."""
+    cap, dim, batch = 128 * 128, 8, 8192
+    t = ProductTable(cap, dim, LRU)
+    keys = unique_keys(6 * batch, seed=11)
+    seen = {}
+    inserted = 0
+    for r in range(6):
+        k = keys[r * batch:(r + 1) * batch]
+        ek, ev, es = t.insert_and_evict(k, values_for(k, dim))
+        inserted += k.size
+        for kk in ek.tolist():
+            assert kk not in seen
+            seen[kk] = True
+        np.testing.assert_array_equal(ev, values_for(ek, dim))
+        assert len(seen) + t.size() == inserted
+        tk, tv, ts = t.export_batch()
+        assert np.intersect1d(tk, ek).size == 0
+        if ek.size:
+            kept_min = {}
+            for b_, s_ in zip(bucket_of(tk, cap).tolist(), ts.tolist()):
+                kept_min[b_] = min(kept_min.get(b_, 2**64), s_)
+            for b_, s_ in zip(bucket_of(ek, cap).tolist(), es.tolist()):
+                assert s_ <= kept_min[b_]
+    assert t.size() == cap
+    assert abs(t.t.load_factor() - 1.0) < 1e-3
+    assert t.t.device_status() == 0
+    t.close()
+
+
+def test_epoch_lfu_churn_and_export_if():
+    """The churn workload in miniature: EpochLfu, insert_and_evict at load
+    factor 1.0 with 30 % new keys per batch, then export_batch_if with
+    score < (epoch - 2) << 32."""
+    cap, dim, batch = 128 * 64, 8, 4096
+    t = ProductTable(cap, dim, EPOCH_LFU)
+    o = OracleTable(cap, dim, EPOCH_LFU)
+    rng = np.random.default_rng(12)
+    pool = unique_keys(40 * batch, seed=12, lo_bits=40)
+    used = 0
+    resident = np.empty(0, dtype=np.uint64)
+    for epoch in range(1, 9):
+        for x in (t, o):
+            x.set_global_epoch(epoch)
+        n_new = batch if resident.size < batch else int(batch * 0.3)
+        new = pool[used:used + n_new]
+        used += n_new
+        old = rng.choice(resident, batch - n_new, replace=False) if n_new < batch else new[:0]
+        k = np.concatenate([new, old])
+        s = rng.integers(1, 100, size=k.size, dtype=np.uint64)
+        out_p = t.insert_and_evict(k, values_for(k, dim, seed=epoch), s)
+        out_o = o.insert_and_evict(k, values_for(k, dim, seed=epoch), s)
+        assert t.size() == o.size()
+        pk, _, ps = t.export_batch()
+        # EpochLfu arithmetic: a key touched this epoch carries the epoch in the high half
+        touched = np.isin(pk, k)
+        assert np.all((ps[touched] >> np.uint64(32)) == epoch)
+        # every evicted score is at most the smallest kept score of its bucket
+        ek, _, es = out_p
+        if ek.size:
+            kept_min = {}
+            for b_, s_ in zip(bucket_of(pk, cap).tolist(), ps.tolist()):
+                kept_min[b_] = min(kept_min.get(b_, 2**64), s_)
+            for b_, s_ in zip(bucket_of(ek, cap).tolist(), es.tolist()):
+                assert s_ <= kept_min[b_]
+        # how many tuples leave differs legitimately: a key of the batch that is
+        # present may be evicted by a new key before its own update arrives,
+        # depending on the order in which the batch is applied
+        resident = pk
+    thr = (8 - 2) << 32
+    ek, ev, es = t.export_batch_if(1, 0, thr)
+    assert np.all(es < thr)
+    allk, _, alls = t.export_batch()
+    assert ek.size == (alls < thr).sum()
+    assert np.unique(ek).size == ek.size
+    t.close()
+
+
+def test_concurrent_streams_under_the_api_lock():
+    """Host threads with their own streams: inserters are exclusive, readers
+    share; every thread's keys are present at the end and reads never see a
+    half-written table (reference: tests/merlin_hashtable_test.cc.cu:3180-3350
+    in miniature, fixed capacity)."""
+    import torch
+
+    cap, dim, per = 128 * 512, 8, 4096
+    t = ProductTable(cap, dim, LRU)
+    keys = unique_keys(8 * per, seed=13)
+    errors = []
+
+    def worker(w):
+        try:
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            k = to_dev(keys[w * per:(w + 1) * per])
+            v = to_dev(values_for(keys[w * per:(w + 1) * per], dim))
+            out = torch.zeros((per, dim), dtype=torch.float32, device="cuda")
+            f = torch.zeros(per, dtype=torch.bool, device="cuda")
+            with torch.cuda.stream(stream):
+                for _ in range(5):
+                    t.t.find(per, k, out, f, None, stream)
+                    t.t.insert_or_assign(per, k, v, None, stream)
+                    t.t.find(per, k, out, f, None, stream)
+                stream.synchronize()
+            if not bool(f.all()) or not torch.equal(out, v):
+                errors.append(f"worker {w}: lost keys or wrong rows")
+        except Exception as e:  # noqa: BLE001
+            errors.append(f"worker {w}: {e}")
+
+    threads = [threading.Thread(target=worker, args=(w,)) for w in range(8)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    assert t.size() == 8 * per
+    assert t.t.device_status() == 0
+    t.close()
+
+
+def test_strategy_argument_checks():
+    """check_evict_strategy (include/merlin_hashtable.cuh:3832-3861 of the reference)."""
+    import hierarchicalkv_b200 as hkv
+
+    keys = unique_keys(64, seed=14)
+    vals = values_for(keys, 4)
+    sc = np.arange(1, 65, dtype=np.uint64)
+    lru = ProductTable(128 * 4, 4, LRU)
+    with pytest.raises(hkv.MerlinException):
+        lru.insert_or_assign(keys, vals, sc)          # LRU takes no scores
+    lru.close()
+    lfu = ProductTable(128 * 4, 4, LFU)
+    with pytest.raises(hkv.MerlinException):
+        lfu.insert_or_assign(keys, vals, None)        # LFU needs scores
+    lfu.close()
+    el = ProductTable(128 * 4, 4, EPOCH_LFU)
+    with pytest.raises(hkv.MerlinException):
+        el.insert_or_assign(keys, vals, sc)           # epoch not set
+    el.set_global_epoch(1)
+    el.insert_or_assign(keys, vals, sc)
+    assert el.size() == 64
+    with pytest.raises(NotImplementedError):
+        el.t.reserve(128 * 8)
+    el.t.reserve(128 * 4)
+    el.close()
+
+
+@pytest.mark.skipif(not ref_available(0), reason="reference library not built")
+def test_config2_shape_small_lru_survivors_match_reference():
+    """dim 64, LRU, overfilled table.  Timer scores grow from batch to batch, so
+    each bucket keeps its newest keys: how many keys of each batch survive is
+    determined (which ones, inside the oldest surviving batch, is not: they
+    tie).  Product and reference kernels must both match that count."""
+    cap, dim, batch = 128 * 256, 64, 16384
+    p = ProductTable(cap, dim, LRU)
+    r = RefTable(cap, dim, LRU)
+    keys = unique_keys(5 * batch, seed=15)
+    for i in range(5):
+        k = keys[i * batch:(i + 1) * batch]
+        for x in (p, r):
+            x.insert_or_assign(k, values_for(k, dim, seed=i))
+    assert p.size() == r.size() == cap
+    buckets = bucket_of(keys, cap).reshape(5, batch)
+    hist = np.stack([np.bincount(buckets[i].astype(np.int64), minlength=cap // 128) for i in range(5)])
+    expect = np.zeros(5, dtype=np.int64)
+    room = np.full(cap // 128, 128, dtype=np.int64)
+    for i in range(4, -1, -1):                     # newest batch first
+        kept = np.minimum(hist[i], room)
+        expect[i] = kept.sum()
+        room -= kept
+    _, pf, _ = p.find(keys)
+    _, rf, _ = r.find(keys)
+    per_p = pf.reshape(5, batch).sum(axis=1)
+    per_r = rf.reshape(5, batch).sum(axis=1)
+    assert per_p.sum() == per_r.sum() == cap
+    # the timer can tick inside a kernel, never backwards: equal within a handful of keys
+    np.testing.assert_allclose(per_r, expect, rtol=0, atol=8)
+    np.testing.assert_allclose(per_p, expect, rtol=0, atol=8)
+    pv, _, _ = p.find(keys[-batch:])
+    np.testing.assert_array_equal(pv, values_for(keys[-batch:], dim, seed=4))
+    p.close()
+    r.close()
