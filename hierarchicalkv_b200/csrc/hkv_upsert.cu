@@ -17,11 +17,12 @@
 //   2. a miss claims the first EMPTY slot from its start position by CAS;
 //   3. digests / scores are written, rows move cooperatively and coalesced,
 //      and the owner lanes publish their keys with a release store;
-//   4. keys whose bucket is full: four at a time, each 8-lane group loads the
-//      bucket's 128 scores (1 KiB, coalesced), reduces the minimum with warp
-//      REDUX, CASes the victim's key, writes, copies and publishes.
+//   4. keys whose bucket is full: 8-lane groups scan the buckets' 128 scores
+//      (1 KiB each, coalesced; warp REDUX for the 64-bit minimum), then all
+//      owner lanes CAS their victims at the same time, then rows move and
+//      keys are published; losers of a CAS go round again.
 // Locks are never held across a wait: phases 1-3 contain no wait at all, and
-// a group of phase 4 waits (bounded) only while it holds nothing.
+// phase 4 polls a foreign lock (bounded) only while the warp holds nothing.
 #include "hkv_device.cuh"
 #include "hkv_internal.h"
 
@@ -30,7 +31,7 @@ namespace hkv {
 namespace {
 
 constexpr int kMutateBlock = 128;
-constexpr uint32_t kEvictRetryLimit = 1u << 20;
+constexpr uint32_t kEvictIterLimit = 1u << 16;  // iterations of the full-bucket loop per warp
 
 enum Result : uint32_t {
   kInitial = 0,
@@ -134,28 +135,6 @@ __device__ __forceinline__ void ld_scores16(const uint64_t* p, uint64_t (&s)[16]
   }
 }
 
-// Copies one row with the 8 lanes of a group.
-__device__ __forceinline__ void group_copy_row(const TableView& t, uint8_t* dst,
-                                               const uint8_t* src, uint32_t sub) {
-  const uint32_t vec = t.vec_bytes;
-  const uint32_t cpr = t.chunks_per_row;
-  if (vec == 16) {
-    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
-      __stcs(reinterpret_cast<uint4*>(dst) + c, __ldcs(reinterpret_cast<const uint4*>(src) + c));
-  } else if (vec == 8) {
-    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
-      reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
-  } else if (vec == 4) {
-    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
-      reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
-  } else if (vec == 2) {
-    for (uint32_t c = sub; c < cpr; c += kGroupLanes)
-      reinterpret_cast<uint16_t*>(dst)[c] = reinterpret_cast<const uint16_t*>(src)[c];
-  } else {
-    for (uint32_t c = sub; c < cpr; c += kGroupLanes) dst[c] = src[c];
-  }
-}
-
 // Distance, in probe order from `start`, of the first set bit of a lane's
 // 16-slot mask; 255 when the mask is empty.
 __device__ __forceinline__ uint32_t first_from_start(uint32_t mask16, uint32_t sub,
@@ -175,138 +154,59 @@ __device__ __forceinline__ uint32_t first_from_start(uint32_t mask16, uint32_t s
   return 255u;
 }
 
-struct EvictOutcome {
-  uint32_t result;
-  uint32_t slot;
-};
-
 // Does the operation copy the batch row into a freshly claimed slot?
 __device__ __forceinline__ constexpr bool op_writes_row_on_insert(int op) {
   return op == kOpInsertOrAssign || op == kOpFindOrInsert || op == kOpInsertAndEvict ||
          op == kOpAccumOrAssign;
 }
 
-// Phase 4 for one key whose bucket is full, run by the 8 lanes of a group (all
-// collectives use the group's mask).  The group holds no lock while it waits:
-// it scans the 128 scores, and when the minimum's slot is LOCKED by somebody
-// else it polls that key (bounded) and scans again -- so the victim is always
-// the true current minimum, as in the reference (upsert.cuh:149-215).  Once the
-// victim is locked the group never waits again: digest and score are written,
-// the old row leaves (insert_and_evict), the new row is copied and the key is
-// published before the function returns.
-template <int OP>
-__device__ __forceinline__ EvictOutcome group_evict(const TableView& t, const MutateArgs& args,
-                                                    const ProbeLane& pl, uint32_t bucket,
-                                                    uint64_t key, uint32_t digest,
-                                                    uint64_t desired, uint64_t in_score,
-                                                    uint64_t batch_index) {
+// Minimum score of a full bucket and its first position, computed by the 8
+// lanes of a group from one coalesced 1-KiB read of the score line.
+__device__ __forceinline__ void group_min_score(const TableView& t, const ProbeLane& pl,
+                                                uint32_t bucket, uint64_t* gmin, uint32_t* gpos) {
   const uint32_t gmask = group_mask(pl.group);
-  const uint64_t slot0 = uint64_t(bucket) << 7;
-  const uint64_t* score_line = t.scores + slot0 + pl.sub * 16u;
-  EvictOutcome out{kInitial, kNoSlot};
-  uint32_t attempts = 0;
-  while (out.result == kInitial) {
-    if (++attempts > kEvictRetryLimit) {
-      if (pl.sub == 0) atomicOr(t.status, kStatusRetryExhausted);
-      out.result = kRefused;
-      break;
-    }
-    uint64_t s[16];
-    ld_scores16(score_line, s);
-    uint64_t ms = s[0];
-    uint32_t mp = 0;
+  uint64_t s[16];
+  ld_scores16(t.scores + (uint64_t(bucket) << 7) + pl.sub * 16u, s);
+  uint64_t ms = s[0];
+  uint32_t mp = 0;
 #pragma unroll
-    for (int b = 1; b < 16; ++b) {
-      if (s[b] < ms) {
-        ms = s[b];
-        mp = b;
-      }
+  for (int b = 1; b < 16; ++b) {
+    if (s[b] < ms) {
+      ms = s[b];
+      mp = b;
     }
-    const uint32_t hi = uint32_t(ms >> 32);
-    const uint32_t ghi = __reduce_min_sync(gmask, hi);
-    const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
-    const uint32_t glo = __reduce_min_sync(gmask, lo);
-    const uint32_t cand = (hi == ghi && lo == glo) ? pl.sub * 16u + mp : 255u;
-    const uint32_t gpos = __reduce_min_sync(gmask, cand);
-    const uint64_t gmin = (uint64_t(ghi) << 32) | glo;
-    const bool refuse = (OP == kOpFindOrInsertPtr) ? (desired <= gmin) : (desired < gmin);
-    if (refuse) {
-      out.result = kRefused;
-      break;
-    }
-    const bool leader = (gpos >> 4) == pl.sub;
-    const uint32_t leader_lane = pl.group * 8u + (gpos >> 4);
-    uint32_t code = 0;  // 1 locked by someone: wait, 2 rescan, 3 victim locked, 4 vacant slot locked, 5 gave up
-    uint64_t victim = 0;
-    if (leader) {
-      uint64_t* kp = t.keys + slot0 + gpos;
-      victim = ld_relaxed(kp);
-      if (victim == t.locked_key) {
-        code = 5;
-        for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-          __nanosleep(spin < 64 ? 32 : 256);
-          if (ld_acquire(kp) != t.locked_key) {
-            code = 1;
-            break;
-          }
-        }
-        if (code == 5) atomicOr(t.status, kStatusLockTimeout);
-      } else if (cas_acquire(kp, victim, t.locked_key) != victim) {
-        code = 2;
-      } else {
-        uint64_t* sp = t.scores + slot0 + gpos;
-        if (ld_relaxed(sp) > gmin) {
-          st_release(kp, victim);
-          code = 2;
-        } else {
-          const bool vacant = victim == t.empty_key || victim == t.reclaim_key;
-          code = vacant ? 4 : 3;
-          st_u8_cg(t.digests + slot0 + gpos, digest);
-          st_relaxed(sp, inserted_score(args.strategy, in_score, desired));
-          if (vacant) atomicAdd(t.bucket_sizes + bucket, 1);
-        }
-      }
-    }
-    code = __shfl_sync(gmask, code, leader_lane);
-    if (code == 5) {
-      out.result = kRefused;
-      break;
-    }
-    if (code < 3) continue;
-    out.slot = uint32_t(slot0 + gpos);
-    out.result = code == 4 ? kOccupiedReclaimed : kEvict;
-    uint8_t* row = row_ptr(t, out.slot);
-    if (OP == kOpInsertAndEvict && code == 3) {
-      unsigned long long ticket = 0;
-      if (leader) {
-        ticket = atomicAdd(args.evicted_counter, 1ull);
-        __stcs(args.evicted_keys + ticket, victim);
-        if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + ticket, gmin);
-      }
-      ticket = __shfl_sync(gmask, ticket, leader_lane);
-      group_copy_row(t, args.evicted_values + ticket * t.row_bytes, row, pl.sub);
-    }
-    if (op_writes_row_on_insert(OP)) {
-      group_copy_row(t, row, args.values + batch_index * t.row_bytes, pl.sub);
-    }
-    __syncwarp(gmask);
-    const bool keep_locked = OP == kOpFindOrInsertPtr && args.locked_key_ptrs != nullptr;
-    if (leader && !keep_locked) st_release(t.keys + out.slot, key);
   }
-  if (OP == kOpInsertAndEvict && out.result == kRefused) {
-    // a refused input leaves through the evicted arrays as well
-    // (upsert_and_evict.cuh:189-194,244-246)
-    unsigned long long ticket = 0;
-    if (pl.sub == 0) {
-      ticket = atomicAdd(args.evicted_counter, 1ull);
-      __stcs(args.evicted_keys + ticket, key);
-      if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + ticket, desired);
-    }
-    ticket = __shfl_sync(gmask, ticket, pl.group * 8u);
-    group_copy_row(t, args.evicted_values + ticket * t.row_bytes,
-                   args.values + batch_index * t.row_bytes, pl.sub);
+  const uint32_t hi = uint32_t(ms >> 32);
+  const uint32_t ghi = __reduce_min_sync(gmask, hi);
+  const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
+  const uint32_t glo = __reduce_min_sync(gmask, lo);
+  const uint32_t cand = (hi == ghi && lo == glo) ? pl.sub * 16u + mp : 255u;
+  *gpos = __reduce_min_sync(gmask, cand);
+  *gmin = (uint64_t(ghi) << 32) | glo;
+}
+
+// Copies one row with all 32 lanes (used for the few rows that do not follow
+// the warp's batch order, e.g. refused inputs leaving through the evicted
+// arrays).
+__device__ __forceinline__ void warp_copy_one_row(const TableView& t, uint8_t* dst,
+                                                  const uint8_t* src, uint32_t lane) {
+  const uint32_t vec = t.vec_bytes;
+  const uint32_t cpr = t.chunks_per_row;
+  if (vec == 16) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+  } else if (vec == 8) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
+  } else if (vec == 4) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
+  } else if (vec == 2) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint16_t*>(dst)[c] = reinterpret_cast<const uint16_t*>(src)[c];
+  } else {
+    for (uint32_t c = lane; c < cpr; c += 32) dst[c] = src[c];
   }
-  return out;
 }
 
 // One warp serves 32 keys.
@@ -317,9 +217,18 @@ __device__ __forceinline__ EvictOutcome group_evict(const TableView& t, const Mu
 //   phase 2  per pass: confirm the hit or claim the first EMPTY slot (CAS)
 //   phase 3  metadata, rows (warp-cooperative, coalesced) and publication of
 //            everything locked so far -- no lock survives into phase 4
-//   phase 4  keys whose bucket is full, four per round (group_evict)
+//   phase 4  keys whose bucket is full, in iterations of
+//              A  8-lane groups scan the score lines (four buckets per round)
+//              B  every owner lane runs its own lock chain at the same time:
+//                 victim key load, CAS, score verification, digest + score
+//              C  evicted rows leave, new rows arrive (whole warp, coalesced),
+//                 keys are published
+//            A lane that meets a LOCKED victim or loses a CAS tries again in
+//            the next iteration; it polls the foreign lock (bounded) only
+//            after step C, when the warp holds nothing.  The victim is always
+//            the true current minimum, as in the reference (upsert.cuh:149-215).
 template <int OP>
-__global__ void __launch_bounds__(kMutateBlock)
+__global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? 4 : 5)
     mutate_kernel(const TableView t, const MutateArgs args) {
   const uint32_t full = 0xFFFFFFFFu;
   const ProbeLane pl = probe_lane();
@@ -329,6 +238,7 @@ __global__ void __launch_bounds__(kMutateBlock)
   if (base >= n) return;
   const uint64_t i = base + pl.lane;
   const int strategy = args.strategy;
+  const uint32_t lane_lt = (1u << pl.lane) - 1u;
 
   // ---- phase 0 ------------------------------------------------------------
   uint64_t key = 0;
@@ -358,33 +268,38 @@ __global__ void __launch_bounds__(kMutateBlock)
   const uint32_t my_bucket = uint32_t(a.bucket);
 
   // ---- phase 1 ------------------------------------------------------------
-  uint4 dg[kPasses];
-  uint32_t bkt[kPasses];
-  uint32_t pmode[kPasses];
-#pragma unroll
-  for (int j = 0; j < kPasses; ++j) {
-    const uint32_t owner = pass_owner(j, pl.group);
-    bkt[j] = __shfl_sync(full, my_bucket, owner);
-    pmode[j] = __shfl_sync(full, mode, owner);
-    dg[j] = make_uint4(0, 0, 0, 0);
-    if (pmode[j] & kModeValid) {
-      dg[j] = ld_meta_v4(t.digests + (uint64_t(bkt[j]) << 7) + pl.sub * 16u);
-    }
-  }
-  uint32_t cand[kPasses];
+  // masks[j]: low half = slots whose digest equals the key's, high half =
+  // slots whose digest is the empty digest (this lane's 16 slots of pass j)
+  uint32_t masks[kPasses];
   uint64_t first_key[kPasses];  // key observed at the first candidate slot
-  uint64_t want[kPasses];
+  {
+    uint4 dg[kPasses];
 #pragma unroll
-  for (int j = 0; j < kPasses; ++j) {
-    const uint32_t owner = pass_owner(j, pl.group);
-    const uint32_t tgt = __shfl_sync(full, a.digest, owner);
-    want[j] = __shfl_sync(full, key, owner);
-    cand[j] = (pmode[j] & kModeValid) ? match16(dg[j], replicate4(tgt)) : 0u;
-    first_key[j] = ~want[j];
-    if (cand[j]) {
-      uint64_t* kp = t.keys + (uint64_t(bkt[j]) << 7) + pl.sub * 16u + (__ffs(cand[j]) - 1);
-      first_key[j] = (pmode[j] & kModeLockOnHit) ? cas_acquire(kp, want[j], t.locked_key)
-                                                 : ld_relaxed(kp);
+    for (int j = 0; j < kPasses; ++j) {
+      const uint32_t owner = pass_owner(j, pl.group);
+      const uint32_t b = __shfl_sync(full, my_bucket, owner);
+      const uint32_t m = __shfl_sync(full, mode, owner);
+      dg[j] = make_uint4(0, 0, 0, 0);
+      if (m & kModeValid) dg[j] = ld_meta_v4(t.digests + (uint64_t(b) << 7) + pl.sub * 16u);
+    }
+#pragma unroll
+    for (int j = 0; j < kPasses; ++j) {
+      const uint32_t owner = pass_owner(j, pl.group);
+      const uint32_t b = __shfl_sync(full, my_bucket, owner);
+      const uint32_t m = __shfl_sync(full, mode, owner);
+      const uint32_t tgt = __shfl_sync(full, a.digest, owner);
+      const uint64_t want = __shfl_sync(full, key, owner);
+      masks[j] = 0;
+      first_key[j] = ~want;
+      if (m & kModeValid) {
+        const uint32_t cand = match16(dg[j], replicate4(tgt));
+        masks[j] = cand | (match16(dg[j], t.empty_digest4) << 16);
+        if (cand) {
+          uint64_t* kp = t.keys + (uint64_t(b) << 7) + pl.sub * 16u + (__ffs(cand) - 1);
+          first_key[j] = (m & kModeLockOnHit) ? cas_acquire(kp, want, t.locked_key)
+                                              : ld_relaxed(kp);
+        }
+      }
     }
   }
 
@@ -395,17 +310,19 @@ __global__ void __launch_bounds__(kMutateBlock)
   for (int j = 0; j < kPasses; ++j) {
     const uint32_t gmask = group_mask(pl.group);
     const uint32_t owner = pass_owner(j, pl.group);
+    const uint32_t pmode = __shfl_sync(full, mode, owner);
     const uint32_t start = __shfl_sync(full, a.start, owner);
-    const uint64_t slot0 = uint64_t(bkt[j]) << 7;
-    const bool lock_on_hit = (pmode[j] & kModeLockOnHit) != 0;
+    const uint64_t want = __shfl_sync(full, key, owner);
+    const uint64_t slot0 = uint64_t(__shfl_sync(full, my_bucket, owner)) << 7;
+    const bool lock_on_hit = (pmode & kModeLockOnHit) != 0;
     uint32_t result = kInitial;
     uint32_t slot = kNoSlot;
-    if (pmode[j] & kModeValid) {
+    if (pmode & kModeValid) {
       uint32_t hit_pos = 255u;
-      if (cand[j]) {
-        uint32_t m = cand[j];
+      uint32_t m = masks[j] & 0xFFFFu;
+      if (m) {
         uint32_t pos = pl.sub * 16u + (__ffs(m) - 1);
-        if (first_key[j] == want[j]) {
+        if (first_key[j] == want) {
           hit_pos = pos;
         } else {
           m &= m - 1;
@@ -413,9 +330,9 @@ __global__ void __launch_bounds__(kMutateBlock)
             pos = pl.sub * 16u + (__ffs(m) - 1);
             m &= m - 1;
             uint64_t* kp = t.keys + slot0 + pos;
-            const uint64_t seen =
-                lock_on_hit ? cas_acquire(kp, want[j], t.locked_key) : ld_relaxed(kp);
-            if (seen == want[j]) {
+            const uint64_t seen = lock_on_hit ? cas_acquire(kp, want, t.locked_key)
+                                              : ld_relaxed(kp);
+            if (seen == want) {
               hit_pos = pos;
               break;
             }
@@ -428,12 +345,12 @@ __global__ void __launch_bounds__(kMutateBlock)
         const uint32_t pos = __shfl_sync(gmask, hit_pos, src);
         result = lock_on_hit ? kDuplicate : kFoundNoLock;
         slot = uint32_t(slot0) + pos;
-      } else if (!(pmode[j] & kModeInsertOnMiss)) {
+      } else if (!(pmode & kModeInsertOnMiss)) {
         result = kMiss;
-      } else if (pmode[j] & kModeBucketFull) {
+      } else if (pmode & kModeBucketFull) {
         result = kNeedEvict;
       } else {
-        uint32_t em = match16(dg[j], t.empty_digest4);
+        uint32_t em = masks[j] >> 16;
         while (true) {
           const uint32_t d = first_from_start(em, pl.sub, start);
           const uint32_t gd = __reduce_min_sync(gmask, d);
@@ -465,85 +382,188 @@ __global__ void __launch_bounds__(kMutateBlock)
   }
 
   // ---- phase 3: everything locked so far is written and published ---------------
-  const bool holds_lock = my_result == kDuplicate || my_result == kOccupiedEmpty;
   const bool keep_locked =
       (OP == kOpFindOrInsertPtr || OP == kOpLockKeys) && args.locked_key_ptrs != nullptr;
-  if (my_result == kOccupiedEmpty) {
-    st_u8_cg(t.digests + my_slot, a.digest);
-    st_relaxed(t.scores + my_slot, inserted_score(strategy, in_score, desired));
-    atomicAdd(t.bucket_sizes + a.bucket, 1);
-  }
-  if (my_result == kDuplicate && OP != kOpAssignValues) {
-    const bool needs_old = strategy == kLfu || strategy == kEpochLfu ||
-                           (OP == kOpFindAndUpdate && args.scores_out != nullptr);
-    const uint64_t old_score = needs_old ? ld_relaxed(t.scores + my_slot) : 0;
-    uint64_t ns = 0;
-    bool write;
-    if (op_inserts(OP) || OP == kOpLockKeys) {
-      write = hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns);
-    } else {
-      write = hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
+  {
+    const bool holds_lock = my_result == kDuplicate || my_result == kOccupiedEmpty;
+    if (my_result == kOccupiedEmpty) {
+      st_u8_cg(t.digests + my_slot, a.digest);
+      st_relaxed(t.scores + my_slot, inserted_score(strategy, in_score, desired));
+      atomicAdd(t.bucket_sizes + a.bucket, 1);
     }
-    if (write) st_relaxed(t.scores + my_slot, ns);
-    if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
-      args.scores_out[i] = write ? ns : old_score;
+    if (my_result == kDuplicate && OP != kOpAssignValues) {
+      const bool needs_old = strategy == kLfu || strategy == kEpochLfu ||
+                             (OP == kOpFindAndUpdate && args.scores_out != nullptr);
+      const uint64_t old_score = needs_old ? ld_relaxed(t.scores + my_slot) : 0;
+      uint64_t ns = 0;
+      bool write;
+      if (op_inserts(OP) || OP == kOpLockKeys) {
+        write = hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns);
+      } else {
+        write = hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
+      }
+      if (write) st_relaxed(t.scores + my_slot, ns);
+      if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
+        args.scores_out[i] = write ? ns : old_score;
+      }
     }
+    if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
+        OP == kOpAssignValues) {
+      warp_move_rows<1>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
+                        pl.lane);
+    } else if (OP == kOpFindOrInsert) {
+      warp_move_rows<0>(t, args.values + base * t.row_bytes,
+                        my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
+      warp_move_rows<1>(t, args.values + base * t.row_bytes,
+                        my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
+    } else if (OP == kOpAccumOrAssign) {
+      warp_move_rows<2>(t, args.values + base * t.row_bytes,
+                        my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
+      warp_move_rows<1>(t, args.values + base * t.row_bytes,
+                        my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
+    }
+    __syncwarp();
+    if (holds_lock && !keep_locked) st_release(t.keys + my_slot, key);
   }
-  if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
-      OP == kOpAssignValues) {
-    warp_move_rows<1>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
-                      pl.lane);
-  } else if (OP == kOpFindOrInsert) {
-    warp_move_rows<0>(t, args.values + base * t.row_bytes,
-                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-    warp_move_rows<1>(t, args.values + base * t.row_bytes,
-                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
-  } else if (OP == kOpAccumOrAssign) {
-    warp_move_rows<2>(t, args.values + base * t.row_bytes,
-                      my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-    warp_move_rows<1>(t, args.values + base * t.row_bytes,
-                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
-  }
-  __syncwarp();
-  if (holds_lock && !keep_locked) st_release(t.keys + my_slot, key);
 
-  // ---- phase 4: full buckets, four keys per round ---------------------------------
+  // ---- phase 4: full buckets ----------------------------------------------------------
   if (op_inserts(OP)) {
-    uint32_t need = __ballot_sync(full, my_result == kNeedEvict);
-    while (need) {
-      const uint32_t k = __fns(need, 0, pl.group + 1);
-      const bool active = k != 0xFFFFFFFFu;
-      const uint32_t src = active ? k : 0u;
-      const uint64_t e_key = __shfl_sync(full, key, src);
-      const uint64_t e_desired = __shfl_sync(full, desired, src);
-      const uint64_t e_in = __shfl_sync(full, in_score, src);
-      const uint32_t e_bucket = __shfl_sync(full, my_bucket, src);
-      const uint32_t e_digest = __shfl_sync(full, a.digest, src);
-      EvictOutcome eo{kInitial, kNoSlot};
-      if (active) {
-        eo = group_evict<OP>(t, args, pl, e_bucket, e_key, e_digest, e_desired, e_in, base + src);
+    uint32_t pending = __ballot_sync(full, my_result == kNeedEvict);
+    uint32_t iterations = 0;
+    while (pending) {
+      const bool mine = (pending >> pl.lane) & 1u;
+      if (++iterations > kEvictIterLimit) {
+        if (mine) {
+          my_result = kRefused;
+          atomicOr(t.status, kStatusRetryExhausted);
+        }
+        break;
+      }
+      // -- A: score scans, four buckets per round
+      uint64_t my_min = kMaxScore;
+      uint32_t my_pos = 255u;
+      for (uint32_t scan = pending; scan != 0;) {
+        const uint32_t k = __fns(scan, 0, pl.group + 1);
+        const bool active = k != 0xFFFFFFFFu;
+        const uint32_t e_bucket = __shfl_sync(full, my_bucket, active ? k : 0u);
+        uint64_t gmin = kMaxScore;
+        uint32_t gpos = 255u;
+        if (active) group_min_score(t, pl, e_bucket, &gmin, &gpos);
+        __syncwarp();
+        const uint32_t rank = __popc(scan & lane_lt);
+        const uint64_t rmin = __shfl_sync(full, gmin, (rank & 3u) * 8u);
+        const uint32_t rpos = __shfl_sync(full, gpos, (rank & 3u) * 8u);
+        if (((scan >> pl.lane) & 1u) && rank < 4u) {
+          my_min = rmin;
+          my_pos = rpos;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) scan &= scan - 1;  // (0 & -1) stays 0
+      }
+      // -- B: every owner lane runs its lock chain, nobody waits
+      uint64_t victim = 0;
+      uint64_t* wait_on = nullptr;
+      bool placed = false;
+      bool refused_now = false;
+      if (mine) {
+        const bool refuse =
+            (OP == kOpFindOrInsertPtr) ? (desired <= my_min) : (desired < my_min);
+        if (refuse) {
+          refused_now = true;
+          my_result = kRefused;
+        } else {
+          const uint32_t slot = (my_bucket << 7) + my_pos;
+          uint64_t* kp = t.keys + slot;
+          victim = ld_relaxed(kp);
+          if (victim == t.locked_key) {
+            wait_on = kp;
+          } else if (cas_acquire(kp, victim, t.locked_key) == victim) {
+            uint64_t* sp = t.scores + slot;
+            if (ld_relaxed(sp) > my_min) {
+              st_release(kp, victim);  // the slot was refreshed in between: scan again
+            } else {
+              placed = true;
+              my_slot = slot;
+              st_u8_cg(t.digests + slot, a.digest);
+              st_relaxed(sp, inserted_score(strategy, in_score, desired));
+              if (victim == t.empty_key || victim == t.reclaim_key) {
+                my_result = kOccupiedReclaimed;
+                atomicAdd(t.bucket_sizes + a.bucket, 1);
+              } else {
+                my_result = kEvict;
+              }
+            }
+          }
+        }
+      }
+      // -- C: rows and publication
+      if (OP == kOpInsertAndEvict) {
+        const uint32_t ev = __ballot_sync(full, placed && my_result == kEvict);
+        const uint32_t rf = __ballot_sync(full, refused_now);
+        if (ev | rf) {
+          unsigned long long first = 0;
+          if (pl.lane == 0) {
+            first = atomicAdd(args.evicted_counter, (unsigned long long)(__popc(ev) + __popc(rf)));
+          }
+          first = __shfl_sync(full, first, 0);
+          if ((ev >> pl.lane) & 1u) {
+            const unsigned long long at = first + __popc(ev & lane_lt);
+            __stcs(args.evicted_keys + at, victim);
+            if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + at, my_min);
+          }
+          if ((rf >> pl.lane) & 1u) {
+            // a refused input leaves through the evicted arrays as well
+            // (upsert_and_evict.cuh:189-194,244-246)
+            const unsigned long long at = first + __popc(ev) + __popc(rf & lane_lt);
+            __stcs(args.evicted_keys + at, key);
+            if (args.evicted_scores != nullptr) __stcs(args.evicted_scores + at, desired);
+          }
+          if (ev) {
+            // lane r carries the slot of the r-th evicting lane
+            const uint32_t src = __fns(ev, 0, pl.lane + 1);
+            const uint32_t s = __shfl_sync(full, my_slot, src & 31u);
+            warp_move_rows<0>(t, args.evicted_values + first * t.row_bytes,
+                              src == 0xFFFFFFFFu ? kNoSlot : s, pl.lane);
+            __syncwarp();  // the old rows are out before the new ones come in
+          }
+          for (uint32_t left = rf, q = 0; left != 0; left &= left - 1, ++q) {
+            const uint32_t src = __ffs(left) - 1;
+            warp_copy_one_row(t, args.evicted_values + (first + __popc(ev) + q) * t.row_bytes,
+                              args.values + (base + src) * t.row_bytes, pl.lane);
+          }
+        }
+      }
+      if (op_writes_row_on_insert(OP)) {
+        warp_move_rows<1>(t, args.values + base * t.row_bytes, placed ? my_slot : kNoSlot,
+                          pl.lane);
       }
       __syncwarp();
-      const uint32_t rank = __popc(need & ((1u << pl.lane) - 1u));
-      const uint32_t r = __shfl_sync(full, eo.result, (rank & 3u) * 8u);
-      const uint32_t s = __shfl_sync(full, eo.slot, (rank & 3u) * 8u);
-      if (((need >> pl.lane) & 1u) && rank < 4u) {
-        my_result = r;
-        my_slot = s;
+      if (placed && !(OP == kOpFindOrInsertPtr && keep_locked)) st_release(t.keys + my_slot, key);
+      pending &= ~__ballot_sync(full, placed || refused_now);
+      // the warp holds no lock now: lanes that met a foreign lock poll it (bounded)
+      if (wait_on != nullptr) {
+        bool freed = false;
+        for (uint32_t spin = 0; spin < kSpinLimit && !freed; ++spin) {
+          __nanosleep(spin < 64 ? 32 : 256);
+          freed = ld_acquire(wait_on) != t.locked_key;
+        }
+        if (!freed) {
+          my_result = kRefused;
+          atomicOr(t.status, kStatusLockTimeout);
+        }
       }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) need &= need - 1;  // (0 & -1) stays 0
+      pending &= ~__ballot_sync(full, mine && my_result == kRefused);
     }
   }
 
   if (OP == kOpFindOrInsertPtr || OP == kOpFindAndUpdate || OP == kOpLockKeys) {
-    const bool placed = my_result == kDuplicate || my_result == kOccupiedEmpty ||
-                        my_result == kOccupiedReclaimed || my_result == kEvict;
+    const bool has_slot = my_result == kDuplicate || my_result == kOccupiedEmpty ||
+                          my_result == kOccupiedReclaimed || my_result == kEvict;
     if (i < n) {
-      if (args.ptrs != nullptr) args.ptrs[i] = placed ? row_ptr(t, my_slot) : nullptr;
+      if (args.ptrs != nullptr) args.ptrs[i] = has_slot ? row_ptr(t, my_slot) : nullptr;
       if (args.founds != nullptr) args.founds[i] = my_result == kDuplicate;
       if (args.locked_key_ptrs != nullptr) {
-        args.locked_key_ptrs[i] = placed ? t.keys + my_slot : nullptr;
+        args.locked_key_ptrs[i] = has_slot ? t.keys + my_slot : nullptr;
       }
     }
   }
