@@ -154,6 +154,8 @@ _SIGNATURES = {
     "hkv_size_if": [_P, _INT, _U64, _U64, _P, _P],
     "hkv_size": [_P, _P, ctypes.POINTER(_U64)],
     "hkv_load_factor": [_P, _P, ctypes.POINTER(ctypes.c_float)],
+    "hkv_size_no_alloc": [_P, _P, ctypes.POINTER(_U64)],
+    "hkv_size_no_alloc_last_error": [],
     "hkv_capacity": [_P],
     "hkv_bucket_count": [_P],
     "hkv_dim": [_P],
@@ -172,6 +174,7 @@ _RESTYPES = {
     "hkv_dim": _U64,
     "hkv_max_bucket_size": _U64,
     "hkv_last_error": ctypes.c_char_p,
+    "hkv_size_no_alloc_last_error": ctypes.c_char_p,
 }
 
 
@@ -409,6 +412,20 @@ class HashTable:
     def size(self, stream=None) -> int:
         out = ctypes.c_uint64(0)
         self._call("hkv_size", _stream(stream), ctypes.byref(out))
+        return out.value
+
+    def size_no_alloc(self, stream=None) -> int:
+        """size() for callers that must not allocate (see hkv_size_no_alloc in
+        include/hkv_b200.h for who they are and for the limits)."""
+        out = ctypes.c_uint64(0)
+        rc = self._lib.hkv_size_no_alloc(self._h, _stream(stream), ctypes.byref(out))
+        if rc:
+            msg = (self._lib.hkv_size_no_alloc_last_error() or b"").decode()
+            if rc == 2:
+                raise CudaException(msg)
+            if rc == 4:
+                raise ValueError(msg)
+            raise RuntimeError(msg)
         return out.value
 
     def empty(self, stream=None) -> bool:

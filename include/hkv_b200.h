@@ -231,6 +231,27 @@ HKV_API uint64_t hkv_bucket_count(const hkv_table* table);
 HKV_API uint64_t hkv_dim(const hkv_table* table);
 HKV_API uint64_t hkv_max_bucket_size(const hkv_table* table);
 
+/* No counterpart in the reference.  hkv_size for callers that must not
+ * allocate: processes whose set-up phase is over and whose memory budget is
+ * fixed (serving loops, plug-ins inside a host application that owns every
+ * allocation, monitoring threads that must not cause the device-wide
+ * synchronisation an allocation implies).  The partial sums live in a fixed
+ * array inside the library image instead of scratch memory obtained at run
+ * time, so the call issues no cudaMalloc / cudaFree and calls no allocating
+ * library routine.  Limits and rules:
+ *   - tables of at most 4,194,304 buckets (2^29 slots); larger ones are
+ *     rejected with HKV_ERR_INVALID_ARG -- use hkv_size for them;
+ *   - every GPU that loads the library holds the array (about 32 KiB) until
+ *     the process exits;
+ *   - the first call on a device resolves the array's device address; make
+ *     that first call before any stream capture begins;
+ *   - all calls share the array: calls that overlap on one GPU (two streams,
+ *     two threads) race and must be serialised by the caller.
+ * Synchronises the stream, like hkv_size.  The message of a failure is
+ * returned by hkv_size_no_alloc_last_error. */
+HKV_API int hkv_size_no_alloc(hkv_table* table, hkv_stream stream, uint64_t* size);
+HKV_API const char* hkv_size_no_alloc_last_error(void);
+
 /* HashTable::set_global_epoch, include/merlin_hashtable.cuh:3760 */
 HKV_API int hkv_set_global_epoch(hkv_table* table, uint64_t epoch);
 
