@@ -63,6 +63,19 @@ def mixed_keys(start: int, n: int, device) -> torch.Tensor:
     return torch.where(reserved, z & 0xFFFF, z)
 
 
+def owner_of(keys: torch.Tensor, world: int) -> torch.Tensor:
+    """Murmur3 finaliser of the key modulo the world size: the shard that owns it."""
+    k = keys
+    k = (k ^ _lsr(k, 33)) * _s64(0xFF51AFD7ED558CCD)
+    k = (k ^ _lsr(k, 33)) * _s64(0xC4CEB9FE1A85EC53)
+    k = k ^ _lsr(k, 33)
+    if world & (world - 1) == 0:
+        return k & (world - 1)
+    # unsigned modulo of a value held in a signed tensor
+    hi = _lsr(k, 1) % world
+    return (hi * 2 + (k & 1)) % world
+
+
 def rows_for(keys: torch.Tensor, dim: int) -> torch.Tensor:
     """Row content is a function of the key: column j holds (key mod 2^20) + j."""
     base = (keys & 0xFFFFF).to(torch.float32)
@@ -261,16 +274,20 @@ class ClockSampler:
                 "power_w_max": round(self.power_w, 1), "reasons": sorted(self.reasons)}
 
 
-def fill_table(arm, capacity: int, dim: int, batch: int, target_lf: float, key_base: int):
+def fill_table(arm, capacity: int, dim: int, batch: int, target_lf: float, key_base: int,
+               rank: int = 0, world: int = 1):
     """insert_or_assign of fresh unique keys until the load factor is reached
     (uniform keys fill some buckets early; they evict under LRU while the
-    others catch up)."""
+    others catch up).  With several ranks every rank walks the same key
+    stream and keeps the keys its shard owns."""
     inserted = 0
     max_batches = int(2.0 * capacity / batch) + 8
     for b in range(max_batches):
-        keys = mixed_keys(key_base + b * batch, batch, "cuda")
+        keys = mixed_keys(key_base + b * batch * world, batch * world, "cuda")
+        if world > 1:
+            keys = keys[owner_of(keys, world) == rank].contiguous()
         arm.insert_or_assign(keys, rows_for(keys, dim))
-        inserted += batch
+        inserted += keys.numel()
         if inserted >= target_lf * capacity and (b % 4 == 3 or inserted >= 1.3 * capacity):
             if arm.size() >= target_lf * capacity - 0.0005 * capacity:
                 break
@@ -376,6 +393,12 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    launched_world = world
+    if args.impl == "reference" and world > 1:
+        # the reference is a single-GPU library: rank 0 alone measures it
+        if rank != 0:
+            return
+        world = 1
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -384,7 +407,7 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     else:
-        torch.cuda.set_device(0)
+        torch.cuda.set_device(local_rank if launched_world > 1 else 0)
     barrier = (lambda: dist.barrier()) if dist else None
 
     capacity, dim, batch = args.capacity, args.dim, args.batch
@@ -402,19 +425,43 @@ def main():
     else:
         arm = ProductArm(capacity, dim, hbm_bytes)
 
-    # Each rank owns one shard of `capacity` slots and serves the batches that
-    # hash to it (weak scaling: per-GPU work is fixed as N grows).
-    key_base = rank << 44
-    inserted = fill_table(arm, capacity, dim, batch, args.load_factor, key_base)
+    # One shard of `capacity` slots per GPU (weak scaling: per-GPU table and
+    # per-GPU batch stay fixed as N grows).  With N > 1 the table is sharded by
+    # key hash and every batch is routed: keys out, rows and flags back.
+    key_base = 0
+    inserted = fill_table(arm, capacity, dim, batch, args.load_factor, key_base, rank, world)
     size = arm.size()
     load_factor = size / arm.capacity()
     n_query_sets = 8
-    queries = present_batches(arm, capacity, batch, n_query_sets, seed=17 + rank)
+    sharded = None
+    if world > 1:
+        from hierarchicalkv_b200.sharded import ShardedHashTable
+
+        sharded = ShardedHashTable(arm.t)
+        share = n_query_sets * batch // world
+        mine = arm.export_keys(0, min(capacity, 2 * share))
+        g = torch.Generator(device="cuda")
+        g.manual_seed(99)
+        mine = mine[torch.randperm(mine.numel(), generator=g, device="cuda")[:share]].contiguous()
+        assert mine.numel() == share
+        pool = torch.empty(share * world, dtype=torch.int64, device="cuda")
+        dist.all_gather_into_tensor(pool, mine)
+        g.manual_seed(1234 + rank)
+        pool = pool[torch.randperm(pool.numel(), generator=g, device="cuda")]
+        queries = [pool[i * batch:(i + 1) * batch].contiguous() for i in range(n_query_sets)]
+    else:
+        queries = present_batches(arm, capacity, batch, n_query_sets, seed=17 + rank)
     out_vals = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
     founds = torch.empty(batch, dtype=torch.bool, device="cuda")
 
+    def do_find(keys):
+        if sharded is not None:
+            sharded.find(batch, keys, out_vals, founds)
+        else:
+            arm.find(keys, out_vals, founds)
+
     def step(i):
-        arm.find(queries[i % n_query_sets], out_vals, founds)
+        do_find(queries[i % n_query_sets])
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -445,7 +492,7 @@ def main():
 
     def e2e_step(i):
         d_keys.copy_(h_keys[i % n_query_sets], non_blocking=True)
-        arm.find(d_keys, out_vals, founds)
+        do_find(d_keys)
         h_vals.copy_(out_vals, non_blocking=True)
         h_founds.copy_(founds, non_blocking=True)
 
@@ -460,7 +507,7 @@ def main():
 
     # ---- the other operations of the workload (not part of `value`) -----------
     ops = {}
-    if not args.no_ops:
+    if not args.no_ops and world == 1:
         reps = 10
 
         def per_kv(ms_total, n_keys):
@@ -522,7 +569,7 @@ def main():
         "metric": "find B-KV/s at LF=1.0, dim=64 (n/s/2^30), all keys present",
         "value": round(value, 4),
         "unit": "B-KV/s",
-        "n_gpus": world,
+        "n_gpus": launched_world,
         "steps": args.steps,
         "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 5),
@@ -537,13 +584,17 @@ def main():
             "load_factor": round(load_factor, 5),
             "keys_inserted_to_fill": inserted,
             "l2": "inputs larger than L2: %.1f GiB of rows hit at random, %d rotating query batches, %d MiB output buffer" % (capacity * row / 2**30, n_query_sets, batch * row >> 20),
-            "sharding": "one shard of this size per GPU, batches pre-routed to their shard" if world > 1 else "single table",
+            "sharding": ("key-hash sharded, owner = Murmur3(key) % N, one shard of this size per GPU; "
+                         "every batch routed by NCCL all-to-all: keys out, rows and flags back")
+            if world > 1 else ("single table" if launched_world == 1 else
+                               "single-GPU reference measured on rank 0 (it has no multi-GPU path)"),
         },
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 4), "unit": "B-KV/s",
                 "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * row + batch,
                 "steps": e2e_steps},
-        "gpu_launches": args.steps * arm.launches_per_find,
+        # N > 1: count, offsets and place kernels of the router, the lookup, three row scatters
+        "gpu_launches": args.steps * (arm.launches_per_find + (6 if world > 1 else 0)),
         "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peak,
                      "unit": "GB/s", "frac": round(achieved_gbs / peak, 4),
                      "traffic": None, "peak_source": peak_src,

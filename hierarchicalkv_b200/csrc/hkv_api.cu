@@ -546,6 +546,22 @@ int hkv_accum_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys,
   });
 }
 
+int hkv_accum_or_assign_unique(hkv_table* t, uint64_t n, const uint64_t* keys,
+                               const void* value_or_deltas, const bool* accum_or_assigns,
+                               const uint64_t* scores, hkv_stream stream,
+                               int ignore_evict_strategy) {
+  return guarded([&] {
+    if (n == 0) return;
+    HKV_CHECK(t->opt.value_size == 4, "accum_or_assign adds float32 elements only.");
+    if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
+    hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores, ignore_evict_strategy != 0);
+    if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
+    a.accum_flags = accum_or_assigns;
+    mutate(t, hkv::kOpAccumOrAssign, a, view_for(t, value_or_deltas), kInserter, true,
+           static_cast<cudaStream_t>(stream));
+  });
+}
+
 int hkv_find_or_insert(hkv_table* t, uint64_t n, const uint64_t* keys, void* values,
                        uint64_t* scores, hkv_stream stream, int unique_key,
                        int ignore_evict_strategy) {

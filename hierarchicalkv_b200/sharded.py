@@ -1,0 +1,268 @@
+"""Key-hash sharded table across the GPUs of one node.
+
+The reference is a single-GPU library; its users shard by hand with one table
+per GPU.  This module is that pattern made explicit: every rank owns one
+independent sub-table, ``owner(key) = Murmur3(key) % world_size`` (the
+table's own hash, include/merlin/utils.cuh:137-145 of the reference), and a
+batch is routed with an all-to-all over NVLink -- keys out, rows and found
+flags back -- around the local operation.
+
+One process per GPU; ``torch.distributed`` (NCCL) carries the exchange, the
+grouping by owner and the row permutations are CUDA kernels of
+libhkv_b200.so (csrc/hkv_shard.cu).  With a world of one rank the exchange is
+skipped and every call is exactly the local table's.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+
+from .table import HashTable, load_library
+
+
+def _stream_ptr() -> Optional[int]:
+    return torch.cuda.current_stream().cuda_stream or None
+
+
+class CudaOps:
+    """Device-side helpers of the router (hkv_shard_* of the C ABI)."""
+
+    def __init__(self):
+        self.lib = load_library()
+
+    def _chk(self, rc: int) -> None:
+        if rc:
+            raise RuntimeError((self.lib.hkv_shard_last_error() or b"").decode())
+
+    def partition(self, keys: torch.Tensor, world: int):
+        """-> (counts on the host, keys grouped by owner, batch index of each grouped key)"""
+        n = keys.numel()
+        dev = keys.device
+        meta = torch.empty(3 * world, dtype=torch.int64, device=dev)
+        grouped = torch.empty(n, dtype=torch.int64, device=dev)
+        origin = torch.empty(n, dtype=torch.int32, device=dev)
+        self._chk(self.lib.hkv_shard_partition(
+            n, keys.data_ptr(), world, meta.data_ptr(), meta[world:].data_ptr(),
+            meta[2 * world:].data_ptr(), grouped.data_ptr(), origin.data_ptr(), _stream_ptr()))
+        counts = meta[:world].cpu().tolist()  # the split sizes are needed on the host
+        return counts, grouped, origin
+
+    def gather_rows(self, src: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+        """dst[i] = src[index[i]]"""
+        n = index.numel()
+        dst = torch.empty((n,) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
+        row_bytes = src.element_size() * (src[0].numel() if src.dim() > 1 else 1)
+        self._chk(self.lib.hkv_shard_gather_rows(n, row_bytes, src.data_ptr(), index.data_ptr(),
+                                                 dst.data_ptr(), _stream_ptr()))
+        return dst
+
+    def scatter_rows(self, src: torch.Tensor, index: torch.Tensor, dst: torch.Tensor) -> None:
+        """dst[index[i]] = src[i]; rows whose index is -1 are skipped"""
+        n = index.numel()
+        row_bytes = src.element_size() * (src[0].numel() if src.dim() > 1 else 1)
+        self._chk(self.lib.hkv_shard_scatter_rows(n, row_bytes, src.data_ptr(), index.data_ptr(),
+                                                  dst.data_ptr(), _stream_ptr()))
+
+
+class _Route:
+    """How one batch travels: who gets how many keys, and the way back."""
+
+    __slots__ = ("send_counts", "recv_counts", "origin", "recv_keys", "n")
+
+    def __init__(self, send_counts, recv_counts, origin, recv_keys, n):
+        self.send_counts: List[int] = send_counts
+        self.recv_counts: List[int] = recv_counts
+        self.origin = origin          # batch index of every grouped key (None: identity)
+        self.recv_keys = recv_keys    # keys this rank has to serve, grouped by source rank
+        self.n = n
+
+
+class ShardedHashTable:
+    """The reference's method names over a table sharded by key hash.
+
+    ``local`` is this rank's sub-table (anything with the HashTable methods);
+    ``group`` a torch.distributed process group (None: the default group, or a
+    single rank when torch.distributed is not initialised).
+    """
+
+    def __init__(self, local: HashTable, group=None, ops=None):
+        self.local = local
+        self.group = group
+        self.dist = None
+        self.world = 1
+        self.rank = 0
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            self.dist = torch.distributed
+            self.world = self.dist.get_world_size(group)
+            self.rank = self.dist.get_rank(group)
+        self.ops = ops if ops is not None else CudaOps()
+
+    # -- routing ------------------------------------------------------------
+    def _all_to_all(self, send: torch.Tensor, send_counts, recv_counts) -> torch.Tensor:
+        out = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype,
+                          device=send.device)
+        self.dist.all_to_all_single(out, send, output_split_sizes=list(recv_counts),
+                                    input_split_sizes=list(send_counts), group=self.group)
+        return out
+
+    def _route(self, n: int, keys: torch.Tensor) -> _Route:
+        if self.world == 1:
+            return _Route([n], [n], None, keys, n)
+        send_counts, grouped, origin = self.ops.partition(keys[:n], self.world)
+        sc = torch.tensor(send_counts, dtype=torch.int64, device=keys.device)
+        rc = torch.empty_like(sc)
+        self.dist.all_to_all_single(rc, sc, group=self.group)
+        recv_counts = rc.cpu().tolist()
+        recv_keys = self._all_to_all(grouped, send_counts, recv_counts)
+        return _Route(send_counts, recv_counts, origin, recv_keys, n)
+
+    def _rows_out(self, route: _Route, rows: torch.Tensor) -> torch.Tensor:
+        """Caller's rows -> the rows this rank has to apply, in recv_keys order."""
+        if self.world == 1:
+            return rows
+        grouped = self.ops.gather_rows(rows, route.origin)
+        return self._all_to_all(grouped, route.send_counts, route.recv_counts)
+
+    def _rows_back(self, route: _Route, served: torch.Tensor, out: torch.Tensor) -> None:
+        """Rows produced for recv_keys -> the caller's buffer, in the caller's order."""
+        if self.world == 1:
+            if served.data_ptr() != out.data_ptr():
+                out[: route.n].copy_(served)
+            return
+        back = self._all_to_all(served, route.recv_counts, route.send_counts)
+        self.ops.scatter_rows(back, route.origin, out)
+
+    # -- duplicates that meet at the owner ---------------------------------------
+    @staticmethod
+    def _dedup(recv_keys: torch.Tensor):
+        """Keys arriving from different ranks may coincide.  -> (unique keys,
+        index of each received key in them, position of the first occurrence)."""
+        uniq, inverse = torch.unique(recv_keys, return_inverse=True)
+        first = torch.full((uniq.numel(),), recv_keys.numel(), dtype=torch.int64,
+                           device=recv_keys.device)
+        first.scatter_reduce_(0, inverse, torch.arange(recv_keys.numel(), device=recv_keys.device),
+                              reduce="amin")
+        return uniq, inverse, first
+
+    # -- operations -----------------------------------------------------------
+    def find(self, n, keys, values, founds, scores=None, stream=None) -> None:
+        """HashTable::find over all shards; misses leave `values` untouched."""
+        if n == 0:
+            return
+        route = self._route(n, keys)
+        m = route.recv_keys.numel()
+        if self.world == 1:
+            self.local.find(n, keys, values, founds, scores, stream)
+            return
+        served = torch.empty((m,) + tuple(values.shape[1:]), dtype=values.dtype,
+                             device=values.device)
+        hit = torch.zeros(m, dtype=torch.bool, device=values.device)
+        sc = torch.zeros(m, dtype=torch.int64, device=values.device) if scores is not None else None
+        if m:
+            self.local.find(m, route.recv_keys, served, hit, sc, stream)
+        back = self._all_to_all(served, route.recv_counts, route.send_counts)
+        hit_back = self._all_to_all(hit.view(torch.uint8), route.recv_counts, route.send_counts)
+        self.ops.scatter_rows(hit_back, route.origin, founds[:n].view(torch.uint8))
+        # only the rows of the hits may be written into the caller's buffer:
+        # a miss gets the "skip" index
+        where = torch.where(hit_back.view(torch.bool), route.origin,
+                            torch.full_like(route.origin, -1))
+        self.ops.scatter_rows(back, where, values)
+        if scores is not None:
+            sc_back = self._all_to_all(sc, route.recv_counts, route.send_counts)
+            self.ops.scatter_rows(sc_back, where, scores)
+
+    def insert_or_assign(self, n, keys, values, scores=None, stream=None) -> None:
+        if n == 0:
+            return
+        if self.world == 1:
+            self.local.insert_or_assign(n, keys, values, scores, stream)
+            return
+        route = self._route(n, keys)
+        rows = self._rows_out(route, values[:n])
+        sc = self._rows_out(route, scores[:n]) if scores is not None else None
+        if route.recv_keys.numel():
+            uniq, inverse, first = self._dedup(route.recv_keys)
+            self.local.insert_or_assign(uniq.numel(), uniq, rows.index_select(0, first).contiguous(),
+                                        sc.index_select(0, first).contiguous() if sc is not None else None,
+                                        stream)
+
+    def find_or_insert(self, n, keys, values, scores=None, stream=None) -> None:
+        """Hits return the stored row, misses insert the caller's row; when the
+        same new key arrives from several ranks the lowest rank's row is stored
+        and every requester gets that row back."""
+        if n == 0:
+            return
+        if self.world == 1:
+            self.local.find_or_insert(n, keys, values, scores, stream)
+            return
+        route = self._route(n, keys)
+        rows = self._rows_out(route, values[:n])
+        sc = self._rows_out(route, scores[:n]) if scores is not None else None
+        if route.recv_keys.numel():
+            uniq, inverse, first = self._dedup(route.recv_keys)
+            urows = rows.index_select(0, first).contiguous()
+            self.local.find_or_insert(uniq.numel(), uniq, urows,
+                                      sc.index_select(0, first).contiguous() if sc is not None else None,
+                                      stream)
+            served = urows.index_select(0, inverse).contiguous()
+        else:
+            served = rows
+        self._rows_back(route, served, values)
+
+    def accum_or_assign(self, n, keys, value_or_deltas, accum_or_assigns, scores=None,
+                        stream=None) -> None:
+        """Deltas for one key coming from several ranks are summed in rank order
+        before the local accum_or_assign, so the fp32 result is reproducible."""
+        if n == 0:
+            return
+        if self.world == 1:
+            self.local.accum_or_assign(n, keys, value_or_deltas, accum_or_assigns, scores, stream)
+            return
+        route = self._route(n, keys)
+        rows = self._rows_out(route, value_or_deltas[:n])
+        flags = self._rows_out(route, accum_or_assigns[:n].view(torch.uint8)).view(torch.bool)
+        sc = self._rows_out(route, scores[:n]) if scores is not None else None
+        if not route.recv_keys.numel():
+            return
+        uniq, inverse, first = self._dedup(route.recv_keys)
+        acc = torch.zeros((uniq.numel(),) + tuple(rows.shape[1:]), dtype=rows.dtype,
+                          device=rows.device)
+        at = 0
+        for c in route.recv_counts:           # one source rank at a time: no collisions inside a call
+            if c:
+                seg = slice(at, at + c)
+                is_acc = flags[seg]
+                idx = inverse[seg]
+                acc.index_add_(0, idx[is_acc], rows[seg][is_acc])
+                # an assignment takes the first occurrence's row
+                take = (~is_acc) & (first.index_select(0, idx) == torch.arange(at, at + c, device=rows.device))
+                acc.index_copy_(0, idx[take], rows[seg][take])
+            at += c
+        uflags = flags.index_select(0, first).contiguous()
+        usc = sc.index_select(0, first).contiguous() if sc is not None else None
+        fn = getattr(self.local, "accum_or_assign_unique", self.local.accum_or_assign)
+        fn(uniq.numel(), uniq, acc, uflags, usc, stream)
+
+    def size(self, stream=None) -> int:
+        s = self.local.size(stream)
+        if self.world == 1:
+            return s
+        t = torch.tensor([s], dtype=torch.int64,
+                         device="cuda" if self.dist.get_backend(self.group) == "nccl" else "cpu")
+        self.dist.all_reduce(t, group=self.group)
+        return int(t.item())
+
+    def owner_of(self, keys: torch.Tensor) -> torch.Tensor:
+        """Owner rank of each key (host-side check of the routing rule)."""
+        k = keys.cpu().numpy().view("uint64").copy()
+        import numpy as np
+
+        k ^= k >> np.uint64(33)
+        k *= np.uint64(0xFF51AFD7ED558CCD)
+        k ^= k >> np.uint64(33)
+        k *= np.uint64(0xC4CEB9FE1A85EC53)
+        k ^= k >> np.uint64(33)
+        return torch.from_numpy((k % np.uint64(self.world)).astype("int64"))

@@ -154,6 +154,11 @@ _SIGNATURES = {
     "hkv_size_if": [_P, _INT, _U64, _U64, _P, _P],
     "hkv_size": [_P, _P, ctypes.POINTER(_U64)],
     "hkv_load_factor": [_P, _P, ctypes.POINTER(ctypes.c_float)],
+    "hkv_shard_partition": [_U64, _P, ctypes.c_uint32, _P, _P, _P, _P, _P, _P],
+    "hkv_shard_gather_rows": [_U64, _U64, _P, _P, _P, _P],
+    "hkv_shard_scatter_rows": [_U64, _U64, _P, _P, _P, _P],
+    "hkv_shard_last_error": [],
+    "hkv_accum_or_assign_unique": [_P, _U64, _P, _P, _P, _P, _P, _INT],
     "hkv_size_no_alloc": [_P, _P, ctypes.POINTER(_U64)],
     "hkv_size_no_alloc_last_error": [],
     "hkv_capacity": [_P],
@@ -175,6 +180,7 @@ _RESTYPES = {
     "hkv_max_bucket_size": _U64,
     "hkv_last_error": ctypes.c_char_p,
     "hkv_size_no_alloc_last_error": ctypes.c_char_p,
+    "hkv_shard_last_error": ctypes.c_char_p,
 }
 
 
@@ -317,6 +323,13 @@ class HashTable:
     def accum_or_assign(self, n, keys, value_or_deltas, accum_or_assigns, scores=None,
                         stream=None, ignore_evict_strategy=False) -> None:
         self._call("hkv_accum_or_assign", n, _ptr(keys), _ptr(value_or_deltas),
+                   _ptr(accum_or_assigns), _ptr(scores), _stream(stream),
+                   int(ignore_evict_strategy))
+
+    def accum_or_assign_unique(self, n, keys, value_or_deltas, accum_or_assigns, scores=None,
+                               stream=None, ignore_evict_strategy=False) -> None:
+        """accum_or_assign for batches that hold each key once (hkv_accum_or_assign_unique)."""
+        self._call("hkv_accum_or_assign_unique", n, _ptr(keys), _ptr(value_or_deltas),
                    _ptr(accum_or_assigns), _ptr(scores), _stream(stream),
                    int(ignore_evict_strategy))
 

@@ -273,6 +273,37 @@ HKV_API int hkv_get_view(const hkv_table* table, hkv_table_view* view);
 HKV_API int hkv_external_begin(hkv_table* table, int group, hkv_stream stream);
 HKV_API int hkv_external_end(hkv_table* table, int group, hkv_stream stream);
 
+/* ---- key-hash sharding across GPUs ------------------------------------------
+ * No counterpart in the reference, which is a single-GPU library: its users
+ * shard by hand, one table per GPU.  owner(key) = Murmur3(key) % world, the
+ * hash being the table's own (include/merlin/utils.cuh:137-145).  The helpers
+ * below are pure device work on the caller's stream; the exchange between
+ * ranks (NCCL all-to-all) is done by the caller. */
+
+/* Groups a batch by owner rank.  d_counts[world] receives the keys per owner,
+ * d_offsets[world] their exclusive prefix sum, grouped_keys[n] the keys owner
+ * by owner, origin[n] the batch index each grouped key came from.
+ * d_cursors[world] is scratch.  All pointers are device memory. */
+HKV_API int hkv_shard_partition(uint64_t n, const uint64_t* keys, uint32_t world,
+                                uint64_t* d_counts, uint64_t* d_offsets, uint64_t* d_cursors,
+                                uint64_t* grouped_keys, uint32_t* origin, hkv_stream stream);
+/* dst[i] = src[index[i]] for rows of row_bytes bytes */
+HKV_API int hkv_shard_gather_rows(uint64_t n, uint64_t row_bytes, const void* src_rows,
+                                  const uint32_t* index, void* dst_rows, hkv_stream stream);
+/* dst[index[i]] = src[i]; rows whose index is 0xFFFFFFFF are skipped */
+HKV_API int hkv_shard_scatter_rows(uint64_t n, uint64_t row_bytes, const void* src_rows,
+                                   const uint32_t* index, void* dst_rows, hkv_stream stream);
+HKV_API const char* hkv_shard_last_error(void);
+
+/* hkv_accum_or_assign for batches the caller guarantees to hold each key once
+ * (the sharded table de-duplicates before routing): runs the probe kernel the
+ * other insert-like operations use instead of the reference's key-scanning
+ * tile kernel (include/merlin/core_kernels/accum_or_assign.cuh:83-174). */
+HKV_API int hkv_accum_or_assign_unique(hkv_table* table, uint64_t n, const uint64_t* keys,
+                                       const void* value_or_deltas, const bool* accum_or_assigns,
+                                       const uint64_t* scores, hkv_stream stream,
+                                       int ignore_evict_strategy);
+
 /* Device status word: bit 0 a bounded slot wait ran out, bit 1 eviction
  * retries ran out.  Reading it synchronises the stream; it is cleared by the
  * read.  (The reference spins without bound in these places:

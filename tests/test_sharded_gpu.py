@@ -1,0 +1,171 @@
+"""The sharding helpers and the sharded table on GPUs: router kernels against
+numpy on one GPU, a world of one rank against the plain table, and (when the
+box has two or more GPUs) two NCCL ranks against one global CPU oracle."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from tests.hkv_testlib import OracleTable, fmix64, to_dev, to_np_u64, unique_keys, values_for  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8, 64])
+@pytest.mark.parametrize("n", [1, 255, 256, 100003])
+def test_partition_groups_keys_by_owner(world, n):
+    from hierarchicalkv_b200.sharded import CudaOps
+
+    ops = CudaOps()
+    keys = unique_keys(n, seed=n + world)
+    counts, grouped, origin = ops.partition(to_dev(keys), world)
+    owner = (fmix64(keys) % np.uint64(world)).astype(np.int64)
+    assert counts == np.bincount(owner, minlength=world).tolist()
+    g = to_np_u64(grouped)
+    o = origin.cpu().numpy().astype(np.int64)
+    np.testing.assert_array_equal(keys[o], g)                 # origin points at the key's place
+    assert np.unique(o).size == n                              # a permutation
+    bounds = np.concatenate([[0], np.cumsum(counts)])
+    for r in range(world):
+        seg = g[bounds[r]:bounds[r + 1]]
+        assert np.all((fmix64(seg) % np.uint64(world)) == r)
+
+
+@pytest.mark.parametrize("shape,dtype", [((1000, 64), torch.float32), ((1000, 3), torch.float32),
+                                         ((777,), torch.uint8), ((513,), torch.int64)])
+def test_gather_and_scatter_rows(shape, dtype):
+    from hierarchicalkv_b200.sharded import CudaOps
+
+    ops = CudaOps()
+    n = shape[0]
+    rng = np.random.default_rng(1)
+    src = torch.from_numpy(rng.integers(0, 100, size=shape)).to(dtype).cuda()
+    perm = torch.from_numpy(rng.permutation(n).astype(np.int32)).cuda()
+    got = ops.gather_rows(src, perm)
+    torch.cuda.synchronize()
+    assert torch.equal(got, src[perm.long()])
+    dst = torch.zeros_like(src)
+    ops.scatter_rows(src, perm, dst)
+    torch.cuda.synchronize()
+    want = torch.zeros_like(src)
+    want[perm.long()] = src
+    assert torch.equal(dst, want)
+    # rows with index -1 are skipped
+    masked = perm.clone()
+    masked[::3] = -1
+    dst.fill_(7)
+    ops.scatter_rows(src, masked, dst)
+    torch.cuda.synchronize()
+    want = torch.full_like(src, 7)
+    keep = masked >= 0
+    want[masked[keep].long()] = src[keep]
+    assert torch.equal(dst, want)
+
+
+def test_world_of_one_is_the_local_table():
+    import hierarchicalkv_b200 as hkv
+    from hierarchicalkv_b200.sharded import ShardedHashTable
+
+    t = hkv.HashTable(hkv.EvictStrategy.kCustomized)
+    t.init(hkv.HashTableOptions(init_capacity=128 * 64, max_capacity=128 * 64,
+                                max_hbm_for_vectors=1 << 30, dim=8))
+    st = ShardedHashTable(t)
+    assert st.world == 1
+    keys = unique_keys(3000, seed=2)
+    k, v = to_dev(keys[:2000]), to_dev(values_for(keys[:2000], 8))
+    s = to_dev(np.arange(1, 2001, dtype=np.uint64))
+    st.insert_or_assign(2000, k, v, s)
+    q = to_dev(keys)
+    out = torch.zeros((3000, 8), device="cuda")
+    f = torch.zeros(3000, dtype=torch.bool, device="cuda")
+    st.find(3000, q, out, f)
+    torch.cuda.synchronize()
+    assert f[:2000].all() and not f[2000:].any() and st.size() == 2000
+    assert torch.equal(out[:2000], v)
+    t.close()
+
+
+def _nccl_worker(rank, world, port, dim, cap):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch.distributed as dist
+
+    import hierarchicalkv_b200 as hkv
+    from hierarchicalkv_b200.sharded import ShardedHashTable
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    t = hkv.HashTable(hkv.EvictStrategy.kCustomized)
+    t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                dim=dim))
+    st = ShardedHashTable(t)
+    keys = unique_keys(40000, seed=55)
+    glob = OracleTable(cap * world, dim, 4)
+    # every rank inserts its own slice; the global oracle sees them in rank order
+    per = 8000
+    for r in range(world):
+        kk = keys[r * per:(r + 1) * per]
+        glob.insert_or_assign(kk, values_for(kk, dim, seed=r),
+                              np.arange(1, per + 1, dtype=np.uint64) + np.uint64(r * 100000))
+    mine = keys[rank * per:(rank + 1) * per]
+    st.insert_or_assign(per, to_dev(mine), to_dev(values_for(mine, dim, seed=rank)),
+                        to_dev(np.arange(1, per + 1, dtype=np.uint64) + np.uint64(rank * 100000)))
+    torch.cuda.synchronize()
+    assert st.size() == glob.size()
+    q = keys[: world * per + 3000]
+    out = torch.full((q.size, dim), -3.0, device="cuda")
+    f = torch.zeros(q.size, dtype=torch.bool, device="cuda")
+    sc = torch.zeros(q.size, dtype=torch.int64, device="cuda")
+    st.find(q.size, to_dev(q), out, f, sc)
+    torch.cuda.synchronize()
+    ev, ef, es = glob.find(q)
+    assert np.array_equal(f.cpu().numpy(), ef)
+    assert np.array_equal(out.cpu().numpy()[ef], ev[ef])
+    assert np.all(out.cpu().numpy()[~ef] == -3.0)
+    assert np.array_equal(to_np_u64(sc)[ef], es[ef])
+    # find_or_insert with keys both ranks ask for, then accum_or_assign of deltas
+    shared = keys[world * per: world * per + 2000]
+    rows = to_dev(values_for(shared, dim, seed=70 + rank))
+    st.find_or_insert(shared.size, to_dev(shared), rows,
+                      to_dev(np.arange(1, shared.size + 1, dtype=np.uint64) + np.uint64(900000)))
+    torch.cuda.synchronize()
+    # the lowest rank's row is stored and returned to everybody
+    assert np.array_equal(rows.cpu().numpy(), values_for(shared, dim, seed=70))
+    deltas = values_for(shared, dim, seed=80 + rank)
+    st.accum_or_assign(shared.size, to_dev(shared), to_dev(deltas),
+                       to_dev(np.ones(shared.size, dtype=np.bool_)),
+                       to_dev(np.arange(1, shared.size + 1, dtype=np.uint64) + np.uint64(950000)))
+    torch.cuda.synchronize()
+    want = values_for(shared, dim, seed=70).copy()
+    acc = np.zeros_like(want)
+    for r in range(world):
+        acc = acc + values_for(shared, dim, seed=80 + r)      # rank order
+    want = want + acc
+    out = torch.zeros((shared.size, dim), device="cuda")
+    f = torch.zeros(shared.size, dtype=torch.bool, device="cuda")
+    st.find(shared.size, to_dev(shared), out, f)
+    torch.cuda.synchronize()
+    assert bool(f.all())
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.astype(np.float32).view(np.uint32))
+    dist.barrier()
+    t.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_nccl_ranks_match_one_global_oracle():
+    import torch.multiprocessing as mp
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_nccl_worker, args=(2, port, 8, 128 * 256), nprocs=2, join=True)
