@@ -387,6 +387,8 @@ def main():
     ap.add_argument("--load-factor", type=float, default=1.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ops", action="store_true", help="skip the secondary operations")
+    ap.add_argument("--nccl-routing", action="store_true",
+                    help="N > 1: route with NCCL all-to-all instead of the fused peer-memory kernels")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -454,8 +456,20 @@ def main():
     out_vals = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
     founds = torch.empty(batch, dtype=torch.bool, device="cuda")
 
+    fused = False
+    if sharded is not None and not args.nccl_routing:
+        try:
+            ws = sharded.enable_fused_find(batch, dim)
+            out_vals, founds = ws.out_values, ws.out_founds     # results land in peer-visible buffers
+            fused = True
+        except Exception as e:  # no peer mappings on this box: route with NCCL instead
+            if rank == 0:
+                print(f"fused routing unavailable ({e}); using NCCL all-to-all", file=sys.stderr)
+
     def do_find(keys):
-        if sharded is not None:
+        if fused:
+            sharded.find_fused(batch, keys)
+        elif sharded is not None:
             sharded.find(batch, keys, out_vals, founds)
         else:
             arm.find(keys, out_vals, founds)
@@ -585,7 +599,10 @@ def main():
             "keys_inserted_to_fill": inserted,
             "l2": "inputs larger than L2: %.1f GiB of rows hit at random, %d rotating query batches, %d MiB output buffer" % (capacity * row / 2**30, n_query_sets, batch * row >> 20),
             "sharding": ("key-hash sharded, owner = Murmur3(key) % N, one shard of this size per GPU; "
-                         "every batch routed by NCCL all-to-all: keys out, rows and flags back")
+                         + ("every batch routed over peer memory: keys stored into the owners' inboxes, "
+                            "hit rows stored by the lookup kernel into the requester's buffer (NVLink)"
+                            if fused else
+                            "every batch routed by NCCL all-to-all: keys out, rows and flags back"))
             if world > 1 else ("single table" if launched_world == 1 else
                                "single-GPU reference measured on rank 0 (it has no multi-GPU path)"),
         },
@@ -594,7 +611,9 @@ def main():
                 "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * row + batch,
                 "steps": e2e_steps},
         # N > 1: count, offsets and place kernels of the router, the lookup, three row scatters
-        "gpu_launches": args.steps * (arm.launches_per_find + (6 if world > 1 else 0)),
+        # fused: route, publish counts, barrier, lookup, barrier
+        "gpu_launches": args.steps * ((5 if fused else arm.launches_per_find + 6) if world > 1
+                                      else arm.launches_per_find),
         "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peak,
                      "unit": "GB/s", "frac": round(achieved_gbs / peak, 4),
                      "traffic": None, "peak_source": peak_src,

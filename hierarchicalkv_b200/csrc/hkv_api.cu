@@ -707,6 +707,29 @@ int hkv_find_and_update(hkv_table* t, uint64_t n, const uint64_t* keys, void** v
   });
 }
 
+int hkv_find_routed(hkv_table* t, uint32_t world, uint64_t segment_capacity,
+                    const uint64_t* inbox_keys, const uint32_t* inbox_origin,
+                    const uint64_t* inbox_counts, const hkv_peer_ptrs* out_values,
+                    const hkv_peer_ptrs* out_founds, hkv_stream stream) {
+  return guarded([&] {
+    if (world == 0 || world > hkv::kMaxPeers) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "world size must be between 1 and 16"};
+    }
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    hkv::PeerPtrs ov{}, of{};
+    for (uint32_t r = 0; r < world; ++r) {
+      ov.p[r] = out_values->p[r];
+      of.p[r] = out_founds->p[r];
+    }
+    LockScope ls(t, kReader, s);
+    hkv::launch_find_routed(t->view, world, segment_capacity, inbox_keys, inbox_origin,
+                            inbox_counts, ov, of, s);
+    ls.done();
+    check_launch();
+  });
+}
+
 int hkv_contains(hkv_table* t, uint64_t n, const uint64_t* keys, bool* founds, hkv_stream stream) {
   return guarded([&] {
     if (n == 0) return;

@@ -296,6 +296,57 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
   }
 }
 
+// Gather variant whose destination is not a contiguous batch: lane r holds the
+// table slot of row r (or kNoSlot) and the row index `dest_row` it goes to in
+// `dest_base` (possibly another GPU's memory, written with plain stores).
+template <int VEC>
+__device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint8_t* dest_base,
+                                                        uint32_t dest_row, uint32_t slot,
+                                                        uint32_t lane) {
+  using T = typename VecType<VEC>::type;
+  constexpr int U = (VEC == 16) ? 8 : 4;
+  const uint32_t cpr = t.chunks_per_row;
+  const int32_t shift = t.chunks_per_row_shift;
+  const uint32_t total = cpr * 32u;
+  for (uint32_t base = 0; base < total; base += 32u * U) {
+    T regs[U];
+    uint32_t drow[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t c = base + u * 32u + lane;
+      const uint32_t r = shift >= 0 ? (c >> shift) : (c / cpr);
+      const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r & 31u);
+      const uint32_t d = __shfl_sync(0xFFFFFFFFu, dest_row, r & 31u);
+      drow[u] = kNoSlot;
+      if (c < total && s != kNoSlot) {
+        regs[u] = ld_stream(reinterpret_cast<const T*>(row_ptr(t, s) + (c - r * cpr) * VEC));
+        drow[u] = d;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (drow[u] != kNoSlot) {
+        const uint32_t c = base + u * 32u + lane;
+        const uint32_t r = shift >= 0 ? (c >> shift) : (c / cpr);
+        *reinterpret_cast<T*>(dest_base + uint64_t(drow[u]) * t.row_bytes + (c - r * cpr) * VEC) =
+            regs[u];
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void warp_gather_rows_to(const TableView& t, uint8_t* dest_base,
+                                                    uint32_t dest_row, uint32_t slot,
+                                                    uint32_t lane) {
+  switch (t.vec_bytes) {
+    case 16: warp_gather_rows_to_vec<16>(t, dest_base, dest_row, slot, lane); break;
+    case 8: warp_gather_rows_to_vec<8>(t, dest_base, dest_row, slot, lane); break;
+    case 4: warp_gather_rows_to_vec<4>(t, dest_base, dest_row, slot, lane); break;
+    case 2: warp_gather_rows_to_vec<2>(t, dest_base, dest_row, slot, lane); break;
+    default: warp_gather_rows_to_vec<1>(t, dest_base, dest_row, slot, lane); break;
+  }
+}
+
 template <int MODE>
 __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
                                                uint32_t slot, uint32_t lane) {

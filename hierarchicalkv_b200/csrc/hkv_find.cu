@@ -136,6 +136,50 @@ __global__ void __launch_bounds__(kFindBlock)
   }
 }
 
+// find for the key-hash sharded table: this rank is the owner, the keys came
+// from `world` source ranks (one inbox segment each), and every hit row goes
+// directly to the source rank's result buffer over NVLink (plain peer stores)
+// while the next buckets are being probed -- lookup and transfer are one kernel.
+__global__ void __launch_bounds__(kFindBlock)
+    find_routed_kernel(const TableView t, const uint32_t blocks_per_segment,
+                       const uint64_t segment_capacity, const uint64_t* __restrict__ inbox_keys,
+                       const uint32_t* __restrict__ inbox_origin,
+                       const uint64_t* __restrict__ inbox_counts, const PeerPtrs out_values,
+                       const PeerPtrs out_founds) {
+  // The key counts are only known on the device, so the grid covers every
+  // segment's full capacity and blocks beyond a segment's count leave at once.
+  const ProbeLane pl = probe_lane();
+  const uint32_t seg = blockIdx.x / blocks_per_segment;
+  const uint64_t base =
+      uint64_t(blockIdx.x - seg * blocks_per_segment) * kFindBlock + (threadIdx.x & ~31u);
+  const uint64_t count = inbox_counts[seg];
+  if (base >= count) return;
+  uint8_t* values_of = nullptr;
+  uint8_t* founds_of = nullptr;
+#pragma unroll
+  for (int s = 0; s < kMaxPeers; ++s) {
+    if (uint32_t(s) == seg) {
+      values_of = static_cast<uint8_t*>(out_values.p[s]);
+      founds_of = static_cast<uint8_t*>(out_founds.p[s]);
+    }
+  }
+  const uint64_t in_seg = base + pl.lane;
+  const bool present = in_seg < count;
+  uint64_t key = 0;
+  uint32_t origin = 0;
+  bool valid = false;
+  if (present) {
+    key = inbox_keys[seg * segment_capacity + in_seg];
+    origin = inbox_origin[seg * segment_capacity + in_seg];
+    valid = !is_reserved(t, key);
+  }
+  Address a{0, 0, 0};
+  if (valid) a = locate(t, key);
+  const uint32_t slot = warp_probe_readonly(t, pl, key, valid, a);
+  if (present) founds_of[origin] = slot != kNoSlot ? 1 : 0;
+  warp_gather_rows_to(t, values_of, origin, slot, pl.lane);
+}
+
 template <int FORM>
 void launch_form(const TableView& t, uint64_t n, const uint64_t* keys, void* values, void** ptrs,
                  bool* founds, uint64_t* scores, uint64_t* missed_keys, int* missed_indices,
@@ -165,6 +209,17 @@ void launch_find_missed(const TableView& t, uint64_t n, const uint64_t* keys, vo
                         uint64_t* scores, cudaStream_t stream) {
   launch_form<2>(t, n, keys, values, nullptr, nullptr, scores, missed_keys, missed_indices,
                  missed_size, stream);
+}
+
+void launch_find_routed(const TableView& t, uint32_t world, uint64_t segment_capacity,
+                        const uint64_t* inbox_keys, const uint32_t* inbox_origin,
+                        const uint64_t* inbox_counts, const PeerPtrs& out_values,
+                        const PeerPtrs& out_founds, cudaStream_t stream) {
+  if (segment_capacity == 0) return;
+  const uint64_t per_segment = (segment_capacity + kFindBlock - 1) / kFindBlock;
+  find_routed_kernel<<<static_cast<unsigned>(per_segment * world), kFindBlock, 0, stream>>>(
+      t, static_cast<uint32_t>(per_segment), segment_capacity, inbox_keys, inbox_origin,
+      inbox_counts, out_values, out_founds);
 }
 
 void launch_contains(const TableView& t, uint64_t n, const uint64_t* keys, bool* founds,

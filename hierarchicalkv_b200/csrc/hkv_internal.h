@@ -50,6 +50,21 @@ void launch_find_missed(const TableView& t, uint64_t n, const uint64_t* keys, vo
 void launch_contains(const TableView& t, uint64_t n, const uint64_t* keys, bool* founds,
                      cudaStream_t stream);
 
+// Peer buffers of the sharded table, one pointer per rank (world <= kMaxPeers).
+constexpr int kMaxPeers = 16;
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+// find over an inbox of keys that arrived from `world` source ranks: segment s
+// holds inbox_counts[s] keys and, for each, the row index it came from in the
+// source's batch.  Hit rows and found flags are stored straight into the
+// source rank's result buffers.
+void launch_find_routed(const TableView& t, uint32_t world, uint64_t segment_capacity,
+                        const uint64_t* inbox_keys, const uint32_t* inbox_origin,
+                        const uint64_t* inbox_counts, const PeerPtrs& out_values,
+                        const PeerPtrs& out_founds, cudaStream_t stream);
+
 // unique_key == false selects the serialising kernel that tolerates repeated
 // keys inside one batch.
 void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool unique_key,

@@ -87,6 +87,81 @@ __global__ void __launch_bounds__(kBlock)
   }
 }
 
+struct Peers {
+  void* p[16];
+};
+
+// Groups a batch by owner and stores every key, with the index it has in the
+// batch, straight into the owner rank's inbox (segment `my_rank` of it).
+__global__ void __launch_bounds__(kBlock)
+    route_p2p_kernel(const uint64_t* __restrict__ keys, uint64_t n, uint32_t world,
+                     uint32_t my_rank, uint64_t segment_capacity,
+                     unsigned long long* __restrict__ cursors, const Peers inbox_keys,
+                     const Peers inbox_origin) {
+  __shared__ uint32_t local[kMaxWorld];
+  __shared__ unsigned long long base[kMaxWorld];
+  const uint64_t tiles = (n + kBlock - 1) / kBlock;
+  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    if (threadIdx.x < kMaxWorld) local[threadIdx.x] = 0;
+    __syncthreads();
+    const uint64_t i = tile * kBlock + threadIdx.x;
+    uint64_t key = 0;
+    uint32_t owner = 0, rank = 0;
+    if (i < n) {
+      key = keys[i];
+      owner = owner_of(key, world);
+      rank = atomicAdd(&local[owner], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x < world && local[threadIdx.x]) {
+      base[threadIdx.x] = atomicAdd(&cursors[threadIdx.x], (unsigned long long)local[threadIdx.x]);
+    }
+    __syncthreads();
+    if (i < n) {
+      const unsigned long long at = uint64_t(my_rank) * segment_capacity + base[owner] + rank;
+      static_cast<uint64_t*>(inbox_keys.p[owner])[at] = key;
+      static_cast<uint32_t*>(inbox_origin.p[owner])[at] = static_cast<uint32_t>(i);
+    }
+    __syncthreads();
+  }
+}
+
+// Tells every owner how many keys this rank put into its inbox.
+__global__ void publish_counts_kernel(const unsigned long long* cursors, uint32_t world,
+                                      uint32_t my_rank, const Peers inbox_counts) {
+  if (threadIdx.x < world) {
+    static_cast<unsigned long long*>(inbox_counts.p[threadIdx.x])[my_rank] = cursors[threadIdx.x];
+  }
+}
+
+// Barrier between the ranks of one node over peer memory.  Thread p raises
+// this rank's flag at peer p to `epoch` (system-scope release) and waits until
+// peer p has raised its flag here (system-scope acquire).  The wait is bounded:
+// when it runs out the kernel records kBarrierTimeout in *status and returns.
+constexpr uint32_t kBarrierTimeout = 1u;
+__global__ void barrier_kernel(uint32_t world, uint32_t my_rank, const Peers flags,
+                               uint32_t epoch, uint32_t* status, uint32_t max_polls) {
+  const uint32_t p = threadIdx.x;
+  if (p >= world) return;
+  uint32_t* theirs = static_cast<uint32_t*>(flags.p[p]) + my_rank;
+  uint32_t* mine = static_cast<uint32_t*>(flags.p[my_rank]) + p;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+  bool arrived = false;
+  for (uint32_t poll = 0; poll < max_polls; ++poll) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    // epochs only grow; a wrapped difference keeps the comparison valid
+    if (int32_t(seen - epoch) >= 0) {
+      arrived = true;
+      break;
+    }
+    __nanosleep(200);
+  }
+  if (!arrived) atomicOr(status, kBarrierTimeout);
+  __threadfence_system();
+}
+
 // MODE 0: dst[i] = src[index[i]]   MODE 1: dst[index[i]] = src[i]
 template <int VEC, int MODE>
 __global__ void __launch_bounds__(kBlock)
@@ -170,6 +245,50 @@ int hkv_shard_partition(uint64_t n, const uint64_t* keys, uint32_t world, uint64
   offsets_kernel<<<1, 32, 0, s>>>(counts, world, offsets, cursors);
   if (n > 0) place_kernel<<<grid_for(n), kBlock, 0, s>>>(keys, n, world, cursors, grouped_keys, origin);
   e = cudaGetLastError();
+  if (e != cudaSuccess) return shard_fail(HKV_ERR_CUDA, cudaGetErrorString(e));
+  return HKV_OK;
+}
+
+int hkv_shard_route_keys_p2p(uint64_t n, const uint64_t* keys, uint32_t world, uint32_t my_rank,
+                             uint64_t segment_capacity, const hkv_peer_ptrs* inbox_keys,
+                             const hkv_peer_ptrs* inbox_origin, const hkv_peer_ptrs* inbox_counts,
+                             uint64_t* d_cursors, hkv_stream stream) {
+  if (world == 0 || world > 16 || my_rank >= world) {
+    return shard_fail(HKV_ERR_INVALID_ARG, "world size must be between 1 and 16");
+  }
+  if (n > segment_capacity || n >= (1ull << 32)) {
+    return shard_fail(HKV_ERR_INVALID_ARG, "batch larger than an inbox segment");
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Peers k{}, o{}, c{};
+  for (uint32_t r = 0; r < world; ++r) {
+    k.p[r] = inbox_keys->p[r];
+    o.p[r] = inbox_origin->p[r];
+    c.p[r] = inbox_counts->p[r];
+  }
+  cudaError_t e = cudaMemsetAsync(d_cursors, 0, sizeof(uint64_t) * world, s);
+  if (e != cudaSuccess) return shard_fail(HKV_ERR_CUDA, cudaGetErrorString(e));
+  auto* cursors = reinterpret_cast<unsigned long long*>(d_cursors);
+  if (n > 0) {
+    route_p2p_kernel<<<grid_for(n), kBlock, 0, s>>>(keys, n, world, my_rank, segment_capacity,
+                                                    cursors, k, o);
+  }
+  publish_counts_kernel<<<1, 32, 0, s>>>(cursors, world, my_rank, c);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return shard_fail(HKV_ERR_CUDA, cudaGetErrorString(e));
+  return HKV_OK;
+}
+
+int hkv_shard_barrier(uint32_t world, uint32_t my_rank, const hkv_peer_ptrs* flags, uint32_t epoch,
+                      uint32_t* d_status, uint32_t max_polls, hkv_stream stream) {
+  if (world == 0 || world > 16 || my_rank >= world) {
+    return shard_fail(HKV_ERR_INVALID_ARG, "world size must be between 1 and 16");
+  }
+  Peers f{};
+  for (uint32_t r = 0; r < world; ++r) f.p[r] = flags->p[r];
+  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(world, my_rank, f, epoch,
+                                                                  d_status, max_polls);
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return shard_fail(HKV_ERR_CUDA, cudaGetErrorString(e));
   return HKV_OK;
 }

@@ -66,6 +66,70 @@ class CudaOps:
                                                   dst.data_ptr(), _stream_ptr()))
 
 
+class _PeerPtrs(ctypes.Structure):
+    """hkv_peer_ptrs"""
+
+    _fields_ = [("p", ctypes.c_void_p * 16)]
+
+
+class PeerWorkspace:
+    """Buffers every rank of the node can store into (torch symmetric memory,
+    i.e. CUDA peer mappings over NVLink): each rank's inbox of routed keys and
+    its result buffers.  Used by ShardedHashTable.find_fused."""
+
+    MAX_WORLD = 16
+
+    def __init__(self, group, max_batch: int, dim: int, dtype: torch.dtype = torch.float32):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > self.MAX_WORLD:
+            raise ValueError("at most 16 ranks")
+        self.max_batch = max_batch
+        self.dim = dim
+        self.dtype = dtype
+        row_bytes = dim * torch.empty((), dtype=dtype).element_size()
+        self.row_bytes = row_bytes
+
+        def up(x):
+            return (x + 255) // 256 * 256
+
+        off = {}
+        at = 0
+        for name, size in (("inbox_keys", self.world * max_batch * 8),
+                           ("inbox_origin", self.world * max_batch * 4),
+                           ("inbox_counts", 16 * 8), ("flags", 16 * 4),
+                           ("out_founds", max_batch), ("out_values", max_batch * row_bytes)):
+            off[name] = at
+            at = up(at + size)
+        self.offsets = off
+        self.buf = symm.empty(at, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        torch.cuda.synchronize()
+        dist.barrier(group)                       # every rank's flags are zero before the first use
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        self.peers = {}
+        for name in off:
+            pp = _PeerPtrs()
+            for r in range(self.world):
+                pp.p[r] = bases[r] + off[name]
+            self.peers[name] = pp
+        self.local = {name: bases[self.rank] + off[name] for name in off}
+        self.scratch = torch.zeros(32, dtype=torch.int64, device="cuda")   # cursors | status
+        self.epoch = 0
+        # views of this rank's result buffers
+        ov = self.buf[off["out_values"]: off["out_values"] + max_batch * row_bytes]
+        self.out_values = ov.view(dtype).view(max_batch, dim)
+        self.out_founds = self.buf[off["out_founds"]: off["out_founds"] + max_batch].view(torch.bool)
+
+    def status(self) -> int:
+        """Non-zero after a barrier timed out (a peer never arrived)."""
+        return int(self.scratch[16].item())
+
+
 class _Route:
     """How one batch travels: who gets how many keys, and the way back."""
 
@@ -173,6 +237,48 @@ class ShardedHashTable:
         if scores is not None:
             sc_back = self._all_to_all(sc, route.recv_counts, route.send_counts)
             self.ops.scatter_rows(sc_back, where, scores)
+
+    def enable_fused_find(self, max_batch: int, dim: int, dtype: torch.dtype = torch.float32):
+        """Allocates the peer-visible inbox and result buffers find_fused needs."""
+        self.peer = PeerWorkspace(self.group, max_batch, dim, dtype)
+        return self.peer
+
+    def find_fused(self, n, keys, max_polls: int = 50_000_000):
+        """HashTable::find over all shards with lookup and transfer fused: keys
+        are grouped by owner and stored straight into the owners' inboxes, every
+        owner runs ONE lookup kernel over what arrived and stores hit rows and
+        found flags straight into the requesters' result buffers over NVLink.
+        No NCCL call and no host synchronisation; two bounded peer barriers.
+        Returns views (rows, found flags) of this rank's result buffers, valid
+        until the next call; rows of misses keep their previous content."""
+        w = self.peer
+        lib = self.ops.lib
+        sp = _stream_ptr()
+        if n > w.max_batch:
+            raise ValueError("batch larger than the workspace")
+
+        def chk(rc):
+            if rc:
+                raise RuntimeError((lib.hkv_shard_last_error() or b"").decode())
+
+        chk(lib.hkv_shard_route_keys_p2p(n, keys.data_ptr(), self.world, self.rank, w.max_batch,
+                                         ctypes.byref(w.peers["inbox_keys"]),
+                                         ctypes.byref(w.peers["inbox_origin"]),
+                                         ctypes.byref(w.peers["inbox_counts"]),
+                                         w.scratch.data_ptr(), sp))
+        w.epoch += 1
+        chk(lib.hkv_shard_barrier(self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
+                                  w.scratch[16:].data_ptr(), max_polls, sp))
+        rc = lib.hkv_find_routed(self.local.handle, self.world, w.max_batch,
+                                 w.local["inbox_keys"], w.local["inbox_origin"],
+                                 w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
+                                 ctypes.byref(w.peers["out_founds"]), sp)
+        if rc:
+            raise RuntimeError((lib.hkv_last_error() or b"").decode())
+        w.epoch += 1
+        chk(lib.hkv_shard_barrier(self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
+                                  w.scratch[16:].data_ptr(), max_polls, sp))
+        return w.out_values[:n], w.out_founds[:n]
 
     def insert_or_assign(self, n, keys, values, scores=None, stream=None) -> None:
         if n == 0:

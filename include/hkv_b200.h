@@ -295,6 +295,40 @@ HKV_API int hkv_shard_scatter_rows(uint64_t n, uint64_t row_bytes, const void* s
                                    const uint32_t* index, void* dst_rows, hkv_stream stream);
 HKV_API const char* hkv_shard_last_error(void);
 
+/* Peer buffers of the ranks of one node: p[r] is rank r's buffer, mapped into
+ * this process (CUDA IPC / symmetric memory).  At most 16 ranks. */
+typedef struct hkv_peer_ptrs {
+  void* p[16];
+} hkv_peer_ptrs;
+
+/* Fused routing, no counterpart in the reference.  Every rank owns an inbox
+ * of `world` segments of `segment_capacity` entries: keys (uint64), origins
+ * (uint32) and one count per segment (uint64).  This call groups the batch by
+ * owner and stores each key and its batch index directly into segment
+ * `my_rank` of the owner's inbox over NVLink, then the counts.  d_cursors is
+ * world x uint64 of local scratch. */
+HKV_API int hkv_shard_route_keys_p2p(uint64_t n, const uint64_t* keys, uint32_t world,
+                                     uint32_t my_rank, uint64_t segment_capacity,
+                                     const hkv_peer_ptrs* inbox_keys,
+                                     const hkv_peer_ptrs* inbox_origin,
+                                     const hkv_peer_ptrs* inbox_counts, uint64_t* d_cursors,
+                                     hkv_stream stream);
+/* Barrier of the node's ranks on `stream` over peer flags (uint32[16] per
+ * rank, zero-initialised; `epoch` grows by one per call on every rank).  The
+ * wait is bounded by max_polls; a time-out sets bit 0 of *d_status instead
+ * of hanging. */
+HKV_API int hkv_shard_barrier(uint32_t world, uint32_t my_rank, const hkv_peer_ptrs* flags,
+                              uint32_t epoch, uint32_t* d_status, uint32_t max_polls,
+                              hkv_stream stream);
+/* HashTable::find (include/merlin_hashtable.cuh:2464-2577) for the owner side
+ * of the sharded table: looks up every key of this rank's inbox and stores
+ * hit rows and found flags straight into the requesting rank's result buffers
+ * (out_values->p[s], out_founds->p[s], indexed by the key's origin). */
+HKV_API int hkv_find_routed(hkv_table* table, uint32_t world, uint64_t segment_capacity,
+                            const uint64_t* inbox_keys, const uint32_t* inbox_origin,
+                            const uint64_t* inbox_counts, const hkv_peer_ptrs* out_values,
+                            const hkv_peer_ptrs* out_founds, hkv_stream stream);
+
 /* hkv_accum_or_assign for batches the caller guarantees to hold each key once
  * (the sharded table de-duplicates before routing): runs the probe kernel the
  * other insert-like operations use instead of the reference's key-scanning

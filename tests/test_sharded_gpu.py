@@ -155,6 +155,21 @@ def _nccl_worker(rank, world, port, dim, cap):
     torch.cuda.synchronize()
     assert bool(f.all())
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want.astype(np.float32).view(np.uint32))
+    # fused find: peer stores instead of NCCL, same answers
+    glob.insert_or_assign(shared, want.astype(np.float32),
+                          np.arange(1, shared.size + 1, dtype=np.uint64) + np.uint64(900000))
+    st.enable_fused_find(max_batch=q.size, dim=dim)
+    for rep in range(3):                      # repeated use of the same inboxes and result buffers
+        qq = np.roll(q, rep * 977)
+        st.peer.out_values.fill_(-3.0)
+        rows, flags = st.find_fused(qq.size, to_dev(qq))
+        torch.cuda.synchronize()
+        ev, ef, _ = glob.find(qq)
+        assert np.array_equal(flags.cpu().numpy(), ef)
+        got = rows.cpu().numpy()
+        assert np.array_equal(got[ef].view(np.uint32), ev[ef].view(np.uint32))
+        assert np.all(got[~ef] == -3.0)
+        assert st.peer.status() == 0
     dist.barrier()
     t.close()
     dist.destroy_process_group()
