@@ -707,12 +707,12 @@ int hkv_find_and_update(hkv_table* t, uint64_t n, const uint64_t* keys, void** v
   });
 }
 
-int hkv_find_routed(hkv_table* t, uint32_t world, uint64_t segment_capacity,
+int hkv_find_routed(hkv_table* t, uint32_t world, uint32_t my_rank, uint64_t segment_capacity,
                     const uint64_t* inbox_keys, const uint32_t* inbox_origin,
                     const uint64_t* inbox_counts, const hkv_peer_ptrs* out_values,
                     const hkv_peer_ptrs* out_founds, hkv_stream stream) {
   return guarded([&] {
-    if (world == 0 || world > hkv::kMaxPeers) {
+    if (world == 0 || world > hkv::kMaxPeers || my_rank >= world) {
       throw HkvError{HKV_ERR_INVALID_ARG, "world size must be between 1 and 16"};
     }
     DeviceGuard dg(t->device);
@@ -723,7 +723,7 @@ int hkv_find_routed(hkv_table* t, uint32_t world, uint64_t segment_capacity,
       of.p[r] = out_founds->p[r];
     }
     LockScope ls(t, kReader, s);
-    hkv::launch_find_routed(t->view, world, segment_capacity, inbox_keys, inbox_origin,
+    hkv::launch_find_routed(t->view, world, my_rank, segment_capacity, inbox_keys, inbox_origin,
                             inbox_counts, ov, of, s);
     ls.done();
     check_launch();

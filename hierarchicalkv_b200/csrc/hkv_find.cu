@@ -141,17 +141,22 @@ __global__ void __launch_bounds__(kFindBlock)
 // directly to the source rank's result buffer over NVLink (plain peer stores)
 // while the next buckets are being probed -- lookup and transfer are one kernel.
 __global__ void __launch_bounds__(kFindBlock)
-    find_routed_kernel(const TableView t, const uint32_t blocks_per_segment,
-                       const uint64_t segment_capacity, const uint64_t* __restrict__ inbox_keys,
+    find_routed_kernel(const TableView t, const uint32_t blocks_per_segment, const uint32_t world,
+                       const uint32_t first_segment, const uint64_t segment_capacity, const uint64_t* __restrict__ inbox_keys,
                        const uint32_t* __restrict__ inbox_origin,
                        const uint64_t* __restrict__ inbox_counts, const PeerPtrs out_values,
                        const PeerPtrs out_founds) {
   // The key counts are only known on the device, so the grid covers every
   // segment's full capacity and blocks beyond a segment's count leave at once.
   const ProbeLane pl = probe_lane();
-  const uint32_t seg = blockIdx.x / blocks_per_segment;
+  // Owners walk the source ranks in a rotated order (rank r starts with r + 1),
+  // so at any moment the owners store into different requesters instead of
+  // all converging on the same GPU's ingress.
+  const uint32_t turn = blockIdx.x / blocks_per_segment;
+  uint32_t seg = turn + first_segment;
+  seg = seg >= world ? seg - world : seg;
   const uint64_t base =
-      uint64_t(blockIdx.x - seg * blocks_per_segment) * kFindBlock + (threadIdx.x & ~31u);
+      uint64_t(blockIdx.x - turn * blocks_per_segment) * kFindBlock + (threadIdx.x & ~31u);
   const uint64_t count = inbox_counts[seg];
   if (base >= count) return;
   uint8_t* values_of = nullptr;
@@ -211,14 +216,16 @@ void launch_find_missed(const TableView& t, uint64_t n, const uint64_t* keys, vo
                  missed_size, stream);
 }
 
-void launch_find_routed(const TableView& t, uint32_t world, uint64_t segment_capacity,
+void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
+                        uint64_t segment_capacity,
                         const uint64_t* inbox_keys, const uint32_t* inbox_origin,
                         const uint64_t* inbox_counts, const PeerPtrs& out_values,
                         const PeerPtrs& out_founds, cudaStream_t stream) {
   if (segment_capacity == 0) return;
   const uint64_t per_segment = (segment_capacity + kFindBlock - 1) / kFindBlock;
   find_routed_kernel<<<static_cast<unsigned>(per_segment * world), kFindBlock, 0, stream>>>(
-      t, static_cast<uint32_t>(per_segment), segment_capacity, inbox_keys, inbox_origin,
+      t, static_cast<uint32_t>(per_segment), world, (my_rank + 1) % world, segment_capacity,
+      inbox_keys, inbox_origin,
       inbox_counts, out_values, out_founds);
 }
 

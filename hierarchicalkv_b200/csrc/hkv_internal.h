@@ -60,7 +60,8 @@ struct PeerPtrs {
 // holds inbox_counts[s] keys and, for each, the row index it came from in the
 // source's batch.  Hit rows and found flags are stored straight into the
 // source rank's result buffers.
-void launch_find_routed(const TableView& t, uint32_t world, uint64_t segment_capacity,
+void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
+                        uint64_t segment_capacity,
                         const uint64_t* inbox_keys, const uint32_t* inbox_origin,
                         const uint64_t* inbox_counts, const PeerPtrs& out_values,
                         const PeerPtrs& out_founds, cudaStream_t stream);

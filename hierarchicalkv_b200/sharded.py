@@ -269,7 +269,7 @@ class ShardedHashTable:
         w.epoch += 1
         chk(lib.hkv_shard_barrier(self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
                                   w.scratch[16:].data_ptr(), max_polls, sp))
-        rc = lib.hkv_find_routed(self.local.handle, self.world, w.max_batch,
+        rc = lib.hkv_find_routed(self.local.handle, self.world, self.rank, w.max_batch,
                                  w.local["inbox_keys"], w.local["inbox_origin"],
                                  w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
                                  ctypes.byref(w.peers["out_founds"]), sp)

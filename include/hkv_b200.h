@@ -324,7 +324,8 @@ HKV_API int hkv_shard_barrier(uint32_t world, uint32_t my_rank, const hkv_peer_p
  * of the sharded table: looks up every key of this rank's inbox and stores
  * hit rows and found flags straight into the requesting rank's result buffers
  * (out_values->p[s], out_founds->p[s], indexed by the key's origin). */
-HKV_API int hkv_find_routed(hkv_table* table, uint32_t world, uint64_t segment_capacity,
+HKV_API int hkv_find_routed(hkv_table* table, uint32_t world, uint32_t my_rank,
+                            uint64_t segment_capacity,
                             const uint64_t* inbox_keys, const uint32_t* inbox_origin,
                             const uint64_t* inbox_counts, const hkv_peer_ptrs* out_values,
                             const hkv_peer_ptrs* out_founds, hkv_stream stream);
