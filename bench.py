@@ -549,7 +549,8 @@ def main():
         # the reference benchmark's mix: 60 % present, 40 % new
         mixk = []
         for i in range(reps + 3):
-            cur = arm.export_keys(((i * 7919) % (capacity // 128 - 8 * batch // 128)) * 128, 8 * batch)
+            span = min(8 * batch, capacity)
+            cur = arm.export_keys(((i * 7919) % max(1, (capacity - span) // 128 + 1)) * 128, span)
             cur = cur[torch.randperm(cur.numel(), device="cuda")[: int(batch * 0.6)]]
             fresh = mixed_keys((1 << 54) + key_base + i * batch, batch - cur.numel(), "cuda")
             mixk.append(torch.cat([cur, fresh]).contiguous())

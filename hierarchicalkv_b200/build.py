@@ -54,7 +54,8 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     def compile_one(src: str) -> str:
         obj = os.path.join(objdir, os.path.basename(src) + ".o")
         if force or _stale(obj, [src] + hdrs):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+            extra = os.environ.get("HKV_EXTRA_NVCC_FLAGS", "").split()
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", src, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             r = subprocess.run(cmd, capture_output=True, text=True)

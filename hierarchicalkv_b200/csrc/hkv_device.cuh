@@ -144,6 +144,23 @@ __device__ __forceinline__ uint64_t cas_acquire(uint64_t* p, uint64_t expected,
   return old;
 }
 
+// Relaxed CAS: several of them can be in flight at once.  A thread that took a
+// lock this way issues one acquire fence (fence_acquire) before it touches what
+// the lock protects -- atomic followed by fence is the acquire pattern.
+__device__ __forceinline__ uint64_t cas_relaxed(uint64_t* p, uint64_t expected,
+                                                uint64_t desired) {
+  uint64_t old;
+  asm volatile("atom.relaxed.gpu.global.cas.b64 %0, [%1], %2, %3;"
+               : "=l"(old)
+               : "l"(p), "l"(expected), "l"(desired)
+               : "memory");
+  return old;
+}
+
+__device__ __forceinline__ void fence_acquire() {
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
+
 __device__ __forceinline__ void st_u8_cg(uint8_t* p, uint32_t v) {
   asm volatile("st.global.cg.u8 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

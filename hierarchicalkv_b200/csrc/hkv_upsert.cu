@@ -162,27 +162,37 @@ __device__ __forceinline__ constexpr bool op_writes_row_on_insert(int op) {
 
 // Minimum score of a full bucket and its first position, computed by the 8
 // lanes of a group from one coalesced 1-KiB read of the score line.
-__device__ __forceinline__ void group_min_score(const TableView& t, const ProbeLane& pl,
-                                                uint32_t bucket, uint64_t* gmin, uint32_t* gpos) {
-  const uint32_t gmask = group_mask(pl.group);
-  uint64_t s[16];
-  ld_scores16(t.scores + (uint64_t(bucket) << 7) + pl.sub * 16u, s);
-  uint64_t ms = s[0];
-  uint32_t mp = 0;
+__device__ __forceinline__ void lane_min16(const uint64_t (&s)[16], uint64_t* ms, uint32_t* mp) {
+  *ms = s[0];
+  *mp = 0;
 #pragma unroll
   for (int b = 1; b < 16; ++b) {
-    if (s[b] < ms) {
-      ms = s[b];
-      mp = b;
+    if (s[b] < *ms) {
+      *ms = s[b];
+      *mp = b;
     }
   }
+}
+
+__device__ __forceinline__ void group_reduce_min(uint32_t gmask, uint32_t sub, uint64_t ms,
+                                                 uint32_t mp, uint64_t* gmin, uint32_t* gpos) {
   const uint32_t hi = uint32_t(ms >> 32);
   const uint32_t ghi = __reduce_min_sync(gmask, hi);
   const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
   const uint32_t glo = __reduce_min_sync(gmask, lo);
-  const uint32_t cand = (hi == ghi && lo == glo) ? pl.sub * 16u + mp : 255u;
+  const uint32_t cand = (hi == ghi && lo == glo) ? sub * 16u + mp : 255u;
   *gpos = __reduce_min_sync(gmask, cand);
   *gmin = (uint64_t(ghi) << 32) | glo;
+}
+
+__device__ __forceinline__ void group_min_score(const TableView& t, const ProbeLane& pl,
+                                                uint32_t bucket, uint64_t* gmin, uint32_t* gpos) {
+  uint64_t s[16];
+  ld_scores16(t.scores + (uint64_t(bucket) << 7) + pl.sub * 16u, s);
+  uint64_t ms;
+  uint32_t mp;
+  lane_min16(s, &ms, &mp);
+  group_reduce_min(group_mask(pl.group), pl.sub, ms, mp, gmin, gpos);
 }
 
 // Copies one row with all 32 lanes (used for the few rows that do not follow
@@ -296,7 +306,7 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? 4 : 5)
         masks[j] = cand | (match16(dg[j], t.empty_digest4) << 16);
         if (cand) {
           uint64_t* kp = t.keys + (uint64_t(b) << 7) + pl.sub * 16u + (__ffs(cand) - 1);
-          first_key[j] = (m & kModeLockOnHit) ? cas_acquire(kp, want, t.locked_key)
+          first_key[j] = (m & kModeLockOnHit) ? cas_relaxed(kp, want, t.locked_key)
                                               : ld_relaxed(kp);
         }
       }
@@ -330,7 +340,7 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? 4 : 5)
             pos = pl.sub * 16u + (__ffs(m) - 1);
             m &= m - 1;
             uint64_t* kp = t.keys + slot0 + pos;
-            const uint64_t seen = lock_on_hit ? cas_acquire(kp, want, t.locked_key)
+            const uint64_t seen = lock_on_hit ? cas_relaxed(kp, want, t.locked_key)
                                               : ld_relaxed(kp);
             if (seen == want) {
               hit_pos = pos;
@@ -361,7 +371,7 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? 4 : 5)
           const uint32_t pos = (start + gd) & (kBucketSlots - 1);
           bool won = false;
           if (d == gd) {
-            won = cas_acquire(t.keys + slot0 + pos, t.empty_key, t.locked_key) == t.empty_key;
+            won = cas_relaxed(t.keys + slot0 + pos, t.empty_key, t.locked_key) == t.empty_key;
             em &= ~(1u << (pos & 15u));
           }
           if (__ballot_sync(gmask, won)) {
@@ -382,6 +392,9 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? 4 : 5)
   }
 
   // ---- phase 3: everything locked so far is written and published ---------------
+  // the locks above were taken with relaxed CAS so that they overlap; this is
+  // their acquire
+  fence_acquire();
   const bool keep_locked =
       (OP == kOpFindOrInsertPtr || OP == kOpLockKeys) && args.locked_key_ptrs != nullptr;
   {
@@ -432,6 +445,12 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? 4 : 5)
     uint32_t iterations = 0;
     while (pending) {
       const bool mine = (pending >> pl.lane) & 1u;
+#ifdef HKV_COUNT_ITERATIONS
+      if (pl.lane == 0) {
+        atomicAdd(t.status + 4, 1u);
+        atomicAdd(t.status + 5, __popc(pending));
+      }
+#endif
       if (++iterations > kEvictIterLimit) {
         if (mine) {
           my_result = kRefused;
