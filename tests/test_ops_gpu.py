@@ -450,3 +450,36 @@ def test_config2_shape_small_lru_survivors_match_reference():
     np.testing.assert_array_equal(pv, values_for(keys[-batch:], dim, seed=4))
     p.close()
     r.close()
+
+
+@pytest.mark.parametrize("offset,n", [(0, 1), (0, 255), (128, 1000), (130, 257), (128 * 40, 128 * 24),
+                                      (128 * 63 + 5, 10**9), (128 * 64, 10), (128 * 70, 128)])
+def test_export_batch_slot_windows(offset, n):
+    """export_batch walks slots [offset, offset + n): n and offset count slots,
+    the window is clamped to the capacity, a window past the end exports
+    nothing (include/merlin_hashtable.cuh:3111-3114, 3206-3212 of the reference).
+    Slot positions differ between implementations, so the window is checked
+    against the product's own full export."""
+    cap, dim = 128 * 64, 4
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(5000, seed=21)
+    t.insert_or_assign(keys, values_for(keys, dim), np.arange(1, keys.size + 1, dtype=np.uint64))
+    view = t.t.view()
+    import torch
+    from cuda.bindings import runtime as cudart
+
+    all_keys = np.zeros(cap, dtype=np.uint64)
+    cudart.cudaMemcpy(all_keys.ctypes.data, view.keys, cap * 8,
+                      cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+    lo, hi = min(offset, cap), min(offset + n, cap)
+    window = all_keys[lo:hi]
+    mask = np.uint64(0xFFFFFFFFFFFFFFFC)
+    want = np.sort(window[(window & mask) != mask])
+    k, v, s = t.export_batch(n=n, offset=offset)
+    np.testing.assert_array_equal(np.sort(k), want)
+    order = {int(kk): i for i, kk in enumerate(keys)}
+    for kk, vv, ss in zip(k[:50], v[:50], s[:50]):
+        i = order[int(kk)]
+        assert ss == i + 1
+        np.testing.assert_array_equal(vv, values_for(keys[i:i + 1], dim)[0])
+    t.close()
