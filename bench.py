@@ -120,6 +120,9 @@ class ProductArm:
         torch.cuda.synchronize()
         return k[: int(c.item())]
 
+    def export_batch(self, n, offset, counter, keys, values, scores):
+        self.t.export_batch(n, offset, counter, keys, values, scores)
+
     launches_per_find = 1
 
     def close(self):
@@ -194,6 +197,10 @@ class ReferenceArm:
                                             self._scratch_rows.data_ptr(), None, self._s()))
         torch.cuda.synchronize()
         return k[: int(c.item())]
+
+    def export_batch(self, n, offset, counter, keys, values, scores):
+        self._chk(self.lib.ref_export_batch(self.h, n, offset, counter.data_ptr(), keys.data_ptr(),
+                                            values.data_ptr(), scores.data_ptr(), self._s()))
 
     # memset of founds + lock kernel + lookup kernel + unlock kernel
     launches_per_find = 4
@@ -603,6 +610,18 @@ def main():
         t_ms = time_steps(lambda i: arm.find_or_insert(newk2[i], newv), reps, 3)
         ops["find_or_insert_all_new"] = {"b_kv_s": per_kv(t_ms, batch * reps),
                                          "achieved_gbs": UPSERT_EVICT_BYTES(row) * batch * reps / (t_ms / 1e3) / 1e9}
+        # export_batch of a window of slots, keys + rows + scores (every slot is live)
+        win = min(capacity, 8 << 20)
+        xk = torch.empty(win, dtype=torch.int64, device="cuda")
+        xs = torch.empty(win, dtype=torch.int64, device="cuda")
+        xv = torch.empty((win, dim), dtype=torch.float32, device="cuda")
+        xc = torch.zeros(1, dtype=torch.int64, device="cuda")
+        n_win = max(1, capacity // win)
+        t_ms = time_steps(lambda i: arm.export_batch(win, (i % n_win) * win, xc, xk, xv, xs), 5, 3)
+        exported = int(xc.item())
+        ops["export_batch"] = {"b_kv_s": per_kv(t_ms, win * 5),
+                               "achieved_gbs": (16 * win + (2 * row + 32) * exported) * 5 / (t_ms / 1e3) / 1e9}
+        del xk, xs, xv
         for v in ops.values():
             v["b_kv_s"] = round(v["b_kv_s"], 4)
             v["achieved_gbs"] = round(v["achieved_gbs"], 1)
