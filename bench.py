@@ -88,12 +88,12 @@ def rows_for(keys: torch.Tensor, dim: int) -> torch.Tensor:
 class ProductArm:
     name = "product"
 
-    def __init__(self, capacity: int, dim: int, hbm_bytes: int):
+    def __init__(self, capacity: int, dim: int, hbm_bytes: int, strategy: int = 0):
         import hierarchicalkv_b200 as hkv
         from hierarchicalkv_b200.build import build_library
 
         build_library()
-        self.t = hkv.HashTable(hkv.EvictStrategy.kLru)
+        self.t = hkv.HashTable(hkv.EvictStrategy(strategy))
         self.t.init(hkv.HashTableOptions(init_capacity=capacity, max_capacity=capacity,
                                          max_hbm_for_vectors=hbm_bytes, dim=dim))
         self.dim = dim
@@ -123,6 +123,15 @@ class ProductArm:
     def export_batch(self, n, offset, counter, keys, values, scores):
         self.t.export_batch(n, offset, counter, keys, values, scores)
 
+    def set_global_epoch(self, epoch):
+        self.t.set_global_epoch(epoch)
+
+    def insert_and_evict(self, keys, values, scores, ek, ev, es, counter):
+        self.t.insert_and_evict(keys.numel(), keys, values, scores, ek, ev, es, counter)
+
+    def export_if_score_below(self, threshold, n, counter, keys, values, scores):
+        self.t.export_batch_if(1, 0, threshold, n, 0, counter, keys, values, scores)
+
     launches_per_find = 1
 
     def close(self):
@@ -136,8 +145,8 @@ class ReferenceArm:
 
     name = "reference"
 
-    def __init__(self, capacity: int, dim: int, hbm_bytes: int):
-        path = os.path.join(ROOT, "oracle", "_ref", "libhkv_ref_s0.so")
+    def __init__(self, capacity: int, dim: int, hbm_bytes: int, strategy: int = 0):
+        path = os.path.join(ROOT, "oracle", "_ref", f"libhkv_ref_s{strategy}.so")
         if not os.path.exists(path):
             raise FileNotFoundError(path)
         self.lib = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
@@ -152,6 +161,9 @@ class ReferenceArm:
         self.lib.ref_size.argtypes = [P, P, ctypes.POINTER(U)]
         self.lib.ref_capacity.argtypes = [P, ctypes.POINTER(U)]
         self.lib.ref_destroy.argtypes = [P]
+        self.lib.ref_set_global_epoch.argtypes = [P, U]
+        self.lib.ref_insert_and_evict.argtypes = [P, U, P, P, P, P, P, P, P, P, ctypes.c_int]
+        self.lib.ref_export_batch_if.argtypes = [P, ctypes.c_int, U, U, U, U, P, P, P, P, P]
         self.h = P()
         self._chk(self.lib.ref_create(capacity, capacity, hbm_bytes, dim, 128, 0, 1,
                                       ctypes.byref(self.h)))
@@ -201,6 +213,20 @@ class ReferenceArm:
     def export_batch(self, n, offset, counter, keys, values, scores):
         self._chk(self.lib.ref_export_batch(self.h, n, offset, counter.data_ptr(), keys.data_ptr(),
                                             values.data_ptr(), scores.data_ptr(), self._s()))
+
+    def set_global_epoch(self, epoch):
+        self._chk(self.lib.ref_set_global_epoch(self.h, epoch))
+
+    def insert_and_evict(self, keys, values, scores, ek, ev, es, counter):
+        self._chk(self.lib.ref_insert_and_evict(self.h, keys.numel(), keys.data_ptr(),
+                                                values.data_ptr(), scores.data_ptr(), ek.data_ptr(),
+                                                ev.data_ptr(), es.data_ptr(), counter.data_ptr(),
+                                                self._s(), 1))
+
+    def export_if_score_below(self, threshold, n, counter, keys, values, scores):
+        self._chk(self.lib.ref_export_batch_if(self.h, 0, 0, threshold, n, 0, counter.data_ptr(),
+                                               keys.data_ptr(), values.data_ptr(),
+                                               scores.data_ptr(), self._s()))
 
     # memset of founds + lock kernel + lookup kernel + unlock kernel
     launches_per_find = 4
@@ -375,6 +401,70 @@ def hybrid_ops(arm_cls, batch: int, reps: int = 5) -> dict:
             "hit_rate": round(hits, 3),
             "table": f"capacity {capacity}, dim {dim}, load factor 0.5, 25 % of the rows in HBM, 75 % in pinned host memory",
             "queries": "Zipf(1.05) over the inserted keys, 10 % fresh keys; duplicates inside a batch kept"}
+
+
+def churn_ops(arm_cls, batch: int) -> dict:
+    """The churn / eviction table: capacity 32 Mi, dim 32 fp32, EpochLfu,
+    steady-state insert_and_evict at load factor 1.0 with batches that are 30 %
+    new keys (uniform in a 2^40 range) and 70 % resident keys, evicted tuples
+    returned; then export_batch_if with score < (epoch - 2) << 32 over the
+    whole table."""
+    capacity, dim = 32 << 20, 32
+    arm = arm_cls(capacity, dim, capacity * dim * 4 + (1 << 30), strategy=3)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(11)
+
+    def new_keys(counter, n):
+        k = _lsr(mixed_keys((1 << 57) + counter, n + n // 64, "cuda"), 24)   # 40-bit keys
+        return torch.unique(k)[:n].contiguous()
+
+    def freqs(n):
+        return torch.randint(1, 100, (n,), device="cuda", generator=g, dtype=torch.int64)
+
+    ek = torch.empty(batch, dtype=torch.int64, device="cuda")
+    es = torch.empty(batch, dtype=torch.int64, device="cuda")
+    ev = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+    cnt = torch.zeros(1, dtype=torch.int64, device="cuda")
+    epoch, drawn = 1, 0
+    arm.set_global_epoch(epoch)
+    while arm.size() < capacity * 0.999 and drawn < 2 * capacity:
+        k = new_keys(drawn, batch)
+        drawn += batch
+        cnt.zero_()
+        arm.insert_and_evict(k, rows_for(k, dim), freqs(k.numel()), ek, ev, es, cnt)
+    resident = arm.export_keys(0, 8 * batch)
+    reps = 10
+    batches = []
+    for i in range(reps + 3):
+        fresh = new_keys(drawn, int(batch * 0.3))
+        drawn += batch
+        old = resident[torch.randperm(resident.numel(), generator=g, device="cuda")[: batch - fresh.numel()]]
+        k = torch.unique(torch.cat([fresh, old]))
+        batches.append((k.contiguous(), rows_for(k, dim), freqs(k.numel())))
+
+    def step(i):
+        arm.set_global_epoch(epoch + 1 + i)
+        cnt.zero_()
+        k, v, s = batches[i]
+        arm.insert_and_evict(k, v, s, ek, ev, es, cnt)
+
+    t_ms = time_steps(step, reps, 3)
+    keys_done = sum(b[0].numel() for b in batches[3:])
+    last_epoch = epoch + reps + 3
+    evicted_last = int(cnt.item())
+    xk = torch.empty(capacity, dtype=torch.int64, device="cuda")
+    xs = torch.empty(capacity, dtype=torch.int64, device="cuda")
+    xv = torch.empty((capacity, dim), dtype=torch.float32, device="cuda")
+    thr = (last_epoch - 2) << 32
+    x_ms = time_steps(lambda i: arm.export_if_score_below(thr, capacity, cnt, xk, xv, xs), 3, 3)
+    matched = int(cnt.item())
+    assert bool((xs[:matched] < thr).all())
+    arm.close()
+    return {"insert_and_evict_b_kv_s": round(keys_done / (t_ms / 1e3) / BINARY_BILLION, 4),
+            "evicted_per_batch": evicted_last,
+            "export_batch_if_b_kv_s": round(capacity * 3 / (x_ms / 1e3) / BINARY_BILLION, 4),
+            "export_batch_if_matched": matched,
+            "table": f"capacity {capacity}, dim {dim}, EpochLfu, load factor 1.0"}
 
 
 def cpu_baseline(dim: int, batch: int, seconds_budget: float = 20.0) -> dict:
@@ -625,6 +715,10 @@ def main():
         for v in ops.values():
             v["b_kv_s"] = round(v["b_kv_s"], 4)
             v["achieved_gbs"] = round(v["achieved_gbs"], 1)
+        try:
+            ops["churn_epoch_lfu"] = churn_ops(type(arm), batch)
+        except Exception as e:
+            ops["churn_epoch_lfu"] = {"failed": str(e)[:200]}
         try:
             ops["hybrid_find_zipf"] = hybrid_ops(type(arm), batch)
         except Exception as e:  # pinned host memory may be scarce on a box

@@ -8,6 +8,8 @@
 // with one warp kernel: 8-lane digest probe of 32 keys with every digest line
 // and every first-candidate key load in flight at once, then a
 // warp-cooperative streaming gather of the hit rows.
+#include <cub/device/device_radix_sort.cuh>
+
 #include "hkv_device.cuh"
 #include "hkv_internal.h"
 
@@ -87,12 +89,15 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
 // FORM 1: value pointers + founds (+scores) (find*, merlin_hashtable.cuh:2729)
 // FORM 2: values + missed keys/indices/size (merlin_hashtable.cuh:2600)
 // FORM 3: founds only                     (contains, merlin_hashtable.cuh:2856)
+// FORM 4: founds (+scores) and, per key, its slot and its batch index: the
+//         first step of find on a table whose rows partly live in host memory
 template <int FORM>
 __global__ void __launch_bounds__(kFindBlock)
     find_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
                 uint8_t* __restrict__ values, void** __restrict__ ptrs, bool* __restrict__ founds,
                 uint64_t* __restrict__ scores, uint64_t* __restrict__ missed_keys,
-                int* __restrict__ missed_indices, int* __restrict__ missed_size) {
+                int* __restrict__ missed_indices, int* __restrict__ missed_size,
+                uint32_t* __restrict__ slot_out, uint32_t* __restrict__ index_out) {
   const ProbeLane pl = probe_lane();
   const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const uint64_t base = warp * 32u;
@@ -114,6 +119,10 @@ __global__ void __launch_bounds__(kFindBlock)
     if (FORM != 2) founds[i] = found;
     if (FORM == 1) ptrs[i] = found ? row_ptr(t, slot) : nullptr;
     if (FORM != 3 && scores != nullptr && found) scores[i] = t.scores[slot];
+    if (FORM == 4) {
+      slot_out[i] = slot;  // kNoSlot sorts behind every real slot
+      index_out[i] = static_cast<uint32_t>(i);
+    }
   }
   if (FORM == 2) {
     const bool missed = (i < n) && !found;
@@ -194,13 +203,72 @@ void launch_form(const TableView& t, uint64_t n, const uint64_t* keys, void* val
   const uint64_t blocks = (warps * 32 + kFindBlock - 1) / kFindBlock;
   find_kernel<FORM><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
       t, keys, n, static_cast<uint8_t*>(values), ptrs, founds, scores, missed_keys, missed_indices,
-      missed_size);
+      missed_size, nullptr, nullptr);
+}
+
+// Second step of the hybrid find: (slot, batch index) pairs sorted by slot.
+// A warp takes 32 pairs and gathers their rows into the caller's buffer at
+// the keys' own positions.  Sorted order makes the reads of host-resident
+// rows walk host memory monotonically and puts repeated keys next to each
+// other, which is what the host link and its address translation want (the
+// reference sorts row addresses for the same reason,
+// include/merlin_hashtable.cuh:2562-2572).
+__global__ void __launch_bounds__(kFindBlock)
+    gather_sorted_kernel(const TableView t, const uint64_t n,
+                         const uint32_t* __restrict__ sorted_slot,
+                         const uint32_t* __restrict__ sorted_index, uint8_t* __restrict__ values) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t i = ((uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) & ~uint64_t(31)) + lane;
+  if (i - lane >= n) return;
+  uint32_t slot = kNoSlot, dest = 0;
+  if (i < n) {
+    slot = sorted_slot[i];
+    dest = sorted_index[i];
+  }
+  if (__ballot_sync(0xFFFFFFFFu, slot != kNoSlot) == 0) return;
+  warp_gather_rows_to(t, values, dest, slot, lane);
+}
+
+// find on a table with rows in pinned host memory: probe, sort by slot, gather.
+bool launch_find_hybrid(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
+                        bool* founds, uint64_t* scores, cudaStream_t stream) {
+  if (n < 4096 || n >= (1ull << 32)) return false;
+  size_t temp_bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, temp_bytes, static_cast<uint32_t*>(nullptr),
+                                  static_cast<uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr),
+                                  static_cast<uint32_t*>(nullptr), static_cast<int>(n), 0, 32,
+                                  stream);
+  const size_t arrays = ((n * sizeof(uint32_t)) + 255) & ~size_t(255);
+  uint8_t* work = nullptr;
+  // stream-ordered scratch: concurrent readers on other streams get their own
+  if (cudaMallocAsync(reinterpret_cast<void**>(&work), 4 * arrays + temp_bytes, stream) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  uint32_t* slot = reinterpret_cast<uint32_t*>(work);
+  uint32_t* index = reinterpret_cast<uint32_t*>(work + arrays);
+  uint32_t* slot_sorted = reinterpret_cast<uint32_t*>(work + 2 * arrays);
+  uint32_t* index_sorted = reinterpret_cast<uint32_t*>(work + 3 * arrays);
+  const uint64_t blocks = (((n + 31) / 32) * 32 + kFindBlock - 1) / kFindBlock;
+  find_kernel<4><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
+      t, keys, n, nullptr, nullptr, founds, scores, nullptr, nullptr, nullptr, slot, index);
+  cub::DeviceRadixSort::SortPairs(work + 4 * arrays, temp_bytes, slot, slot_sorted, index,
+                                  index_sorted, static_cast<int>(n), 0, 32, stream);
+  gather_sorted_kernel<<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
+      t, n, slot_sorted, index_sorted, static_cast<uint8_t*>(values));
+  cudaFreeAsync(work, stream);
+  return true;
 }
 
 }  // namespace
 
 void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values, bool* founds,
                  uint64_t* scores, cudaStream_t stream) {
+  if (t.hbm_slots < t.capacity && values != nullptr &&
+      launch_find_hybrid(t, n, keys, values, founds, scores, stream)) {
+    return;
+  }
   launch_form<0>(t, n, keys, values, nullptr, founds, scores, nullptr, nullptr, nullptr, stream);
 }
 
