@@ -18,6 +18,10 @@ namespace hkv {
 namespace {
 
 constexpr int kFindBlock = 128;
+#ifndef HKV_FIND_MIN_BLOCKS
+#define HKV_FIND_MIN_BLOCKS 8
+#endif
+constexpr int kFindMinBlocks = HKV_FIND_MIN_BLOCKS;  // resident blocks per SM asked of the compiler
 
 // Probes the 32 keys of a warp.  Returns in the owner lane the global slot of
 // its key, or kNoSlot.
@@ -92,7 +96,7 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
 // FORM 4: founds (+scores) and, per key, its slot and its batch index: the
 //         first step of find on a table whose rows partly live in host memory
 template <int FORM>
-__global__ void __launch_bounds__(kFindBlock)
+__global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
     find_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
                 uint8_t* __restrict__ values, void** __restrict__ ptrs, bool* __restrict__ founds,
                 uint64_t* __restrict__ scores, uint64_t* __restrict__ missed_keys,
