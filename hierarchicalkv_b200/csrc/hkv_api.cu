@@ -754,6 +754,29 @@ int hkv_erase(hkv_table* t, uint64_t n, const uint64_t* keys, hkv_stream stream)
   });
 }
 
+int hkv_erase_if(hkv_table* t, int predicate, uint64_t pattern, uint64_t threshold,
+                 hkv_stream stream, uint64_t* erased) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (predicate < HKV_PRED_ALL || predicate > HKV_PRED_SCORE_LESS_EQ) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "unknown predicate"};
+    }
+    unsigned long long* ctr = t->d_scratch + 4;
+    {
+      LockScope ls(t, kInserter, s);
+      HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
+      hkv::launch_erase_if(t->view, predicate, pattern, threshold, ctr, s);
+      ls.done();
+    }
+    check_launch();
+    unsigned long long h = 0;
+    HKV_CUDA(cudaMemcpyAsync(&h, ctr, sizeof(h), cudaMemcpyDeviceToHost, s));
+    HKV_CUDA(cudaStreamSynchronize(s));
+    if (erased != nullptr) *erased = h;
+  });
+}
+
 int hkv_clear(hkv_table* t, hkv_stream stream) {
   return guarded([&] {
     DeviceGuard dg(t->device);

@@ -91,6 +91,8 @@ void launch_export(const TableView& t, int pred, uint64_t pattern, uint64_t thre
                    uint64_t* scores, cudaStream_t stream);
 void launch_size_if(const TableView& t, int pred, uint64_t pattern, uint64_t threshold,
                     unsigned long long* d_counter, cudaStream_t stream);
+void launch_erase_if(const TableView& t, int pred, uint64_t pattern, uint64_t threshold,
+                     unsigned long long* d_counter, cudaStream_t stream);
 void launch_clear(const TableView& t, cudaStream_t stream);
 void launch_sum_sizes(const TableView& t, unsigned long long* d_total, cudaStream_t stream);
 

@@ -101,6 +101,29 @@ __global__ void __launch_bounds__(kScanBlock)
   if ((threadIdx.x & 31u) == 0 && local) atomicAdd(d_counter, local);
 }
 
+// erase_if: every live slot the predicate selects becomes a tombstone (RECLAIM
+// key, reclaim digest, score 0), as remove_kernel does
+// (include/merlin/core_kernels.cuh:736-792).  Runs under the exclusive lock.
+__global__ void __launch_bounds__(kScanBlock)
+    erase_if_kernel(const TableView t, const int pred, const uint64_t pattern,
+                    const uint64_t threshold, unsigned long long* __restrict__ d_counter) {
+  unsigned long long local = 0;
+  for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < t.capacity;
+       slot += uint64_t(gridDim.x) * blockDim.x) {
+    const uint64_t key = t.keys[slot];
+    const uint64_t score = t.scores[slot];
+    if (keep(t, pred, key, score, pattern, threshold)) {
+      t.keys[slot] = t.reclaim_key;
+      t.digests[slot] = static_cast<uint8_t>(t.reclaim_digest);
+      t.scores[slot] = 0;
+      atomicSub(t.bucket_sizes + (slot >> 7), 1);
+      ++local;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_down_sync(0xFFFFFFFFu, local, o);
+  if ((threadIdx.x & 31u) == 0 && local) atomicAdd(d_counter, local);
+}
+
 __global__ void __launch_bounds__(kScanBlock)
     sum_sizes_kernel(const TableView t, unsigned long long* __restrict__ d_total) {
   unsigned long long local = 0;
@@ -153,6 +176,12 @@ void launch_export(const TableView& t, int pred, uint64_t pattern, uint64_t thre
 void launch_size_if(const TableView& t, int pred, uint64_t pattern, uint64_t threshold,
                     unsigned long long* d_counter, cudaStream_t stream) {
   size_if_kernel<<<scan_grid(kScanBlock * 4, t.capacity), kScanBlock, 0, stream>>>(
+      t, pred, pattern, threshold, d_counter);
+}
+
+void launch_erase_if(const TableView& t, int pred, uint64_t pattern, uint64_t threshold,
+                     unsigned long long* d_counter, cudaStream_t stream) {
+  erase_if_kernel<<<scan_grid(kScanBlock * 4, t.capacity), kScanBlock, 0, stream>>>(
       t, pred, pattern, threshold, d_counter);
 }
 

@@ -147,6 +147,7 @@ _SIGNATURES = {
     "hkv_find_and_update": [_P, _U64, _P, _P, _P, _P, _P, _INT],
     "hkv_contains": [_P, _U64, _P, _P, _P],
     "hkv_erase": [_P, _U64, _P, _P],
+    "hkv_erase_if": [_P, _INT, _U64, _U64, _P, ctypes.POINTER(_U64)],
     "hkv_clear": [_P, _P],
     "hkv_export_batch": [_P, _U64, _U64, _P, _P, _P, _P, _P],
     "hkv_export_batch_count": [_P, _U64, _U64, _P, _P, _P, _P, ctypes.POINTER(_U64)],
@@ -400,6 +401,13 @@ class HashTable:
     # -- erase / clear ------------------------------------------------------
     def erase(self, n, keys, stream=None) -> None:
         self._call("hkv_erase", n, _ptr(keys), _stream(stream))
+
+    def erase_if(self, pred, pattern, threshold, stream=None) -> int:
+        """erase_if with a built-in predicate; returns the number of erased keys."""
+        out = ctypes.c_uint64(0)
+        self._call("hkv_erase_if", int(pred), pattern, threshold, _stream(stream),
+                   ctypes.byref(out))
+        return out.value
 
     def clear(self, stream=None) -> None:
         self._call("hkv_clear", _stream(stream))

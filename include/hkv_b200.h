@@ -201,6 +201,10 @@ HKV_API int hkv_contains(hkv_table* table, uint64_t n, const uint64_t* keys, boo
 
 /* HashTable::erase, include/merlin_hashtable.cuh:2904-2930 */
 HKV_API int hkv_erase(hkv_table* table, uint64_t n, const uint64_t* keys, hkv_stream stream);
+/* HashTable::erase_if<PredFunctor>, include/merlin_hashtable.cuh:2964-2996, for
+ * the built-in predicates; returns the number of erased keys (synchronises). */
+HKV_API int hkv_erase_if(hkv_table* table, int predicate, uint64_t pattern, uint64_t threshold,
+                         hkv_stream stream, uint64_t* erased);
 /* HashTable::clear, include/merlin_hashtable.cuh:3059-3073 */
 HKV_API int hkv_clear(hkv_table* table, hkv_stream stream);
 

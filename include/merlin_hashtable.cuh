@@ -197,6 +197,29 @@ __global__ void size_if_kernel(const hkv_table_view v, const K pattern, const S 
   }
 }
 
+// erase_if<PredFunctor>: selected slots become tombstones (RECLAIM key,
+// reclaim digest, score 0).  Runs under the table's exclusive lock.
+template <class K, class S, template <typename, typename> class PredFunctor>
+__global__ void erase_if_kernel(const hkv_table_view v, const K pattern, const S threshold,
+                                const uint8_t reclaim_digest, unsigned long long* d_counter) {
+  PredFunctor<K, S> pred;
+  unsigned long long local = 0;
+  for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < v.capacity;
+       slot += uint64_t(gridDim.x) * blockDim.x) {
+    K key = static_cast<K>(v.keys[slot]);
+    S score = static_cast<S>(v.scores[slot]);
+    if (!view_is_reserved(v, static_cast<uint64_t>(key)) && pred(key, score, pattern, threshold)) {
+      v.keys[slot] = v.reclaim_key;
+      v.digests[slot] = reclaim_digest;
+      v.scores[slot] = 0;
+      atomicSub(v.bucket_sizes + (slot >> 7), 1);
+      ++local;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_down_sync(0xFFFFFFFFu, local, o);
+  if ((threadIdx.x & 31u) == 0 && local) atomicAdd(d_counter, local);
+}
+
 }  // namespace detail
 
 // The pure-virtual interface, merlin_hashtable.cuh:187-885.
@@ -526,6 +549,35 @@ class HashTable : public HashTableBase<K, V, S> {
     }
     detail::rethrow(hkv_external_end(table_, 0, stream));
     CUDA_CHECK(err);
+  }
+
+  // erase_if<PredFunctor>, merlin_hashtable.cuh:2964-2996: returns the number
+  // of erased keys (synchronises the stream).
+  template <template <typename, typename> class PredFunctor>
+  size_type erase_if(const key_type& pattern, const score_type& threshold,
+                     cudaStream_t stream = 0) {
+    hkv_table_view v{};
+    detail::rethrow(hkv_get_view(table_, &v));
+    unsigned long long* d_count = nullptr;
+    CUDA_CHECK(cudaMallocAsync(reinterpret_cast<void**>(&d_count), sizeof(*d_count), stream));
+    detail::rethrow(hkv_external_begin(table_, 2, stream));
+    cudaError_t err = cudaMemsetAsync(d_count, 0, sizeof(*d_count), stream);
+    if (err == cudaSuccess) {
+      const uint8_t reclaim_digest =
+          static_cast<uint8_t>(Murmur3HashHost(v.reclaim_key) >> 32);
+      detail::erase_if_kernel<K, S, PredFunctor>
+          <<<148 * 8, 256, 0, stream>>>(v, pattern, threshold, reclaim_digest, d_count);
+      err = cudaGetLastError();
+    }
+    detail::rethrow(hkv_external_end(table_, 2, stream));
+    unsigned long long count = 0;
+    if (err == cudaSuccess) {
+      err = cudaMemcpyAsync(&count, d_count, sizeof(count), cudaMemcpyDeviceToHost, stream);
+    }
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    cudaFreeAsync(d_count, stream);
+    CUDA_CHECK(err);
+    return count;
   }
 
   bool empty(cudaStream_t stream = 0) const override { return size(stream) == 0; }

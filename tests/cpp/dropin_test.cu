@@ -170,6 +170,18 @@ static void test_basic() {
     EXPECT(xv[i * kDim + kDim - 1] == static_cast<float>(xk[i] * 0.00001));
   }
 
+  // erase_if with the same functor removes exactly those keys; a second pass finds none
+  {
+    std::unique_ptr<Table> victim = std::make_unique<Table>();
+    victim->init(opt);
+    victim->insert_or_assign(kN, dk.p, dv.p, ds.p, stream);
+    size_t below = 0;
+    for (size_t i = 0; i < kN; ++i) below += hs[i] < threshold ? 1 : 0;
+    EXPECT(victim->erase_if<ScoreBelow>(K(0), threshold, stream) == below);
+    EXPECT(victim->size(stream) == kN - below);
+    EXPECT(victim->erase_if<ScoreBelow>(K(0), threshold, stream) == 0);
+  }
+
   // save / load round trip through LocalKVFile
   {
     nv::merlin::LocalKVFile<K, V, S> file;

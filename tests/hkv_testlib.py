@@ -101,6 +101,7 @@ _ORACLE_SIGS = {
     "orc_assign": ([_P, _INT, _U64, _P, _P, _P], None),
     "orc_erase": ([_P, _U64, _P], None),
     "orc_export_batch_if": ([_P, _INT, _U64, _U64, _U64, _U64, _P, _P, _P], _U64),
+    "orc_erase_if": ([_P, _INT, _U64, _U64], _U64),
     "orc_bucket_min_score": ([_P, _U64], _U64),
     "orc_hardware_threads": ([], _INT),
 }
@@ -218,6 +219,9 @@ class OracleTable:
 
     def erase(self, keys):
         self.lib.orc_erase(self.h, keys.size, _np(keys))
+
+    def erase_if(self, pred, pattern, threshold):
+        return self.lib.orc_erase_if(self.h, pred, pattern, threshold)
 
     def export_batch_if(self, pred=0, pattern=0, threshold=0, n=None, offset=0):
         cap = self.capacity()
@@ -403,6 +407,9 @@ class ProductTable:
     def erase(self, keys):
         self.t.erase(keys.size, to_dev(keys))
         self.torch.cuda.synchronize()
+
+    def erase_if(self, pred, pattern, threshold):
+        return self.t.erase_if(pred, pattern, threshold)
 
     def export_batch_if(self, pred=0, pattern=0, threshold=0, n=None, offset=0):
         torch = self.torch

@@ -483,3 +483,28 @@ def test_export_batch_slot_windows(offset, n):
         assert ss == i + 1
         np.testing.assert_array_equal(vv, values_for(keys[i:i + 1], dim)[0])
     t.close()
+
+
+@pytest.mark.parametrize("pred,pattern,threshold", [(1, 0, 1500), (2, 0, 2500), (3, 0x3, 0x7), (0, 0, 0)])
+def test_erase_if_built_in_predicates(pred, pattern, threshold):
+    """erase_if tombstones what the predicate selects; the slots are reusable
+    afterwards (reference: tests/merlin_hashtable_test.cc.cu erase_if cases)."""
+    cap, dim = 128 * 32, 4
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(5000, seed=31)
+    sc = np.arange(1, 3001, dtype=np.uint64)
+    for x in (t, o):
+        x.insert_or_assign(keys[:3000], values_for(keys[:3000], dim), sc)
+    assert t.erase_if(pred, pattern, threshold) == o.erase_if(pred, pattern, threshold)
+    assert t.size() == o.size()
+    for a, b in zip(sorted_by_key(*t.export_batch()), sorted_by_key(*o.export_batch())):
+        np.testing.assert_array_equal(a, b)
+    more = keys[3000:5000]
+    s2 = np.arange(10001, 12001, dtype=np.uint64)
+    for x in (t, o):
+        x.insert_or_assign(more, values_for(more, dim), s2)
+    assert t.size() == o.size()
+    for a, b in zip(sorted_by_key(*t.export_batch()), sorted_by_key(*o.export_batch())):
+        np.testing.assert_array_equal(a, b)
+    t.close()
