@@ -508,3 +508,38 @@ def test_erase_if_built_in_predicates(pred, pattern, threshold):
     for a, b in zip(sorted_by_key(*t.export_batch()), sorted_by_key(*o.export_batch())):
         np.testing.assert_array_equal(a, b)
     t.close()
+
+
+def test_bounded_wait_on_a_slot_that_stays_locked():
+    """Every device-side wait has a limit.  Keys locked with lock_keys stay
+    LOCKED; a duplicate-tolerant insert into their bucket has to wait for
+    LOCKED slots, gives up after its bound, refuses the key and raises the
+    status bit -- no hang, and the table works again after unlock_keys."""
+    import torch
+
+    cap, dim = 128 * 4, 4
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    pool = unique_keys(60000, seed=41)
+    in_b0 = pool[bucket_of(pool, cap) == 0]
+    held, late = in_b0[:8], in_b0[8:12]
+    t.insert_or_assign(held, values_for(held, dim), np.arange(1, 9, dtype=np.uint64))
+    k = to_dev(held)
+    lk = torch.zeros(8, dtype=torch.int64, device="cuda")
+    ok = torch.zeros(8, dtype=torch.bool, device="cuda")
+    t.t.lock_keys(8, k, lk, ok)
+    torch.cuda.synchronize()
+    assert bool(ok.all())
+    assert t.t.device_status() == 0
+    t.insert_or_assign(late, values_for(late, dim), np.arange(101, 105, dtype=np.uint64),
+                       unique_key=False)
+    assert t.t.device_status() & 1                      # a bounded slot wait ran out
+    assert t.t.device_status() == 0                     # reading clears the word
+    assert not t.contains(late).any()                   # the keys were refused, nothing half-written
+    t.t.unlock_keys(8, lk, k, ok)
+    torch.cuda.synchronize()
+    assert bool(ok.all())
+    t.insert_or_assign(late, values_for(late, dim), np.arange(101, 105, dtype=np.uint64),
+                       unique_key=False)
+    assert t.contains(late).all() and t.contains(held).all()
+    assert t.t.device_status() == 0
+    t.close()

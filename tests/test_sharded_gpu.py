@@ -184,3 +184,32 @@ def test_two_nccl_ranks_match_one_global_oracle():
     port = s.getsockname()[1]
     s.close()
     mp.spawn(_nccl_worker, args=(2, port, 8, 128 * 256), nprocs=2, join=True)
+
+
+def test_peer_barrier_times_out_instead_of_hanging():
+    """The barrier of the fused routing waits for flags the peers raise.  With a
+    peer that never arrives the wait runs out after its poll limit, the kernel
+    returns, and the status word says so; the context stays usable."""
+    import ctypes
+
+    from hierarchicalkv_b200.sharded import CudaOps, _PeerPtrs
+
+    lib = CudaOps().lib
+    flags = torch.zeros((2, 16), dtype=torch.int32, device="cuda")   # "rank 0" and "rank 1" flags
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    peers = _PeerPtrs()
+    peers.p[0] = flags[0].data_ptr()
+    peers.p[1] = flags[1].data_ptr()
+    sp = torch.cuda.current_stream().cuda_stream or None
+    # rank 0 arrives at epoch 1; nobody plays rank 1
+    rc = lib.hkv_shard_barrier(2, 0, ctypes.byref(peers), 1, status.data_ptr(), 2000, sp)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    assert int(flags[1, 0].item()) == 1            # the arrival was announced to the peer
+    # once the peer's flag is there the same barrier passes
+    status.zero_()
+    flags[0, 1] = 1
+    rc = lib.hkv_shard_barrier(2, 0, ctypes.byref(peers), 1, status.data_ptr(), 2000, sp)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == 0
