@@ -141,6 +141,10 @@ struct hkv_table {
   int device = 0;
   void* meta_block = nullptr;  // digests + keys + scores + sizes + status
   void* host_rows = nullptr;   // host address of the pinned value rows
+  // reserve() and the automatic growth of the insert-like calls stop once the
+  // capacity cannot double below max_capacity
+  // (reach_max_capacity_, include/merlin_hashtable.cuh:1064, 3508-3538)
+  std::atomic<bool> reach_max_capacity{true};
 };
 
 namespace {
@@ -285,11 +289,165 @@ hkv::MutateArgs base_args(hkv_table* t, uint64_t n, const uint64_t* keys, const 
   return a;
 }
 
-void mutate(hkv_table* t, int op, hkv::MutateArgs& args, const hkv::TableView& v, Group g,
-            bool unique_key, cudaStream_t stream) {
+// The planes of one table size: a metadata block (digests | keys | scores |
+// bucket sizes | status) and the value rows, whole buckets in HBM while
+// max_hbm_for_vectors lasts and the rest in mapped pinned host memory (a static
+// split by bucket index, as include/merlin/core_kernels.cuh:204-232 does per
+// slice).
+struct Planes {
+  void* meta_block = nullptr;
+  void* values_hbm = nullptr;
+  void* host_rows = nullptr;
+  unsigned long long* d_scratch = nullptr;
+};
+
+void free_planes(hkv_table* t, Planes& p) {
+  if (p.meta_block) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, p.meta_block);
+  if (p.values_hbm) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, p.values_hbm);
+  if (p.host_rows) t->alloc.free(t->alloc.ctx, HKV_MEM_PINNED, p.host_rows);
+  p = Planes{};
+}
+
+// Fills the size-dependent fields of `v` (the others are taken as they are)
+// and clears the new table on `stream`.
+void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& p,
+                     cudaStream_t stream) {
+  const uint64_t capacity = buckets * hkv::kBucketSlots;
+  HKV_CHECK(capacity <= (1ull << 31), "capacity above 2^31 slots is not supported.");
+  const uint64_t row_bytes = v.row_bytes;
+  v.buckets = buckets;
+  v.capacity = capacity;
+  v.capacity_pow2 = (capacity & (capacity - 1)) == 0 ? 1u : 0u;
+  try {
+    auto align256 = [](uint64_t x) { return (x + 255) & ~255ull; };
+    const uint64_t off_digests = 0;
+    const uint64_t off_keys = align256(off_digests + capacity);
+    const uint64_t off_scores = align256(off_keys + capacity * 8);
+    const uint64_t off_sizes = align256(off_scores + capacity * 8);
+    const uint64_t off_status = align256(off_sizes + buckets * 4);
+    const uint64_t meta_bytes = off_status + 256;
+    if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &p.meta_block, meta_bytes, 0) != 0 ||
+        p.meta_block == nullptr) {
+      cudaGetLastError();
+      throw HkvError{HKV_ERR_CUDA, "device allocation of the table metadata failed"};
+    }
+    uint8_t* mb = static_cast<uint8_t*>(p.meta_block);
+    v.digests = mb + off_digests;
+    v.keys = reinterpret_cast<uint64_t*>(mb + off_keys);
+    v.scores = reinterpret_cast<uint64_t*>(mb + off_scores);
+    v.bucket_sizes = reinterpret_cast<int32_t*>(mb + off_sizes);
+    v.status = reinterpret_cast<uint32_t*>(mb + off_status);
+    p.d_scratch = reinterpret_cast<unsigned long long*>(mb + off_status + 64);
+    HKV_CUDA(cudaMemsetAsync(mb + off_status, 0, 256, stream));
+
+    uint64_t hbm_buckets = t->opt.max_hbm_for_vectors / (row_bytes * hkv::kBucketSlots);
+    if (hbm_buckets > buckets) hbm_buckets = buckets;
+    v.hbm_slots = hbm_buckets * hkv::kBucketSlots;
+    v.values_hbm = nullptr;
+    v.values_host = nullptr;
+    if (v.hbm_slots > 0) {
+      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &p.values_hbm, v.hbm_slots * row_bytes,
+                         0) != 0 ||
+          p.values_hbm == nullptr) {
+        cudaGetLastError();
+        throw HkvError{HKV_ERR_CUDA, "device allocation of the value rows failed"};
+      }
+      v.values_hbm = static_cast<uint8_t*>(p.values_hbm);
+    }
+    if (v.hbm_slots < capacity) {
+      const uint64_t bytes = (capacity - v.hbm_slots) * row_bytes;
+      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_PINNED, &p.host_rows, bytes,
+                         cudaHostAllocMapped | cudaHostAllocPortable) != 0 ||
+          p.host_rows == nullptr) {
+        cudaGetLastError();
+        throw HkvError{HKV_ERR_CUDA, "pinned host allocation of the value rows failed"};
+      }
+      void* dp = nullptr;
+      HKV_CUDA(cudaHostGetDevicePointer(&dp, p.host_rows, 0));
+      v.values_host = static_cast<uint8_t*>(dp);
+    }
+    hkv::launch_clear(v, stream);
+    check_launch();
+  } catch (...) {
+    free_planes(t, p);
+    throw;
+  }
+}
+
+// fast_load_factor, include/merlin_hashtable.cuh:3796-3828: the load the table
+// would have after `delta` more keys, estimated from the first 1024 buckets.
+float fast_load_factor(hkv_table* t, uint64_t delta, cudaStream_t s) {
+  unsigned long long* ctr = nullptr;
+  uint64_t sampled = 0, capacity = 0;
+  {
+    LockScope ls(t, kReader, s);
+    ctr = t->d_scratch + 5;
+    sampled = t->view.buckets < 1024 ? t->view.buckets : 1024;
+    capacity = t->view.capacity;
+    HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
+    hkv::launch_sum_sizes(t->view, sampled, ctr, s);
+    ls.done();
+  }
+  check_launch();
+  unsigned long long h = 0;
+  HKV_CUDA(cudaMemcpyAsync(&h, ctr, sizeof(h), cudaMemcpyDeviceToHost, s));
+  HKV_CUDA(cudaStreamSynchronize(s));
+  return static_cast<float>((delta * 1.0) / (capacity * 1.0) +
+                            (h * 1.0) / (hkv::kBucketSlots * sampled * 1.0));
+}
+
+// reserve, include/merlin_hashtable.cuh:3503-3545.  Each doubling builds the
+// planes of the larger table, moves the live entries over and frees the old
+// planes: pointers into the table handed out earlier (find / find_or_insert
+// pointer forms, lock_keys) are invalid afterwards, as in the reference.
+void reserve(hkv_table* t, uint64_t new_capacity, cudaStream_t s) {
+  if (t->reach_max_capacity.load() || new_capacity > t->opt.max_capacity) {
+    t->reach_max_capacity.store(t->view.capacity * 2 > t->opt.max_capacity);
+    return;
+  }
+  LockScope ls(t, kInserter, s);
+  HKV_CUDA(cudaDeviceSynchronize());
+  while (t->view.capacity < new_capacity && t->view.capacity * 2 <= t->opt.max_capacity) {
+    hkv::TableView grown = t->view;
+    Planes fresh;
+    allocate_planes(t, t->view.buckets * 2, grown, fresh, s);
+    hkv::launch_rehash(t->view, grown, s);
+    // the status word moves with the table
+    cudaMemcpyAsync(grown.status, t->view.status, 64, cudaMemcpyDeviceToDevice, s);
+    if (cudaStreamSynchronize(s) != cudaSuccess || cudaGetLastError() != cudaSuccess) {
+      free_planes(t, fresh);
+      throw HkvError{HKV_ERR_CUDA, "rehash into the doubled table failed"};
+    }
+    Planes old;
+    old.meta_block = t->meta_block;
+    old.values_hbm = t->view.values_hbm;
+    old.host_rows = t->host_rows;
+    t->view = grown;
+    t->meta_block = fresh.meta_block;
+    t->host_rows = fresh.host_rows;
+    t->d_scratch = fresh.d_scratch;
+    free_planes(t, old);
+  }
+  t->reach_max_capacity.store(t->view.capacity * 2 > t->opt.max_capacity);
+  ls.done();
+  check_launch();
+}
+
+// `batch_a` / `batch_b` are the caller's row buffers; their alignment bounds
+// the row access width of the view the kernel gets.
+void mutate(hkv_table* t, int op, hkv::MutateArgs& args, const void* batch_a, const void* batch_b,
+            Group g, bool unique_key, cudaStream_t stream) {
   DeviceGuard dg(t->device);
+  if (op <= hkv::kOpAccumOrAssign) {
+    // the insert-like calls grow the table first
+    // (include/merlin_hashtable.cuh:1151-1154, 1369-1372, 1604-1607, 1712-1715, 1898-1901)
+    while (!t->reach_max_capacity.load() &&
+           fast_load_factor(t, args.n, stream) > t->opt.max_load_factor) {
+      reserve(t, t->view.capacity * 2, stream);
+    }
+  }
   LockScope ls(t, g, stream);
-  hkv::launch_mutate(op, v, args, unique_key, stream);
+  hkv::launch_mutate(op, view_for(t, batch_a, batch_b), args, unique_key, stream);
   ls.done();
   check_launch();
 }
@@ -355,14 +513,11 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
         buckets = 1;
         while (buckets * hkv::kBucketSlots < o.init_capacity) buckets *= 2;
       }
-      const uint64_t capacity = buckets * hkv::kBucketSlots;
-      HKV_CHECK(capacity <= (1ull << 31), "capacity above 2^31 slots is not supported.");
       const uint64_t row_bytes = o.dim * uint64_t(o.value_size);
       HKV_CHECK(row_bytes < (1ull << 24), "value rows above 16 MiB are not supported.");
+      t->reach_max_capacity.store(o.init_capacity * 2 > o.max_capacity);
 
       hkv::TableView& v = t->view;
-      v.buckets = buckets;
-      v.capacity = capacity;
       v.row_bytes = uint32_t(row_bytes);
       v.vec_bytes = widest_vec(row_bytes);
       v.chunks_per_row = uint32_t(row_bytes / v.vec_bytes);
@@ -372,8 +527,6 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
         while ((1u << s) < v.chunks_per_row) ++s;
         v.chunks_per_row_shift = s;
       }
-      v.capacity_pow2 = (capacity & (capacity - 1)) == 0 ? 1u : 0u;
-
       // reserved keys, include/merlin/types.cuh:80-109
       const int bit = o.reserved_key_start_bit;
       if (bit == 0) {
@@ -395,61 +548,11 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
       v.empty_digest4 = ed * 0x01010101u;
       v.reclaim_digest = uint32_t(hkv::fmix64(v.reclaim_key) >> 32) & 0xFFu;
 
-      // one metadata block: digests | keys | scores | bucket sizes | status
-      auto align256 = [](uint64_t x) { return (x + 255) & ~255ull; };
-      const uint64_t off_digests = 0;
-      const uint64_t off_keys = align256(off_digests + capacity);
-      const uint64_t off_scores = align256(off_keys + capacity * 8);
-      const uint64_t off_sizes = align256(off_scores + capacity * 8);
-      const uint64_t off_status = align256(off_sizes + buckets * 4);
-      const uint64_t meta_bytes = off_status + 256;
-      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &t->meta_block, meta_bytes, 0) != 0 ||
-          t->meta_block == nullptr) {
-        cudaGetLastError();
-        throw HkvError{HKV_ERR_CUDA, "device allocation of the table metadata failed"};
-      }
-      uint8_t* mb = static_cast<uint8_t*>(t->meta_block);
-      v.digests = mb + off_digests;
-      v.keys = reinterpret_cast<uint64_t*>(mb + off_keys);
-      v.scores = reinterpret_cast<uint64_t*>(mb + off_scores);
-      v.bucket_sizes = reinterpret_cast<int32_t*>(mb + off_sizes);
-      v.status = reinterpret_cast<uint32_t*>(mb + off_status);
-      t->d_scratch = reinterpret_cast<unsigned long long*>(mb + off_status + 64);
-      HKV_CUDA(cudaMemset(mb + off_status, 0, 256));
-
-      // value rows: whole buckets in HBM while max_hbm_for_vectors lasts, the
-      // rest in mapped pinned host memory (static split by bucket index, as
-      // include/merlin/core_kernels.cuh:204-232 does per slice)
-      uint64_t hbm_buckets = o.max_hbm_for_vectors / (row_bytes * hkv::kBucketSlots);
-      if (hbm_buckets > buckets) hbm_buckets = buckets;
-      v.hbm_slots = hbm_buckets * hkv::kBucketSlots;
-      v.values_hbm = nullptr;
-      v.values_host = nullptr;
-      if (v.hbm_slots > 0) {
-        void* p = nullptr;
-        if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &p, v.hbm_slots * row_bytes, 0) != 0 ||
-            p == nullptr) {
-          cudaGetLastError();
-          throw HkvError{HKV_ERR_CUDA, "device allocation of the value rows failed"};
-        }
-        v.values_hbm = static_cast<uint8_t*>(p);
-      }
-      if (v.hbm_slots < capacity) {
-        void* p = nullptr;
-        const uint64_t bytes = (capacity - v.hbm_slots) * row_bytes;
-        if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_PINNED, &p, bytes,
-                           cudaHostAllocMapped | cudaHostAllocPortable) != 0 ||
-            p == nullptr) {
-          cudaGetLastError();
-          throw HkvError{HKV_ERR_CUDA, "pinned host allocation of the value rows failed"};
-        }
-        t->host_rows = p;
-        void* dp = nullptr;
-        HKV_CUDA(cudaHostGetDevicePointer(&dp, p, 0));
-        v.values_host = static_cast<uint8_t*>(dp);
-      }
-      hkv::launch_clear(v, nullptr);
-      check_launch();
+      Planes planes;
+      allocate_planes(t, buckets, v, planes, nullptr);
+      t->meta_block = planes.meta_block;
+      t->host_rows = planes.host_rows;
+      t->d_scratch = planes.d_scratch;
       HKV_CUDA(cudaDeviceSynchronize());
     } catch (...) {
       hkv_table_destroy(t);
@@ -479,7 +582,7 @@ int hkv_insert_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const v
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
     hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
-    mutate(t, hkv::kOpInsertOrAssign, a, view_for(t, values), kInserter, unique_key != 0,
+    mutate(t, hkv::kOpInsertOrAssign, a, values, nullptr, kInserter, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -501,7 +604,7 @@ int hkv_insert_and_evict(hkv_table* t, uint64_t n, const uint64_t* keys, const v
     a.evicted_values = static_cast<uint8_t*>(evicted_values);
     a.evicted_scores = evicted_scores;
     a.evicted_counter = reinterpret_cast<unsigned long long*>(d_evicted_counter);
-    mutate(t, hkv::kOpInsertAndEvict, a, view_for(t, values, evicted_values), kInserter,
+    mutate(t, hkv::kOpInsertAndEvict, a, values, evicted_values, kInserter,
            unique_key != 0, static_cast<cudaStream_t>(stream));
   });
 }
@@ -541,7 +644,7 @@ int hkv_accum_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys,
     a.accum_flags = accum_or_assigns;
     // the reference has no unique_key argument here and always runs its
     // duplicate-tolerant tile kernel (include/merlin_hashtable.cuh:1618-1631)
-    mutate(t, hkv::kOpAccumOrAssign, a, view_for(t, value_or_deltas), kInserter, false,
+    mutate(t, hkv::kOpAccumOrAssign, a, value_or_deltas, nullptr, kInserter, false,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -557,7 +660,7 @@ int hkv_accum_or_assign_unique(hkv_table* t, uint64_t n, const uint64_t* keys,
     hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores, ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
     a.accum_flags = accum_or_assigns;
-    mutate(t, hkv::kOpAccumOrAssign, a, view_for(t, value_or_deltas), kInserter, true,
+    mutate(t, hkv::kOpAccumOrAssign, a, value_or_deltas, nullptr, kInserter, true,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -570,7 +673,7 @@ int hkv_find_or_insert(hkv_table* t, uint64_t n, const uint64_t* keys, void* val
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
     hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
-    mutate(t, hkv::kOpFindOrInsert, a, view_for(t, values), kInserter, unique_key != 0,
+    mutate(t, hkv::kOpFindOrInsert, a, values, nullptr, kInserter, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -586,7 +689,7 @@ int hkv_find_or_insert_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void*
     a.ptrs = values;
     a.founds = founds;
     a.locked_key_ptrs = locked_key_ptrs;
-    mutate(t, hkv::kOpFindOrInsertPtr, a, t->view, kInserter, unique_key != 0,
+    mutate(t, hkv::kOpFindOrInsertPtr, a, nullptr, nullptr, kInserter, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -601,7 +704,8 @@ int hkv_lock_keys(hkv_table* t, uint64_t n, const uint64_t* keys, uint64_t** loc
     hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
     a.founds = success;
     a.locked_key_ptrs = locked_key_ptrs;
-    mutate(t, hkv::kOpLockKeys, a, t->view, kInserter, true, static_cast<cudaStream_t>(stream));
+    mutate(t, hkv::kOpLockKeys, a, nullptr, nullptr, kInserter, true,
+           static_cast<cudaStream_t>(stream));
   });
 }
 
@@ -624,7 +728,7 @@ int hkv_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const void* value
     if (n == 0) return;
     check_strategy(t, t->opt.evict_strategy, scores);
     hkv::MutateArgs a = base_args(t, n, keys, values, scores, false);
-    mutate(t, hkv::kOpAssign, a, view_for(t, values), kUpdater, unique_key != 0,
+    mutate(t, hkv::kOpAssign, a, values, nullptr, kUpdater, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -635,7 +739,7 @@ int hkv_assign_scores(hkv_table* t, uint64_t n, const uint64_t* keys, const uint
     if (n == 0) return;
     check_strategy(t, t->opt.evict_strategy, scores);
     hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
-    mutate(t, hkv::kOpAssignScores, a, t->view, kUpdater, unique_key != 0,
+    mutate(t, hkv::kOpAssignScores, a, nullptr, nullptr, kUpdater, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -645,7 +749,7 @@ int hkv_assign_values(hkv_table* t, uint64_t n, const uint64_t* keys, const void
   return guarded([&] {
     if (n == 0) return;
     hkv::MutateArgs a = base_args(t, n, keys, values, nullptr, false);
-    mutate(t, hkv::kOpAssignValues, a, view_for(t, values), kUpdater, unique_key != 0,
+    mutate(t, hkv::kOpAssignValues, a, values, nullptr, kUpdater, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -702,7 +806,7 @@ int hkv_find_and_update(hkv_table* t, uint64_t n, const uint64_t* keys, void** v
     a.scores_out = scores;
     a.ptrs = values;
     a.founds = founds;
-    mutate(t, hkv::kOpFindAndUpdate, a, t->view, kUpdater, unique_key != 0,
+    mutate(t, hkv::kOpFindAndUpdate, a, nullptr, nullptr, kUpdater, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
 }
@@ -858,7 +962,7 @@ int hkv_size(hkv_table* t, hkv_stream stream, uint64_t* size) {
     {
       LockScope ls(t, kReader, s);
       HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
-      hkv::launch_sum_sizes(t->view, ctr, s);
+      hkv::launch_sum_sizes(t->view, t->view.buckets, ctr, s);
       ls.done();
     }
     check_launch();
@@ -887,12 +991,25 @@ int hkv_set_global_epoch(hkv_table* t, uint64_t epoch) {
   return HKV_OK;
 }
 
-int hkv_reserve(hkv_table* t, uint64_t new_capacity, hkv_stream) {
+int hkv_reserve(hkv_table* t, uint64_t new_capacity, hkv_stream stream) {
   return guarded([&] {
-    if (new_capacity > t->view.capacity) {
-      throw HkvError{HKV_ERR_UNSUPPORTED,
-                     "reserve beyond the current capacity: rehash is not part of this library"};
+    DeviceGuard dg(t->device);
+    reserve(t, new_capacity, static_cast<cudaStream_t>(stream));
+  });
+}
+
+int hkv_set_max_capacity(hkv_table* t, uint64_t new_max_capacity) {
+  return guarded([&] {
+    // set_max_capacity, include/merlin_hashtable.cuh:3561-3579
+    if (new_max_capacity == 0 || (new_max_capacity & (new_max_capacity - 1)) != 0) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "None power-of-2 new_max_capacity is not supported."};
     }
+    LockScope ls(t, kInserter, nullptr);
+    if (new_max_capacity >= t->view.capacity) {
+      t->reach_max_capacity.store(false);
+      t->opt.max_capacity = new_max_capacity;
+    }
+    ls.done();
   });
 }
 

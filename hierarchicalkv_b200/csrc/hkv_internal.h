@@ -94,6 +94,11 @@ void launch_size_if(const TableView& t, int pred, uint64_t pattern, uint64_t thr
 void launch_erase_if(const TableView& t, int pred, uint64_t pattern, uint64_t threshold,
                      unsigned long long* d_counter, cudaStream_t stream);
 void launch_clear(const TableView& t, cudaStream_t stream);
-void launch_sum_sizes(const TableView& t, unsigned long long* d_total, cudaStream_t stream);
+// Sum of the sizes of the first `buckets` buckets.
+void launch_sum_sizes(const TableView& t, uint64_t buckets, unsigned long long* d_total,
+                      cudaStream_t stream);
+// Moves every live entry of `src` into the cleared table `dst`, which must have
+// exactly twice the buckets and a power-of-two capacity.
+void launch_rehash(const TableView& src, const TableView& dst, cudaStream_t stream);
 
 }  // namespace hkv

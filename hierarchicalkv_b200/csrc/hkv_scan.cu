@@ -6,6 +6,8 @@
 //   include/merlin/core_kernels.cuh:1116-1151 size_if_kernel
 //   include/merlin/core_kernels.cuh:657-676   clear_kernel
 //   include/merlin/core_kernels.cuh:1396-1423 SumOp            (size)
+//   include/merlin/core_kernels.cuh:385-401, 531-590  double_capacity +
+//                                             rehash_kernel_for_fast_mode (reserve)
 //
 // Export is a compacting scan: a block of 256 threads reads 256 consecutive
 // slots (keys and scores are linear planes, so these are two fully coalesced
@@ -125,9 +127,10 @@ __global__ void __launch_bounds__(kScanBlock)
 }
 
 __global__ void __launch_bounds__(kScanBlock)
-    sum_sizes_kernel(const TableView t, unsigned long long* __restrict__ d_total) {
+    sum_sizes_kernel(const TableView t, const uint64_t buckets,
+                     unsigned long long* __restrict__ d_total) {
   unsigned long long local = 0;
-  for (uint64_t b = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < t.buckets;
+  for (uint64_t b = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < buckets;
        b += uint64_t(gridDim.x) * blockDim.x) {
     local += static_cast<unsigned long long>(t.bucket_sizes[b]);
   }
@@ -150,6 +153,72 @@ __global__ void __launch_bounds__(kScanBlock) clear_kernel(const TableView t) {
       s[q] = make_ulonglong2(0ull, 0ull);
     }
     if ((g & 7u) == 0) t.bucket_sizes[g >> 3] = 0;
+  }
+}
+
+// Doubling rehash.  `dst` has twice the buckets of `src` and was cleared.  With
+// a power-of-two capacity a key of old bucket b lands in new bucket b or
+// b + src.buckets, so one block owns one old bucket and both of its targets
+// and no atomics are needed: thread i carries old slot i, the live keys of each
+// side are ranked in slot order with ballots, and the new position is the rank
+// (a compacted bucket; tombstones are dropped).  Lookups and inserts probe the
+// whole digest line, so any position inside the bucket is valid.  Rows are then
+// copied one per warp instruction group, coalesced.
+constexpr int kRehashBlock = kBucketSlots;
+constexpr int kRehashWarps = kRehashBlock / 32;
+
+__global__ void __launch_bounds__(kRehashBlock)
+    rehash_kernel(const TableView src, const TableView dst) {
+  __shared__ uint32_t side_count[2][kRehashWarps];
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t wid = threadIdx.x >> 5;
+  const uint32_t below = (1u << lane) - 1u;
+  for (uint64_t b = blockIdx.x; b < src.buckets; b += gridDim.x) {
+    const uint64_t slot = b * kBucketSlots + threadIdx.x;
+    const uint64_t key = src.keys[slot];
+    const bool live = !is_reserved(src, key);
+    const Address a = locate(dst, key);
+    const bool high = live && a.bucket != b;
+    const uint32_t votes_low = __ballot_sync(0xFFFFFFFFu, live && !high);
+    const uint32_t votes_high = __ballot_sync(0xFFFFFFFFu, high);
+    if (lane == 0) {
+      side_count[0][wid] = __popc(votes_low);
+      side_count[1][wid] = __popc(votes_high);
+    }
+    __syncthreads();
+    uint32_t rank = __popc((high ? votes_high : votes_low) & below);
+    for (uint32_t w = 0; w < wid; ++w) rank += side_count[high ? 1 : 0][w];
+    uint64_t to = 0;
+    if (live) {
+      to = a.bucket * kBucketSlots + rank;
+      dst.keys[to] = key;
+      dst.digests[to] = static_cast<uint8_t>(a.digest);
+      dst.scores[to] = src.scores[slot];
+    }
+    if (threadIdx.x < 2) {
+      uint32_t total = 0;
+#pragma unroll
+      for (int w = 0; w < kRehashWarps; ++w) total += side_count[threadIdx.x][w];
+      dst.bucket_sizes[b + threadIdx.x * src.buckets] = static_cast<int32_t>(total);
+    }
+    // rows: the warp walks its live lanes; all 32 lanes copy one row together
+    uint32_t todo = votes_low | votes_high;
+    while (todo) {
+      const uint32_t r = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const uint64_t from_slot = __shfl_sync(0xFFFFFFFFu, slot, r);
+      const uint64_t to_slot = __shfl_sync(0xFFFFFFFFu, to, r);
+      const uint8_t* from_row = row_ptr(src, from_slot);
+      uint8_t* to_row = row_ptr(dst, to_slot);
+      if (src.vec_bytes == 16) {
+        for (uint32_t off = lane * 16; off < src.row_bytes; off += 32 * 16) {
+          *reinterpret_cast<uint4*>(to_row + off) = *reinterpret_cast<const uint4*>(from_row + off);
+        }
+      } else {
+        for (uint32_t off = lane; off < src.row_bytes; off += 32) to_row[off] = from_row[off];
+      }
+    }
+    __syncthreads();  // side_count is rewritten by the next bucket
   }
 }
 
@@ -189,8 +258,14 @@ void launch_clear(const TableView& t, cudaStream_t stream) {
   clear_kernel<<<scan_grid(kScanBlock, t.capacity / 16), kScanBlock, 0, stream>>>(t);
 }
 
-void launch_sum_sizes(const TableView& t, unsigned long long* d_total, cudaStream_t stream) {
-  sum_sizes_kernel<<<scan_grid(kScanBlock * 4, t.buckets), kScanBlock, 0, stream>>>(t, d_total);
+void launch_sum_sizes(const TableView& t, uint64_t buckets, unsigned long long* d_total,
+                      cudaStream_t stream) {
+  sum_sizes_kernel<<<scan_grid(kScanBlock * 4, buckets), kScanBlock, 0, stream>>>(t, buckets,
+                                                                                  d_total);
+}
+
+void launch_rehash(const TableView& src, const TableView& dst, cudaStream_t stream) {
+  rehash_kernel<<<scan_grid(1, src.buckets), kRehashBlock, 0, stream>>>(src, dst);
 }
 
 }  // namespace hkv

@@ -172,6 +172,7 @@ _SIGNATURES = {
     "hkv_max_bucket_size": [_P],
     "hkv_set_global_epoch": [_P, _U64],
     "hkv_reserve": [_P, _U64, _P],
+    "hkv_set_max_capacity": [_P, _U64],
     "hkv_get_view": [_P, ctypes.POINTER(TableView)],
     "hkv_external_begin": [_P, _INT, _P],
     "hkv_external_end": [_P, _INT, _P],
@@ -478,6 +479,10 @@ class HashTable:
 
     def reserve(self, new_capacity: int, stream=None) -> None:
         self._call("hkv_reserve", new_capacity, _stream(stream))
+
+    def set_max_capacity(self, new_max_capacity: int) -> None:
+        """Raises ValueError (std::invalid_argument in the reference) unless a power of two."""
+        self._call("hkv_set_max_capacity", new_max_capacity)
 
     def view(self) -> TableView:
         v = TableView()

@@ -259,10 +259,20 @@ HKV_API const char* hkv_size_no_alloc_last_error(void);
 /* HashTable::set_global_epoch, include/merlin_hashtable.cuh:3760 */
 HKV_API int hkv_set_global_epoch(hkv_table* table, uint64_t epoch);
 
-/* HashTable::reserve / set_max_capacity, include/merlin_hashtable.cuh:3503-3579.
- * Capacity is fixed in this library: reserve succeeds only when the request
- * fits the current capacity. */
+/* HashTable::reserve, include/merlin_hashtable.cuh:3503-3545.  Doubles the
+ * capacity (rehashing every entry) until it reaches new_capacity or the next
+ * doubling would pass max_capacity; a request above max_capacity is ignored.
+ * The insert-like calls grow the same way before they run, while the load
+ * estimated from the first 1024 buckets plus the batch is above
+ * max_load_factor (include/merlin_hashtable.cuh:1151-1154, 3796-3828).  Only
+ * tables created with init_capacity * 2 <= max_capacity grow.  Synchronises
+ * the device; row and key pointers handed out before are invalid afterwards. */
 HKV_API int hkv_reserve(hkv_table* table, uint64_t new_capacity, hkv_stream stream);
+
+/* HashTable::set_max_capacity, include/merlin_hashtable.cuh:3561-3579.
+ * HKV_ERR_INVALID_ARG (std::invalid_argument in the reference) unless
+ * new_max_capacity is a power of two; ignored when below the capacity. */
+HKV_API int hkv_set_max_capacity(hkv_table* table, uint64_t new_max_capacity);
 
 /* Planes of the table for header-side functor kernels.  No counterpart in
  * the reference, whose templated kernels live in the class itself. */

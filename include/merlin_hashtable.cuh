@@ -601,13 +601,9 @@ class HashTable : public HashTableBase<K, V, S> {
   }
 
   void set_max_capacity(size_type new_max_capacity) override {
-    // merlin_hashtable.cuh:3561-3579: the capacity can only stay or grow
-    if (new_max_capacity < capacity()) {
-      throw std::invalid_argument(
-          "None of init_capacity, max_capacity and hbm_for_vectors can be zero or smaller than "
-          "the current capacity.");
-    }
-    options_.max_capacity = new_max_capacity;
+    // merlin_hashtable.cuh:3561-3579
+    detail::rethrow(hkv_set_max_capacity(table_, new_max_capacity));
+    if (new_max_capacity >= capacity()) options_.max_capacity = new_max_capacity;
   }
 
   size_type dim() const noexcept override { return options_.dim; }

@@ -127,6 +127,50 @@ REF_API int ref_create(uint64_t init_capacity, uint64_t max_capacity,
   });
 }
 
+// A table that may grow: init_capacity * 2 <= max_capacity, and the insert-like
+// calls double it while the estimated load is above max_load_factor.
+REF_API int ref_create_growable(uint64_t init_capacity, uint64_t max_capacity,
+                                uint64_t max_hbm_for_vectors, uint64_t dim,
+                                float max_load_factor, void** out) {
+  return guarded([&] {
+    nv::merlin::HashTableOptions o;
+    o.init_capacity = init_capacity;
+    o.max_capacity = max_capacity;
+    o.max_hbm_for_vectors = max_hbm_for_vectors;
+    o.dim = dim;
+    o.max_load_factor = max_load_factor;
+    size_t buckets = 1;
+    while (buckets * 2 * o.max_bucket_size <= init_capacity) buckets *= 2;
+    o.num_of_buckets_per_alloc = buckets;
+    auto* t = new Table();
+    try {
+      t->init(o);
+    } catch (...) {
+      delete t;
+      throw;
+    }
+    *out = t;
+  });
+}
+
+REF_API int ref_reserve(void* t, uint64_t new_capacity, cudaStream_t stream) {
+  return guarded([&] { static_cast<Table*>(t)->reserve(new_capacity, stream); });
+}
+
+// 0 ok, 1 the reference threw std::invalid_argument, -1 anything else
+REF_API int ref_set_max_capacity(void* t, uint64_t new_max_capacity) {
+  try {
+    static_cast<Table*>(t)->set_max_capacity(new_max_capacity);
+    return 0;
+  } catch (const std::invalid_argument& e) {
+    g_err = e.what();
+    return 1;
+  } catch (const std::exception& e) {
+    g_err = e.what();
+    return -1;
+  }
+}
+
 REF_API int ref_destroy(void* t) {
   return guarded([&] { delete static_cast<Table*>(t); });
 }

@@ -288,7 +288,66 @@ static void test_errors() {
   std::printf("errors ok\n");
 }
 
+// tests/merlin_hashtable_test.cc.cu:1080-1222 (test_rehash): the table doubles
+// on the insert path and by reserve(); entries keep their rows and scores.
+static void test_rehash() {
+  constexpr size_t kDim = 8, kInit = 1024, kMax = 8 * kInit, kN = 700;
+  using Table = nv::merlin::HashTable<K, V, S, EvictStrategy::kCustomized>;
+  HashTableOptions opt;
+  opt.init_capacity = kInit;
+  opt.max_capacity = kMax;
+  opt.max_hbm_for_vectors = nv::merlin::GB(1);
+  opt.dim = kDim;
+  opt.max_load_factor = 0.5f;
+  Table table;
+  table.init(opt);
+  std::vector<K> hk;
+  std::vector<V> hv;
+  std::vector<S> hs;
+  make_batch(777, kN, kDim, hk, hv, hs);
+  DeviceBuffer<K> dk(kN);
+  DeviceBuffer<V> dv(kN * kDim);
+  DeviceBuffer<S> ds(kN);
+  DeviceBuffer<bool> df(kN);
+  dk.upload(hk);
+  dv.upload(hv);
+  ds.upload(hs);
+  table.insert_or_assign(kN, dk.p, dv.p, ds.p);
+  EXPECT(table.capacity() == 2 * kInit);  // 700 / 1024 is above 0.5
+  EXPECT(table.size() == kN);
+  table.reserve(kMax);
+  EXPECT(table.capacity() == kMax);
+  table.reserve(2 * kMax);                 // above max_capacity: ignored
+  EXPECT(table.capacity() == kMax);
+  bool threw = false;
+  try {
+    table.set_max_capacity(3 * kMax);
+  } catch (const std::invalid_argument&) {
+    threw = true;
+  }
+  EXPECT(threw);
+  table.set_max_capacity(2 * kMax);
+  table.reserve(2 * kMax);
+  EXPECT(table.capacity() == 2 * kMax);
+  EXPECT(table.size() == kN);
+  CUDA_CHECK(cudaMemset(dv.p, 0, sizeof(V) * kN * kDim));
+  CUDA_CHECK(cudaMemset(ds.p, 0, sizeof(S) * kN));
+  table.find(kN, dk.p, dv.p, df.p, ds.p);
+  CUDA_CHECK(cudaDeviceSynchronize());
+  std::vector<V> gv = dv.download(kN * kDim);
+  std::vector<S> gs = ds.download(kN);
+  std::vector<uint8_t> gf(kN);
+  CUDA_CHECK(cudaMemcpy(gf.data(), df.p, kN, cudaMemcpyDeviceToHost));
+  for (size_t i = 0; i < kN; ++i) {
+    EXPECT(gf[i] == 1);
+    EXPECT(gs[i] == hs[i]);
+    for (size_t j = 0; j < kDim; ++j) EXPECT(gv[i * kDim + j] == hv[i * kDim + j]);
+  }
+  std::printf("rehash ok\n");
+}
+
 int main() {
+  test_rehash();
   test_errors();
   test_basic();
   test_insert_and_evict_conservation();

@@ -20,7 +20,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 
 from tests.hkv_testlib import RefTable, load_ref, to_dev  # noqa: E402
-from tests.scenarios import build_scenarios, flatten, run_scenario  # noqa: E402
+from tests.scenarios import build_scenarios, flatten, run_scenario, table_kwargs  # noqa: E402
 
 
 def device_pins(out_dir: str) -> None:
@@ -54,8 +54,7 @@ def main() -> None:
     os.makedirs(out_dir, exist_ok=True)
     device_pins(out_dir)
     for name, sc in build_scenarios().items():
-        t = RefTable(sc["capacity"], sc["dim"], sc["strategy"],
-                     reserved_key_start_bit=sc.get("reserved_key_start_bit", 0))
+        t = RefTable(sc["capacity"], sc["dim"], sc["strategy"], **table_kwargs(sc))
         res = run_scenario(t, sc)
         t.close()
         np.savez_compressed(os.path.join(out_dir, f"ref_{name}.npz"), **flatten(res))

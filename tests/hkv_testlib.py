@@ -80,6 +80,9 @@ def bucket_of(keys: np.ndarray, capacity: int) -> np.ndarray:
 _ORACLE_SIGS = {
     "orc_create": ([_U64, _U64, _U64, ctypes.c_uint32, _INT, _INT], _P),
     "orc_destroy": ([_P], None),
+    "orc_reserve": ([_P, _U64], None),
+    "orc_set_max_capacity": ([_P, _U64], _INT),
+    "orc_set_max_load_factor": ([_P, ctypes.c_float], None),
     "orc_capacity": ([_P], _U64),
     "orc_bucket_count": ([_P], _U64),
     "orc_set_global_epoch": ([_P, _U64], None),
@@ -136,12 +139,22 @@ class OracleTable:
     """Sequential CPU model with the reference's method names (numpy in/out)."""
 
     def __init__(self, capacity: int, dim: int, strategy: int = 0, reserved_key_start_bit: int = 0,
-                 max_capacity: Optional[int] = None, value_size: int = 4):
+                 max_capacity: Optional[int] = None, value_size: int = 4,
+                 max_load_factor: Optional[float] = None):
         self.lib = load_oracle()
         self.dim = dim
         self.strategy = strategy
         self.h = self.lib.orc_create(capacity, max_capacity or capacity, dim, value_size, strategy,
                                      reserved_key_start_bit)
+        if max_load_factor is not None:
+            self.lib.orc_set_max_load_factor(self.h, max_load_factor)
+
+    def reserve(self, new_capacity):
+        self.lib.orc_reserve(self.h, new_capacity)
+
+    def set_max_capacity(self, new_max_capacity):
+        if not self.lib.orc_set_max_capacity(self.h, new_max_capacity):
+            raise ValueError("None power-of-2 new_max_capacity is not supported.")
 
     def __del__(self):
         if getattr(self, "h", None):
@@ -266,7 +279,7 @@ class ProductTable:
     the parity tests (every call goes through the C ABI)."""
 
     def __init__(self, capacity, dim, strategy=0, reserved_key_start_bit=0, max_capacity=None,
-                 max_hbm_for_vectors=None, api_lock=True):
+                 max_hbm_for_vectors=None, api_lock=True, max_load_factor=None):
         import torch
         import hierarchicalkv_b200 as hkv
 
@@ -274,10 +287,17 @@ class ProductTable:
         self.dim = dim
         self.t = hkv.HashTable(hkv.EvictStrategy(strategy))
         hbm = (16 << 30) if max_hbm_for_vectors is None else max_hbm_for_vectors
+        extra = {} if max_load_factor is None else {"max_load_factor": max_load_factor}
         self.t.init(hkv.HashTableOptions(
             init_capacity=capacity, max_capacity=max_capacity or capacity,
             max_hbm_for_vectors=hbm, dim=dim, reserved_key_start_bit=reserved_key_start_bit,
-            api_lock=api_lock))
+            api_lock=api_lock, **extra))
+
+    def reserve(self, new_capacity):
+        self.t.reserve(new_capacity, self.torch.cuda.current_stream().cuda_stream)
+
+    def set_max_capacity(self, new_max_capacity):
+        self.t.set_max_capacity(new_max_capacity)
 
     def close(self):
         self.t.close()
@@ -460,6 +480,9 @@ def load_ref(strategy: int, private: bool = False) -> ctypes.CDLL:
     sig = {
         "ref_create": [_U64, _U64, _U64, _U64, _U64, _INT, _INT, ctypes.POINTER(_P)],
         "ref_destroy": [_P],
+        "ref_create_growable": [_U64, _U64, _U64, _U64, ctypes.c_float, ctypes.POINTER(_P)],
+        "ref_reserve": [_P, _U64, _P],
+        "ref_set_max_capacity": [_P, _U64],
         "ref_set_global_epoch": [_P, _U64],
         "ref_insert_or_assign": [_P, _U64, _P, _P, _P, _P, _INT],
         "ref_insert_and_evict": [_P, _U64, _P, _P, _P, _P, _P, _P, _P, _P, _INT],
@@ -499,7 +522,7 @@ class RefTable:
     _PRED = {1: 0, 2: 1, 3: 2}
 
     def __init__(self, capacity, dim, strategy=0, reserved_key_start_bit=0, max_capacity=None,
-                 max_hbm_for_vectors=None, api_lock=True):
+                 max_hbm_for_vectors=None, api_lock=True, max_load_factor=None):
         import torch
 
         self.torch = torch
@@ -507,9 +530,23 @@ class RefTable:
         self.lib = load_ref(strategy, private=reserved_key_start_bit != 0)
         self.h = _P()
         hbm = (16 << 30) if max_hbm_for_vectors is None else max_hbm_for_vectors
-        self._chk(self.lib.ref_create(capacity, max_capacity or capacity, hbm, dim, 128,
-                                      reserved_key_start_bit, int(api_lock),
-                                      ctypes.byref(self.h)))
+        if max_load_factor is not None:
+            assert reserved_key_start_bit == 0 and api_lock
+            self._chk(self.lib.ref_create_growable(capacity, max_capacity or capacity, hbm, dim,
+                                                   max_load_factor, ctypes.byref(self.h)))
+        else:
+            self._chk(self.lib.ref_create(capacity, max_capacity or capacity, hbm, dim, 128,
+                                          reserved_key_start_bit, int(api_lock),
+                                          ctypes.byref(self.h)))
+
+    def reserve(self, new_capacity):
+        self._chk(self.lib.ref_reserve(self.h, new_capacity, self._s()))
+
+    def set_max_capacity(self, new_max_capacity):
+        rc = self.lib.ref_set_max_capacity(self.h, new_max_capacity)
+        if rc == 1:
+            raise ValueError((self.lib.ref_last_error() or b"").decode())
+        self._chk(rc)
 
     def _chk(self, rc):
         if rc:

@@ -156,7 +156,54 @@ def build_scenarios() -> dict:
         ("find", np.concatenate([gk, g[1000:1200]])),
         ("export",),
     ])
+
+    # -- a table that grows: auto-rehash on the insert path, reserve, set_max_capacity ------
+    w = unique_keys(30000, seed=303)
+    steps = [("capacity",)]
+    at = 0
+    for r, n in enumerate([300, 300, 500, 900]):       # 1024 -> 2048 -> 4096 along the way
+        steps += [("insert_or_assign", w[at:at + n], _scores(1 + at, n)), ("capacity",)]
+        at += n
+    steps += [
+        ("erase", w[100:600]),                          # tombstones do not survive a rehash
+        ("size",),
+        ("reserve", 8192), ("capacity",), ("size",),
+        ("find", w[:2200]),
+        ("export",),
+        ("reserve", 1 << 20), ("capacity",),            # above max_capacity: ignored
+        ("find_or_insert", w[at:at + 3000], _scores(1 + at, 3000)), ("capacity",),
+    ]
+    at += 3000
+    for r in range(6):                                  # reaches 16384, then overfills it
+        steps += [("insert_or_assign", w[at:at + 2500], _scores(1 + at, 2500)), ("capacity",)]
+        at += 2500
+    steps += [
+        ("size",),
+        ("find", w[:at]),
+        ("set_max_capacity_rejected", 40000),           # not a power of two
+        ("set_max_capacity", 8192), ("capacity",),      # below the capacity: ignored
+        ("insert_or_assign", w[at:at + 1000], _scores(1 + at, 1000)), ("capacity",),
+        ("set_max_capacity", 65536),                    # growth resumes
+        ("insert_and_evict", w[at + 1000:at + 3000], _scores(1001 + at, 2000)), ("capacity",),
+        ("accum_or_assign", w[at + 3000:at + 4000], np.zeros(1000, dtype=bool),
+         _scores(3001 + at, 1000)),
+        ("capacity",), ("size",),
+        ("find", w[:at + 4000]),
+        ("export",),
+    ]
+    sc["customized_growth"] = dict(capacity=1024, max_capacity=16384, max_load_factor=0.5,
+                                   dim=dim, strategy=CUSTOMIZED, steps=steps)
     return sc
+
+
+def table_kwargs(scenario: dict) -> dict:
+    """Constructor keywords of OracleTable / ProductTable / RefTable beyond
+    (capacity, dim, strategy)."""
+    kw = {"reserved_key_start_bit": scenario.get("reserved_key_start_bit", 0)}
+    for name in ("max_capacity", "max_load_factor"):
+        if name in scenario:
+            kw[name] = scenario[name]
+    return kw
 
 
 def run_scenario(table, scenario: dict) -> list:
@@ -173,6 +220,18 @@ def run_scenario(table, scenario: dict) -> list:
             table.insert_or_assign(step[1], values_for(step[1], dim, seed=idx), step[2])
         elif op == "size":
             res["size"] = np.array([table.size()], dtype=np.uint64)
+        elif op == "capacity":
+            res["capacity"] = np.array([table.capacity()], dtype=np.uint64)
+        elif op == "reserve":
+            table.reserve(step[1])
+        elif op == "set_max_capacity":
+            table.set_max_capacity(step[1])
+        elif op == "set_max_capacity_rejected":
+            try:
+                table.set_max_capacity(step[1])
+                res["rejected"] = np.array([0], dtype=np.uint64)
+            except ValueError:
+                res["rejected"] = np.array([1], dtype=np.uint64)
         elif op == "find":
             v, f, s = table.find(step[1])
             res["founds"] = f

@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 from tests.hkv_testlib import OracleTable, fmix64, is_reserved, load_oracle, unique_keys, values_for
-from tests.scenarios import build_scenarios, compare, run_scenario
+from tests.scenarios import build_scenarios, compare, run_scenario, table_kwargs
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 SCENARIOS = build_scenarios()
@@ -97,6 +97,6 @@ def test_oracle_matches_recordings_of_the_reference_kernels(name):
     for field in npz.files:
         step, what = field.split(".")
         want[int(step[4:])][what] = npz[field]
-    got = run_scenario(OracleTable(sc["capacity"], sc["dim"], sc["strategy"],
-                                   reserved_key_start_bit=sc.get("reserved_key_start_bit", 0)), sc)
+    got = run_scenario(OracleTable(sc["capacity"], sc["dim"], sc["strategy"], **table_kwargs(sc)),
+                       sc)
     compare(got, want, f"{name}: oracle vs recording of the reference")

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from tests.hkv_testlib import OracleTable, ProductTable, RefTable, ref_available
-from tests.scenarios import build_scenarios, compare, flatten, run_scenario
+from tests.scenarios import build_scenarios, compare, flatten, run_scenario, table_kwargs
 
 pytestmark = pytest.mark.gpu
 
@@ -27,15 +27,14 @@ def unflatten(npz, n_steps):
 @pytest.mark.parametrize("name", sorted(SCENARIOS))
 def test_product_matches_oracle_and_reference(name):
     sc = SCENARIOS[name]
-    bit = sc.get("reserved_key_start_bit", 0)
-    prod = ProductTable(sc["capacity"], sc["dim"], sc["strategy"], reserved_key_start_bit=bit)
+    kw = table_kwargs(sc)
+    prod = ProductTable(sc["capacity"], sc["dim"], sc["strategy"], **kw)
     got = run_scenario(prod, sc)
     prod.close()
-    want = run_scenario(OracleTable(sc["capacity"], sc["dim"], sc["strategy"],
-                                    reserved_key_start_bit=bit), sc)
+    want = run_scenario(OracleTable(sc["capacity"], sc["dim"], sc["strategy"], **kw), sc)
     compare(got, want, f"{name}: product vs oracle")
     if ref_available(sc["strategy"]):
-        ref = RefTable(sc["capacity"], sc["dim"], sc["strategy"], reserved_key_start_bit=bit)
+        ref = RefTable(sc["capacity"], sc["dim"], sc["strategy"], **kw)
         live = run_scenario(ref, sc)
         ref.close()
         compare(got, live, f"{name}: product vs reference kernels")
@@ -49,7 +48,7 @@ def test_product_serialising_kernel_matches_oracle(name):
     """unique_key=false routes through the kernel that tolerates repeated keys;
     on unique batches it must give the same results."""
     sc = SCENARIOS[name]
-    bit = sc.get("reserved_key_start_bit", 0)
+    kw = table_kwargs(sc)
 
     class NonUnique(ProductTable):
         def insert_or_assign(self, keys, values, scores=None, **kw):
@@ -61,9 +60,8 @@ def test_product_serialising_kernel_matches_oracle(name):
         def insert_and_evict(self, keys, values, scores=None, **kw):
             return super().insert_and_evict(keys, values, scores, unique_key=False)
 
-    prod = NonUnique(sc["capacity"], sc["dim"], sc["strategy"], reserved_key_start_bit=bit)
+    prod = NonUnique(sc["capacity"], sc["dim"], sc["strategy"], **kw)
     got = run_scenario(prod, sc)
     prod.close()
-    want = run_scenario(OracleTable(sc["capacity"], sc["dim"], sc["strategy"],
-                                    reserved_key_start_bit=bit), sc)
+    want = run_scenario(OracleTable(sc["capacity"], sc["dim"], sc["strategy"], **kw), sc)
     compare(got, want, f"{name}: serialising kernel vs oracle")
