@@ -251,6 +251,7 @@ hkv::TableView view_for(const hkv_table* t, const void* a, const void* b = nullp
       while ((1u << shift) < v.chunks_per_row) ++shift;
     }
     v.chunks_per_row_shift = shift;
+    v.chunks_per_row_magic = hkv::chunks_per_row_magic_of(v.chunks_per_row);
   }
   return v;
 }
@@ -527,6 +528,7 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
         while ((1u << s) < v.chunks_per_row) ++s;
         v.chunks_per_row_shift = s;
       }
+      v.chunks_per_row_magic = hkv::chunks_per_row_magic_of(v.chunks_per_row);
       // reserved keys, include/merlin/types.cuh:80-109
       const int bit = o.reserved_key_start_bit;
       if (bit == 0) {

@@ -60,6 +60,7 @@ struct TableView {
   uint32_t vec_bytes;     // widest power-of-two access usable on a row
   uint32_t chunks_per_row;        // row_bytes / vec_bytes
   int32_t chunks_per_row_shift;   // log2(chunks_per_row) or -1
+  uint32_t chunks_per_row_magic;  // floor(2^32 / chunks_per_row) + 1 (when not a power of two)
   uint32_t capacity_pow2;         // 1 when capacity is a power of two
   uint64_t empty_key;
   uint64_t reclaim_key;
@@ -140,6 +141,16 @@ __device__ __forceinline__ uint64_t cas_acquire(uint64_t* p, uint64_t expected,
   asm volatile("atom.acquire.gpu.global.cas.b64 %0, [%1], %2, %3;"
                : "=l"(old)
                : "l"(p), "l"(expected), "l"(desired)
+               : "memory");
+  return old;
+}
+
+// Swaps `desired` in and returns what was there.
+__device__ __forceinline__ uint64_t exch_acquire(uint64_t* p, uint64_t desired) {
+  uint64_t old;
+  asm volatile("atom.acquire.gpu.global.exch.b64 %0, [%1], %2;"
+               : "=l"(old)
+               : "l"(p), "l"(desired)
                : "memory");
   return old;
 }
@@ -265,6 +276,20 @@ __device__ __forceinline__ uint32_t replicate4(uint32_t byte) {
   return byte * 0x01010101u;
 }
 
+// Row of chunk c (c / chunks_per_row) without an integer division: a shift for
+// power-of-two rows, otherwise a multiply by the rounded-up reciprocal, which
+// can only overshoot by one.
+__host__ __device__ __forceinline__ uint32_t chunks_per_row_magic_of(uint32_t cpr) {
+  return cpr > 1 ? uint32_t((uint64_t(1) << 32) / cpr) + 1u : 0u;
+}
+
+__device__ __forceinline__ uint32_t row_of_chunk(const TableView& t, uint32_t c) {
+  if (t.chunks_per_row_shift >= 0) return c >> t.chunks_per_row_shift;
+  uint32_t r = __umulhi(c, t.chunks_per_row_magic);
+  if (r * t.chunks_per_row > c) --r;
+  return r;
+}
+
 // ---- warp-cooperative row copy --------------------------------------------
 //
 // A warp owns up to 32 consecutive rows of a batch buffer (`batch_rows` points
@@ -282,7 +307,6 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
   using T = typename VecType<VEC>::type;
   constexpr int U = (VEC == 16) ? 8 : 4;  // chunks in flight per lane
   const uint32_t cpr = t.chunks_per_row;
-  const int32_t shift = t.chunks_per_row_shift;
   const uint32_t total = cpr * 32u;
   for (uint32_t base = 0; base < total; base += 32u * U) {
     T regs[U];
@@ -291,7 +315,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t c = base + u * 32u + lane;
-      const uint32_t r = shift >= 0 ? (c >> shift) : (c / cpr);
+      const uint32_t r = row_of_chunk(t, c);
       const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r & 31u);
       ok[u] = (c < total) && (s != kNoSlot);
       const uint32_t off = (c - r * cpr) * VEC;
@@ -337,7 +361,6 @@ __device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint
   using T = typename VecType<VEC>::type;
   constexpr int U = (VEC == 16) ? 8 : 4;
   const uint32_t cpr = t.chunks_per_row;
-  const int32_t shift = t.chunks_per_row_shift;
   const uint32_t total = cpr * 32u;
   for (uint32_t base = 0; base < total; base += 32u * U) {
     T regs[U];
@@ -345,7 +368,7 @@ __device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t c = base + u * 32u + lane;
-      const uint32_t r = shift >= 0 ? (c >> shift) : (c / cpr);
+      const uint32_t r = row_of_chunk(t, c);
       const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r & 31u);
       const uint32_t d = __shfl_sync(0xFFFFFFFFu, dest_row, r & 31u);
       drow[u] = kNoSlot;
@@ -358,7 +381,7 @@ __device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint
     for (int u = 0; u < U; ++u) {
       if (drow[u] != kNoSlot) {
         const uint32_t c = base + u * 32u + lane;
-        const uint32_t r = shift >= 0 ? (c >> shift) : (c / cpr);
+        const uint32_t r = row_of_chunk(t, c);
         *reinterpret_cast<T*>(dest_base + uint64_t(drow[u]) * t.row_bytes + (c - r * cpr) * VEC) =
             regs[u];
       }
@@ -378,9 +401,16 @@ __device__ __forceinline__ void warp_gather_rows_to(const TableView& t, uint8_t*
   }
 }
 
-template <int MODE>
+// VEC != 0 fixes the access width at compile time (the launcher picks the
+// instantiation that matches t.vec_bytes), which keeps the four other unrolled
+// copy loops out of the hot kernels' instruction footprint.
+template <int MODE, int VEC = 0>
 __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
                                                uint32_t slot, uint32_t lane) {
+  if constexpr (VEC != 0) {
+    warp_move_rows_vec<VEC, MODE>(t, batch_rows, slot, lane);
+    return;
+  }
   // vec_bytes is warp-uniform; the host lowers it when a batch pointer is
   // less aligned than the rows.
   switch (t.vec_bytes) {

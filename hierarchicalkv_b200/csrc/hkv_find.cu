@@ -95,7 +95,7 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
 // FORM 3: founds only                     (contains, merlin_hashtable.cuh:2856)
 // FORM 4: founds (+scores) and, per key, its slot and its batch index: the
 //         first step of find on a table whose rows partly live in host memory
-template <int FORM>
+template <int FORM, int VEC>
 __global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
     find_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
                 uint8_t* __restrict__ values, void** __restrict__ ptrs, bool* __restrict__ founds,
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
   }
   if (FORM == 0 || FORM == 2) {
     if (values != nullptr) {
-      warp_move_rows<0>(t, values + base * t.row_bytes, slot, pl.lane);
+      warp_move_rows<0, VEC>(t, values + base * t.row_bytes, slot, pl.lane);
     }
   }
 }
@@ -205,7 +205,8 @@ void launch_form(const TableView& t, uint64_t n, const uint64_t* keys, void* val
   if (n == 0) return;
   const uint64_t warps = (n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kFindBlock - 1) / kFindBlock;
-  find_kernel<FORM><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
+  auto kernel = t.vec_bytes == 16 ? find_kernel<FORM, 16> : find_kernel<FORM, 0>;
+  kernel<<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
       t, keys, n, static_cast<uint8_t*>(values), ptrs, founds, scores, missed_keys, missed_indices,
       missed_size, nullptr, nullptr);
 }
@@ -255,7 +256,7 @@ bool launch_find_hybrid(const TableView& t, uint64_t n, const uint64_t* keys, vo
   uint32_t* slot_sorted = reinterpret_cast<uint32_t*>(work + 2 * arrays);
   uint32_t* index_sorted = reinterpret_cast<uint32_t*>(work + 3 * arrays);
   const uint64_t blocks = (((n + 31) / 32) * 32 + kFindBlock - 1) / kFindBlock;
-  find_kernel<4><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
+  find_kernel<4, 0><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
       t, keys, n, nullptr, nullptr, founds, scores, nullptr, nullptr, nullptr, slot, index);
   cub::DeviceRadixSort::SortPairs(work + 4 * arrays, temp_bytes, slot, slot_sorted, index,
                                   index_sorted, static_cast<int>(n), 0, 32, stream);

@@ -205,9 +205,10 @@ __device__ __forceinline__ void group_min_score(const TableView& t, const ProbeL
 // Copies one row with all 32 lanes (used for the few rows that do not follow
 // the warp's batch order, e.g. refused inputs leaving through the evicted
 // arrays).
+template <int VEC = 0>
 __device__ __forceinline__ void warp_copy_one_row(const TableView& t, uint8_t* dst,
                                                   const uint8_t* src, uint32_t lane) {
-  const uint32_t vec = t.vec_bytes;
+  const uint32_t vec = VEC != 0 ? uint32_t(VEC) : t.vec_bytes;
   const uint32_t cpr = t.chunks_per_row;
   if (vec == 16) {
     for (uint32_t c = lane; c < cpr; c += 32)
@@ -244,7 +245,7 @@ __device__ __forceinline__ void warp_copy_one_row(const TableView& t, uint8_t* d
 //            the next iteration; it polls the foreign lock (bounded) only
 //            after step C, when the warp holds nothing.  The victim is always
 //            the true current minimum, as in the reference (upsert.cuh:149-215).
-template <int OP>
+template <int OP, int VEC>
 __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutateMinBlocks - 2 : kMutateMinBlocks)
     mutate_kernel(const TableView t, const MutateArgs args) {
   const uint32_t full = 0xFFFFFFFFu;
@@ -429,17 +430,17 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
     }
     if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
         OP == kOpAssignValues) {
-      warp_move_rows<1>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
+      warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
                         pl.lane);
     } else if (OP == kOpFindOrInsert) {
-      warp_move_rows<0>(t, args.values + base * t.row_bytes,
+      warp_move_rows<0, VEC>(t, args.values + base * t.row_bytes,
                         my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-      warp_move_rows<1>(t, args.values + base * t.row_bytes,
+      warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes,
                         my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
     } else if (OP == kOpAccumOrAssign) {
-      warp_move_rows<2>(t, args.values + base * t.row_bytes,
+      warp_move_rows<2, VEC>(t, args.values + base * t.row_bytes,
                         my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-      warp_move_rows<1>(t, args.values + base * t.row_bytes,
+      warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes,
                         my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
     }
     __syncwarp();
@@ -500,10 +501,12 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
         } else {
           const uint32_t slot = (my_bucket << 7) + my_pos;
           uint64_t* kp = t.keys + slot;
-          victim = ld_relaxed(kp);
+          // one round trip: swapping LOCKED in returns the victim; over a slot
+          // that is already LOCKED the swap changes nothing
+          victim = exch_acquire(kp, t.locked_key);
           if (victim == t.locked_key) {
             wait_on = kp;
-          } else if (cas_acquire(kp, victim, t.locked_key) == victim) {
+          } else {
             uint64_t* sp = t.scores + slot;
             if (ld_relaxed(sp) > my_min) {
               st_release(kp, victim);  // the slot was refreshed in between: scan again
@@ -548,19 +551,19 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
             // lane r carries the slot of the r-th evicting lane
             const uint32_t src = __fns(ev, 0, pl.lane + 1);
             const uint32_t s = __shfl_sync(full, my_slot, src & 31u);
-            warp_move_rows<0>(t, args.evicted_values + first * t.row_bytes,
+            warp_move_rows<0, VEC>(t, args.evicted_values + first * t.row_bytes,
                               src == 0xFFFFFFFFu ? kNoSlot : s, pl.lane);
             __syncwarp();  // the old rows are out before the new ones come in
           }
           for (uint32_t left = rf, q = 0; left != 0; left &= left - 1, ++q) {
             const uint32_t src = __ffs(left) - 1;
-            warp_copy_one_row(t, args.evicted_values + (first + __popc(ev) + q) * t.row_bytes,
+            warp_copy_one_row<VEC>(t, args.evicted_values + (first + __popc(ev) + q) * t.row_bytes,
                               args.values + (base + src) * t.row_bytes, pl.lane);
           }
         }
       }
       if (op_writes_row_on_insert(OP)) {
-        warp_move_rows<1>(t, args.values + base * t.row_bytes, placed ? my_slot : kNoSlot,
+        warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes, placed ? my_slot : kNoSlot,
                           pl.lane);
       }
       __syncwarp();
@@ -888,7 +891,8 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
   const uint64_t warps = (args.n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kMutateBlock - 1) / kMutateBlock;
   if (unique_key) {
-    mutate_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+    auto kernel = t.vec_bytes == 16 ? mutate_kernel<OP, 16> : mutate_kernel<OP, 0>;
+    kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
   } else {
     mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
   }

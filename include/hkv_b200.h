@@ -275,7 +275,9 @@ HKV_API int hkv_reserve(hkv_table* table, uint64_t new_capacity, hkv_stream stre
 HKV_API int hkv_set_max_capacity(hkv_table* table, uint64_t new_max_capacity);
 
 /* Planes of the table for header-side functor kernels.  No counterpart in
- * the reference, whose templated kernels live in the class itself. */
+ * the reference, whose templated kernels live in the class itself.  The planes
+ * are replaced when the table doubles (hkv_reserve, growth on the insert
+ * path): fetch the view between hkv_external_begin and hkv_external_end. */
 HKV_API int hkv_get_view(const hkv_table* table, hkv_table_view* view);
 
 /* Bracket a kernel the CALLER launches on `stream` over hkv_get_view's planes

@@ -2,8 +2,15 @@
 // include/merlin/utils.cuh:127-135, 338-342).
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include <cstddef>
 #include <cstdint>
+
+// Functors written for export_batch_if_v2 / erase_if_v2 / for_each name the
+// tile type as cg::thread_block_tile<GroupSize>; the reference provides this
+// alias at global scope (include/merlin/utils.cuh:30).
+namespace cg = cooperative_groups;
 
 namespace nv {
 namespace merlin {

@@ -10,8 +10,9 @@
 //   t.insert_or_assign(n, d_keys, d_values, nullptr, stream);
 //
 // Link with -lhkv_b200.  User-templated functors (export_batch_if<Pred>,
-// size_if<Pred>) are evaluated by small kernels in this header over the
-// table's planes (hkv_get_view); everything else runs inside the library.
+// export_batch_if_v2, size_if<Pred>, erase_if<Pred>, erase_if_v2, for_each)
+// are evaluated by small kernels in this header over the table's planes
+// (hkv_get_view); everything else runs inside the library.
 //
 // Differences a caller can observe are listed in INTEGRATION.md.
 #pragma once
@@ -218,6 +219,111 @@ __global__ void erase_if_kernel(const hkv_table_view v, const K pattern, const S
   }
   for (int o = 16; o > 0; o >>= 1) local += __shfl_down_sync(0xFFFFFFFFu, local, o);
   if ((threadIdx.x & 31u) == 0 && local) atomicAdd(d_counter, local);
+}
+
+// ---- functors that see the value row and a cooperative tile ------------------
+//
+// export_batch_if_v2 / erase_if_v2 / for_each hand each slot's key, row and
+// score to a functor together with a tile of GroupSize threads that hold
+// GroupSize consecutive slots; the functor may exchange data inside the tile
+// (merlin_hashtable.cuh:3306-3407, 3007-3053).  The tile width follows the
+// reference: the widest of 32 / 16 / 8 that does not exceed dim and divides the
+// number of slots scanned, else 1, so whole tiles enter and leave the loop
+// together.
+template <class Launch>
+inline void dispatch_tile(uint64_t dim, uint64_t n, Launch&& launch) {
+  if (dim >= 32 && n % 32 == 0) {
+    launch(std::integral_constant<uint32_t, 32>{});
+  } else if (dim >= 16 && n % 16 == 0) {
+    launch(std::integral_constant<uint32_t, 16>{});
+  } else if (dim >= 8 && n % 8 == 0) {
+    launch(std::integral_constant<uint32_t, 8>{});
+  } else {
+    launch(std::integral_constant<uint32_t, 1>{});
+  }
+}
+
+inline unsigned tile_scan_blocks(uint64_t n) {
+  return static_cast<unsigned>(std::min<uint64_t>((n + 127) / 128, 148 * 16));
+}
+
+template <class K, class V, class S, class PredFunctor, uint32_t G>
+__global__ void export_if_v2_kernel(const hkv_table_view v, PredFunctor pred, const uint64_t n,
+                                    const uint64_t offset, size_t* d_counter, K* out_keys,
+                                    V* out_values, S* out_scores) {
+  cg::thread_block_tile<G> g = cg::tiled_partition<G>(cg::this_thread_block());
+  const uint64_t dim = v.row_bytes / sizeof(V);
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += uint64_t(gridDim.x) * blockDim.x) {
+    const uint64_t slot = offset + i;
+    const K key = static_cast<K>(v.keys[slot]);
+    const S score = static_cast<S>(v.scores[slot]);
+    const V* value = reinterpret_cast<const V*>(view_row(v, slot));
+    bool match = pred.template operator()<G>(key, value, score, g);
+    match = match && !view_is_reserved(v, static_cast<uint64_t>(key));
+    const uint32_t votes = g.ballot(match);
+    if (votes == 0) continue;
+    unsigned long long at = 0;
+    if (g.thread_rank() == 0) {
+      at = atomicAdd(reinterpret_cast<unsigned long long*>(d_counter),
+                     static_cast<unsigned long long>(__popc(votes)));
+    }
+    at = g.shfl(at, 0);
+    if (match) {
+      const uint32_t mine = __popc(votes & ((1u << g.thread_rank()) - 1u));
+      out_keys[at + mine] = key;
+      if (out_scores != nullptr) out_scores[at + mine] = score;
+    }
+    uint32_t left = votes;
+    while (left) {
+      const uint32_t src = __ffs(left) - 1;
+      left &= left - 1;
+      const V* row = g.shfl(value, src);
+      V* dst = out_values + at * dim;
+      for (uint64_t j = g.thread_rank(); j < dim; j += G) dst[j] = row[j];
+      ++at;
+    }
+  }
+}
+
+template <class K, class V, class S, class PredFunctor, uint32_t G>
+__global__ void erase_if_v2_kernel(const hkv_table_view v, PredFunctor pred, const uint64_t n,
+                                   const uint8_t reclaim_digest,
+                                   unsigned long long* d_counter) {
+  cg::thread_block_tile<G> g = cg::tiled_partition<G>(cg::this_thread_block());
+  for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < n;
+       slot += uint64_t(gridDim.x) * blockDim.x) {
+    const K key = static_cast<K>(v.keys[slot]);
+    const S score = static_cast<S>(v.scores[slot]);
+    const V* value = reinterpret_cast<const V*>(view_row(v, slot));
+    bool match = pred.template operator()<G>(key, value, score, g);
+    match = match && !view_is_reserved(v, static_cast<uint64_t>(key));
+    const uint32_t votes = g.ballot(match);
+    if (g.thread_rank() == 0 && votes) {
+      atomicAdd(d_counter, static_cast<unsigned long long>(__popc(votes)));
+      // G divides 128: a tile never straddles two buckets
+      atomicSub(v.bucket_sizes + (slot >> 7), __popc(votes));
+    }
+    if (match) {
+      v.keys[slot] = v.reclaim_key;
+      v.digests[slot] = reclaim_digest;
+      v.scores[slot] = 0;
+    }
+  }
+}
+
+template <class K, class V, class S, class ExecutionFunc, uint32_t G>
+__global__ void for_each_kernel(const hkv_table_view v, ExecutionFunc f, const uint64_t n,
+                                const uint64_t first) {
+  cg::thread_block_tile<G> g = cg::tiled_partition<G>(cg::this_thread_block());
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += uint64_t(gridDim.x) * blockDim.x) {
+    const uint64_t slot = first + i;
+    const K key = static_cast<K>(v.keys[slot]);
+    S* score = reinterpret_cast<S*>(v.scores + slot);
+    V* value = reinterpret_cast<V*>(const_cast<uint8_t*>(view_row(v, slot)));
+    f.template operator()<G>(key, value, score, g);
+  }
 }
 
 }  // namespace detail
@@ -517,9 +623,9 @@ class HashTable : public HashTableBase<K, V, S> {
                        const size_type offset, size_type* d_counter, key_type* keys,
                        value_type* values, score_type* scores = nullptr,
                        cudaStream_t stream = 0) const {
-    hkv_table_view v{};
-    detail::rethrow(hkv_get_view(table_, &v));
     detail::rethrow(hkv_external_begin(table_, 0, stream));
+    hkv_table_view v{};
+    hkv_get_view(table_, &v);  // after the lock: a doubling replaces the planes
     cudaError_t err = cudaMemsetAsync(d_counter, 0, sizeof(size_type), stream);
     if (err == cudaSuccess && offset < v.capacity) {
       n = std::min<size_type>(v.capacity - offset, n);
@@ -538,9 +644,9 @@ class HashTable : public HashTableBase<K, V, S> {
   template <template <typename, typename> class PredFunctor>
   void size_if(const key_type& pattern, const score_type& threshold, size_type* d_counter,
                cudaStream_t stream = 0) const {
-    hkv_table_view v{};
-    detail::rethrow(hkv_get_view(table_, &v));
     detail::rethrow(hkv_external_begin(table_, 0, stream));
+    hkv_table_view v{};
+    hkv_get_view(table_, &v);  // after the lock: a doubling replaces the planes
     cudaError_t err = cudaMemsetAsync(d_counter, 0, sizeof(size_type), stream);
     if (err == cudaSuccess) {
       detail::size_if_kernel<K, S, PredFunctor>
@@ -556,11 +662,11 @@ class HashTable : public HashTableBase<K, V, S> {
   template <template <typename, typename> class PredFunctor>
   size_type erase_if(const key_type& pattern, const score_type& threshold,
                      cudaStream_t stream = 0) {
-    hkv_table_view v{};
-    detail::rethrow(hkv_get_view(table_, &v));
     unsigned long long* d_count = nullptr;
     CUDA_CHECK(cudaMallocAsync(reinterpret_cast<void**>(&d_count), sizeof(*d_count), stream));
     detail::rethrow(hkv_external_begin(table_, 2, stream));
+    hkv_table_view v{};
+    hkv_get_view(table_, &v);  // after the lock: a doubling replaces the planes
     cudaError_t err = cudaMemsetAsync(d_count, 0, sizeof(*d_count), stream);
     if (err == cudaSuccess) {
       const uint8_t reclaim_digest =
@@ -578,6 +684,87 @@ class HashTable : public HashTableBase<K, V, S> {
     cudaFreeAsync(d_count, stream);
     CUDA_CHECK(err);
     return count;
+  }
+
+  // export_batch_if_v2<PredFunctor>, merlin_hashtable.cuh:3306-3347.  The
+  // functor is the reference's: pred.operator()<GroupSize>(key, value, score,
+  // tile).  Reserved keys (empty slots, tombstones) are never exported.
+  template <typename PredFunctor>
+  void export_batch_if_v2(PredFunctor& pred, size_type n, const size_type offset,
+                          size_type* d_counter, key_type* keys, value_type* values,
+                          score_type* scores = nullptr, cudaStream_t stream = 0) const {
+    detail::rethrow(hkv_external_begin(table_, 0, stream));
+    hkv_table_view v{};
+    int rc = hkv_get_view(table_, &v);
+    cudaError_t err = cudaMemsetAsync(d_counter, 0, sizeof(size_type), stream);
+    if (rc == HKV_OK && err == cudaSuccess && offset < v.capacity) {
+      n = std::min<size_type>(v.capacity - offset, n);
+      if (n > 0) {
+        detail::dispatch_tile(options_.dim, n, [&](auto tile) {
+          detail::export_if_v2_kernel<K, V, S, PredFunctor, decltype(tile)::value>
+              <<<detail::tile_scan_blocks(n), 128, 0, stream>>>(v, pred, n, offset, d_counter,
+                                                               keys, values, scores);
+        });
+        err = cudaGetLastError();
+      }
+    }
+    detail::rethrow(hkv_external_end(table_, 0, stream));
+    detail::rethrow(rc);
+    CUDA_CHECK(err);
+  }
+
+  // erase_if_v2<PredFunctor>, merlin_hashtable.cuh:3007-3053: returns the
+  // number of erased keys (synchronises the stream).
+  template <typename PredFunctor>
+  size_type erase_if_v2(PredFunctor& pred, cudaStream_t stream = 0) {
+    unsigned long long* d_count = nullptr;
+    CUDA_CHECK(cudaMallocAsync(reinterpret_cast<void**>(&d_count), sizeof(*d_count), stream));
+    detail::rethrow(hkv_external_begin(table_, 2, stream));
+    hkv_table_view v{};
+    int rc = hkv_get_view(table_, &v);
+    cudaError_t err = cudaMemsetAsync(d_count, 0, sizeof(*d_count), stream);
+    if (rc == HKV_OK && err == cudaSuccess) {
+      const uint8_t reclaim_digest = static_cast<uint8_t>(Murmur3HashHost(v.reclaim_key) >> 32);
+      const uint64_t n = v.capacity;
+      detail::dispatch_tile(options_.dim, n, [&](auto tile) {
+        detail::erase_if_v2_kernel<K, V, S, PredFunctor, decltype(tile)::value>
+            <<<detail::tile_scan_blocks(n), 128, 0, stream>>>(v, pred, n, reclaim_digest, d_count);
+      });
+      err = cudaGetLastError();
+    }
+    detail::rethrow(hkv_external_end(table_, 2, stream));
+    unsigned long long count = 0;
+    if (err == cudaSuccess) {
+      err = cudaMemcpyAsync(&count, d_count, sizeof(count), cudaMemcpyDeviceToHost, stream);
+    }
+    if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+    cudaFreeAsync(d_count, stream);
+    detail::rethrow(rc);
+    CUDA_CHECK(err);
+    return count;
+  }
+
+  // for_each<ExecutionFunc>, merlin_hashtable.cuh:3371-3407: applies
+  // f.operator()<GroupSize>(key, value*, score*, tile) to every slot of
+  // [first, last), occupied or not, under the exclusive lock.
+  template <typename ExecutionFunc>
+  void for_each(const size_type first, const size_type last, ExecutionFunc& f,
+                cudaStream_t stream = 0) {
+    detail::rethrow(hkv_external_begin(table_, 2, stream));
+    hkv_table_view v{};
+    int rc = hkv_get_view(table_, &v);
+    cudaError_t err = cudaSuccess;
+    if (rc == HKV_OK && first < v.capacity && last <= v.capacity && first < last) {
+      const uint64_t n = last - first;
+      detail::dispatch_tile(options_.dim, n, [&](auto tile) {
+        detail::for_each_kernel<K, V, S, ExecutionFunc, decltype(tile)::value>
+            <<<detail::tile_scan_blocks(n), 128, 0, stream>>>(v, f, n, first);
+      });
+      err = cudaGetLastError();
+    }
+    detail::rethrow(hkv_external_end(table_, 2, stream));
+    detail::rethrow(rc);
+    CUDA_CHECK(err);
   }
 
   bool empty(cudaStream_t stream = 0) const override { return size(stream) == 0; }

@@ -43,6 +43,51 @@ struct ScoreBelow {
   }
 };
 
+// Functors of the forms export_batch_if_v2 / erase_if_v2 / for_each take
+// (tests/export_batch_if_test.cc.cu:34-130 of the reference shows the shapes).
+// ScoreBelowAndRowIntact checks the score alone, then lets the tile verify the
+// selected rows together: every element must equal float(key * 1e-5).
+template <class K_, class V_, class S_>
+struct ScoreBelowAndRowIntact {
+  S_ threshold;
+  int dim;
+  template <int GroupSize>
+  __forceinline__ __device__ bool operator()(const K_& key, const V_* value, const S_& score,
+                                             cg::thread_block_tile<GroupSize>& g) {
+    bool keep = score < threshold;
+    for (int r = 0; r < GroupSize; ++r) {
+      const bool r_keep = g.shfl(keep, r);
+      if (!r_keep) continue;
+      const V_* row = g.shfl(value, r);
+      const V_ want = static_cast<V_>(g.shfl(key, r) * 0.00001);
+      bool bad = false;
+      for (int j = g.thread_rank(); j < dim; j += GroupSize) bad |= row[j] != want;
+      if (g.any(bad) && g.thread_rank() == r) keep = false;
+    }
+    return keep;
+  }
+};
+
+// for_each body: rows of keys with score < threshold are negated by the tile
+// and their score is raised by one.
+template <class K_, class V_, class S_>
+struct NegateRowsBelow {
+  S_ threshold;
+  int dim;
+  template <int GroupSize>
+  __forceinline__ __device__ void operator()(const K_& key, V_* value, S_* score,
+                                             cg::thread_block_tile<GroupSize>& g) {
+    // empty slots and tombstones are visited too
+    const bool hit = (key & 0xFFFFFFFFFFFFFFFCull) != 0xFFFFFFFFFFFFFFFCull && *score < threshold;
+    for (int r = 0; r < GroupSize; ++r) {
+      if (!g.shfl(hit, r)) continue;
+      V_* row = g.shfl(value, r);
+      for (int j = g.thread_rank(); j < dim; j += GroupSize) row[j] = -row[j];
+    }
+    if (hit) *score += 1;
+  }
+};
+
 template <class T>
 struct DeviceBuffer {
   T* p = nullptr;
@@ -346,8 +391,109 @@ static void test_rehash() {
   std::printf("rehash ok\n");
 }
 
+// export_batch_if_v2, erase_if_v2 and for_each with functors that use the
+// value row and the cooperative tile; dim 16 and dim 4 select tiles of 16 and
+// of 1 thread.
+template <size_t kDim>
+static void test_tile_functors() {
+  constexpr size_t kCap = 64 * 1024, kN = 24 * 1024;
+  using Table = nv::merlin::HashTable<K, V, S, EvictStrategy::kCustomized>;
+  HashTableOptions opt;
+  opt.init_capacity = opt.max_capacity = kCap;
+  opt.max_hbm_for_vectors = nv::merlin::GB(1);
+  opt.dim = kDim;
+  Table table;
+  table.init(opt);
+  std::vector<K> hk;
+  std::vector<V> hv;
+  std::vector<S> hs;
+  make_batch(31337, kN, kDim, hk, hv, hs);
+  // damage every 7th row: the predicate must drop those
+  for (size_t i = 0; i < kN; i += 7) hv[i * kDim + (i % kDim)] *= -1.0f;
+  DeviceBuffer<K> dk(kN);
+  DeviceBuffer<V> dv(kN * kDim);
+  DeviceBuffer<S> ds(kN);
+  dk.upload(hk);
+  dv.upload(hv);
+  ds.upload(hs);
+  table.insert_or_assign(kN, dk.p, dv.p, ds.p);
+  EXPECT(table.size() == kN);
+
+  std::vector<S> sorted = hs;
+  std::sort(sorted.begin(), sorted.end());
+  const S threshold = sorted[kN / 3];
+  std::set<K> want;
+  for (size_t i = 0; i < kN; ++i) {
+    if (hs[i] < threshold && i % 7 != 0) want.insert(hk[i]);
+  }
+
+  DeviceBuffer<size_t> dc(1);
+  DeviceBuffer<K> ek(kCap);
+  DeviceBuffer<V> ev(kCap * kDim);
+  DeviceBuffer<S> es(kCap);
+  ScoreBelowAndRowIntact<K, V, S> pred{threshold, int(kDim)};
+  table.export_batch_if_v2(pred, table.capacity(), 0, dc.p, ek.p, ev.p, es.p);
+  CUDA_CHECK(cudaDeviceSynchronize());
+  const size_t got = dc.download(1)[0];
+  EXPECT(got == want.size());
+  auto xk = ek.download(got);
+  auto xv = ev.download(got * kDim);
+  auto xs = es.download(got);
+  for (size_t i = 0; i < got; ++i) {
+    EXPECT(want.count(xk[i]) == 1);
+    EXPECT(xs[i] == xk[i]);
+    for (size_t j = 0; j < kDim; ++j) EXPECT(xv[i * kDim + j] == static_cast<float>(xk[i] * 0.00001));
+  }
+  // a window that is not a multiple of 8 runs with tiles of one thread
+  table.export_batch_if_v2(pred, table.capacity() - 3, 1, dc.p, ek.p, ev.p, es.p);
+  CUDA_CHECK(cudaDeviceSynchronize());
+  EXPECT(dc.download(1)[0] <= got && dc.download(1)[0] + 3 >= got);
+
+  // for_each: negate the selected rows, bump their scores
+  NegateRowsBelow<K, V, S> body{threshold, int(kDim)};
+  table.for_each(0, table.capacity(), body);
+  DeviceBuffer<bool> df(kN);
+  table.find(kN, dk.p, dv.p, df.p, ds.p);
+  CUDA_CHECK(cudaDeviceSynchronize());
+  auto fv = dv.download(kN * kDim);
+  auto fs = ds.download(kN);
+  for (size_t i = 0; i < kN; ++i) {
+    const bool hit = hs[i] < threshold;
+    EXPECT(fs[i] == hs[i] + (hit ? 1 : 0));
+    for (size_t j = 0; j < kDim; ++j) {
+      EXPECT(fv[i * kDim + j] == (hit ? -hv[i * kDim + j] : hv[i * kDim + j]));
+    }
+  }
+  // put the rows back, then erase with the tile predicate
+  table.for_each(0, table.capacity(), body);   // scores are now +1 or +2, rows of hits restored
+  ScoreBelowAndRowIntact<K, V, S> erase_pred{threshold + 2, int(kDim)};
+  size_t want_erased = 0;
+  std::vector<uint8_t> erased(kN, 0);
+  for (size_t i = 0; i < kN; ++i) {
+    // the second for_each saw score+1 < threshold for all but the keys just below it
+    const S after = hs[i] + (hs[i] < threshold ? 1 : 0) + (hs[i] + 1 < threshold ? 1 : 0);
+    const bool twice = hs[i] < threshold && hs[i] + 1 < threshold;
+    const bool once = hs[i] < threshold && !twice;
+    const bool intact = (i % 7 != 0) && !once;   // negated once: no longer key * 1e-5
+    erased[i] = after < threshold + 2 && intact;
+    want_erased += erased[i];
+  }
+  EXPECT(table.erase_if_v2(erase_pred) == want_erased);
+  EXPECT(table.size() == kN - want_erased);
+  dk.upload(hk);
+  table.find(kN, dk.p, dv.p, df.p, ds.p);
+  CUDA_CHECK(cudaDeviceSynchronize());
+  std::vector<uint8_t> gf(kN);
+  CUDA_CHECK(cudaMemcpy(gf.data(), df.p, kN, cudaMemcpyDeviceToHost));
+  for (size_t i = 0; i < kN; ++i) EXPECT(gf[i] == (erased[i] ? 0 : 1));
+  EXPECT(table.erase_if_v2(erase_pred) == 0);
+  std::printf("tile functors ok (dim %zu)\n", kDim);
+}
+
 int main() {
   test_rehash();
+  test_tile_functors<16>();
+  test_tile_functors<4>();
   test_errors();
   test_basic();
   test_insert_and_evict_conservation();
