@@ -389,9 +389,14 @@ __device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint
   }
 }
 
+template <int VEC = 0>
 __device__ __forceinline__ void warp_gather_rows_to(const TableView& t, uint8_t* dest_base,
                                                     uint32_t dest_row, uint32_t slot,
                                                     uint32_t lane) {
+  if constexpr (VEC != 0) {
+    warp_gather_rows_to_vec<VEC>(t, dest_base, dest_row, slot, lane);
+    return;
+  }
   switch (t.vec_bytes) {
     case 16: warp_gather_rows_to_vec<16>(t, dest_base, dest_row, slot, lane); break;
     case 8: warp_gather_rows_to_vec<8>(t, dest_base, dest_row, slot, lane); break;

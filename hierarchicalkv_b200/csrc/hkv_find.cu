@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
 // from `world` source ranks (one inbox segment each), and every hit row goes
 // directly to the source rank's result buffer over NVLink (plain peer stores)
 // while the next buckets are being probed -- lookup and transfer are one kernel.
+template <int VEC>
 __global__ void __launch_bounds__(kFindBlock)
     find_routed_kernel(const TableView t, const uint32_t blocks_per_segment, const uint32_t world,
                        const uint32_t first_segment, const uint64_t segment_capacity, const uint64_t* __restrict__ inbox_keys,
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(kFindBlock)
   if (valid) a = locate(t, key);
   const uint32_t slot = warp_probe_readonly(t, pl, key, valid, a);
   if (present) founds_of[origin] = slot != kNoSlot ? 1 : 0;
-  warp_gather_rows_to(t, values_of, origin, slot, pl.lane);
+  warp_gather_rows_to<VEC>(t, values_of, origin, slot, pl.lane);
 }
 
 template <int FORM>
@@ -296,7 +297,8 @@ void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
                         const PeerPtrs& out_founds, cudaStream_t stream) {
   if (segment_capacity == 0) return;
   const uint64_t per_segment = (segment_capacity + kFindBlock - 1) / kFindBlock;
-  find_routed_kernel<<<static_cast<unsigned>(per_segment * world), kFindBlock, 0, stream>>>(
+  auto kernel = t.vec_bytes == 16 ? find_routed_kernel<16> : find_routed_kernel<0>;
+  kernel<<<static_cast<unsigned>(per_segment * world), kFindBlock, 0, stream>>>(
       t, static_cast<uint32_t>(per_segment), world, (my_rank + 1) % world, segment_capacity,
       inbox_keys, inbox_origin,
       inbox_counts, out_values, out_founds);
