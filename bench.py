@@ -467,6 +467,58 @@ def churn_ops(arm_cls, batch: int) -> dict:
             "table": f"capacity {capacity}, dim {dim}, EpochLfu, load factor 1.0"}
 
 
+def embedding_step_ops(sharded, rank: int, world: int, batch: int, dim: int, barrier, dist) -> dict:
+    """One step of the key-hash sharded embedding table: every rank draws
+    `batch` Zipf(1.1) keys over a 2^34 key space, removes its own repeats, and
+    runs find_or_insert (rows come back) followed by accum_or_assign of fp32
+    deltas U(-1e-3, 1e-3) for the same keys.  Routing, update and transfer are
+    the fused peer-memory path (no NCCL call inside the step)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4321 + rank)
+    reps, warm = 10, 3
+    ws = sharded.peer
+    batches = []
+    for _ in range(reps + warm):
+        ranks = zipf_ranks(batch, 1 << 34, 1.1, g)
+        # rank -> key through the splitmix bijection: hot keys spread over the owners
+        z = ranks + _s64(0x9E3779B97F4A7C15)
+        z = (z ^ _lsr(z, 30)) * _s64(0xBF58476D1CE4E5B9)
+        z = (z ^ _lsr(z, 27)) * _s64(0x94D049BB133111EB)
+        z = z ^ _lsr(z, 31)
+        z = torch.where((z & -4) == -4, z & 0xFFFF, z)
+        batches.append(torch.unique(z))
+    init_rows = torch.rand((batch, dim), device="cuda", generator=g) * 2 - 1
+    deltas = (torch.rand((batch, dim), device="cuda", generator=g) * 2 - 1) * 1e-3
+    unique_total = sum(int(b.numel()) for b in batches[warm:])
+
+    def step(i):
+        k = batches[i]
+        n = k.numel()
+        ws.out_values[:n].copy_(init_rows[:n])              # rows for the keys that are new
+        sharded.upsert_fused("find_or_insert", n, k)         # rows of all keys are now in the buffer
+        ws.out_values[:n].copy_(deltas[:n])                  # the "gradients"
+        ws.out_founds[:n].fill_(True)
+        sharded.upsert_fused("accum_or_assign", n, k)
+
+    ms = time_steps(step, reps, warm, barrier)
+    if dist:
+        t = torch.tensor([ms, float(unique_total)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
+        dist.all_reduce(t[1:], op=dist.ReduceOp.SUM)
+        ms, unique_all = float(t[0].item()), float(t[1].item())
+    else:
+        unique_all = float(unique_total)
+    assert sharded.peer.status() == 0
+    return {
+        "b_kv_s_drawn": round(batch * reps * world / (ms / 1e3) / BINARY_BILLION, 4),
+        "b_kv_s_unique": round(unique_all / (ms / 1e3) / BINARY_BILLION, 4),
+        "ms_per_step": round(ms / reps, 4),
+        "unique_fraction": round(unique_all / (batch * reps * world), 4),
+        "step": "find_or_insert + accum_or_assign, Zipf(1.1) over 2^34 keys, per-rank dedup, fused "
+                "peer-memory routing",
+    }
+
+
 def cpu_baseline(dim: int, batch: int, seconds_budget: float = 20.0) -> dict:
     """The CPU restatement (oracle/hkv_oracle.cpp) on all host threads, on a
     bounded sample: a 1/8-size table filled to the same load factor, then
@@ -660,6 +712,9 @@ def main():
 
     # ---- the other operations of the workload (not part of `value`) -----------
     ops = {}
+    if not args.no_ops and world > 1 and fused:
+        ops["sharded_embedding_step"] = embedding_step_ops(sharded, rank, world, batch, dim, barrier,
+                                                           dist)
     if not args.no_ops and world == 1:
         reps = 10
 

@@ -836,6 +836,50 @@ int hkv_find_routed(hkv_table* t, uint32_t world, uint32_t my_rank, uint64_t seg
   });
 }
 
+int hkv_upsert_routed(hkv_table* t, int op, uint32_t world, uint32_t my_rank,
+                      uint64_t segment_capacity, const uint64_t* inbox_keys,
+                      const uint32_t* inbox_origin, const uint64_t* inbox_counts,
+                      const hkv_peer_ptrs* values, const hkv_peer_ptrs* accum_flags,
+                      hkv_stream stream) {
+  return guarded([&] {
+    if (world == 0 || world > hkv::kMaxPeers || my_rank >= world) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "world size must be between 1 and 16"};
+    }
+    int kernel_op;
+    switch (op) {
+      case HKV_ROUTED_INSERT_OR_ASSIGN: kernel_op = hkv::kOpInsertOrAssign; break;
+      case HKV_ROUTED_FIND_OR_INSERT: kernel_op = hkv::kOpFindOrInsert; break;
+      case HKV_ROUTED_ACCUM_OR_ASSIGN: kernel_op = hkv::kOpAccumOrAssign; break;
+      default: throw HkvError{HKV_ERR_INVALID_ARG, "op must be 0, 1 or 2"};
+    }
+    if (op == HKV_ROUTED_ACCUM_OR_ASSIGN && accum_flags == nullptr) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "accum_or_assign needs the ranks' flag arrays"};
+    }
+    if (segment_capacity % 32 != 0) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "segment_capacity must be a multiple of 32"};
+    }
+    check_strategy(t, t->opt.evict_strategy, nullptr);  // only the score-free strategies pass
+    if (t->view.hbm_slots < t->view.capacity || !t->reach_max_capacity.load()) {
+      throw HkvError{HKV_ERR_UNSUPPORTED,
+                     "the routed form needs a pure-HBM table of fixed capacity"};
+    }
+    DeviceGuard dg(t->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    hkv::PeerPtrs pv{}, pf{};
+    for (uint32_t r = 0; r < world; ++r) {
+      pv.p[r] = values->p[r];
+      pf.p[r] = accum_flags != nullptr ? accum_flags->p[r] : nullptr;
+    }
+    hkv::MutateArgs a = base_args(t, 0, inbox_keys, nullptr, nullptr, false);
+    a.row_index = inbox_origin;
+    LockScope ls(t, kInserter, s);
+    hkv::launch_mutate_routed(kernel_op, t->view, a, world, (my_rank + 1) % world,
+                              segment_capacity, inbox_counts, pv, pf, s);
+    ls.done();
+    check_launch();
+  });
+}
+
 int hkv_contains(hkv_table* t, uint64_t n, const uint64_t* keys, bool* founds, hkv_stream stream) {
   return guarded([&] {
     if (n == 0) return;

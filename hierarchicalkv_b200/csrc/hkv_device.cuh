@@ -301,9 +301,14 @@ __device__ __forceinline__ uint32_t row_of_chunk(const TableView& t, uint32_t c)
 //
 // MODE 0: table -> batch (gather)   MODE 1: batch -> table (scatter)
 // MODE 2: table += batch (fp32 accumulate; needs VEC % 4 == 0)
-template <int VEC, int MODE>
+//
+// INDEXED: the batch rows are not the warp's 32 consecutive rows; lane r holds
+// in `row_index` which row of `batch_rows` belongs to it.  `batch_rows` may
+// then be another GPU's memory and is accessed with plain loads and stores.
+template <int VEC, int MODE, bool INDEXED = false>
 __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* batch_rows,
-                                                   uint32_t slot, uint32_t lane) {
+                                                   uint32_t slot, uint32_t lane,
+                                                   uint32_t row_index = 0) {
   using T = typename VecType<VEC>::type;
   constexpr int U = (VEC == 16) ? 8 : 4;  // chunks in flight per lane
   const uint32_t cpr = t.chunks_per_row;
@@ -311,6 +316,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
   for (uint32_t base = 0; base < total; base += 32u * U) {
     T regs[U];
     uint8_t* tab[U];
+    uint8_t* bat[U];
     bool ok[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -320,9 +326,15 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
       ok[u] = (c < total) && (s != kNoSlot);
       const uint32_t off = (c - r * cpr) * VEC;
       tab[u] = ok[u] ? row_ptr(t, s) + off : nullptr;
+      if (INDEXED) {
+        const uint32_t at = __shfl_sync(0xFFFFFFFFu, row_index, r & 31u);
+        bat[u] = batch_rows + uint64_t(at) * t.row_bytes + off;
+      }
       if (ok[u]) {
         if (MODE == 0) {
           regs[u] = ld_table_row<T>(tab[u], s >= t.hbm_slots);
+        } else if (INDEXED) {
+          regs[u] = *reinterpret_cast<const T*>(bat[u]);
         } else {
           regs[u] = ld_stream(reinterpret_cast<const T*>(batch_rows + size_t(c) * VEC));
         }
@@ -333,7 +345,11 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
       const uint32_t c = base + u * 32u + lane;
       if (ok[u]) {
         if (MODE == 0) {
-          st_stream(reinterpret_cast<T*>(batch_rows + size_t(c) * VEC), regs[u]);
+          if (INDEXED) {
+            *reinterpret_cast<T*>(bat[u]) = regs[u];
+          } else {
+            st_stream(reinterpret_cast<T*>(batch_rows + size_t(c) * VEC), regs[u]);
+          }
         } else if (MODE == 1) {
           st_stream(reinterpret_cast<T*>(tab[u]), regs[u]);
         } else {
@@ -409,21 +425,22 @@ __device__ __forceinline__ void warp_gather_rows_to(const TableView& t, uint8_t*
 // VEC != 0 fixes the access width at compile time (the launcher picks the
 // instantiation that matches t.vec_bytes), which keeps the four other unrolled
 // copy loops out of the hot kernels' instruction footprint.
-template <int MODE, int VEC = 0>
+template <int MODE, int VEC = 0, bool INDEXED = false>
 __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
-                                               uint32_t slot, uint32_t lane) {
+                                               uint32_t slot, uint32_t lane,
+                                               uint32_t row_index = 0) {
   if constexpr (VEC != 0) {
-    warp_move_rows_vec<VEC, MODE>(t, batch_rows, slot, lane);
+    warp_move_rows_vec<VEC, MODE, INDEXED>(t, batch_rows, slot, lane, row_index);
     return;
   }
   // vec_bytes is warp-uniform; the host lowers it when a batch pointer is
   // less aligned than the rows.
   switch (t.vec_bytes) {
-    case 16: warp_move_rows_vec<16, MODE>(t, batch_rows, slot, lane); break;
-    case 8: warp_move_rows_vec<8, MODE>(t, batch_rows, slot, lane); break;
-    case 4: warp_move_rows_vec<4, MODE>(t, batch_rows, slot, lane); break;
-    case 2: warp_move_rows_vec<2, MODE>(t, batch_rows, slot, lane); break;
-    default: warp_move_rows_vec<1, MODE>(t, batch_rows, slot, lane); break;
+    case 16: warp_move_rows_vec<16, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
+    case 8: warp_move_rows_vec<8, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
+    case 4: warp_move_rows_vec<4, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
+    case 2: warp_move_rows_vec<2, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
+    default: warp_move_rows_vec<1, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
   }
 }
 

@@ -38,6 +38,12 @@ struct MutateArgs {
   unsigned long long* evicted_counter = nullptr;
   int strategy = kLru;
   uint64_t epoch = kIgnoredEpoch;
+  // Routed form (launch_mutate_routed): the keys are one source rank's segment
+  // of the owner's inbox; key i's row is row row_index[i] of `values` (the
+  // source rank's buffer, possibly peer memory), its accumulate flag is
+  // accum_flags[row_index[i]], and the number of keys is read on the device.
+  const uint32_t* row_index = nullptr;
+  const uint64_t* n_device = nullptr;
 };
 
 void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values, bool* founds,
@@ -70,6 +76,16 @@ void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
 // keys inside one batch.
 void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool unique_key,
                    cudaStream_t stream);
+
+// insert_or_assign / find_or_insert / accum_or_assign over the inbox segments
+// of a key-hash sharded table: one launch per source rank, in the order
+// first_segment, first_segment + 1, ... (wrapping), so that keys requested by
+// several ranks are applied one rank after the other.  args.keys / row_index
+// point at segment 0; values_of / flags_of give each source rank's buffers.
+void launch_mutate_routed(int op, const TableView& t, const MutateArgs& args, uint32_t world,
+                          uint32_t first_segment, uint64_t segment_capacity,
+                          const uint64_t* inbox_counts, const PeerPtrs& values_of,
+                          const PeerPtrs& flags_of, cudaStream_t stream);
 
 void launch_unlock_keys(const TableView& t, uint64_t n, uint64_t** locked_key_ptrs,
                         const uint64_t* keys, bool* success, cudaStream_t stream);

@@ -245,14 +245,22 @@ __device__ __forceinline__ void warp_copy_one_row(const TableView& t, uint8_t* d
 //            the next iteration; it polls the foreign lock (bounded) only
 //            after step C, when the warp holds nothing.  The victim is always
 //            the true current minimum, as in the reference (upsert.cuh:149-215).
-template <int OP, int VEC>
+//
+// INDEXED is the routed form of the key-hash sharded table: the batch is one
+// source rank's inbox segment, the number of keys is read from device memory
+// and key i's row is row args.row_index[i] of the source rank's buffer.
+template <int OP, int VEC, bool INDEXED>
 __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutateMinBlocks - 2 : kMutateMinBlocks)
     mutate_kernel(const TableView t, const MutateArgs args) {
+  static_assert(!INDEXED || OP == kOpInsertOrAssign || OP == kOpFindOrInsert ||
+                    OP == kOpAccumOrAssign,
+                "the routed form exists for the three operations the sharded table routes");
   const uint32_t full = 0xFFFFFFFFu;
   const ProbeLane pl = probe_lane();
   const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const uint64_t base = warp * 32u;
-  const uint64_t n = args.n;
+  uint64_t n = args.n;
+  if (INDEXED) n = min(n, *args.n_device);
   if (base >= n) return;
   const uint64_t i = base + pl.lane;
   const int strategy = args.strategy;
@@ -264,8 +272,11 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
   uint64_t desired = 0;
   uint32_t mode = 0;
   Address a{0, 0, 0};
+  uint32_t my_row = 0;  // INDEXED: this key's row in the source rank's buffer
+  uint8_t* const batch_rows = INDEXED ? args.values : args.values + base * t.row_bytes;
   if (i < n) {
     key = args.keys[i];
+    if (INDEXED) my_row = args.row_index[i];
     if (!is_reserved(t, key)) {
       mode = kModeValid;
       a = locate(t, key);
@@ -274,7 +285,8 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
         desired = desired_score(strategy, args.scores, in_score, args.epoch);
       }
       if (OP == kOpAccumOrAssign) {
-        mode |= args.accum_flags[i] ? kModeLockOnHit : kModeInsertOnMiss;
+        mode |= args.accum_flags[INDEXED ? uint64_t(my_row) : i] ? kModeLockOnHit
+                                                                  : kModeInsertOnMiss;
       } else if (op_inserts(OP)) {
         mode |= kModeLockOnHit | kModeInsertOnMiss;
       } else {
@@ -442,18 +454,20 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
     }
     if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
         OP == kOpAssignValues) {
-      warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes, holds_lock ? my_slot : kNoSlot,
-                        pl.lane);
+      warp_move_rows<1, VEC, INDEXED>(t, batch_rows, holds_lock ? my_slot : kNoSlot, pl.lane,
+                                      my_row);
     } else if (OP == kOpFindOrInsert) {
-      warp_move_rows<0, VEC>(t, args.values + base * t.row_bytes,
-                        my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-      warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes,
-                        my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
+      warp_move_rows<0, VEC, INDEXED>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot,
+                                      pl.lane, my_row);
+      warp_move_rows<1, VEC, INDEXED>(t, batch_rows,
+                                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane,
+                                      my_row);
     } else if (OP == kOpAccumOrAssign) {
-      warp_move_rows<2, VEC>(t, args.values + base * t.row_bytes,
-                        my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
-      warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes,
-                        my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane);
+      warp_move_rows<2, VEC, INDEXED>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot,
+                                      pl.lane, my_row);
+      warp_move_rows<1, VEC, INDEXED>(t, batch_rows,
+                                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane,
+                                      my_row);
     }
     __syncwarp();
     if (holds_lock && !keep_locked) st_release(t.keys + my_slot, key);
@@ -575,8 +589,8 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
         }
       }
       if (op_writes_row_on_insert(OP)) {
-        warp_move_rows<1, VEC>(t, args.values + base * t.row_bytes, placed ? my_slot : kNoSlot,
-                          pl.lane);
+        warp_move_rows<1, VEC, INDEXED>(t, batch_rows, placed ? my_slot : kNoSlot, pl.lane,
+                                        my_row);
       }
       __syncwarp();
       if (placed && !(OP == kOpFindOrInsertPtr && keep_locked)) st_release(t.keys + my_slot, key);
@@ -903,7 +917,7 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
   const uint64_t warps = (args.n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kMutateBlock - 1) / kMutateBlock;
   if (unique_key) {
-    auto kernel = t.vec_bytes == 16 ? mutate_kernel<OP, 16> : mutate_kernel<OP, 0>;
+    auto kernel = t.vec_bytes == 16 ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
     kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
   } else {
     mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
@@ -926,6 +940,48 @@ void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool uniq
     case kOpAssignValues: launch_op<kOpAssignValues>(t, args, unique_key, stream); break;
     case kOpFindAndUpdate: launch_op<kOpFindAndUpdate>(t, args, unique_key, stream); break;
     case kOpLockKeys: launch_op<kOpLockKeys>(t, args, unique_key, stream); break;
+    default: break;
+  }
+}
+
+template <int OP>
+void launch_routed_op(const TableView& t, MutateArgs args, uint32_t world, uint32_t first_segment,
+                      uint64_t segment_capacity, const uint64_t* inbox_counts,
+                      const PeerPtrs& values_of, const PeerPtrs& flags_of, cudaStream_t stream) {
+  const uint64_t* keys0 = args.keys;
+  const uint32_t* index0 = args.row_index;
+  const uint64_t blocks = (segment_capacity + kMutateBlock - 1) / kMutateBlock;
+  auto kernel = t.vec_bytes == 16 ? mutate_kernel<OP, 16, true> : mutate_kernel<OP, 0, true>;
+  for (uint32_t turn = 0; turn < world; ++turn) {
+    const uint32_t seg = (first_segment + turn) % world;
+    args.keys = keys0 + uint64_t(seg) * segment_capacity;
+    args.row_index = index0 + uint64_t(seg) * segment_capacity;
+    args.n = segment_capacity;
+    args.n_device = inbox_counts + seg;
+    args.values = static_cast<uint8_t*>(values_of.p[seg]);
+    args.accum_flags = static_cast<const bool*>(flags_of.p[seg]);
+    kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+  }
+}
+
+void launch_mutate_routed(int op, const TableView& t, const MutateArgs& args, uint32_t world,
+                          uint32_t first_segment, uint64_t segment_capacity,
+                          const uint64_t* inbox_counts, const PeerPtrs& values_of,
+                          const PeerPtrs& flags_of, cudaStream_t stream) {
+  if (segment_capacity == 0 || world == 0) return;
+  switch (op) {
+    case kOpInsertOrAssign:
+      launch_routed_op<kOpInsertOrAssign>(t, args, world, first_segment, segment_capacity,
+                                          inbox_counts, values_of, flags_of, stream);
+      break;
+    case kOpFindOrInsert:
+      launch_routed_op<kOpFindOrInsert>(t, args, world, first_segment, segment_capacity,
+                                        inbox_counts, values_of, flags_of, stream);
+      break;
+    case kOpAccumOrAssign:
+      launch_routed_op<kOpAccumOrAssign>(t, args, world, first_segment, segment_capacity,
+                                         inbox_counts, values_of, flags_of, stream);
+      break;
     default: break;
   }
 }

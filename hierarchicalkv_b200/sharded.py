@@ -75,7 +75,8 @@ class _PeerPtrs(ctypes.Structure):
 class PeerWorkspace:
     """Buffers every rank of the node can store into (torch symmetric memory,
     i.e. CUDA peer mappings over NVLink): each rank's inbox of routed keys and
-    its result buffers.  Used by ShardedHashTable.find_fused."""
+    its batch / result buffers.  Used by ShardedHashTable.find_fused and
+    upsert_fused."""
 
     MAX_WORLD = 16
 
@@ -87,6 +88,7 @@ class PeerWorkspace:
         self.rank = dist.get_rank(group)
         if self.world > self.MAX_WORLD:
             raise ValueError("at most 16 ranks")
+        max_batch = (max_batch + 31) // 32 * 32   # inbox segments hold whole warps of keys
         self.max_batch = max_batch
         self.dim = dim
         self.dtype = dtype
@@ -243,6 +245,29 @@ class ShardedHashTable:
         self.peer = PeerWorkspace(self.group, max_batch, dim, dtype)
         return self.peer
 
+    # -- fused paths: routing, lookup / update and transfer without NCCL ----------
+    def _chk_shard(self, rc: int) -> None:
+        if rc:
+            raise RuntimeError((self.ops.lib.hkv_shard_last_error() or b"").decode())
+
+    def _route_p2p(self, n, keys) -> None:
+        """Groups the batch by owner and stores keys and batch indices straight
+        into the owners' inboxes over NVLink."""
+        w = self.peer
+        if n > w.max_batch:
+            raise ValueError("batch larger than the workspace")
+        self._chk_shard(self.ops.lib.hkv_shard_route_keys_p2p(
+            n, keys.data_ptr(), self.world, self.rank, w.max_batch,
+            ctypes.byref(w.peers["inbox_keys"]), ctypes.byref(w.peers["inbox_origin"]),
+            ctypes.byref(w.peers["inbox_counts"]), w.scratch.data_ptr(), _stream_ptr()))
+
+    def _peer_barrier(self, max_polls: int) -> None:
+        w = self.peer
+        w.epoch += 1
+        self._chk_shard(self.ops.lib.hkv_shard_barrier(
+            self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
+            w.scratch[16:].data_ptr(), max_polls, _stream_ptr()))
+
     def find_fused(self, n, keys, max_polls: int = 50_000_000):
         """HashTable::find over all shards with lookup and transfer fused: keys
         are grouped by owner and stored straight into the owners' inboxes, every
@@ -253,32 +278,45 @@ class ShardedHashTable:
         until the next call; rows of misses keep their previous content."""
         w = self.peer
         lib = self.ops.lib
-        sp = _stream_ptr()
-        if n > w.max_batch:
-            raise ValueError("batch larger than the workspace")
-
-        def chk(rc):
-            if rc:
-                raise RuntimeError((lib.hkv_shard_last_error() or b"").decode())
-
-        chk(lib.hkv_shard_route_keys_p2p(n, keys.data_ptr(), self.world, self.rank, w.max_batch,
-                                         ctypes.byref(w.peers["inbox_keys"]),
-                                         ctypes.byref(w.peers["inbox_origin"]),
-                                         ctypes.byref(w.peers["inbox_counts"]),
-                                         w.scratch.data_ptr(), sp))
-        w.epoch += 1
-        chk(lib.hkv_shard_barrier(self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
-                                  w.scratch[16:].data_ptr(), max_polls, sp))
+        self._route_p2p(n, keys)
+        self._peer_barrier(max_polls)
         rc = lib.hkv_find_routed(self.local.handle, self.world, self.rank, w.max_batch,
                                  w.local["inbox_keys"], w.local["inbox_origin"],
                                  w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
-                                 ctypes.byref(w.peers["out_founds"]), sp)
+                                 ctypes.byref(w.peers["out_founds"]), _stream_ptr())
         if rc:
             raise RuntimeError((lib.hkv_last_error() or b"").decode())
-        w.epoch += 1
-        chk(lib.hkv_shard_barrier(self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
-                                  w.scratch[16:].data_ptr(), max_polls, sp))
+        self._peer_barrier(max_polls)
         return w.out_values[:n], w.out_founds[:n]
+
+    _ROUTED_OPS = {"insert_or_assign": 0, "find_or_insert": 1, "accum_or_assign": 2}
+
+    def upsert_fused(self, op: str, n, keys, max_polls: int = 50_000_000):
+        """insert_or_assign / find_or_insert / accum_or_assign over all shards
+        with the update and the transfer fused.  The batch rows are the first n
+        rows of this rank's peer-visible buffer ``peer.out_values`` (for
+        accum_or_assign the flags are ``peer.out_founds[:n]``): the caller
+        fills them before the call, the owners' kernels read new rows and deltas
+        from them and -- find_or_insert -- write the stored rows of the hits
+        back into them, all over NVLink.  No NCCL call, no host
+        synchronisation, no staging copy; two bounded peer barriers.
+
+        At each owner the requesting ranks' batches are applied one after the
+        other, starting with rank owner + 1 (wrapping), so a key that several
+        ranks send in one step behaves as if those ranks had called the table
+        in that order.  Needs a score-free strategy (kLru / kEpochLru)."""
+        w = self.peer
+        lib = self.ops.lib
+        self._route_p2p(n, keys)
+        self._peer_barrier(max_polls)
+        rc = lib.hkv_upsert_routed(self.local.handle, self._ROUTED_OPS[op], self.world, self.rank,
+                                   w.max_batch, w.local["inbox_keys"], w.local["inbox_origin"],
+                                   w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
+                                   ctypes.byref(w.peers["out_founds"]), _stream_ptr())
+        if rc:
+            raise RuntimeError((lib.hkv_last_error() or b"").decode())
+        self._peer_barrier(max_polls)
+        return w.out_values[:n]
 
     def insert_or_assign(self, n, keys, values, scores=None, stream=None) -> None:
         if n == 0:

@@ -163,6 +163,8 @@ _SIGNATURES = {
     "hkv_shard_barrier": [ctypes.c_uint32, ctypes.c_uint32, _P, ctypes.c_uint32, _P,
                           ctypes.c_uint32, _P],
     "hkv_find_routed": [_P, ctypes.c_uint32, ctypes.c_uint32, _U64, _P, _P, _P, _P, _P, _P],
+    "hkv_upsert_routed": [_P, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32, _U64, _P, _P, _P, _P,
+                          _P, _P],
     "hkv_accum_or_assign_unique": [_P, _U64, _P, _P, _P, _P, _P, _INT],
     "hkv_size_no_alloc": [_P, _P, ctypes.POINTER(_U64)],
     "hkv_size_no_alloc_last_error": [],

@@ -346,6 +346,26 @@ HKV_API int hkv_find_routed(hkv_table* table, uint32_t world, uint32_t my_rank,
                             const uint64_t* inbox_counts, const hkv_peer_ptrs* out_values,
                             const hkv_peer_ptrs* out_founds, hkv_stream stream);
 
+/* insert_or_assign (op 0), find_or_insert (op 1) and accum_or_assign (op 2)
+ * (include/merlin_hashtable.cuh:1125, 1699, 1589) for the owner side of the
+ * sharded table, on the same inbox as hkv_find_routed.  Key i of segment s
+ * owns row inbox_origin[i] of values->p[s], the requesting rank's batch buffer,
+ * which the kernels read (new rows, deltas) and write (rows found by
+ * find_or_insert) in place over NVLink; accum_flags->p[s] is that rank's
+ * accum_or_assigns array, indexed like the rows (op 2 only).  The segments are
+ * applied one after the other, starting with rank my_rank + 1 and wrapping, so
+ * a key requested by several ranks behaves as if those ranks had called the
+ * table in that order.  Scores cannot be routed: the table's strategy must be
+ * kLru or kEpochLru. */
+#define HKV_ROUTED_INSERT_OR_ASSIGN 0
+#define HKV_ROUTED_FIND_OR_INSERT 1
+#define HKV_ROUTED_ACCUM_OR_ASSIGN 2
+HKV_API int hkv_upsert_routed(hkv_table* table, int op, uint32_t world, uint32_t my_rank,
+                              uint64_t segment_capacity, const uint64_t* inbox_keys,
+                              const uint32_t* inbox_origin, const uint64_t* inbox_counts,
+                              const hkv_peer_ptrs* values, const hkv_peer_ptrs* accum_flags,
+                              hkv_stream stream);
+
 /* hkv_accum_or_assign for batches the caller guarantees to hold each key once
  * (the sharded table de-duplicates before routing): runs the probe kernel the
  * other insert-like operations use instead of the reference's key-scanning

@@ -170,7 +170,53 @@ def _nccl_worker(rank, world, port, dim, cap):
         assert np.array_equal(got[ef].view(np.uint32), ev[ef].view(np.uint32))
         assert np.all(got[~ef] == -3.0)
         assert st.peer.status() == 0
+    # fused update path on an LRU table: rows travel straight between the ranks' buffers
+    t2 = hkv.HashTable(hkv.EvictStrategy.kLru)
+    t2.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                 dim=dim))
+    st2 = ShardedHashTable(t2)
+    st2.peer = st.peer                       # same workspace
+    w = st2.peer
+    both = keys[30000:33000]                 # every rank sends the same keys: all of them collide
+    own = keys[33000 + rank * 1500: 33000 + (rank + 1) * 1500]
+    mine2 = np.concatenate([both, own])
+    w.out_values[:mine2.size].copy_(to_dev(values_for(mine2, dim, seed=200 + rank)))
+    got = st2.upsert_fused("find_or_insert", mine2.size, to_dev(mine2))
+    torch.cuda.synchronize()
+    owner = (fmix64(both) % np.uint64(world)).astype(np.int64)
+    first = (owner + 1) % world              # the rank whose batch an owner applies first
+    def rows_of(seed_base, src):
+        """row i as rank src[i] sent it"""
+        out = np.zeros((both.size, dim), dtype=np.float32)
+        for r in range(world):
+            out[src == r] = values_for(both, dim, seed=seed_base + r)[src == r]
+        return out
+
+    want_both = rows_of(200, first)
+    g = got.cpu().numpy()
+    assert np.array_equal(g[:both.size].view(np.uint32), want_both.view(np.uint32))
+    assert np.array_equal(g[both.size:].view(np.uint32),
+                          values_for(own, dim, seed=200 + rank).view(np.uint32))
+    # deltas from both ranks: (row + delta_first) + delta_second in the owner's order
+    w.out_values[:mine2.size].copy_(to_dev(values_for(mine2, dim, seed=300 + rank)))
+    w.out_founds[:mine2.size].fill_(True)
+    st2.upsert_fused("accum_or_assign", mine2.size, to_dev(mine2))
+    torch.cuda.synchronize()
+    rows, flags = st2.find_fused(mine2.size, to_dev(mine2))
+    torch.cuda.synchronize()
+    assert bool(flags.all())
+    want = want_both.copy()
+    for turn in range(world):
+        src = (first + turn) % world
+        want = (want + rows_of(300, src)).astype(np.float32)
+    g = rows.cpu().numpy()
+    assert np.array_equal(g[:both.size].view(np.uint32), want.view(np.uint32))
+    want_own = (values_for(own, dim, seed=200 + rank) + values_for(own, dim, seed=300 + rank))
+    assert np.array_equal(g[both.size:].view(np.uint32), want_own.astype(np.float32).view(np.uint32))
+    assert st2.size() == both.size + world * 1500
+    assert w.status() == 0
     dist.barrier()
+    t2.close()
     t.close()
     dist.destroy_process_group()
 
@@ -184,6 +230,136 @@ def test_two_nccl_ranks_match_one_global_oracle():
     port = s.getsockname()[1]
     s.close()
     mp.spawn(_nccl_worker, args=(2, port, 8, 128 * 256), nprocs=2, join=True)
+
+
+def _routed_call(lib, table, op, world, my_rank, cap_seg, inbox_keys, inbox_origin, counts, bufs,
+                 flags=None):
+    import ctypes
+
+    from hierarchicalkv_b200.sharded import _PeerPtrs
+
+    pv, pf = _PeerPtrs(), _PeerPtrs()
+    for r in range(world):
+        pv.p[r] = bufs[r].data_ptr()
+        if flags is not None:
+            pf.p[r] = flags[r].data_ptr()
+    rc = lib.hkv_upsert_routed(table.handle, op, world, my_rank, cap_seg, inbox_keys.data_ptr(),
+                               inbox_origin.data_ptr(), counts.data_ptr(), ctypes.byref(pv),
+                               ctypes.byref(pf) if flags is not None else None, None)
+    assert rc == 0, (lib.hkv_last_error() or b"").decode()
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dim", [8, 5])
+def test_upsert_routed_applies_the_ranks_one_after_the_other(dim):
+    """The owner side of the fused sharded update on one GPU: three source
+    ranks' inbox segments, their batch buffers standing in for peer memory.
+    Keys that several ranks send are applied in the order rank owner + 1,
+    owner + 2, ... -- checked against the CPU oracle fed in that order."""
+    import hierarchicalkv_b200 as hkv
+    from hierarchicalkv_b200.sharded import CudaOps
+
+    lib = CudaOps().lib
+    world, me, cap_seg, nbuf = 3, 1, 2048, 3000
+    cap = 128 * 64
+    t = hkv.HashTable(hkv.EvictStrategy.kLru)
+    t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                dim=dim))
+    o = OracleTable(cap, dim, 0)
+    keys = unique_keys(5200, seed=91)
+    old = keys[:1500]
+    t.insert_or_assign(old.size, to_dev(old), to_dev(values_for(old, dim, seed=1)))
+    o.insert_or_assign(old, values_for(old, dim, seed=1))
+    rng = np.random.default_rng(5)
+    order = [(me + 1 + k) % world for k in range(world)]
+
+    def make_step(pool, seed):
+        """per source rank: keys (a random subset of the pool, so ranks overlap),
+        their rows in that rank's buffer, and where the rows sit in the buffer"""
+        per = {}
+        for r in range(world):
+            n = int(rng.integers(1200, 2000))
+            kk = rng.choice(pool, size=n, replace=False)
+            at = rng.permutation(nbuf)[:n].astype(np.uint32)      # origin: any row of the buffer
+            buf = np.full((nbuf, dim), -7.0, dtype=np.float32)
+            buf[at] = values_for(kk, dim, seed=seed + r)
+            per[r] = (kk, at, buf)
+        inbox_keys = np.zeros(world * cap_seg, dtype=np.uint64)
+        inbox_origin = np.zeros(world * cap_seg, dtype=np.uint32)
+        counts = np.zeros(16, dtype=np.uint64)
+        for r in range(world):
+            kk, at, _ = per[r]
+            inbox_keys[r * cap_seg: r * cap_seg + kk.size] = kk
+            inbox_keys[r * cap_seg + kk.size: (r + 1) * cap_seg] = 12345    # stale entries beyond the count
+            inbox_origin[r * cap_seg: r * cap_seg + kk.size] = at
+            counts[r] = kk.size
+        return per, to_dev(inbox_keys), torch.from_numpy(inbox_origin.view(np.int32)).cuda(), to_dev(counts)
+
+    def table_rows(which):
+        out = torch.zeros((which.size, dim), device="cuda")
+        f = torch.zeros(which.size, dtype=torch.bool, device="cuda")
+        t.find(which.size, to_dev(which), out, f)
+        torch.cuda.synchronize()
+        return out.cpu().numpy(), f.cpu().numpy()
+
+    def check_table(which):
+        got, gf = table_rows(which)
+        want, wf, _ = o.find(which)
+        np.testing.assert_array_equal(gf, wf)
+        np.testing.assert_array_equal(got[gf].view(np.uint32), want[wf].view(np.uint32))
+
+    # find_or_insert: hits return the stored row into the rank's buffer, misses store the rank's row
+    pool = keys[1000:3000]                      # 500 old keys, 1500 new ones
+    per, ik, io, cnt = make_step(pool, seed=20)
+    bufs = [torch.from_numpy(per[r][2].copy()).cuda() for r in range(world)]
+    _routed_call(lib, t, 1, world, me, cap_seg, ik, io, cnt, bufs)
+    for r in order:
+        kk, at, buf = per[r]
+        rows = np.ascontiguousarray(buf[at])
+        got_rows = o.find_or_insert(kk, rows)
+        back = bufs[r].cpu().numpy()
+        np.testing.assert_array_equal(back[at].view(np.uint32), got_rows.view(np.uint32))
+        untouched = np.ones(nbuf, dtype=bool)
+        untouched[at] = False
+        assert np.all(back[untouched] == -7.0)
+    check_table(keys[:3500])
+    assert t.size() == o.size()
+
+    # accum_or_assign: deltas add up rank after rank; assignments only insert missing keys
+    pool = keys[2000:4200]
+    per, ik, io, cnt = make_step(pool, seed=40)
+    bufs = [torch.from_numpy(per[r][2].copy()).cuda() for r in range(world)]
+    flag_np = [rng.integers(0, 4, size=nbuf) != 0 for _ in range(world)]     # 75 % accumulate
+    flags = [torch.from_numpy(f).cuda() for f in flag_np]
+    _routed_call(lib, t, 2, world, me, cap_seg, ik, io, cnt, bufs, flags)
+    for r in order:
+        kk, at, buf = per[r]
+        o.accum_or_assign(kk, np.ascontiguousarray(buf[at]), np.ascontiguousarray(flag_np[r][at]))
+    check_table(keys[:4500])
+    assert t.size() == o.size()
+
+    # insert_or_assign: the last rank in the order wins
+    pool = keys[3200:5200]
+    per, ik, io, cnt = make_step(pool, seed=60)
+    bufs = [torch.from_numpy(per[r][2].copy()).cuda() for r in range(world)]
+    _routed_call(lib, t, 0, world, me, cap_seg, ik, io, cnt, bufs)
+    for r in order:
+        kk, at, buf = per[r]
+        o.insert_or_assign(kk, np.ascontiguousarray(buf[at]))
+    check_table(keys)
+    assert t.size() == o.size()
+    assert t.device_status() == 0
+    # strategies that need scores cannot be routed
+    lfu = hkv.HashTable(hkv.EvictStrategy.kLfu)
+    lfu.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                  dim=dim))
+    from hierarchicalkv_b200.sharded import _PeerPtrs
+    import ctypes
+    pv = _PeerPtrs()
+    assert lib.hkv_upsert_routed(lfu.handle, 0, world, me, cap_seg, ik.data_ptr(), io.data_ptr(),
+                                 cnt.data_ptr(), ctypes.byref(pv), None, None) != 0
+    lfu.close()
+    t.close()
 
 
 def test_peer_barrier_times_out_instead_of_hanging():
