@@ -256,6 +256,18 @@ hkv::TableView view_for(const hkv_table* t, const void* a, const void* b = nullp
   return v;
 }
 
+// accum_or_assign adds elements of V (include/merlin/core_kernels/accum_or_assign.cuh:139-172):
+// the element type must be known and a row chunk must hold whole elements.
+void check_accum_type(const hkv_table* t, const void* batch) {
+  static const uint32_t size_of_kind[] = {4, 4, 8, 4, 8, 2, 2};
+  const uint32_t kind = t->view.value_kind;
+  HKV_CHECK(kind <= hkv::kValueBF16 && t->opt.value_size == size_of_kind[kind],
+            "accum_or_assign needs a float32, float64, int32, int64, float16 or bfloat16 value type "
+            "(hkv_options.value_kind).");
+  HKV_CHECK(view_for(t, batch).vec_bytes >= t->opt.value_size,
+            "accum_or_assign needs value_or_deltas aligned to the element size.");
+}
+
 // check_evict_strategy, include/merlin_hashtable.cuh:3832-3861
 void check_strategy(const hkv_table* t, int strategy, const uint64_t* scores) {
   if (strategy == HKV_LRU || strategy == HKV_EPOCH_LRU) {
@@ -529,6 +541,8 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
         v.chunks_per_row_shift = s;
       }
       v.chunks_per_row_magic = hkv::chunks_per_row_magic_of(v.chunks_per_row);
+      HKV_CHECK(o.value_kind <= hkv::kValueBF16, "hkv_options.value_kind out of range.");
+      v.value_kind = o.value_kind;
       // reserved keys, include/merlin/types.cuh:80-109
       const int bit = o.reserved_key_start_bit;
       if (bit == 0) {
@@ -639,7 +653,7 @@ int hkv_accum_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys,
                         const uint64_t* scores, hkv_stream stream, int ignore_evict_strategy) {
   return guarded([&] {
     if (n == 0) return;
-    HKV_CHECK(t->opt.value_size == 4, "accum_or_assign adds float32 elements only.");
+    check_accum_type(t, value_or_deltas);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
     hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores, ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
@@ -657,7 +671,7 @@ int hkv_accum_or_assign_unique(hkv_table* t, uint64_t n, const uint64_t* keys,
                                int ignore_evict_strategy) {
   return guarded([&] {
     if (n == 0) return;
-    HKV_CHECK(t->opt.value_size == 4, "accum_or_assign adds float32 elements only.");
+    check_accum_type(t, value_or_deltas);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
     hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores, ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
@@ -855,6 +869,7 @@ int hkv_upsert_routed(hkv_table* t, int op, uint32_t world, uint32_t my_rank,
     if (op == HKV_ROUTED_ACCUM_OR_ASSIGN && accum_flags == nullptr) {
       throw HkvError{HKV_ERR_INVALID_ARG, "accum_or_assign needs the ranks' flag arrays"};
     }
+    if (op == HKV_ROUTED_ACCUM_OR_ASSIGN) check_accum_type(t, nullptr);
     if (segment_capacity % 32 != 0) {
       throw HkvError{HKV_ERR_INVALID_ARG, "segment_capacity must be a multiple of 32"};
     }

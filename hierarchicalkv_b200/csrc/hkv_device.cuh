@@ -16,6 +16,8 @@
 //   key-as-lock slot protocol       include/merlin/core_kernels/upsert.cuh:89-110,199-232
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -45,6 +47,18 @@ enum Strategy : int {
 // Kernel-parameter view of a table.  Reserved keys travel with the view (not
 // in __constant__ memory) so tables with different reserved_key_start_bit can
 // live side by side in one process.
+// Element types accum_or_assign can add (the reference adds with V's own
+// operator+=, include/merlin/core_kernels/accum_or_assign.cuh:139-172).
+enum ValueKind : uint32_t {
+  kValueOpaque = 0,  // rows are bytes; float32 is assumed when sizeof(V) == 4
+  kValueF32 = 1,
+  kValueF64 = 2,
+  kValueI32 = 3,
+  kValueI64 = 4,
+  kValueF16 = 5,
+  kValueBF16 = 6,
+};
+
 struct TableView {
   uint8_t* digests;
   uint64_t* keys;
@@ -62,6 +76,7 @@ struct TableView {
   int32_t chunks_per_row_shift;   // log2(chunks_per_row) or -1
   uint32_t chunks_per_row_magic;  // floor(2^32 / chunks_per_row) + 1 (when not a power of two)
   uint32_t capacity_pow2;         // 1 when capacity is a power of two
+  uint32_t value_kind;            // element type of a row, used by accum_or_assign only (ValueKind)
   uint64_t empty_key;
   uint64_t reclaim_key;
   uint64_t locked_key;
@@ -290,6 +305,58 @@ __device__ __forceinline__ uint32_t row_of_chunk(const TableView& t, uint32_t c)
   return r;
 }
 
+// cur += add, element by element, for a chunk of VEC bytes.  A chunk never
+// splits an element: the access width is at least the element size.
+template <int VEC, class T>
+__device__ __forceinline__ void accumulate_chunk(T& cur, const T& add, uint32_t kind) {
+  if constexpr (VEC >= 2) {
+    if (kind == kValueF16) {
+      __half* a = reinterpret_cast<__half*>(&cur);
+      const __half* b = reinterpret_cast<const __half*>(&add);
+#pragma unroll
+      for (int e = 0; e < VEC / 2; ++e) a[e] = __hadd(a[e], b[e]);
+      return;
+    }
+    if (kind == kValueBF16) {
+      __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&cur);
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&add);
+#pragma unroll
+      for (int e = 0; e < VEC / 2; ++e) a[e] = __hadd(a[e], b[e]);
+      return;
+    }
+  }
+  if constexpr (VEC >= 8) {
+    if (kind == kValueF64) {
+      double* a = reinterpret_cast<double*>(&cur);
+      const double* b = reinterpret_cast<const double*>(&add);
+#pragma unroll
+      for (int e = 0; e < VEC / 8; ++e) a[e] += b[e];
+      return;
+    }
+    if (kind == kValueI64) {
+      uint64_t* a = reinterpret_cast<uint64_t*>(&cur);
+      const uint64_t* b = reinterpret_cast<const uint64_t*>(&add);
+#pragma unroll
+      for (int e = 0; e < VEC / 8; ++e) a[e] += b[e];
+      return;
+    }
+  }
+  if constexpr (VEC >= 4) {
+    if (kind == kValueI32) {
+      uint32_t* a = reinterpret_cast<uint32_t*>(&cur);
+      const uint32_t* b = reinterpret_cast<const uint32_t*>(&add);
+#pragma unroll
+      for (int e = 0; e < VEC / 4; ++e) a[e] += b[e];
+      return;
+    }
+    // kValueF32, and kValueOpaque with 4-byte elements
+    float* a = reinterpret_cast<float*>(&cur);
+    const float* b = reinterpret_cast<const float*>(&add);
+#pragma unroll
+    for (int e = 0; e < VEC / 4; ++e) a[e] += b[e];
+  }
+}
+
 // ---- warp-cooperative row copy --------------------------------------------
 //
 // A warp owns up to 32 consecutive rows of a batch buffer (`batch_rows` points
@@ -300,7 +367,7 @@ __device__ __forceinline__ uint32_t row_of_chunk(const TableView& t, uint32_t c)
 // contiguous segment per row.
 //
 // MODE 0: table -> batch (gather)   MODE 1: batch -> table (scatter)
-// MODE 2: table += batch (fp32 accumulate; needs VEC % 4 == 0)
+// MODE 2: table += batch (element type t.value_kind; VEC >= element size)
 //
 // INDEXED: the batch rows are not the warp's 32 consecutive rows; lane r holds
 // in `row_index` which row of `batch_rows` belongs to it.  `batch_rows` may
@@ -353,14 +420,9 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
         } else if (MODE == 1) {
           st_stream(reinterpret_cast<T*>(tab[u]), regs[u]);
         } else {
-          if constexpr (VEC % 4 == 0) {
-            T cur = *reinterpret_cast<const T*>(tab[u]);
-            float* a = reinterpret_cast<float*>(&cur);
-            const float* b = reinterpret_cast<const float*>(&regs[u]);
-#pragma unroll
-            for (int e = 0; e < VEC / 4; ++e) a[e] += b[e];
-            *reinterpret_cast<T*>(tab[u]) = cur;
-          }
+          T cur = *reinterpret_cast<const T*>(tab[u]);
+          accumulate_chunk<VEC>(cur, regs[u], t.value_kind);
+          *reinterpret_cast<T*>(tab[u]) = cur;
         }
       }
     }

@@ -71,6 +71,7 @@ class _Options(ctypes.Structure):
         ("evict_strategy", ctypes.c_int32),
         ("value_size", ctypes.c_uint32),
         ("score_size", ctypes.c_uint32),
+        ("value_kind", ctypes.c_uint32),
     ]
 
 
@@ -247,6 +248,13 @@ _VALUE_SIZES = {
 }
 
 
+# hkv_value_kind: the element types accum_or_assign can add
+_VALUE_KINDS = {
+    torch.float32: 1, torch.float64: 2, torch.int32: 3, torch.int64: 4, torch.float16: 5,
+    torch.bfloat16: 6,
+}
+
+
 class HashTable:
     """Mirror of nv::merlin::HashTable<K, V, S, Strategy>.
 
@@ -279,7 +287,8 @@ class HashTable:
             num_of_buckets_per_alloc=options.num_of_buckets_per_alloc,
             api_lock=int(options.api_lock), table_mode=int(options.table_mode),
             evict_strategy=int(self.evict_strategy),
-            value_size=_VALUE_SIZES[self.value_dtype], score_size=8)
+            value_size=_VALUE_SIZES[self.value_dtype], score_size=8,
+            value_kind=_VALUE_KINDS.get(self.value_dtype, 0))
         h = ctypes.c_void_p()
         rc = self._lib.hkv_table_create(ctypes.byref(o), None, ctypes.byref(h))
         if rc:

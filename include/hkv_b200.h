@@ -86,7 +86,21 @@ typedef struct hkv_options {
   int32_t evict_strategy; /* hkv_evict_strategy */
   uint32_t value_size;    /* sizeof(V) */
   uint32_t score_size;    /* sizeof(S): 8 */
+  uint32_t value_kind;    /* hkv_value_kind: what accum_or_assign adds */
 } hkv_options;
+
+/* Element type of V.  Rows are opaque bytes to every operation except
+ * accum_or_assign, which adds elements as V's operator+= does in the reference
+ * (include/merlin/core_kernels/accum_or_assign.cuh:139-172). */
+typedef enum hkv_value_kind {
+  HKV_VALUE_OPAQUE = 0, /* accum_or_assign: float32 when sizeof(V) == 4, else rejected */
+  HKV_VALUE_F32 = 1,
+  HKV_VALUE_F64 = 2,
+  HKV_VALUE_I32 = 3,
+  HKV_VALUE_I64 = 4,
+  HKV_VALUE_F16 = 5,
+  HKV_VALUE_BF16 = 6
+} hkv_value_kind;
 
 /* Predicates that cross the ABI by number (export_batch_if / size_if /
  * erase_if with the functors the reference's tests and benchmarks use). */

@@ -17,6 +17,8 @@
 // Differences a caller can observe are listed in INTEGRATION.md.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -98,6 +100,18 @@ inline void rethrow(int rc) {
     case HKV_ERR_INVALID_ARG: throw std::invalid_argument(msg);
     default: throw std::runtime_error(msg);
   }
+}
+
+// hkv_value_kind of V: the element types accum_or_assign can add.
+template <class V>
+constexpr uint32_t value_kind_of() {
+  if (std::is_same<V, float>::value) return HKV_VALUE_F32;
+  if (std::is_same<V, double>::value) return HKV_VALUE_F64;
+  if (std::is_integral<V>::value && sizeof(V) == 4) return HKV_VALUE_I32;
+  if (std::is_integral<V>::value && sizeof(V) == 8) return HKV_VALUE_I64;
+  if (std::is_same<V, __half>::value) return HKV_VALUE_F16;
+  if (std::is_same<V, __nv_bfloat16>::value) return HKV_VALUE_BF16;
+  return HKV_VALUE_OPAQUE;
 }
 
 // BaseAllocator* -> hkv_allocator trampolines.
@@ -468,6 +482,7 @@ class HashTable : public HashTableBase<K, V, S> {
     o.table_mode = static_cast<int32_t>(options.table_mode);
     o.evict_strategy = Strategy;
     o.value_size = sizeof(V);
+    o.value_kind = detail::value_kind_of<V>();
     o.score_size = sizeof(S);
     hkv_allocator bridge{allocator, detail::alloc_trampoline, detail::free_trampoline};
     detail::rethrow(hkv_table_create(&o, allocator ? &bridge : nullptr, &table_));

@@ -83,6 +83,7 @@ _ORACLE_SIGS = {
     "orc_reserve": ([_P, _U64], None),
     "orc_set_max_capacity": ([_P, _U64], _INT),
     "orc_set_max_load_factor": ([_P, ctypes.c_float], None),
+    "orc_set_value_kind": ([_P, _INT], None),
     "orc_capacity": ([_P], _U64),
     "orc_bucket_count": ([_P], _U64),
     "orc_set_global_epoch": ([_P, _U64], None),

@@ -132,6 +132,91 @@ def test_find_and_update_and_assign_values():
     t.close()
 
 
+@pytest.mark.parametrize("dtype,dim", [("float32", 8), ("float64", 6), ("int32", 5), ("int64", 3),
+                                       ("float16", 12), ("bfloat16", 7)])
+@pytest.mark.parametrize("unique", [True, False])
+def test_accum_or_assign_adds_in_the_value_type(dtype, dim, unique):
+    """accum_or_assign adds with V's own arithmetic (the reference's kernel does
+    `+=` on V, include/merlin/core_kernels/accum_or_assign.cuh:139-172): every
+    supported element type, fast and serialising kernel, against the CPU oracle
+    (float / double / integers) or exactly representable data (half types)."""
+    import torch
+    import hierarchicalkv_b200 as hkv
+
+    tdt = getattr(torch, dtype)
+    cap, n = 128 * 32, 1800
+    t = hkv.HashTable(hkv.EvictStrategy.kCustomized, value_dtype=tdt)
+    t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                dim=dim))
+    keys = unique_keys(2 * n, seed=23)
+    rng = np.random.default_rng(4)
+    if dtype in ("float32", "float64"):
+        base = rng.standard_normal((n, dim))
+        delta = rng.standard_normal((2 * n, dim))
+    else:
+        base = rng.integers(-50, 50, size=(n, dim))     # small integers: exact in every type
+        delta = rng.integers(-50, 50, size=(2 * n, dim))
+    base_t = torch.from_numpy(base).to(tdt).cuda()
+    delta_t = torch.from_numpy(delta).to(tdt).cuda()
+    sc = to_dev(np.arange(1, n + 1, dtype=np.uint64))
+    t.insert_or_assign(n, to_dev(keys[:n]), base_t, sc)
+    # first half of the batch: resident keys, second half: new keys; a third of each only assigns
+    flags = (np.arange(2 * n) % 3) != 0
+    q = np.concatenate([keys[:n], keys[n:]])
+    sc2 = to_dev(np.arange(5001, 5001 + 2 * n, dtype=np.uint64))
+    fn = t.accum_or_assign_unique if unique else t.accum_or_assign
+    fn(2 * n, to_dev(q), delta_t, torch.from_numpy(flags).cuda(), sc2)
+    out = torch.zeros((2 * n, dim), dtype=tdt, device="cuda")
+    f = torch.zeros(2 * n, dtype=torch.bool, device="cuda")
+    t.find(2 * n, to_dev(q), out, f)
+    torch.cuda.synchronize()
+    f = f.cpu().numpy()
+    # resident keys stay; new keys appear only where the flag says "assign"
+    np.testing.assert_array_equal(f[:n], True)
+    np.testing.assert_array_equal(f[n:], ~flags[n:])
+    want = torch.zeros((2 * n, dim), dtype=tdt)
+    bt, dt = base_t.cpu(), delta_t.cpu()
+    acc = torch.from_numpy(flags[:n])
+    want[:n] = torch.where(acc[:, None], bt + dt[:n], bt)        # (assign, hit) is a no-op
+    want[n:] = torch.where(torch.from_numpy(~flags[n:])[:, None], dt[n:], torch.zeros_like(dt[n:]))
+    got = out.cpu()
+    assert torch.equal(got[torch.from_numpy(f)].view(torch.uint8), want[torch.from_numpy(f)].view(torch.uint8))
+    if dtype in ("float64", "int32", "int64"):
+        kind = {"float64": 2, "int32": 3, "int64": 4}[dtype]
+        o = OracleTable(cap, dim, CUSTOMIZED, value_size=base_t.element_size())
+        o.lib.orc_set_value_kind(o.h, kind)
+        raw = lambda x: np.ascontiguousarray(x.cpu().numpy())
+        k0, b0 = np.ascontiguousarray(keys[:n]), raw(base_t)     # kept alive across the call
+        s0 = np.arange(1, n + 1, dtype=np.uint64)
+        o.lib.orc_insert_or_assign(o.h, n, k0.ctypes.data, b0.ctypes.data, s0.ctypes.data, 0, 1)
+        d = raw(delta_t)
+        fl = np.ascontiguousarray(flags)
+        s2 = np.arange(5001, 5001 + 2 * n, dtype=np.uint64)
+        o.lib.orc_accum_or_assign(o.h, 2 * n, q.ctypes.data, d.ctypes.data, fl.ctypes.data,
+                                  s2.ctypes.data, 1)
+        ov = np.zeros_like(d)
+        of = np.zeros(2 * n, dtype=np.bool_)
+        o.lib.orc_find(o.h, 2 * n, q.ctypes.data, ov.ctypes.data, of.ctypes.data, None, 1)
+        np.testing.assert_array_equal(of, f)
+        np.testing.assert_array_equal(ov[of].view(np.uint8), raw(out)[f].view(np.uint8))
+    t.close()
+
+
+def test_accum_or_assign_rejects_types_it_cannot_add():
+    import torch
+    import hierarchicalkv_b200 as hkv
+
+    t = hkv.HashTable(hkv.EvictStrategy.kCustomized, value_dtype=torch.int8)
+    t.init(hkv.HashTableOptions(init_capacity=1024, max_capacity=1024, max_hbm_for_vectors=1 << 30,
+                                dim=16))
+    k = to_dev(unique_keys(8, seed=1))
+    v = torch.zeros((8, 16), dtype=torch.int8, device="cuda")
+    fl = torch.ones(8, dtype=torch.bool, device="cuda")
+    with pytest.raises(hkv.MerlinException):
+        t.accum_or_assign(8, k, v, fl, to_dev(np.arange(1, 9, dtype=np.uint64)))
+    t.close()
+
+
 @pytest.mark.parametrize("n", [0, 1, 31, 32, 33, 127, 1000])
 def test_ragged_and_empty_batches(n):
     cap, dim = 128 * 16, 8
