@@ -256,6 +256,45 @@ hkv::TableView view_for(const hkv_table* t, const void* a, const void* b = nullp
   return v;
 }
 
+// sizeof(S) == 4 (only with kCustomized, include/merlin_hashtable.cuh:939-949
+// of the reference): the caller's score arrays hold uint32 while the kernels
+// work on uint64.  An array is widened into a stream-ordered temporary before
+// the kernels run; an output array is narrowed back afterwards (it was widened
+// first so that entries the kernels leave alone keep their value).  With
+// 64-bit scores this is the caller's pointer and nothing else.
+class Scores {
+ public:
+  Scores(hkv_table* t, const uint64_t* user, uint64_t n, hkv_stream stream, bool is_output)
+      : user_(const_cast<uint64_t*>(user)),
+        n_(n),
+        stream_(static_cast<cudaStream_t>(stream)),
+        output_(is_output),
+        exceptions_(std::uncaught_exceptions()) {
+    if (user == nullptr || n == 0 || t->opt.score_size == 8) return;
+    DeviceGuard dg(t->device);
+    HKV_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&wide_), n * sizeof(uint64_t), stream_));
+    hkv::launch_widen_scores(reinterpret_cast<const uint32_t*>(user), wide_, n, stream_);
+  }
+  Scores(const Scores&) = delete;
+  Scores& operator=(const Scores&) = delete;
+  ~Scores() {
+    if (wide_ == nullptr) return;
+    if (output_ && std::uncaught_exceptions() == exceptions_) {
+      hkv::launch_narrow_scores(wide_, reinterpret_cast<uint32_t*>(user_), n_, stream_);
+    }
+    cudaFreeAsync(wide_, stream_);
+  }
+  uint64_t* get() const { return wide_ != nullptr ? wide_ : user_; }
+
+ private:
+  uint64_t* user_;
+  uint64_t* wide_ = nullptr;
+  uint64_t n_;
+  cudaStream_t stream_;
+  bool output_;
+  int exceptions_;
+};
+
 // accum_or_assign adds elements of V (include/merlin/core_kernels/accum_or_assign.cuh:139-172):
 // the element type must be known and a row chunk must hold whole elements.
 void check_accum_type(const hkv_table* t, const void* batch) {
@@ -495,7 +534,9 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
               "[HierarchicalKV] `io_by_cpu` should not be true when `max_hbm_for_vectors` is "
               "not 0!");
     HKV_CHECK(!o.io_by_cpu, "`io_by_cpu` is not part of this library.");
-    HKV_CHECK(o.score_size == 8, "only 64-bit scores are supported by this library.");
+    HKV_CHECK(o.score_size == 8 || o.score_size == 4, "The score_type must be uint64_t or uint32_t.");
+    HKV_CHECK(o.score_size == 8 || o.evict_strategy == HKV_CUSTOMIZED,
+              "score_type uint32_t is only compatible with Customized; use uint64_t.");
     HKV_CHECK(o.evict_strategy >= HKV_LRU && o.evict_strategy <= HKV_CUSTOMIZED,
               "unknown evict strategy");
     HKV_CHECK(o.dim > 0 && o.value_size > 0, "dim and value_size must be positive");
@@ -595,8 +636,9 @@ int hkv_insert_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const v
                          int ignore_evict_strategy) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores_w.get(), ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
     mutate(t, hkv::kOpInsertOrAssign, a, values, nullptr, kInserter, unique_key != 0,
            static_cast<cudaStream_t>(stream));
@@ -609,16 +651,18 @@ int hkv_insert_and_evict(hkv_table* t, uint64_t n, const uint64_t* keys, const v
                          int unique_key, int ignore_evict_strategy) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
+    Scores evicted_scores_w(t, evicted_scores, n, stream, true);
     if (t->view.hbm_slots < t->view.capacity) {
       // include/merlin_hashtable.cuh:1384-1386
       throw HkvError{HKV_ERR_RUNTIME, "Only allow insert_and_evict in pure HBM mode."};
     }
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores_w.get(), ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
     a.evicted_keys = evicted_keys;
     a.evicted_values = static_cast<uint8_t*>(evicted_values);
-    a.evicted_scores = evicted_scores;
+    a.evicted_scores = evicted_scores_w.get();
     a.evicted_counter = reinterpret_cast<unsigned long long*>(d_evicted_counter);
     mutate(t, hkv::kOpInsertAndEvict, a, values, evicted_values, kInserter,
            unique_key != 0, static_cast<cudaStream_t>(stream));
@@ -653,9 +697,10 @@ int hkv_accum_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys,
                         const uint64_t* scores, hkv_stream stream, int ignore_evict_strategy) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     check_accum_type(t, value_or_deltas);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores, ignore_evict_strategy != 0);
+    hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores_w.get(), ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
     a.accum_flags = accum_or_assigns;
     // the reference has no unique_key argument here and always runs its
@@ -671,9 +716,10 @@ int hkv_accum_or_assign_unique(hkv_table* t, uint64_t n, const uint64_t* keys,
                                int ignore_evict_strategy) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     check_accum_type(t, value_or_deltas);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores, ignore_evict_strategy != 0);
+    hkv::MutateArgs a = base_args(t, n, keys, value_or_deltas, scores_w.get(), ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
     a.accum_flags = accum_or_assigns;
     mutate(t, hkv::kOpAccumOrAssign, a, value_or_deltas, nullptr, kInserter, true,
@@ -686,8 +732,9 @@ int hkv_find_or_insert(hkv_table* t, uint64_t n, const uint64_t* keys, void* val
                        int ignore_evict_strategy) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, values, scores, ignore_evict_strategy != 0);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores_w.get(), ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
     mutate(t, hkv::kOpFindOrInsert, a, values, nullptr, kInserter, unique_key != 0,
            static_cast<cudaStream_t>(stream));
@@ -699,8 +746,9 @@ int hkv_find_or_insert_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void*
                            int ignore_evict_strategy, uint64_t** locked_key_ptrs) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, ignore_evict_strategy != 0);
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores_w.get(), ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
     a.ptrs = values;
     a.founds = founds;
@@ -714,10 +762,11 @@ int hkv_lock_keys(hkv_table* t, uint64_t n, const uint64_t* keys, uint64_t** loc
                   bool* success, hkv_stream stream, const uint64_t* scores) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     if (locked_key_ptrs == nullptr) {
       throw HkvError{HKV_ERR_INVALID_ARG, "locked_key_ptrs must not be null"};
     }
-    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores_w.get(), false);
     a.founds = success;
     a.locked_key_ptrs = locked_key_ptrs;
     mutate(t, hkv::kOpLockKeys, a, nullptr, nullptr, kInserter, true,
@@ -742,8 +791,9 @@ int hkv_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const void* value
                const uint64_t* scores, hkv_stream stream, int unique_key) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, values, scores, false);
+    hkv::MutateArgs a = base_args(t, n, keys, values, scores_w.get(), false);
     mutate(t, hkv::kOpAssign, a, values, nullptr, kUpdater, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
@@ -753,8 +803,9 @@ int hkv_assign_scores(hkv_table* t, uint64_t n, const uint64_t* keys, const uint
                       hkv_stream stream, int unique_key) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, false);
     check_strategy(t, t->opt.evict_strategy, scores);
-    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores_w.get(), false);
     mutate(t, hkv::kOpAssignScores, a, nullptr, nullptr, kUpdater, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
@@ -774,10 +825,11 @@ int hkv_find(hkv_table* t, uint64_t n, const uint64_t* keys, void* values, bool*
              uint64_t* scores, hkv_stream stream) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     LockScope ls(t, kReader, s);
-    hkv::launch_find(view_for(t, values), n, keys, values, founds, scores, s);
+    hkv::launch_find(view_for(t, values), n, keys, values, founds, scores_w.get(), s);
     ls.done();
     check_launch();
   });
@@ -788,12 +840,13 @@ int hkv_find_missed(hkv_table* t, uint64_t n, const uint64_t* keys, void* values
                     hkv_stream stream) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     HKV_CUDA(cudaMemsetAsync(missed_size, 0, sizeof(int), s));
     LockScope ls(t, kReader, s);
     hkv::launch_find_missed(view_for(t, values), n, keys, values, missed_keys, missed_indices,
-                            missed_size, scores, s);
+                            missed_size, scores_w.get(), s);
     ls.done();
     check_launch();
   });
@@ -803,10 +856,11 @@ int hkv_find_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void** values, 
                  uint64_t* scores, hkv_stream stream, int /*unique_key*/) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     LockScope ls(t, kReader, s);
-    hkv::launch_find_ptr(t->view, n, keys, values, founds, scores, s);
+    hkv::launch_find_ptr(t->view, n, keys, values, founds, scores_w.get(), s);
     ls.done();
     check_launch();
   });
@@ -816,10 +870,11 @@ int hkv_find_and_update(hkv_table* t, uint64_t n, const uint64_t* keys, void** v
                         bool* founds, uint64_t* scores, hkv_stream stream, int unique_key) {
   return guarded([&] {
     if (n == 0) return;
+    Scores scores_w(t, scores, n, stream, true);
     // scores are an input here for the strategies that take them and are
     // overwritten with the stored score
-    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores, false);
-    a.scores_out = scores;
+    hkv::MutateArgs a = base_args(t, n, keys, nullptr, scores_w.get(), false);
+    a.scores_out = scores_w.get();
     a.ptrs = values;
     a.founds = founds;
     mutate(t, hkv::kOpFindAndUpdate, a, nullptr, nullptr, kUpdater, unique_key != 0,
@@ -957,6 +1012,7 @@ int hkv_export_batch_if(hkv_table* t, int predicate, uint64_t pattern, uint64_t 
                         uint64_t n, uint64_t offset, uint64_t* d_counter, uint64_t* keys,
                         void* values, uint64_t* scores, hkv_stream stream) {
   return guarded([&] {
+    Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (predicate < HKV_PRED_ALL || predicate > HKV_PRED_SCORE_LESS_EQ) {
@@ -968,7 +1024,7 @@ int hkv_export_batch_if(hkv_table* t, int predicate, uint64_t pattern, uint64_t 
       const uint64_t left = t->view.capacity - offset;
       if (n > left) n = left;
       hkv::launch_export(view_for(t, values), predicate, pattern, threshold, n, offset,
-                         reinterpret_cast<unsigned long long*>(d_counter), keys, values, scores,
+                         reinterpret_cast<unsigned long long*>(d_counter), keys, values, scores_w.get(),
                          s);
     }
     ls.done();

@@ -113,6 +113,9 @@ void launch_clear(const TableView& t, cudaStream_t stream);
 // Sum of the sizes of the first `buckets` buckets.
 void launch_sum_sizes(const TableView& t, uint64_t buckets, unsigned long long* d_total,
                       cudaStream_t stream);
+// uint32 score arrays of the API boundary (sizeof(S) == 4) to and from uint64.
+void launch_widen_scores(const uint32_t* in, uint64_t* out, uint64_t n, cudaStream_t stream);
+void launch_narrow_scores(const uint64_t* in, uint32_t* out, uint64_t n, cudaStream_t stream);
 // Moves every live entry of `src` into the cleared table `dst`, which must have
 // exactly twice the buckets and a power-of-two capacity.
 void launch_rehash(const TableView& src, const TableView& dst, cudaStream_t stream);

@@ -222,6 +222,23 @@ __global__ void __launch_bounds__(kRehashBlock)
   }
 }
 
+// 32-bit score arrays at the API boundary <-> the 64-bit scores the kernels use.
+__global__ void __launch_bounds__(kScanBlock)
+    widen_scores_kernel(const uint32_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n) {
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += uint64_t(gridDim.x) * blockDim.x) {
+    out[i] = in[i];
+  }
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+    narrow_scores_kernel(const uint64_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t n) {
+  for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += uint64_t(gridDim.x) * blockDim.x) {
+    out[i] = static_cast<uint32_t>(in[i]);
+  }
+}
+
 unsigned scan_grid(uint64_t items_per_block_pass, uint64_t items) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -262,6 +279,16 @@ void launch_sum_sizes(const TableView& t, uint64_t buckets, unsigned long long* 
                       cudaStream_t stream) {
   sum_sizes_kernel<<<scan_grid(kScanBlock * 4, buckets), kScanBlock, 0, stream>>>(t, buckets,
                                                                                   d_total);
+}
+
+void launch_widen_scores(const uint32_t* in, uint64_t* out, uint64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  widen_scores_kernel<<<scan_grid(kScanBlock * 4, n), kScanBlock, 0, stream>>>(in, out, n);
+}
+
+void launch_narrow_scores(const uint64_t* in, uint32_t* out, uint64_t n, cudaStream_t stream) {
+  if (n == 0) return;
+  narrow_scores_kernel<<<scan_grid(kScanBlock * 4, n), kScanBlock, 0, stream>>>(in, out, n);
 }
 
 void launch_rehash(const TableView& src, const TableView& dst, cudaStream_t stream) {

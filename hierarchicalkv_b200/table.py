@@ -259,13 +259,19 @@ class HashTable:
     """Mirror of nv::merlin::HashTable<K, V, S, Strategy>.
 
     K is a 64-bit integer (torch.int64 tensors carry uint64 bit patterns),
-    S is uint64 (carried as torch.int64), V is ``value_dtype``.
+    S is uint64 (carried as torch.int64) or, with kCustomized only, uint32
+    (``score_dtype=torch.int32``: every score tensor is then int32), V is
+    ``value_dtype``.
     """
 
     def __init__(self, evict_strategy: EvictStrategy = EvictStrategy.kLru,
-                 value_dtype: torch.dtype = torch.float32):
+                 value_dtype: torch.dtype = torch.float32,
+                 score_dtype: torch.dtype = torch.int64):
         self.evict_strategy = EvictStrategy(evict_strategy)
         self.value_dtype = value_dtype
+        if score_dtype not in (torch.int64, torch.int32):
+            raise ValueError("The score_type must be uint64_t or uint32_t.")
+        self.score_dtype = score_dtype
         self._lib = load_library()
         self._h = ctypes.c_void_p()
         self._opts: Optional[HashTableOptions] = None
@@ -287,7 +293,8 @@ class HashTable:
             num_of_buckets_per_alloc=options.num_of_buckets_per_alloc,
             api_lock=int(options.api_lock), table_mode=int(options.table_mode),
             evict_strategy=int(self.evict_strategy),
-            value_size=_VALUE_SIZES[self.value_dtype], score_size=8,
+            value_size=_VALUE_SIZES[self.value_dtype],
+            score_size=8 if self.score_dtype == torch.int64 else 4,
             value_kind=_VALUE_KINDS.get(self.value_dtype, 0))
         h = ctypes.c_void_p()
         rc = self._lib.hkv_table_create(ctypes.byref(o), None, ctypes.byref(h))

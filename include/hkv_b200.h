@@ -85,7 +85,8 @@ typedef struct hkv_options {
   /* template parameters of HashTable<K,V,S,Strategy> */
   int32_t evict_strategy; /* hkv_evict_strategy */
   uint32_t value_size;    /* sizeof(V) */
-  uint32_t score_size;    /* sizeof(S): 8 */
+  uint32_t score_size;    /* sizeof(S): 8, or 4 with HKV_CUSTOMIZED; with 4 every `scores` array of
+                             this header holds uint32 values (the pointer type stays uint64_t*) */
   uint32_t value_kind;    /* hkv_value_kind: what accum_or_assign adds */
 } hkv_options;
 

@@ -440,8 +440,11 @@ template <typename K, typename V, typename S = uint64_t, int Strategy = EvictStr
 class HashTable : public HashTableBase<K, V, S> {
   static_assert(sizeof(K) == 8 && std::is_integral<K>::value,
                 "The key_type must be int64_t or uint64_t.");
-  static_assert(std::is_same<S, uint64_t>::value,
-                "The score_type must be uint64_t in this library.");
+  static_assert(std::is_same<S, uint64_t>::value || std::is_same<S, uint32_t>::value,
+                "The score_type must be uint64_t or uint32_t.");
+  // merlin_hashtable.cuh:944-948: the epoch strategies pack epoch | score into 64 bits
+  static_assert(!(std::is_same<S, uint32_t>::value && Strategy != EvictStrategy::kCustomized),
+                "score_type uint32_t is only compatible with Customized; use uint64_t.");
 
  public:
   using size_type = size_t;
@@ -491,7 +494,7 @@ class HashTable : public HashTableBase<K, V, S> {
   void insert_or_assign(const size_type n, const key_type* keys, const value_type* values,
                         const score_type* scores = nullptr, cudaStream_t stream = 0,
                         bool unique_key = true, bool ignore_evict_strategy = false) override {
-    detail::rethrow(hkv_insert_or_assign(table_, n, u(keys), values, scores, stream, unique_key,
+    detail::rethrow(hkv_insert_or_assign(table_, n, u(keys), values, w(scores), stream, unique_key,
                                          ignore_evict_strategy));
   }
 
@@ -500,8 +503,8 @@ class HashTable : public HashTableBase<K, V, S> {
                         value_type* evicted_values, score_type* evicted_scores,
                         size_type* d_evicted_counter, cudaStream_t stream = 0,
                         bool unique_key = true, bool ignore_evict_strategy = false) override {
-    detail::rethrow(hkv_insert_and_evict(table_, n, u(keys), values, scores, u(evicted_keys),
-                                         evicted_values, evicted_scores,
+    detail::rethrow(hkv_insert_and_evict(table_, n, u(keys), values, w(scores), u(evicted_keys),
+                                         evicted_values, w(evicted_scores),
                                          reinterpret_cast<uint64_t*>(d_evicted_counter), stream,
                                          unique_key, ignore_evict_strategy));
   }
@@ -512,8 +515,8 @@ class HashTable : public HashTableBase<K, V, S> {
                              cudaStream_t stream = 0, bool unique_key = true,
                              bool ignore_evict_strategy = false) override {
     uint64_t count = 0;
-    detail::rethrow(hkv_insert_and_evict_count(table_, n, u(keys), values, scores, u(evicted_keys),
-                                               evicted_values, evicted_scores, stream, unique_key,
+    detail::rethrow(hkv_insert_and_evict_count(table_, n, u(keys), values, w(scores), u(evicted_keys),
+                                               evicted_values, w(evicted_scores), stream, unique_key,
                                                ignore_evict_strategy, &count));
     return count;
   }
@@ -522,13 +525,13 @@ class HashTable : public HashTableBase<K, V, S> {
                        const bool* accum_or_assigns, const score_type* scores = nullptr,
                        cudaStream_t stream = 0, bool ignore_evict_strategy = false) override {
     detail::rethrow(hkv_accum_or_assign(table_, n, u(keys), value_or_deltas, accum_or_assigns,
-                                        scores, stream, ignore_evict_strategy));
+                                        w(scores), stream, ignore_evict_strategy));
   }
 
   void find_or_insert(const size_type n, const key_type* keys, value_type* values,
                       score_type* scores = nullptr, cudaStream_t stream = 0,
                       bool unique_key = true, bool ignore_evict_strategy = false) override {
-    detail::rethrow(hkv_find_or_insert(table_, n, u(keys), values, scores, stream, unique_key,
+    detail::rethrow(hkv_find_or_insert(table_, n, u(keys), values, w(scores), stream, unique_key,
                                        ignore_evict_strategy));
   }
 
@@ -537,7 +540,7 @@ class HashTable : public HashTableBase<K, V, S> {
                       bool unique_key = true, bool ignore_evict_strategy = false,
                       key_type** locked_key_ptrs = nullptr) override {
     detail::rethrow(hkv_find_or_insert_ptr(table_, n, u(keys), reinterpret_cast<void**>(values),
-                                           founds, scores, stream, unique_key,
+                                           founds, w(scores), stream, unique_key,
                                            ignore_evict_strategy,
                                            reinterpret_cast<uint64_t**>(locked_key_ptrs)));
   }
@@ -547,7 +550,7 @@ class HashTable : public HashTableBase<K, V, S> {
                  score_type const* scores = nullptr) override {
     detail::rethrow(hkv_lock_keys(table_, n, u(keys),
                                   reinterpret_cast<uint64_t**>(locked_key_ptrs), succeededs,
-                                  stream, scores));
+                                  stream, w(scores)));
   }
 
   void unlock_keys(const size_type n, key_type** locked_key_ptrs, const key_type* keys,
@@ -559,12 +562,12 @@ class HashTable : public HashTableBase<K, V, S> {
   void assign(const size_type n, const key_type* keys, const value_type* values,
               const score_type* scores = nullptr, cudaStream_t stream = 0,
               bool unique_key = true) override {
-    detail::rethrow(hkv_assign(table_, n, u(keys), values, scores, stream, unique_key));
+    detail::rethrow(hkv_assign(table_, n, u(keys), values, w(scores), stream, unique_key));
   }
 
   void assign_scores(const size_type n, const key_type* keys, const score_type* scores = nullptr,
                      cudaStream_t stream = 0, bool unique_key = true) override {
-    detail::rethrow(hkv_assign_scores(table_, n, u(keys), scores, stream, unique_key));
+    detail::rethrow(hkv_assign_scores(table_, n, u(keys), w(scores), stream, unique_key));
   }
 
   // alias of assign_scores, merlin_hashtable.cuh:2278-2283
@@ -580,28 +583,28 @@ class HashTable : public HashTableBase<K, V, S> {
 
   void find(const size_type n, const key_type* keys, value_type* values, bool* founds,
             score_type* scores = nullptr, cudaStream_t stream = 0) const override {
-    detail::rethrow(hkv_find(table_, n, u(keys), values, founds, scores, stream));
+    detail::rethrow(hkv_find(table_, n, u(keys), values, founds, w(scores), stream));
   }
 
   void find(const size_type n, const key_type* keys, value_type* values, key_type* missed_keys,
             int* missed_indices, int* missed_size, score_type* scores = nullptr,
             cudaStream_t stream = 0) const override {
     detail::rethrow(hkv_find_missed(table_, n, u(keys), values, u(missed_keys), missed_indices,
-                                    missed_size, scores, stream));
+                                    missed_size, w(scores), stream));
   }
 
   void find(const size_type n, const key_type* keys, value_type** values, bool* founds,
             score_type* scores = nullptr, cudaStream_t stream = 0,
             bool unique_key = true) const override {
     detail::rethrow(hkv_find_ptr(table_, n, u(keys), reinterpret_cast<void**>(values), founds,
-                                 scores, stream, unique_key));
+                                 w(scores), stream, unique_key));
   }
 
   void find_and_update(const size_type n, const key_type* keys, value_type** values, bool* founds,
                        score_type* scores = nullptr, cudaStream_t stream = 0,
                        bool unique_key = true) override {
     detail::rethrow(hkv_find_and_update(table_, n, u(keys), reinterpret_cast<void**>(values),
-                                        founds, scores, stream, unique_key));
+                                        founds, w(scores), stream, unique_key));
   }
 
   void contains(const size_type n, const key_type* keys, bool* founds,
@@ -619,7 +622,7 @@ class HashTable : public HashTableBase<K, V, S> {
                     value_type* values, score_type* scores = nullptr,
                     cudaStream_t stream = 0) const override {
     detail::rethrow(hkv_export_batch(table_, n, offset, reinterpret_cast<uint64_t*>(d_counter),
-                                     u(keys), values, scores, stream));
+                                     u(keys), values, w(scores), stream));
   }
 
   size_type export_batch(const size_type n, const size_type offset, key_type* keys,
@@ -627,7 +630,7 @@ class HashTable : public HashTableBase<K, V, S> {
                          cudaStream_t stream = 0) const override {
     uint64_t count = 0;
     detail::rethrow(
-        hkv_export_batch_count(table_, n, offset, u(keys), values, scores, stream, &count));
+        hkv_export_batch_count(table_, n, offset, u(keys), values, w(scores), stream, &count));
     return count;
   }
 
@@ -882,6 +885,10 @@ class HashTable : public HashTableBase<K, V, S> {
  private:
   static const uint64_t* u(const K* p) { return reinterpret_cast<const uint64_t*>(p); }
   static uint64_t* u(K* p) { return reinterpret_cast<uint64_t*>(p); }
+  // score arrays cross the ABI as they are: hkv_options.score_size tells the
+  // library whether they hold 64-bit or 32-bit scores
+  static const uint64_t* w(const S* p) { return reinterpret_cast<const uint64_t*>(p); }
+  static uint64_t* w(S* p) { return reinterpret_cast<uint64_t*>(p); }
 
   struct Workspace {
     K* d_keys = nullptr;

@@ -490,7 +490,48 @@ static void test_tile_functors() {
   std::printf("tile functors ok (dim %zu)\n", kDim);
 }
 
+// S = uint32_t (Customized only): 32-bit score arrays in and out.
+static void test_uint32_scores() {
+  constexpr size_t kDim = 4, kCap = 8 * 1024, kN = 4096;
+  using Table = nv::merlin::HashTable<K, V, uint32_t, EvictStrategy::kCustomized>;
+  HashTableOptions opt;
+  opt.init_capacity = opt.max_capacity = kCap;
+  opt.max_hbm_for_vectors = nv::merlin::GB(1);
+  opt.dim = kDim;
+  Table table;
+  table.init(opt);
+  std::vector<K> hk;
+  std::vector<V> hv;
+  std::vector<S> unused;
+  make_batch(4242, kN, kDim, hk, hv, unused);
+  std::vector<uint32_t> hs(kN);
+  for (size_t i = 0; i < kN; ++i) hs[i] = 0x80000000u + static_cast<uint32_t>(i);
+  DeviceBuffer<K> dk(kN);
+  DeviceBuffer<V> dv(kN * kDim);
+  DeviceBuffer<uint32_t> ds(kN);
+  DeviceBuffer<bool> df(kN);
+  dk.upload(hk);
+  dv.upload(hv);
+  ds.upload(hs);
+  table.insert_or_assign(kN, dk.p, dv.p, ds.p);
+  EXPECT(table.size() == kN);
+  CUDA_CHECK(cudaMemset(ds.p, 0, sizeof(uint32_t) * kN));
+  table.find(kN, dk.p, dv.p, df.p, ds.p);
+  CUDA_CHECK(cudaDeviceSynchronize());
+  auto gs = ds.download(kN);
+  for (size_t i = 0; i < kN; ++i) EXPECT(gs[i] == hs[i]);
+  DeviceBuffer<K> ek(kCap);
+  DeviceBuffer<V> ev(kCap * kDim);
+  DeviceBuffer<uint32_t> es(kCap);
+  const size_t exported = table.export_batch(table.capacity(), 0, ek.p, ev.p, es.p);
+  EXPECT(exported == kN);
+  auto xs = es.download(exported);
+  for (size_t i = 0; i < exported; ++i) EXPECT(xs[i] >= 0x80000000u && xs[i] < 0x80000000u + kN);
+  std::printf("uint32 scores ok\n");
+}
+
 int main() {
+  test_uint32_scores();
   test_rehash();
   test_tile_functors<16>();
   test_tile_functors<4>();

@@ -202,6 +202,77 @@ def test_accum_or_assign_adds_in_the_value_type(dtype, dim, unique):
     t.close()
 
 
+def test_uint32_scores_customized():
+    """S = uint32_t with the Customized strategy (tests/uint32_score_test.cc.cu of
+    the reference): 32-bit score arrays in and out, same decisions as 64-bit scores."""
+    import torch
+    import hierarchicalkv_b200 as hkv
+
+    cap, dim = 128 * 8, 4
+    t = hkv.HashTable(hkv.EvictStrategy.kCustomized, score_dtype=torch.int32)
+    t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                dim=dim))
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(3 * cap, seed=77)
+    rng = np.random.default_rng(9)
+    sc = rng.permutation(3 * cap).astype(np.uint64) + np.uint64(0x7FFF0000)   # distinct, above 2^31 too
+    s32 = lambda a: torch.from_numpy(a.astype(np.uint32).view(np.int32)).cuda()
+    for part in range(3):                       # overfills: evictions and refusals by score
+        sl = slice(part * cap, (part + 1) * cap)
+        v = values_for(keys[sl], dim, seed=part)
+        t.insert_or_assign(cap, to_dev(keys[sl]), to_dev(v), s32(sc[sl]))
+        o.insert_or_assign(keys[sl], v, sc[sl])
+    assert t.size() == o.size()
+    out = torch.zeros((3 * cap, dim), device="cuda")
+    f = torch.zeros(3 * cap, dtype=torch.bool, device="cuda")
+    got_s = torch.full((3 * cap,), -1, dtype=torch.int32, device="cuda")
+    t.find(3 * cap, to_dev(keys), out, f, got_s)
+    torch.cuda.synchronize()
+    ov, of, os_ = o.find(keys)
+    np.testing.assert_array_equal(f.cpu().numpy(), of)
+    np.testing.assert_array_equal(out.cpu().numpy()[of], ov[of])
+    gs = got_s.cpu().numpy().view(np.uint32)
+    np.testing.assert_array_equal(gs[of].astype(np.uint64), os_[of])
+    assert np.all(gs[~of] == 0xFFFFFFFF)        # misses leave the caller's scores alone
+    # assign_scores, then export with 32-bit scores
+    upd = keys[of][:300]
+    new_sc = np.arange(1, 301, dtype=np.uint64)
+    t.assign_scores(300, to_dev(upd), s32(new_sc))
+    o.assign_scores(upd, new_sc)
+    ek = torch.zeros(cap, dtype=torch.int64, device="cuda")
+    ev = torch.zeros((cap, dim), device="cuda")
+    es = torch.zeros(cap, dtype=torch.int32, device="cuda")
+    n = t.export_batch(cap, 0, None, ek, ev, es)
+    torch.cuda.synchronize()
+    k, v, s = sorted_by_key(to_np_u64(ek[:n]), ev[:n].cpu().numpy(),
+                            es[:n].cpu().numpy().view(np.uint32).astype(np.uint64))
+    wk, wv, ws = sorted_by_key(*o.export_batch())
+    np.testing.assert_array_equal(k, wk)
+    np.testing.assert_array_equal(v, wv)
+    np.testing.assert_array_equal(s, ws)
+    # insert_and_evict returns 32-bit evicted scores
+    fresh = unique_keys(256, seed=78)
+    fs = np.arange(0xF0000000, 0xF0000000 + 256, dtype=np.uint64)
+    evk = torch.zeros(256, dtype=torch.int64, device="cuda")
+    evv = torch.zeros((256, dim), device="cuda")
+    evs = torch.zeros(256, dtype=torch.int32, device="cuda")
+    cnt = t.insert_and_evict(256, to_dev(fresh), to_dev(values_for(fresh, dim)), s32(fs), evk, evv, evs)
+    torch.cuda.synchronize()
+    wk2, wv2, ws2 = o.insert_and_evict(fresh, values_for(fresh, dim), fs)
+    assert cnt == wk2.size
+    a = sorted_by_key(to_np_u64(evk[:cnt]), evv[:cnt].cpu().numpy(),
+                      evs[:cnt].cpu().numpy().view(np.uint32).astype(np.uint64))
+    b = sorted_by_key(wk2, wv2, ws2)
+    for x, y in zip(a, b):
+        np.testing.assert_array_equal(x, y)
+    t.close()
+    # the other strategies need 64-bit scores
+    bad = hkv.HashTable(hkv.EvictStrategy.kLfu, score_dtype=torch.int32)
+    with pytest.raises(hkv.MerlinException):
+        bad.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap,
+                                      max_hbm_for_vectors=1 << 30, dim=dim))
+
+
 def test_accum_or_assign_rejects_types_it_cannot_add():
     import torch
     import hierarchicalkv_b200 as hkv
