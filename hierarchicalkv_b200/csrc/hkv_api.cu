@@ -7,6 +7,7 @@
 // (include/merlin/core_kernels.cuh:327-381).
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -377,7 +378,13 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
     const uint64_t off_scores = align256(off_keys + capacity * 8);
     const uint64_t off_sizes = align256(off_scores + capacity * 8);
     const uint64_t off_status = align256(off_sizes + buckets * 4);
-    const uint64_t meta_bytes = off_status + 256;
+    uint64_t hbm_buckets = t->opt.max_hbm_for_vectors / (row_bytes * hkv::kBucketSlots);
+    if (hbm_buckets > buckets) hbm_buckets = buckets;
+    // a table with rows on both sides gets a bucket map and hit counters
+    const bool mapped = hbm_buckets > 0 && hbm_buckets < buckets;
+    const uint64_t off_map = align256(off_status + 256);
+    const uint64_t off_heat = align256(off_map + (mapped ? buckets * 4 : 0));
+    const uint64_t meta_bytes = mapped ? align256(off_heat + buckets * 4) : off_status + 256;
     if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &p.meta_block, meta_bytes, 0) != 0 ||
         p.meta_block == nullptr) {
       cudaGetLastError();
@@ -391,9 +398,9 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
     v.status = reinterpret_cast<uint32_t*>(mb + off_status);
     p.d_scratch = reinterpret_cast<unsigned long long*>(mb + off_status + 64);
     HKV_CUDA(cudaMemsetAsync(mb + off_status, 0, 256, stream));
+    v.bucket_map = mapped ? reinterpret_cast<uint32_t*>(mb + off_map) : nullptr;
+    v.bucket_heat = mapped ? reinterpret_cast<uint32_t*>(mb + off_heat) : nullptr;
 
-    uint64_t hbm_buckets = t->opt.max_hbm_for_vectors / (row_bytes * hkv::kBucketSlots);
-    if (hbm_buckets > buckets) hbm_buckets = buckets;
     v.hbm_slots = hbm_buckets * hkv::kBucketSlots;
     v.values_hbm = nullptr;
     v.values_host = nullptr;
@@ -419,11 +426,57 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
       v.values_host = static_cast<uint8_t*>(dp);
     }
     hkv::launch_clear(v, stream);
+    if (mapped) hkv::launch_identity_map(v, stream);
     check_launch();
   } catch (...) {
     free_planes(t, p);
     throw;
   }
+}
+
+// Hot buckets of a hybrid table move into HBM: the host-resident buckets with
+// the most lookup hits since the last call trade row blocks with the coldest
+// HBM-resident ones, as long as the bucket moving in was hit more than twice
+// as often as the one moving out.  The
+// choice is made on the host from the hit counters; the rows move in one kernel.
+uint64_t promote_hot_buckets(hkv_table* t, cudaStream_t s) {
+  const hkv::TableView& v = t->view;
+  if (v.bucket_map == nullptr) return 0;
+  LockScope ls(t, kInserter, s);
+  const uint64_t buckets = v.buckets;
+  const uint32_t hbm_blocks = static_cast<uint32_t>(v.hbm_slots / hkv::kBucketSlots);
+  std::vector<uint32_t> map(buckets), heat(buckets);
+  HKV_CUDA(cudaMemcpyAsync(map.data(), v.bucket_map, buckets * 4, cudaMemcpyDeviceToHost, s));
+  HKV_CUDA(cudaMemcpyAsync(heat.data(), v.bucket_heat, buckets * 4, cudaMemcpyDeviceToHost, s));
+  HKV_CUDA(cudaStreamSynchronize(s));
+  std::vector<uint32_t> in_hbm, in_host;
+  for (uint64_t b = 0; b < buckets; ++b) {
+    (map[b] < hbm_blocks ? in_hbm : in_host).push_back(static_cast<uint32_t>(b));
+  }
+  std::sort(in_hbm.begin(), in_hbm.end(),
+            [&](uint32_t a, uint32_t b) { return heat[a] != heat[b] ? heat[a] < heat[b] : a < b; });
+  std::sort(in_host.begin(), in_host.end(),
+            [&](uint32_t a, uint32_t b) { return heat[a] != heat[b] ? heat[a] > heat[b] : a < b; });
+  std::vector<uint32_t> pairs;
+  for (size_t i = 0; i < in_hbm.size() && i < in_host.size(); ++i) {
+    // a move costs two row blocks over the host link: it has to pay
+    if (uint64_t(heat[in_host[i]]) < 2ull * heat[in_hbm[i]] + 8) break;
+    pairs.push_back(in_host[i]);
+    pairs.push_back(in_hbm[i]);
+  }
+  const uint64_t n_pairs = pairs.size() / 2;
+  if (n_pairs > 0) {
+    uint32_t* d_pairs = nullptr;
+    HKV_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&d_pairs), pairs.size() * 4, s));
+    cudaMemcpyAsync(d_pairs, pairs.data(), pairs.size() * 4, cudaMemcpyHostToDevice, s);
+    hkv::launch_swap_row_blocks(v, d_pairs, n_pairs, s);
+    cudaFreeAsync(d_pairs, s);
+    // `pairs` is pageable host memory: the copy above has been staged when it returns
+  }
+  hkv::launch_decay_heat(v, s);
+  ls.done();
+  check_launch();
+  return n_pairs;
 }
 
 // fast_load_factor, include/merlin_hashtable.cuh:3796-3828: the load the table
@@ -1130,6 +1183,14 @@ int hkv_set_max_capacity(hkv_table* t, uint64_t new_max_capacity) {
   });
 }
 
+int hkv_promote_hot_buckets(hkv_table* t, hkv_stream stream, uint64_t* promoted) {
+  return guarded([&] {
+    DeviceGuard dg(t->device);
+    const uint64_t n = promote_hot_buckets(t, static_cast<cudaStream_t>(stream));
+    if (promoted != nullptr) *promoted = n;
+  });
+}
+
 int hkv_get_view(const hkv_table* t, hkv_table_view* view) {
   return guarded([&] {
     const hkv::TableView& v = t->view;
@@ -1142,6 +1203,7 @@ int hkv_get_view(const hkv_table* t, hkv_table_view* view) {
     view->buckets = v.buckets;
     view->capacity = v.capacity;
     view->hbm_slots = v.hbm_slots;
+    view->bucket_map = v.bucket_map;
     view->row_bytes = v.row_bytes;
     view->empty_key = v.empty_key;
     view->reclaim_key = v.reclaim_key;

@@ -63,8 +63,14 @@ struct TableView {
   uint8_t* digests;
   uint64_t* keys;
   uint64_t* scores;
-  uint8_t* values_hbm;    // rows of slots [0, hbm_slots)
-  uint8_t* values_host;   // rows of slots [hbm_slots, capacity), pinned+mapped
+  uint8_t* values_hbm;    // rows of row slots [0, hbm_slots)
+  uint8_t* values_host;   // rows of row slots [hbm_slots, capacity), pinned+mapped
+  // Hybrid tables only (else null): bucket b keeps its 128 rows in row block
+  // bucket_map[b] (blocks below hbm_slots / 128 are in HBM), so hot buckets
+  // can trade places with cold ones; bucket_heat[b] counts the hits lookups
+  // found in bucket b since the last promotion.
+  uint32_t* bucket_map;
+  uint32_t* bucket_heat;
   int32_t* bucket_sizes;
   uint32_t* status;       // device status word (kStatus* bits)
   uint64_t buckets;
@@ -121,10 +127,25 @@ __device__ __forceinline__ Address locate(const TableView& t, uint64_t key) {
   return a;
 }
 
+// Host side: may the kernels specialised for 16-byte chunks of pure-HBM rows run?
+inline bool fast_rows(const TableView& t) {
+  return t.vec_bytes == 16 && t.hbm_slots == t.capacity && t.bucket_map == nullptr;
+}
+
+// Where slot's row lives: the slot itself, or its place in the row block the
+// bucket map assigns to the slot's bucket.
+__device__ __forceinline__ uint64_t row_slot(const TableView& t, uint64_t slot) {
+  if (t.bucket_map == nullptr) return slot;
+  return (uint64_t(t.bucket_map[slot >> 7]) << 7) | (slot & (kBucketSlots - 1));
+}
+
+__device__ __forceinline__ uint8_t* row_ptr_of_row_slot(const TableView& t, uint64_t rs) {
+  return rs < t.hbm_slots ? t.values_hbm + rs * t.row_bytes
+                          : t.values_host + (rs - t.hbm_slots) * t.row_bytes;
+}
+
 __device__ __forceinline__ uint8_t* row_ptr(const TableView& t, uint64_t slot) {
-  return slot < t.hbm_slots
-             ? t.values_hbm + slot * t.row_bytes
-             : t.values_host + (slot - t.hbm_slots) * t.row_bytes;
+  return row_ptr_of_row_slot(t, row_slot(t, slot));
 }
 
 // ---- slot atomics (64-bit keys and scores, device scope) -------------------
@@ -372,7 +393,10 @@ __device__ __forceinline__ void accumulate_chunk(T& cur, const T& add, uint32_t 
 // INDEXED: the batch rows are not the warp's 32 consecutive rows; lane r holds
 // in `row_index` which row of `batch_rows` belongs to it.  `batch_rows` may
 // then be another GPU's memory and is accessed with plain loads and stores.
-template <int VEC, int MODE, bool INDEXED = false>
+//
+// PURE: every row is in HBM at its slot's own place (no host rows, no bucket
+// map), which the launcher checks before it picks such an instantiation.
+template <int VEC, int MODE, bool INDEXED = false, bool PURE = false>
 __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* batch_rows,
                                                    uint32_t slot, uint32_t lane,
                                                    uint32_t row_index = 0) {
@@ -392,14 +416,17 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
       const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r & 31u);
       ok[u] = (c < total) && (s != kNoSlot);
       const uint32_t off = (c - r * cpr) * VEC;
-      tab[u] = ok[u] ? row_ptr(t, s) + off : nullptr;
+      const uint64_t rs = (ok[u] && !PURE) ? row_slot(t, s) : s;
+      tab[u] = !ok[u] ? nullptr
+                      : (PURE ? t.values_hbm + uint64_t(s) * t.row_bytes
+                              : row_ptr_of_row_slot(t, rs)) + off;
       if (INDEXED) {
         const uint32_t at = __shfl_sync(0xFFFFFFFFu, row_index, r & 31u);
         bat[u] = batch_rows + uint64_t(at) * t.row_bytes + off;
       }
       if (ok[u]) {
         if (MODE == 0) {
-          regs[u] = ld_table_row<T>(tab[u], s >= t.hbm_slots);
+          regs[u] = ld_table_row<T>(tab[u], !PURE && rs >= t.hbm_slots);
         } else if (INDEXED) {
           regs[u] = *reinterpret_cast<const T*>(bat[u]);
         } else {
@@ -432,7 +459,9 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
 // Gather variant whose destination is not a contiguous batch: lane r holds the
 // table slot of row r (or kNoSlot) and the row index `dest_row` it goes to in
 // `dest_base` (possibly another GPU's memory, written with plain stores).
-template <int VEC>
+// ROW_SLOTS: `slot` already names the place of the row (row_slot()), not the
+// table slot.
+template <int VEC, bool ROW_SLOTS = false, bool PURE = false>
 __device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint8_t* dest_base,
                                                         uint32_t dest_row, uint32_t slot,
                                                         uint32_t lane) {
@@ -451,7 +480,9 @@ __device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint
       const uint32_t d = __shfl_sync(0xFFFFFFFFu, dest_row, r & 31u);
       drow[u] = kNoSlot;
       if (c < total && s != kNoSlot) {
-        regs[u] = ld_stream(reinterpret_cast<const T*>(row_ptr(t, s) + (c - r * cpr) * VEC));
+        const uint8_t* row = PURE ? t.values_hbm + uint64_t(s) * t.row_bytes
+                                  : (ROW_SLOTS ? row_ptr_of_row_slot(t, s) : row_ptr(t, s));
+        regs[u] = ld_stream(reinterpret_cast<const T*>(row + (c - r * cpr) * VEC));
         drow[u] = d;
       }
     }
@@ -467,32 +498,34 @@ __device__ __forceinline__ void warp_gather_rows_to_vec(const TableView& t, uint
   }
 }
 
-template <int VEC = 0>
+template <int VEC = 0, bool ROW_SLOTS = false>
 __device__ __forceinline__ void warp_gather_rows_to(const TableView& t, uint8_t* dest_base,
                                                     uint32_t dest_row, uint32_t slot,
                                                     uint32_t lane) {
   if constexpr (VEC != 0) {
-    warp_gather_rows_to_vec<VEC>(t, dest_base, dest_row, slot, lane);
+    warp_gather_rows_to_vec<VEC, ROW_SLOTS, true>(t, dest_base, dest_row, slot, lane);
     return;
   }
   switch (t.vec_bytes) {
-    case 16: warp_gather_rows_to_vec<16>(t, dest_base, dest_row, slot, lane); break;
-    case 8: warp_gather_rows_to_vec<8>(t, dest_base, dest_row, slot, lane); break;
-    case 4: warp_gather_rows_to_vec<4>(t, dest_base, dest_row, slot, lane); break;
-    case 2: warp_gather_rows_to_vec<2>(t, dest_base, dest_row, slot, lane); break;
-    default: warp_gather_rows_to_vec<1>(t, dest_base, dest_row, slot, lane); break;
+    case 16: warp_gather_rows_to_vec<16, ROW_SLOTS>(t, dest_base, dest_row, slot, lane); break;
+    case 8: warp_gather_rows_to_vec<8, ROW_SLOTS>(t, dest_base, dest_row, slot, lane); break;
+    case 4: warp_gather_rows_to_vec<4, ROW_SLOTS>(t, dest_base, dest_row, slot, lane); break;
+    case 2: warp_gather_rows_to_vec<2, ROW_SLOTS>(t, dest_base, dest_row, slot, lane); break;
+    default: warp_gather_rows_to_vec<1, ROW_SLOTS>(t, dest_base, dest_row, slot, lane); break;
   }
 }
 
-// VEC != 0 fixes the access width at compile time (the launcher picks the
-// instantiation that matches t.vec_bytes), which keeps the four other unrolled
-// copy loops out of the hot kernels' instruction footprint.
+// VEC != 0 fixes the access width at compile time and promises a pure-HBM
+// table (the launcher picks the instantiation: t.vec_bytes == VEC and no host
+// rows), which keeps the four other unrolled copy loops, the bucket map and
+// the host-memory cases out of the hot kernels' instruction footprint.
 template <int MODE, int VEC = 0, bool INDEXED = false>
 __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
                                                uint32_t slot, uint32_t lane,
                                                uint32_t row_index = 0) {
   if constexpr (VEC != 0) {
-    warp_move_rows_vec<VEC, MODE, INDEXED>(t, batch_rows, slot, lane, row_index);
+    // the fixed-width instantiations serve pure-HBM tables only
+    warp_move_rows_vec<VEC, MODE, INDEXED, true>(t, batch_rows, slot, lane, row_index);
     return;
   }
   // vec_bytes is warp-uniform; the host lowers it when a batch pointer is

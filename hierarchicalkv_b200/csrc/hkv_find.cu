@@ -93,8 +93,9 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
 // FORM 1: value pointers + founds (+scores) (find*, merlin_hashtable.cuh:2729)
 // FORM 2: values + missed keys/indices/size (merlin_hashtable.cuh:2600)
 // FORM 3: founds only                     (contains, merlin_hashtable.cuh:2856)
-// FORM 4: founds (+scores) and, per key, its slot and its batch index: the
-//         first step of find on a table whose rows partly live in host memory
+// FORM 4: founds (+scores) and, per key, the place of its row and its batch
+//         index: the first step of find on a table whose rows partly live in
+//         host memory
 template <int FORM, int VEC>
 __global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
     find_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
@@ -124,8 +125,11 @@ __global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
     if (FORM == 1) ptrs[i] = found ? row_ptr(t, slot) : nullptr;
     if (FORM != 3 && scores != nullptr && found) scores[i] = t.scores[slot];
     if (FORM == 4) {
-      slot_out[i] = slot;  // kNoSlot sorts behind every real slot
+      // where the row lives (kNoSlot sorts behind every real place); the
+      // bucket's hit counter feeds the promotion of hot buckets into HBM
+      slot_out[i] = found ? static_cast<uint32_t>(row_slot(t, slot)) : kNoSlot;
       index_out[i] = static_cast<uint32_t>(i);
+      if (found && t.bucket_heat != nullptr) atomicAdd(t.bucket_heat + (slot >> 7), 1u);
     }
   }
   if (FORM == 2) {
@@ -206,7 +210,7 @@ void launch_form(const TableView& t, uint64_t n, const uint64_t* keys, void* val
   if (n == 0) return;
   const uint64_t warps = (n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kFindBlock - 1) / kFindBlock;
-  auto kernel = t.vec_bytes == 16 ? find_kernel<FORM, 16> : find_kernel<FORM, 0>;
+  auto kernel = fast_rows(t) ? find_kernel<FORM, 16> : find_kernel<FORM, 0>;
   kernel<<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
       t, keys, n, static_cast<uint8_t*>(values), ptrs, founds, scores, missed_keys, missed_indices,
       missed_size, nullptr, nullptr);
@@ -232,7 +236,7 @@ __global__ void __launch_bounds__(kFindBlock)
     dest = sorted_index[i];
   }
   if (__ballot_sync(0xFFFFFFFFu, slot != kNoSlot) == 0) return;
-  warp_gather_rows_to(t, values, dest, slot, lane);
+  warp_gather_rows_to<0, true>(t, values, dest, slot, lane);
 }
 
 // find on a table with rows in pinned host memory: probe, sort by slot, gather.
@@ -297,7 +301,7 @@ void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
                         const PeerPtrs& out_founds, cudaStream_t stream) {
   if (segment_capacity == 0) return;
   const uint64_t per_segment = (segment_capacity + kFindBlock - 1) / kFindBlock;
-  auto kernel = t.vec_bytes == 16 ? find_routed_kernel<16> : find_routed_kernel<0>;
+  auto kernel = fast_rows(t) ? find_routed_kernel<16> : find_routed_kernel<0>;
   kernel<<<static_cast<unsigned>(per_segment * world), kFindBlock, 0, stream>>>(
       t, static_cast<uint32_t>(per_segment), world, (my_rank + 1) % world, segment_capacity,
       inbox_keys, inbox_origin,

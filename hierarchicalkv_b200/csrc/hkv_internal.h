@@ -113,6 +113,12 @@ void launch_clear(const TableView& t, cudaStream_t stream);
 // Sum of the sizes of the first `buckets` buckets.
 void launch_sum_sizes(const TableView& t, uint64_t buckets, unsigned long long* d_total,
                       cudaStream_t stream);
+// Hybrid tables: bucket b keeps its rows in row block bucket_map[b].
+void launch_identity_map(const TableView& t, cudaStream_t stream);
+void launch_decay_heat(const TableView& t, cudaStream_t stream);
+// pairs[2p], pairs[2p+1]: buckets that trade row blocks (each bucket at most once).
+void launch_swap_row_blocks(const TableView& t, const uint32_t* pairs, uint64_t n_pairs,
+                            cudaStream_t stream);
 // uint32 score arrays of the API boundary (sizeof(S) == 4) to and from uint64.
 void launch_widen_scores(const uint32_t* in, uint64_t* out, uint64_t n, cudaStream_t stream);
 void launch_narrow_scores(const uint64_t* in, uint32_t* out, uint64_t n, cudaStream_t stream);

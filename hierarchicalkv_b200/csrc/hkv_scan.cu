@@ -222,6 +222,60 @@ __global__ void __launch_bounds__(kRehashBlock)
   }
 }
 
+// ---- hybrid tables: which row block holds which bucket ------------------------
+__global__ void __launch_bounds__(kScanBlock) identity_map_kernel(const TableView t) {
+  for (uint64_t b = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < t.buckets;
+       b += uint64_t(gridDim.x) * blockDim.x) {
+    t.bucket_map[b] = static_cast<uint32_t>(b);
+    t.bucket_heat[b] = 0;
+  }
+}
+
+// Hit counters fade: what was hot before the previous promotion counts half.
+__global__ void __launch_bounds__(kScanBlock) decay_heat_kernel(const TableView t) {
+  for (uint64_t b = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < t.buckets;
+       b += uint64_t(gridDim.x) * blockDim.x) {
+    t.bucket_heat[b] >>= 1;
+  }
+}
+
+// One block per pair (a, b) of buckets: the two buckets trade row blocks --
+// the 128 rows of each are copied to the other's place (16-byte chunks,
+// coalesced; one of the two places is pinned host memory) and the map entries
+// are exchanged.  Runs under the exclusive lock.
+__global__ void __launch_bounds__(kScanBlock)
+    swap_row_blocks_kernel(const TableView t, const uint32_t* __restrict__ pairs,
+                           const uint64_t n_pairs) {
+  const uint64_t block_bytes = uint64_t(kBucketSlots) * t.row_bytes;
+  for (uint64_t p = blockIdx.x; p < n_pairs; p += gridDim.x) {
+    const uint32_t a = pairs[2 * p], b = pairs[2 * p + 1];
+    const uint32_t place_a = t.bucket_map[a], place_b = t.bucket_map[b];
+    uint8_t* rows_a = row_ptr_of_row_slot(t, uint64_t(place_a) << 7);
+    uint8_t* rows_b = row_ptr_of_row_slot(t, uint64_t(place_b) << 7);
+    if (t.row_bytes % 16 == 0) {
+      for (uint64_t off = uint64_t(threadIdx.x) * 16; off < block_bytes;
+           off += uint64_t(blockDim.x) * 16) {
+        const uint4 x = *reinterpret_cast<const uint4*>(rows_a + off);
+        const uint4 y = *reinterpret_cast<const uint4*>(rows_b + off);
+        *reinterpret_cast<uint4*>(rows_a + off) = y;
+        *reinterpret_cast<uint4*>(rows_b + off) = x;
+      }
+    } else {
+      for (uint64_t off = threadIdx.x; off < block_bytes; off += blockDim.x) {
+        const uint8_t x = rows_a[off], y = rows_b[off];
+        rows_a[off] = y;
+        rows_b[off] = x;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      t.bucket_map[a] = place_b;
+      t.bucket_map[b] = place_a;
+    }
+    __syncthreads();
+  }
+}
+
 // 32-bit score arrays at the API boundary <-> the 64-bit scores the kernels use.
 __global__ void __launch_bounds__(kScanBlock)
     widen_scores_kernel(const uint32_t* __restrict__ in, uint64_t* __restrict__ out, uint64_t n) {
@@ -279,6 +333,20 @@ void launch_sum_sizes(const TableView& t, uint64_t buckets, unsigned long long* 
                       cudaStream_t stream) {
   sum_sizes_kernel<<<scan_grid(kScanBlock * 4, buckets), kScanBlock, 0, stream>>>(t, buckets,
                                                                                   d_total);
+}
+
+void launch_identity_map(const TableView& t, cudaStream_t stream) {
+  identity_map_kernel<<<scan_grid(kScanBlock * 4, t.buckets), kScanBlock, 0, stream>>>(t);
+}
+
+void launch_decay_heat(const TableView& t, cudaStream_t stream) {
+  decay_heat_kernel<<<scan_grid(kScanBlock * 4, t.buckets), kScanBlock, 0, stream>>>(t);
+}
+
+void launch_swap_row_blocks(const TableView& t, const uint32_t* pairs, uint64_t n_pairs,
+                            cudaStream_t stream) {
+  if (n_pairs == 0) return;
+  swap_row_blocks_kernel<<<scan_grid(1, n_pairs), kScanBlock, 0, stream>>>(t, pairs, n_pairs);
 }
 
 void launch_widen_scores(const uint32_t* in, uint64_t* out, uint64_t n, cudaStream_t stream) {

@@ -944,7 +944,7 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
   const uint64_t warps = (args.n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kMutateBlock - 1) / kMutateBlock;
   if (unique_key) {
-    auto kernel = t.vec_bytes == 16 ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
+    auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
     kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
   } else {
     mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
@@ -978,7 +978,7 @@ void launch_routed_op(const TableView& t, MutateArgs args, uint32_t world, uint3
   const uint64_t* keys0 = args.keys;
   const uint32_t* index0 = args.row_index;
   const uint64_t blocks = (segment_capacity + kMutateBlock - 1) / kMutateBlock;
-  auto kernel = t.vec_bytes == 16 ? mutate_kernel<OP, 16, true> : mutate_kernel<OP, 0, true>;
+  auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, true> : mutate_kernel<OP, 0, true>;
   for (uint32_t turn = 0; turn < world; ++turn) {
     const uint32_t seg = (first_segment + turn) % world;
     args.keys = keys0 + uint64_t(seg) * segment_capacity;

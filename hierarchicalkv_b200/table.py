@@ -85,6 +85,7 @@ class TableView(ctypes.Structure):
         ("values_hbm", ctypes.c_void_p),
         ("values_host", ctypes.c_void_p),
         ("bucket_sizes", ctypes.c_void_p),
+        ("bucket_map", ctypes.c_void_p),
         ("buckets", ctypes.c_uint64),
         ("capacity", ctypes.c_uint64),
         ("hbm_slots", ctypes.c_uint64),
@@ -176,6 +177,7 @@ _SIGNATURES = {
     "hkv_set_global_epoch": [_P, _U64],
     "hkv_reserve": [_P, _U64, _P],
     "hkv_set_max_capacity": [_P, _U64],
+    "hkv_promote_hot_buckets": [_P, _P, ctypes.POINTER(ctypes.c_uint64)],
     "hkv_get_view": [_P, ctypes.POINTER(TableView)],
     "hkv_external_begin": [_P, _INT, _P],
     "hkv_external_end": [_P, _INT, _P],
@@ -497,6 +499,13 @@ class HashTable:
 
     def reserve(self, new_capacity: int, stream=None) -> None:
         self._call("hkv_reserve", new_capacity, _stream(stream))
+
+    def promote_hot_buckets(self, stream=None) -> int:
+        """Hybrid tables: moves the rows of the most looked-up host-resident
+        buckets into HBM (no counterpart in the reference).  Returns how many."""
+        out = ctypes.c_uint64(0)
+        self._call("hkv_promote_hot_buckets", _stream(stream), ctypes.byref(out))
+        return out.value
 
     def set_max_capacity(self, new_max_capacity: int) -> None:
         """Raises ValueError (std::invalid_argument in the reference) unless a power of two."""

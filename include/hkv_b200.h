@@ -121,9 +121,11 @@ typedef struct hkv_table_view {
   uint8_t* digests;      /* [buckets][128] */
   uint64_t* keys;        /* [buckets][128] */
   uint64_t* scores;      /* [buckets][128] */
-  uint8_t* values_hbm;   /* rows of slots [0, hbm_slots) */
-  uint8_t* values_host;  /* rows of slots [hbm_slots, capacity), mapped pinned */
+  uint8_t* values_hbm;   /* rows of row slots [0, hbm_slots) */
+  uint8_t* values_host;  /* rows of row slots [hbm_slots, capacity), mapped pinned */
   int32_t* bucket_sizes; /* [buckets] */
+  uint32_t* bucket_map;  /* null, or [buckets]: the row of slot s is row slot
+                            bucket_map[s / 128] * 128 + s % 128 (hybrid tables) */
   uint64_t buckets;
   uint64_t capacity;
   uint64_t hbm_slots;
@@ -288,6 +290,15 @@ HKV_API int hkv_reserve(hkv_table* table, uint64_t new_capacity, hkv_stream stre
  * HKV_ERR_INVALID_ARG (std::invalid_argument in the reference) unless
  * new_max_capacity is a power of two; ignored when below the capacity. */
 HKV_API int hkv_set_max_capacity(hkv_table* table, uint64_t new_max_capacity);
+
+/* Hybrid tables (rows partly in HBM, partly in pinned host memory): moves the
+ * rows of the host-resident buckets with the most lookup hits since the last
+ * call into HBM, in exchange for the coldest HBM-resident buckets, and halves
+ * the hit counters.  *promoted receives the number of buckets moved in (0 for
+ * a table that is not hybrid).  Exclusive like clear; synchronises the stream.
+ * Row pointers handed out before are invalid afterwards.  No counterpart in the
+ * reference, whose README lists a warm-up of hot rows as planned. */
+HKV_API int hkv_promote_hot_buckets(hkv_table* table, hkv_stream stream, uint64_t* promoted);
 
 /* Planes of the table for header-side functor kernels.  No counterpart in
  * the reference, whose templated kernels live in the class itself.  The planes

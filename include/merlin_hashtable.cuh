@@ -137,6 +137,7 @@ __device__ __forceinline__ bool view_is_reserved(const hkv_table_view& v, uint64
 }
 
 __device__ __forceinline__ const uint8_t* view_row(const hkv_table_view& v, uint64_t slot) {
+  if (v.bucket_map != nullptr) slot = (uint64_t(v.bucket_map[slot >> 7]) << 7) | (slot & 127u);
   return slot < v.hbm_slots ? v.values_hbm + slot * v.row_bytes
                             : v.values_host + (slot - v.hbm_slots) * v.row_bytes;
 }
@@ -797,6 +798,15 @@ class HashTable : public HashTableBase<K, V, S> {
 
   void reserve(const size_type new_capacity, cudaStream_t stream = 0) override {
     detail::rethrow(hkv_reserve(table_, new_capacity, stream));
+  }
+
+  // Not in the reference: on a hybrid table, moves the rows of the buckets
+  // that lookups hit most into HBM (hkv_promote_hot_buckets).  Returns the
+  // number of buckets moved in.
+  size_type promote_hot_buckets(cudaStream_t stream = 0) {
+    uint64_t promoted = 0;
+    detail::rethrow(hkv_promote_hot_buckets(table_, stream, &promoted));
+    return promoted;
   }
 
   float load_factor(cudaStream_t stream = 0) const override {

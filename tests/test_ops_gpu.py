@@ -421,6 +421,82 @@ def test_hybrid_hbm_and_pinned_host_values(hbm_fraction):
     t.close()
 
 
+def test_promotion_moves_hot_buckets_into_hbm():
+    """A hybrid table counts lookup hits per bucket; promote_hot_buckets trades
+    the row blocks of the hottest host-resident buckets against the coldest
+    HBM-resident ones.  Contents are unchanged for every operation, the hot
+    keys' rows end up in HBM, and later updates land in the moved rows."""
+    import ctypes
+
+    cap, dim = 128 * 64, 16
+    hbm_buckets = 16
+    t = ProductTable(cap, dim, CUSTOMIZED, max_hbm_for_vectors=hbm_buckets * 128 * dim * 4)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(6000, seed=21)
+    sc = np.arange(1, keys.size + 1, dtype=np.uint64)
+    for x in (t, o):
+        x.insert_or_assign(keys, values_for(keys, dim), sc)
+    assert t.size() == o.size()
+    present = keys[t.contains(keys)]
+    bucket = bucket_of(present, cap)
+    view = t.t.view()
+    assert view.bucket_map and view.hbm_slots == hbm_buckets * 128
+
+    def read_map():
+        from cuda.bindings import runtime as cudart
+        m = np.zeros(64, dtype=np.uint32)
+        (err,) = cudart.cudaMemcpy(m.ctypes.data, int(t.t.view().bucket_map), 64 * 4,
+                                   cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+        assert int(err) == 0
+        return m
+
+    np.testing.assert_array_equal(read_map(), np.arange(64, dtype=np.uint32))
+    assert t.t.promote_hot_buckets() == 0            # nothing looked up yet
+    # the hot set: all keys of eight host-resident buckets, asked for again and again
+    hot_buckets = np.array([20, 25, 31, 40, 47, 52, 60, 63])
+    hot = present[np.isin(bucket, hot_buckets)]
+    cold = present[~np.isin(bucket, hot_buckets)]
+    rng = np.random.default_rng(3)
+    q = np.concatenate([rng.choice(hot, size=6000), rng.choice(cold, size=64)])
+    for _ in range(3):
+        pv, pf, _ = t.find(q)                        # 6064 keys: the sorted hybrid path
+        ov, of, _ = o.find(q)
+        np.testing.assert_array_equal(pf, of)
+        np.testing.assert_array_equal(pv, ov)
+    moved = t.t.promote_hot_buckets()
+    assert moved == hot_buckets.size
+    m = read_map()
+    assert np.all(m[hot_buckets] < hbm_buckets)      # the hot buckets' rows are in HBM now
+    assert np.unique(m).size == 64                   # still a permutation
+    # every operation sees the same table as before
+    pv, pf, ps = t.find(keys)
+    ov, of, os_ = o.find(keys)
+    np.testing.assert_array_equal(pf, of)
+    np.testing.assert_array_equal(pv, ov)
+    np.testing.assert_array_equal(ps[pf], os_[of])
+    ptrs, f2, _ = t.find_ptr(hot[:64])
+    base, end = int(view.values_hbm), int(view.values_hbm) + hbm_buckets * 128 * dim * 4
+    assert np.all((ptrs >= base) & (ptrs < end))
+    np.testing.assert_array_equal(read_rows(ptrs, dim), values_for(hot[:64], dim))
+    for a, b in zip(sorted_by_key(*t.export_batch()), sorted_by_key(*o.export_batch())):
+        np.testing.assert_array_equal(a, b)
+    # updates and evictions after the move
+    more = unique_keys(9000, seed=22)[6000:]
+    s2 = np.arange(100001, 100001 + more.size, dtype=np.uint64)
+    for x in (t, o):
+        x.insert_or_assign(more, values_for(more, dim, seed=5), s2)
+        x.assign(hot[:500], values_for(hot[:500], dim, seed=6), np.arange(200001, 200501, dtype=np.uint64))
+    assert t.size() == o.size()
+    for a, b in zip(sorted_by_key(*t.export_batch()), sorted_by_key(*o.export_batch())):
+        np.testing.assert_array_equal(a, b)
+    assert t.t.promote_hot_buckets() == 0            # counters halved, nothing hotter outside
+    # a table without host rows has no map
+    plain = ProductTable(cap, dim, CUSTOMIZED)
+    assert not plain.t.view().bucket_map and plain.t.promote_hot_buckets() == 0
+    plain.close()
+    t.close()
+
+
 def test_lru_eviction_invariants_under_score_ties():
     """LRU at load factor 1.0: thousands of keys written by one kernel share a
     timer value, so the victim among equal minima is not unique.  Checked:
