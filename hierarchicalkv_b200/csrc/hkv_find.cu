@@ -125,11 +125,13 @@ __global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
     if (FORM == 1) ptrs[i] = found ? row_ptr(t, slot) : nullptr;
     if (FORM != 3 && scores != nullptr && found) scores[i] = t.scores[slot];
     if (FORM == 4) {
-      // where the row lives (kNoSlot sorts behind every real place); the
-      // bucket's hit counter feeds the promotion of hot buckets into HBM
+      // where the row lives (kNoSlot sorts behind every real place)
       slot_out[i] = found ? static_cast<uint32_t>(row_slot(t, slot)) : kNoSlot;
       index_out[i] = static_cast<uint32_t>(i);
-      if (found && t.bucket_heat != nullptr) atomicAdd(t.bucket_heat + (slot >> 7), 1u);
+    }
+    // hybrid tables (they never run the VEC != 0 instantiations): hits per bucket
+    if (VEC == 0 && FORM != 3 && found && t.bucket_heat != nullptr) {
+      atomicAdd(t.bucket_heat + (slot >> 7), 1u);
     }
   }
   if (FORM == 2) {
