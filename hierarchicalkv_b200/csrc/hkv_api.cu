@@ -296,6 +296,17 @@ class Scores {
   int exceptions_;
 };
 
+// Dual-bucket tables serve insert_or_assign and find and the whole-table scans;
+// everything else that addresses a bucket by key is refused, in the reference's
+// words where it has some (include/merlin_hashtable.cuh:1361, 1596, 1704, 2232, 2303, 2859,
+// 2905, 3504).
+void refuse_in_memory_mode(const hkv_table* t, const char* what) {
+  if (t->opt.table_mode == 1) {
+    throw HkvError{HKV_ERR_MERLIN, std::string("[MEMORY_MODE] ") + what +
+                                       "() is not supported in dual-bucket mode."};
+  }
+}
+
 // accum_or_assign adds elements of V (include/merlin/core_kernels/accum_or_assign.cuh:139-172):
 // the element type must be known and a row chunk must hold whole elements.
 void check_accum_type(const hkv_table* t, const void* batch) {
@@ -569,8 +580,21 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
       throw HkvError{HKV_ERR_INVALID_ARG, "options and out must not be null"};
     }
     const hkv_options& o = *options;
-    HKV_CHECK(o.table_mode == 0,
-              "[MEMORY_MODE] dual-bucket tables are not part of this library.");
+    HKV_CHECK(o.table_mode == 0 || o.table_mode == 1, "options.table_mode should be 0 or 1.");
+    if (o.table_mode == 1) {
+      // include/merlin_hashtable.cuh:991-1015
+      HKV_CHECK(o.init_capacity == o.max_capacity,
+                "[MEMORY_MODE] init_capacity must equal max_capacity. Auto-rehash is not "
+                "supported in dual-bucket mode.");
+      HKV_CHECK(o.max_hbm_for_vectors == 0,
+                "[MEMORY_MODE] Only pure HBM (fast mode) is supported. Set max_hbm_for_vectors = 0.");
+      HKV_CHECK(o.dim * uint64_t(o.value_size) <= 224 * sizeof(float),
+                "[MEMORY_MODE] dim * sizeof(V) must not exceed 896 bytes (i.e. dim <= 224 for "
+                "float).");
+      HKV_CHECK(o.max_bucket_size != 0 && o.init_capacity / o.max_bucket_size >= 2,
+                "[MEMORY_MODE] capacity must provide at least 2 buckets (capacity >= 2 * "
+                "max_bucket_size).");
+    }
     HKV_CHECK(o.reserved_key_start_bit >= 0 && o.reserved_key_start_bit <= 62,
               "options.reserved_key_start_bit should >= 0 and <= 62.");
     HKV_CHECK(o.max_bucket_size != 0 && (o.max_bucket_size & (o.max_bucket_size - 1)) == 0,
@@ -622,7 +646,7 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
       }
       const uint64_t row_bytes = o.dim * uint64_t(o.value_size);
       HKV_CHECK(row_bytes < (1ull << 24), "value rows above 16 MiB are not supported.");
-      t->reach_max_capacity.store(o.init_capacity * 2 > o.max_capacity);
+      t->reach_max_capacity.store(o.init_capacity * 2 > o.max_capacity || o.table_mode == 1);
 
       hkv::TableView& v = t->view;
       v.row_bytes = uint32_t(row_bytes);
@@ -654,9 +678,12 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
         v.reclaim_key = (~(1ull << bit)) & ~1ull;
         v.locked_key = v.empty_key & ~(2ull << bit);
       }
-      const uint32_t ed = uint32_t(hkv::fmix64(v.empty_key) >> 32) & 0xFFu;
+      // digest byte: bits 32-39 of the hash, bits 56-63 on a dual-bucket table
+      // (include/merlin/core_kernels/dual_bucket_utils.cuh:47-65)
+      const int digest_shift = o.table_mode == 1 ? 56 : 32;
+      const uint32_t ed = uint32_t(hkv::fmix64(v.empty_key) >> digest_shift) & 0xFFu;
       v.empty_digest4 = ed * 0x01010101u;
-      v.reclaim_digest = uint32_t(hkv::fmix64(v.reclaim_key) >> 32) & 0xFFu;
+      v.reclaim_digest = uint32_t(hkv::fmix64(v.reclaim_key) >> digest_shift) & 0xFFu;
 
       Planes planes;
       allocate_planes(t, buckets, v, planes, nullptr);
@@ -693,6 +720,18 @@ int hkv_insert_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const v
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
     hkv::MutateArgs a = base_args(t, n, keys, values, scores_w.get(), ignore_evict_strategy != 0);
     if (ignore_evict_strategy) a.epoch = hkv::kIgnoredEpoch;
+    if (t->opt.table_mode == 1) {
+      // include/merlin_hashtable.cuh:1165-1170
+      HKV_CHECK(unique_key != 0,
+                "[MEMORY_MODE] insert_or_assign requires unique_key=true in dual-bucket mode.");
+      DeviceGuard dg(t->device);
+      cudaStream_t s = static_cast<cudaStream_t>(stream);
+      LockScope ls(t, kInserter, s);
+      hkv::launch_dual_upsert(t->view, a, s);
+      ls.done();
+      check_launch();
+      return;
+    }
     mutate(t, hkv::kOpInsertOrAssign, a, values, nullptr, kInserter, unique_key != 0,
            static_cast<cudaStream_t>(stream));
   });
@@ -703,6 +742,7 @@ int hkv_insert_and_evict(hkv_table* t, uint64_t n, const uint64_t* keys, const v
                          uint64_t* evicted_scores, uint64_t* d_evicted_counter, hkv_stream stream,
                          int unique_key, int ignore_evict_strategy) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "insert_and_evict");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     Scores evicted_scores_w(t, evicted_scores, n, stream, true);
@@ -749,6 +789,7 @@ int hkv_accum_or_assign(hkv_table* t, uint64_t n, const uint64_t* keys,
                         const void* value_or_deltas, const bool* accum_or_assigns,
                         const uint64_t* scores, hkv_stream stream, int ignore_evict_strategy) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "accum_or_assign");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     check_accum_type(t, value_or_deltas);
@@ -768,6 +809,7 @@ int hkv_accum_or_assign_unique(hkv_table* t, uint64_t n, const uint64_t* keys,
                                const uint64_t* scores, hkv_stream stream,
                                int ignore_evict_strategy) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "accum_or_assign");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     check_accum_type(t, value_or_deltas);
@@ -784,6 +826,7 @@ int hkv_find_or_insert(hkv_table* t, uint64_t n, const uint64_t* keys, void* val
                        uint64_t* scores, hkv_stream stream, int unique_key,
                        int ignore_evict_strategy) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "find_or_insert");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
@@ -798,6 +841,7 @@ int hkv_find_or_insert_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void*
                            bool* founds, uint64_t* scores, hkv_stream stream, int unique_key,
                            int ignore_evict_strategy, uint64_t** locked_key_ptrs) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "find_or_insert");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     if (!ignore_evict_strategy) check_strategy(t, t->opt.evict_strategy, scores);
@@ -814,6 +858,7 @@ int hkv_find_or_insert_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void*
 int hkv_lock_keys(hkv_table* t, uint64_t n, const uint64_t* keys, uint64_t** locked_key_ptrs,
                   bool* success, hkv_stream stream, const uint64_t* scores) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "lock_keys");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     if (locked_key_ptrs == nullptr) {
@@ -843,6 +888,7 @@ int hkv_unlock_keys(hkv_table* t, uint64_t n, uint64_t** locked_key_ptrs, const 
 int hkv_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
                const uint64_t* scores, hkv_stream stream, int unique_key) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "assign");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     check_strategy(t, t->opt.evict_strategy, scores);
@@ -855,6 +901,7 @@ int hkv_assign(hkv_table* t, uint64_t n, const uint64_t* keys, const void* value
 int hkv_assign_scores(hkv_table* t, uint64_t n, const uint64_t* keys, const uint64_t* scores,
                       hkv_stream stream, int unique_key) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "assign_scores");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
     check_strategy(t, t->opt.evict_strategy, scores);
@@ -867,6 +914,7 @@ int hkv_assign_scores(hkv_table* t, uint64_t n, const uint64_t* keys, const uint
 int hkv_assign_values(hkv_table* t, uint64_t n, const uint64_t* keys, const void* values,
                       hkv_stream stream, int unique_key) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "assign_values");
     if (n == 0) return;
     hkv::MutateArgs a = base_args(t, n, keys, values, nullptr, false);
     mutate(t, hkv::kOpAssignValues, a, values, nullptr, kUpdater, unique_key != 0,
@@ -882,7 +930,11 @@ int hkv_find(hkv_table* t, uint64_t n, const uint64_t* keys, void* values, bool*
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     LockScope ls(t, kReader, s);
-    hkv::launch_find(view_for(t, values), n, keys, values, founds, scores_w.get(), s);
+    if (t->opt.table_mode == 1) {
+      hkv::launch_dual_find(view_for(t, values), n, keys, values, founds, scores_w.get(), s);
+    } else {
+      hkv::launch_find(view_for(t, values), n, keys, values, founds, scores_w.get(), s);
+    }
     ls.done();
     check_launch();
   });
@@ -892,6 +944,7 @@ int hkv_find_missed(hkv_table* t, uint64_t n, const uint64_t* keys, void* values
                     uint64_t* missed_keys, int* missed_indices, int* missed_size, uint64_t* scores,
                     hkv_stream stream) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "find");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
@@ -908,6 +961,7 @@ int hkv_find_missed(hkv_table* t, uint64_t n, const uint64_t* keys, void* values
 int hkv_find_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void** values, bool* founds,
                  uint64_t* scores, hkv_stream stream, int /*unique_key*/) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "find");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
@@ -922,6 +976,7 @@ int hkv_find_ptr(hkv_table* t, uint64_t n, const uint64_t* keys, void** values, 
 int hkv_find_and_update(hkv_table* t, uint64_t n, const uint64_t* keys, void** values,
                         bool* founds, uint64_t* scores, hkv_stream stream, int unique_key) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "find_and_update");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, true);
     // scores are an input here for the strategies that take them and are
@@ -940,6 +995,7 @@ int hkv_find_routed(hkv_table* t, uint32_t world, uint32_t my_rank, uint64_t seg
                     const uint64_t* inbox_counts, const hkv_peer_ptrs* out_values,
                     const hkv_peer_ptrs* out_founds, hkv_stream stream) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "find");
     if (world == 0 || world > hkv::kMaxPeers || my_rank >= world) {
       throw HkvError{HKV_ERR_INVALID_ARG, "world size must be between 1 and 16"};
     }
@@ -964,6 +1020,7 @@ int hkv_upsert_routed(hkv_table* t, int op, uint32_t world, uint32_t my_rank,
                       const hkv_peer_ptrs* values, const hkv_peer_ptrs* accum_flags,
                       hkv_stream stream) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "insert_or_assign");
     if (world == 0 || world > hkv::kMaxPeers || my_rank >= world) {
       throw HkvError{HKV_ERR_INVALID_ARG, "world size must be between 1 and 16"};
     }
@@ -1005,6 +1062,7 @@ int hkv_upsert_routed(hkv_table* t, int op, uint32_t world, uint32_t my_rank,
 
 int hkv_contains(hkv_table* t, uint64_t n, const uint64_t* keys, bool* founds, hkv_stream stream) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "contains");
     if (n == 0) return;
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1017,6 +1075,7 @@ int hkv_contains(hkv_table* t, uint64_t n, const uint64_t* keys, bool* founds, h
 
 int hkv_erase(hkv_table* t, uint64_t n, const uint64_t* keys, hkv_stream stream) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "erase");
     if (n == 0) return;
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1163,6 +1222,7 @@ int hkv_set_global_epoch(hkv_table* t, uint64_t epoch) {
 
 int hkv_reserve(hkv_table* t, uint64_t new_capacity, hkv_stream stream) {
   return guarded([&] {
+    refuse_in_memory_mode(t, "reserve");
     DeviceGuard dg(t->device);
     reserve(t, new_capacity, static_cast<cudaStream_t>(stream));
   });

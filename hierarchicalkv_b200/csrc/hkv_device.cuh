@@ -127,6 +127,33 @@ __device__ __forceinline__ Address locate(const TableView& t, uint64_t key) {
   return a;
 }
 
+// Dual-bucket addressing (TableMode::kMemory of the reference,
+// include/merlin/core_kernels/dual_bucket_utils.cuh:31-65): a key may live in
+// one of two buckets, chosen from the low and the high half of its hash; the
+// digest is the top byte of the hash.
+struct DualAddress {
+  Address first;   // bucket from the low 32 bits
+  Address second;  // bucket from the high 32 bits, never the same bucket
+};
+
+__host__ __device__ __forceinline__ uint32_t dual_digest(uint64_t hashed) {
+  return static_cast<uint32_t>(hashed >> 56);
+}
+
+__device__ __forceinline__ DualAddress locate_dual(const TableView& t, uint64_t key) {
+  const uint64_t h = fmix64(key);
+  const uint32_t lo = static_cast<uint32_t>(h);
+  const uint32_t hi = static_cast<uint32_t>(h >> 32);
+  DualAddress d;
+  d.first.bucket = lo % t.buckets;
+  d.second.bucket = hi % t.buckets;
+  if (d.second.bucket == d.first.bucket) d.second.bucket = (d.second.bucket + 1) % t.buckets;
+  d.first.start = static_cast<uint32_t>(lo % t.capacity) & (kBucketSlots - 1);
+  d.second.start = static_cast<uint32_t>(hi % t.capacity) & (kBucketSlots - 1);
+  d.first.digest = d.second.digest = dual_digest(h);
+  return d;
+}
+
 // Host side: may the kernels specialised for 16-byte chunks of pure-HBM rows run?
 inline bool fast_rows(const TableView& t) {
   return t.vec_bytes == 16 && t.hbm_slots == t.capacity && t.bucket_map == nullptr;

@@ -205,6 +205,40 @@ __global__ void __launch_bounds__(kFindBlock)
   warp_gather_rows_to<VEC>(t, values_of, origin, slot, pl.lane);
 }
 
+// find on a dual-bucket table (include/merlin/core_kernels/dual_bucket_lookup.cuh):
+// the first bucket of every key is probed, then the second bucket of the keys
+// that were not there.
+__global__ void __launch_bounds__(kFindBlock)
+    dual_find_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
+                     uint8_t* __restrict__ values, bool* __restrict__ founds,
+                     uint64_t* __restrict__ scores) {
+  const ProbeLane pl = probe_lane();
+  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t base = warp * 32u;
+  if (base >= n) return;
+  const uint64_t i = base + pl.lane;
+  uint64_t key = 0;
+  bool valid = false;
+  if (i < n) {
+    key = keys[i];
+    valid = !is_reserved(t, key);
+  }
+  DualAddress a{};
+  if (valid) a = locate_dual(t, key);
+  uint32_t slot = warp_probe_readonly(t, pl, key, valid, a.first);
+  const bool again = valid && slot == kNoSlot;
+  if (__ballot_sync(0xFFFFFFFFu, again)) {
+    const uint32_t second = warp_probe_readonly(t, pl, key, again, a.second);
+    if (again) slot = second;
+  }
+  const bool found = slot != kNoSlot;
+  if (i < n) {
+    founds[i] = found;
+    if (scores != nullptr && found) scores[i] = t.scores[slot];
+  }
+  if (values != nullptr) warp_move_rows<0>(t, values + base * t.row_bytes, slot, pl.lane);
+}
+
 template <int FORM>
 void launch_form(const TableView& t, uint64_t n, const uint64_t* keys, void* values, void** ptrs,
                  bool* founds, uint64_t* scores, uint64_t* missed_keys, int* missed_indices,
@@ -282,6 +316,14 @@ void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* val
     return;
   }
   launch_form<0>(t, n, keys, values, nullptr, founds, scores, nullptr, nullptr, nullptr, stream);
+}
+
+void launch_dual_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
+                      bool* founds, uint64_t* scores, cudaStream_t stream) {
+  if (n == 0) return;
+  const uint64_t blocks = (((n + 31) / 32) * 32 + kFindBlock - 1) / kFindBlock;
+  dual_find_kernel<<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
+      t, keys, n, static_cast<uint8_t*>(values), founds, scores);
 }
 
 void launch_find_ptr(const TableView& t, uint64_t n, const uint64_t* keys, void** ptrs,

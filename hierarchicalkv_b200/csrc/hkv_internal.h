@@ -56,6 +56,11 @@ void launch_find_missed(const TableView& t, uint64_t n, const uint64_t* keys, vo
 void launch_contains(const TableView& t, uint64_t n, const uint64_t* keys, bool* founds,
                      cudaStream_t stream);
 
+// Dual-bucket tables (TableMode::kMemory): find and insert_or_assign of unique keys.
+void launch_dual_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
+                      bool* founds, uint64_t* scores, cudaStream_t stream);
+void launch_dual_upsert(const TableView& t, const MutateArgs& args, cudaStream_t stream);
+
 // Peer buffers of the sharded table, one pointer per rank (world <= kMaxPeers).
 constexpr int kMaxPeers = 16;
 struct PeerPtrs {

@@ -939,6 +939,209 @@ __global__ void __launch_bounds__(kMutateBlock)
   }
 }
 
+// ---- dual-bucket tables (TableMode::kMemory) ----------------------------------------
+//
+// insert_or_assign of unique keys on a table where a key may live in one of
+// two buckets (include/merlin/core_kernels/dual_bucket_upsert.cuh:27-48):
+//   0  the key is looked for in BOTH buckets before anything is claimed;
+//   1  a new key goes to the emptier bucket (the first one on a tie), into the
+//      first EMPTY slot from its start position there, else into the other;
+//   2  with both buckets full the entry with the smallest score of the two
+//      buckets (the first bucket on a tie) is evicted, unless the new score is
+//      below it.
+// One warp walks its 32 keys one after the other, reading both buckets' 128
+// keys directly (4 per lane and bucket).
+struct BucketScan {
+  uint32_t eq;      // bit c: slot c * 32 + lane holds the key
+  uint32_t locked;  // bit c: that slot is LOCKED
+  uint32_t empty;   // bit c: that slot is EMPTY
+};
+
+__device__ __forceinline__ BucketScan scan_bucket_keys(const TableView& t, uint64_t slot0,
+                                                       uint64_t key, uint32_t lane) {
+  BucketScan r{0, 0, 0};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint64_t k = ld_acquire(t.keys + slot0 + c * 32 + lane);
+    r.eq |= (k == key) ? (1u << c) : 0u;
+    r.locked |= (k == t.locked_key) ? (1u << c) : 0u;
+    r.empty |= (k == t.empty_key) ? (1u << c) : 0u;
+  }
+  return r;
+}
+
+// Distance from `start` to the first EMPTY slot of the scan (255: none).
+__device__ __forceinline__ uint32_t first_empty_distance(const BucketScan& s, uint32_t start,
+                                                         uint32_t lane) {
+  uint32_t best = 255u;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    if ((s.empty >> c) & 1u) {
+      best = min(best, (uint32_t(c) * 32u + lane - start) & (kBucketSlots - 1));
+    }
+  }
+  return __reduce_min_sync(0xFFFFFFFFu, best);
+}
+
+// Minimum score of a bucket and its first position.
+__device__ __forceinline__ void bucket_min_score(const TableView& t, uint64_t slot0, uint32_t lane,
+                                                 uint64_t* gmin, uint32_t* gpos) {
+  uint64_t ms = kMaxScore;
+  uint32_t mp = 255u;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint64_t s = ld_relaxed(t.scores + slot0 + c * 32 + lane);
+    if (mp == 255u || s < ms) {
+      ms = s;
+      mp = c * 32 + lane;
+    }
+  }
+  const uint32_t hi = uint32_t(ms >> 32);
+  const uint32_t ghi = __reduce_min_sync(0xFFFFFFFFu, hi);
+  const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
+  const uint32_t glo = __reduce_min_sync(0xFFFFFFFFu, lo);
+  const uint32_t cp = (hi == ghi && lo == glo) ? mp : 255u;
+  *gpos = __reduce_min_sync(0xFFFFFFFFu, cp);
+  *gmin = (uint64_t(ghi) << 32) | glo;
+}
+
+__global__ void __launch_bounds__(kMutateBlock)
+    dual_upsert_kernel(const TableView t, const MutateArgs args) {
+  const uint32_t full = 0xFFFFFFFFu;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const uint64_t base = warp * 32u;
+  const uint64_t n = args.n;
+  if (base >= n) return;
+  const int strategy = args.strategy;
+  const uint32_t count = uint32_t(min(uint64_t(32), n - base));
+
+  for (uint32_t q = 0; q < count; ++q) {
+    const uint64_t i = base + q;
+    const uint64_t key = args.keys[i];
+    if (is_reserved(t, key)) continue;
+    const DualAddress a = locate_dual(t, key);
+    const uint64_t in_score = args.scores != nullptr ? args.scores[i] : 0;
+    const uint64_t desired = desired_score(strategy, args.scores, in_score, args.epoch);
+    const uint64_t slot0[2] = {a.first.bucket << 7, a.second.bucket << 7};
+    const uint32_t start[2] = {a.first.start, a.second.start};
+    const uint64_t bucket[2] = {a.first.bucket, a.second.bucket};
+
+    uint32_t result = kInitial;
+    uint32_t which = 0, pos = 0;
+    uint64_t victim = 0;
+    uint32_t attempts = 0;
+    while (result == kInitial) {
+      if (++attempts > kSpinLimit) {
+        if (lane == 0) atomicOr(t.status, kStatusLockTimeout);
+        result = kRefused;
+        break;
+      }
+      const BucketScan s0 = scan_bucket_keys(t, slot0[0], key, lane);
+      const BucketScan s1 = scan_bucket_keys(t, slot0[1], key, lane);
+      // phase 0: the key itself, in either bucket
+      const uint32_t eq0 = __ballot_sync(full, s0.eq != 0);
+      const uint32_t eq1 = __ballot_sync(full, s1.eq != 0);
+      if (eq0 | eq1) {
+        const uint32_t w = eq0 ? 0u : 1u;
+        const uint32_t src = __ffs(eq0 ? eq0 : eq1) - 1;
+        const uint32_t mine = (__ffs(w == 0 ? s0.eq : s1.eq) - 1) * 32 + lane;
+        const uint32_t p = __shfl_sync(full, mine, src);
+        uint32_t ok = 0;
+        if (lane == src) ok = cas_acquire(t.keys + slot0[w] + p, key, t.locked_key) == key;
+        if (__shfl_sync(full, ok, src)) {
+          result = kDuplicate;
+          which = w;
+          pos = p;
+        }
+        continue;
+      }
+      if (__ballot_sync(full, (s0.locked | s1.locked) != 0)) {
+        __nanosleep(128);  // somebody is writing one of these buckets
+        continue;
+      }
+      // phase 1: the emptier bucket first
+      const int size0 = *reinterpret_cast<volatile int32_t*>(t.bucket_sizes + bucket[0]);
+      const int size1 = *reinterpret_cast<volatile int32_t*>(t.bucket_sizes + bucket[1]);
+      const uint32_t prefer = size0 <= size1 ? 0u : 1u;
+      bool retry = false;
+      for (uint32_t turn = 0; turn < 2 && result == kInitial && !retry; ++turn) {
+        const uint32_t w = turn == 0 ? prefer : 1u - prefer;
+        if ((w == 0 ? size0 : size1) >= kBucketSlots) continue;
+        const uint32_t d = first_empty_distance(w == 0 ? s0 : s1, start[w], lane);
+        if (d == 255u) continue;
+        const uint32_t p = (start[w] + d) & (kBucketSlots - 1);
+        uint32_t ok = 0;
+        if (lane == 0) {
+          ok = cas_acquire(t.keys + slot0[w] + p, t.empty_key, t.locked_key) == t.empty_key;
+        }
+        if (__shfl_sync(full, ok, 0)) {
+          result = kOccupiedEmpty;
+          which = w;
+          pos = p;
+        } else {
+          retry = true;  // lost the slot to another warp: look again
+        }
+      }
+      if (result != kInitial || retry) continue;
+      // phase 2: the smallest score of both buckets
+      uint64_t min0, min1;
+      uint32_t pos0, pos1;
+      bucket_min_score(t, slot0[0], lane, &min0, &pos0);
+      bucket_min_score(t, slot0[1], lane, &min1, &pos1);
+      const uint32_t w = min0 <= min1 ? 0u : 1u;
+      const uint64_t gmin = w == 0 ? min0 : min1;
+      const uint32_t gpos = w == 0 ? pos0 : pos1;
+      if (desired < gmin) {
+        result = kRefused;
+        break;
+      }
+      uint32_t code = 0;
+      if (lane == 0) {
+        uint64_t* kp = t.keys + slot0[w] + gpos;
+        const uint64_t v = ld_relaxed(kp);
+        if (v != t.locked_key && cas_acquire(kp, v, t.locked_key) == v) {
+          if (ld_relaxed(t.scores + slot0[w] + gpos) > gmin) {
+            st_release(kp, v);  // refreshed in between: scan again
+          } else {
+            victim = v;
+            code = (v == t.empty_key || v == t.reclaim_key) ? 2 : 1;
+          }
+        }
+      }
+      code = __shfl_sync(full, code, 0);
+      if (code) {
+        result = code == 2 ? kOccupiedReclaimed : kEvict;
+        which = w;
+        pos = gpos;
+      }
+    }
+    if (result == kRefused || result == kInitial) continue;
+
+    const uint32_t slot = uint32_t(slot0[which]) + pos;
+    if (lane == 0) {
+      if (result == kDuplicate) {
+        const uint64_t old_score = ld_relaxed(t.scores + slot);
+        uint64_t ns = 0;
+        if (hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns)) {
+          st_relaxed(t.scores + slot, ns);
+        }
+      } else {
+        st_u8_cg(t.digests + slot, a.first.digest);
+        st_relaxed(t.scores + slot, inserted_score(strategy, in_score, desired));
+        if (result != kEvict) atomicAdd(t.bucket_sizes + bucket[which], 1);
+      }
+    }
+    warp_copy_one_row<0>(t, row_ptr(t, slot), args.values + i * t.row_bytes, lane);
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence();
+      st_release(t.keys + slot, key);
+    }
+    __syncwarp();
+  }
+}
+
 template <int OP>
 void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cudaStream_t stream) {
   const uint64_t warps = (args.n + 31) / 32;
@@ -1011,6 +1214,12 @@ void launch_mutate_routed(int op, const TableView& t, const MutateArgs& args, ui
       break;
     default: break;
   }
+}
+
+void launch_dual_upsert(const TableView& t, const MutateArgs& args, cudaStream_t stream) {
+  if (args.n == 0) return;
+  const uint64_t blocks = (((args.n + 31) / 32) * 32 + kMutateBlock - 1) / kMutateBlock;
+  dual_upsert_kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
 }
 
 void launch_unlock_keys(const TableView& t, uint64_t n, uint64_t** locked_key_ptrs,

@@ -153,6 +153,29 @@ REF_API int ref_create_growable(uint64_t init_capacity, uint64_t max_capacity,
   });
 }
 
+// TableMode::kMemory: dual-bucket table (insert_or_assign of unique keys and find).
+REF_API int ref_create_memory_mode(uint64_t capacity, uint64_t dim, void** out) {
+  return guarded([&] {
+    nv::merlin::HashTableOptions o;
+    o.init_capacity = capacity;
+    o.max_capacity = capacity;
+    o.max_hbm_for_vectors = 0;
+    o.dim = dim;
+    o.table_mode = nv::merlin::TableMode::kMemory;
+    size_t buckets = 1;
+    while (buckets * 2 * o.max_bucket_size <= capacity) buckets *= 2;
+    o.num_of_buckets_per_alloc = buckets;
+    auto* t = new Table();
+    try {
+      t->init(o);
+    } catch (...) {
+      delete t;
+      throw;
+    }
+    *out = t;
+  });
+}
+
 REF_API int ref_reserve(void* t, uint64_t new_capacity, cudaStream_t stream) {
   return guarded([&] { static_cast<Table*>(t)->reserve(new_capacity, stream); });
 }

@@ -84,6 +84,7 @@ _ORACLE_SIGS = {
     "orc_set_max_capacity": ([_P, _U64], _INT),
     "orc_set_max_load_factor": ([_P, ctypes.c_float], None),
     "orc_set_value_kind": ([_P, _INT], None),
+    "orc_set_dual_bucket": ([_P], None),
     "orc_capacity": ([_P], _U64),
     "orc_bucket_count": ([_P], _U64),
     "orc_set_global_epoch": ([_P, _U64], None),
@@ -141,7 +142,7 @@ class OracleTable:
 
     def __init__(self, capacity: int, dim: int, strategy: int = 0, reserved_key_start_bit: int = 0,
                  max_capacity: Optional[int] = None, value_size: int = 4,
-                 max_load_factor: Optional[float] = None):
+                 max_load_factor: Optional[float] = None, memory_mode: bool = False):
         self.lib = load_oracle()
         self.dim = dim
         self.strategy = strategy
@@ -149,6 +150,8 @@ class OracleTable:
                                      reserved_key_start_bit)
         if max_load_factor is not None:
             self.lib.orc_set_max_load_factor(self.h, max_load_factor)
+        if memory_mode:
+            self.lib.orc_set_dual_bucket(self.h)
 
     def reserve(self, new_capacity):
         self.lib.orc_reserve(self.h, new_capacity)
@@ -280,7 +283,8 @@ class ProductTable:
     the parity tests (every call goes through the C ABI)."""
 
     def __init__(self, capacity, dim, strategy=0, reserved_key_start_bit=0, max_capacity=None,
-                 max_hbm_for_vectors=None, api_lock=True, max_load_factor=None):
+                 max_hbm_for_vectors=None, api_lock=True, max_load_factor=None,
+                 memory_mode=False):
         import torch
         import hierarchicalkv_b200 as hkv
 
@@ -289,6 +293,9 @@ class ProductTable:
         self.t = hkv.HashTable(hkv.EvictStrategy(strategy))
         hbm = (16 << 30) if max_hbm_for_vectors is None else max_hbm_for_vectors
         extra = {} if max_load_factor is None else {"max_load_factor": max_load_factor}
+        if memory_mode:          # the reference's dual-bucket tables want max_hbm_for_vectors == 0
+            extra["table_mode"] = 1
+            hbm = 0
         self.t.init(hkv.HashTableOptions(
             init_capacity=capacity, max_capacity=max_capacity or capacity,
             max_hbm_for_vectors=hbm, dim=dim, reserved_key_start_bit=reserved_key_start_bit,
@@ -484,6 +491,7 @@ def load_ref(strategy: int, private: bool = False) -> ctypes.CDLL:
         "ref_create_growable": [_U64, _U64, _U64, _U64, ctypes.c_float, ctypes.POINTER(_P)],
         "ref_reserve": [_P, _U64, _P],
         "ref_set_max_capacity": [_P, _U64],
+        "ref_create_memory_mode": [_U64, _U64, ctypes.POINTER(_P)],
         "ref_set_global_epoch": [_P, _U64],
         "ref_insert_or_assign": [_P, _U64, _P, _P, _P, _P, _INT],
         "ref_insert_and_evict": [_P, _U64, _P, _P, _P, _P, _P, _P, _P, _P, _INT],
@@ -523,7 +531,8 @@ class RefTable:
     _PRED = {1: 0, 2: 1, 3: 2}
 
     def __init__(self, capacity, dim, strategy=0, reserved_key_start_bit=0, max_capacity=None,
-                 max_hbm_for_vectors=None, api_lock=True, max_load_factor=None):
+                 max_hbm_for_vectors=None, api_lock=True, max_load_factor=None,
+                 memory_mode=False):
         import torch
 
         self.torch = torch
@@ -531,7 +540,10 @@ class RefTable:
         self.lib = load_ref(strategy, private=reserved_key_start_bit != 0)
         self.h = _P()
         hbm = (16 << 30) if max_hbm_for_vectors is None else max_hbm_for_vectors
-        if max_load_factor is not None:
+        if memory_mode:
+            assert reserved_key_start_bit == 0 and api_lock and max_capacity in (None, capacity)
+            self._chk(self.lib.ref_create_memory_mode(capacity, dim, ctypes.byref(self.h)))
+        elif max_load_factor is not None:
             assert reserved_key_start_bit == 0 and api_lock
             self._chk(self.lib.ref_create_growable(capacity, max_capacity or capacity, hbm, dim,
                                                    max_load_factor, ctypes.byref(self.h)))

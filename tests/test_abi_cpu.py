@@ -59,7 +59,12 @@ def test_each_declaration_cites_the_reference():
     (dict(init_capacity=128, max_capacity=128, num_of_buckets_per_alloc=2), hkv.MerlinException,
      "num_of_buckets_per_alloc"),
     (dict(io_by_cpu=True, max_hbm_for_vectors=1 << 20), hkv.MerlinException, "io_by_cpu"),
-    (dict(table_mode=1), hkv.MerlinException, "MEMORY_MODE"),
+    # dual-bucket tables: include/merlin_hashtable.cuh:991-1015 of the reference
+    (dict(table_mode=1, max_capacity=2048), hkv.MerlinException, "init_capacity must equal"),
+    (dict(table_mode=1, max_hbm_for_vectors=1 << 20), hkv.MerlinException, "max_hbm_for_vectors = 0"),
+    (dict(table_mode=1, init_capacity=128, max_capacity=128), hkv.MerlinException, "at least 2 buckets"),
+    (dict(table_mode=1, dim=225), hkv.MerlinException, "896 bytes"),
+    (dict(table_mode=2), hkv.MerlinException, "table_mode"),
 ])
 def test_option_checks_raise_like_the_reference(product_lib, kwargs, exc, fragment):
     opts = dict(init_capacity=1024, max_capacity=1024, dim=4)

@@ -421,6 +421,83 @@ def test_hybrid_hbm_and_pinned_host_values(hbm_fraction):
     t.close()
 
 
+def test_memory_mode_dual_bucket_tables():
+    """TableMode::kMemory (tests/dual_bucket_test.cc.cu of the reference): a key
+    lives in one of two buckets, new keys go to the emptier one, and the table
+    fills far beyond what single-bucket addressing reaches before it evicts.
+    Product, CPU oracle and (when built) the reference's kernels."""
+    import hierarchicalkv_b200 as hkv
+
+    cap, dim = 128 * 64, 8
+    kw = dict(memory_mode=True)
+    p = ProductTable(cap, dim, CUSTOMIZED, **kw)
+    o = OracleTable(cap, dim, CUSTOMIZED, **kw)
+    r = RefTable(cap, dim, CUSTOMIZED, **kw) if ref_available(CUSTOMIZED) else None
+    tables = [x for x in (p, o, r) if x is not None]
+    keys = unique_keys(cap + 2000, seed=41)
+    # below the point where both buckets of a key fill up, the outcome does not
+    # depend on the order inside a batch: everything is kept
+    at = 0
+    for n in (3000, 2500, 1500):                       # to load factor 0.85
+        k = keys[at:at + n]
+        sc = np.arange(at + 1, at + n + 1, dtype=np.uint64)
+        for x in tables:
+            x.insert_or_assign(k, values_for(k, dim, seed=at), sc)
+        at += n
+        assert [x.size() for x in tables] == [at] * len(tables)
+    q = keys[:at + 500]
+    want = o.find(q)
+    assert want[1][:at].all() and not want[1][at:].any()
+    for x in tables:
+        got = x.find(q)
+        np.testing.assert_array_equal(got[1], want[1])
+        np.testing.assert_array_equal(got[0][want[1]], want[0][want[1]])
+        np.testing.assert_array_equal(got[2][want[1]], want[2][want[1]])
+    # assignment of resident keys: new rows and scores, same size
+    k = keys[1000:2000]
+    sc = np.arange(50001, 51001, dtype=np.uint64)
+    for x in tables:
+        x.insert_or_assign(k, values_for(k, dim, seed=99), sc)
+    for x in tables:
+        v, f, s = x.find(k)
+        assert f.all()
+        np.testing.assert_array_equal(v, values_for(k, dim, seed=99))
+        np.testing.assert_array_equal(s, sc)
+        assert x.size() == at
+    exp = sorted_by_key(*o.export_batch())
+    for a, b in zip(sorted_by_key(*p.export_batch()), exp):
+        np.testing.assert_array_equal(a, b)
+    # overfill with ever higher scores: the table ends full or nearly so, keeps
+    # only keys it was given, and what it keeps carries its own row and score
+    rest = keys[at:]
+    sc = np.arange(100001, 100001 + rest.size, dtype=np.uint64)
+    p.insert_or_assign(rest, values_for(rest, dim, seed=7), sc)
+    o.insert_or_assign(rest, values_for(rest, dim, seed=7), sc)
+    assert p.size() >= int(0.97 * cap) and abs(p.size() - o.size()) <= cap // 100
+    v, f, s = p.find(rest)
+    assert f.mean() > 0.9                                # high scores get in
+    np.testing.assert_array_equal(v[f], values_for(rest, dim, seed=7)[f])
+    np.testing.assert_array_equal(s[f], sc[f])
+    ek, ev, es = p.export_batch()
+    assert np.unique(ek).size == ek.size == p.size()
+    # what the mode does not offer is refused, in the reference's words
+    for call in (lambda: p.t.contains(1, to_dev(keys[:1]), to_dev(np.zeros(1, dtype=np.bool_))),
+                 lambda: p.t.erase(1, to_dev(keys[:1])),
+                 lambda: p.t.reserve(cap * 2),
+                 lambda: p.assign_values(keys[:4], values_for(keys[:4], dim))):
+        with pytest.raises(hkv.MerlinException, match="MEMORY_MODE"):
+            call()
+    with pytest.raises(hkv.MerlinException, match="unique_key"):
+        p.insert_or_assign(keys[:4], values_for(keys[:4], dim), sc[:4], unique_key=False)
+    bad = hkv.HashTable(hkv.EvictStrategy.kCustomized)
+    with pytest.raises(hkv.MerlinException, match="init_capacity must equal max_capacity"):
+        bad.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=2 * cap, dim=dim,
+                                      max_hbm_for_vectors=0, table_mode=1))
+    p.close()
+    if r is not None:
+        r.close()
+
+
 def test_promotion_moves_hot_buckets_into_hbm():
     """A hybrid table counts lookup hits per bucket; promote_hot_buckets trades
     the row blocks of the hottest host-resident buckets against the coldest
