@@ -353,55 +353,39 @@ __device__ __forceinline__ uint32_t row_of_chunk(const TableView& t, uint32_t c)
   return r;
 }
 
-// cur += add, element by element, for a chunk of VEC bytes.  A chunk never
-// splits an element: the access width is at least the element size.
-template <int VEC, class T>
-__device__ __forceinline__ void accumulate_chunk(T& cur, const T& add, uint32_t kind) {
-  if constexpr (VEC >= 2) {
-    if (kind == kValueF16) {
-      __half* a = reinterpret_cast<__half*>(&cur);
-      const __half* b = reinterpret_cast<const __half*>(&add);
-#pragma unroll
-      for (int e = 0; e < VEC / 2; ++e) a[e] = __hadd(a[e], b[e]);
-      return;
-    }
-    if (kind == kValueBF16) {
-      __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&cur);
-      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&add);
-#pragma unroll
-      for (int e = 0; e < VEC / 2; ++e) a[e] = __hadd(a[e], b[e]);
-      return;
-    }
-  }
-  if constexpr (VEC >= 8) {
-    if (kind == kValueF64) {
-      double* a = reinterpret_cast<double*>(&cur);
-      const double* b = reinterpret_cast<const double*>(&add);
-#pragma unroll
-      for (int e = 0; e < VEC / 8; ++e) a[e] += b[e];
-      return;
-    }
-    if (kind == kValueI64) {
-      uint64_t* a = reinterpret_cast<uint64_t*>(&cur);
-      const uint64_t* b = reinterpret_cast<const uint64_t*>(&add);
-#pragma unroll
-      for (int e = 0; e < VEC / 8; ++e) a[e] += b[e];
-      return;
-    }
-  }
-  if constexpr (VEC >= 4) {
-    if (kind == kValueI32) {
-      uint32_t* a = reinterpret_cast<uint32_t*>(&cur);
-      const uint32_t* b = reinterpret_cast<const uint32_t*>(&add);
-#pragma unroll
-      for (int e = 0; e < VEC / 4; ++e) a[e] += b[e];
-      return;
-    }
-    // kValueF32, and kValueOpaque with 4-byte elements
-    float* a = reinterpret_cast<float*>(&cur);
-    const float* b = reinterpret_cast<const float*>(&add);
-#pragma unroll
-    for (int e = 0; e < VEC / 4; ++e) a[e] += b[e];
+// row += delta for one row, all 32 lanes, in the row's own element type.  The
+// float32 case does not come here: it is folded into the chunked row mover.
+__device__ __forceinline__ void warp_accumulate_row(uint8_t* row, const uint8_t* delta,
+                                                    uint32_t row_bytes, uint32_t kind,
+                                                    uint32_t lane) {
+  switch (kind) {
+    case kValueF64:
+      for (uint32_t e = lane; e < row_bytes / 8; e += 32)
+        reinterpret_cast<double*>(row)[e] += reinterpret_cast<const double*>(delta)[e];
+      break;
+    case kValueI64:
+      for (uint32_t e = lane; e < row_bytes / 8; e += 32)
+        reinterpret_cast<uint64_t*>(row)[e] += reinterpret_cast<const uint64_t*>(delta)[e];
+      break;
+    case kValueI32:
+      for (uint32_t e = lane; e < row_bytes / 4; e += 32)
+        reinterpret_cast<uint32_t*>(row)[e] += reinterpret_cast<const uint32_t*>(delta)[e];
+      break;
+    case kValueF16:
+      for (uint32_t e = lane; e < row_bytes / 2; e += 32)
+        reinterpret_cast<__half*>(row)[e] =
+            __hadd(reinterpret_cast<__half*>(row)[e], reinterpret_cast<const __half*>(delta)[e]);
+      break;
+    case kValueBF16:
+      for (uint32_t e = lane; e < row_bytes / 2; e += 32)
+        reinterpret_cast<__nv_bfloat16*>(row)[e] =
+            __hadd(reinterpret_cast<__nv_bfloat16*>(row)[e],
+                   reinterpret_cast<const __nv_bfloat16*>(delta)[e]);
+      break;
+    default:
+      for (uint32_t e = lane; e < row_bytes / 4; e += 32)
+        reinterpret_cast<float*>(row)[e] += reinterpret_cast<const float*>(delta)[e];
+      break;
   }
 }
 
@@ -415,7 +399,8 @@ __device__ __forceinline__ void accumulate_chunk(T& cur, const T& add, uint32_t 
 // contiguous segment per row.
 //
 // MODE 0: table -> batch (gather)   MODE 1: batch -> table (scatter)
-// MODE 2: table += batch (element type t.value_kind; VEC >= element size)
+// MODE 2: table += batch, float32 elements (needs VEC % 4 == 0); the other
+//         element types go through warp_accumulate_rows
 //
 // INDEXED: the batch rows are not the warp's 32 consecutive rows; lane r holds
 // in `row_index` which row of `batch_rows` belongs to it.  `batch_rows` may
@@ -474,9 +459,14 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
         } else if (MODE == 1) {
           st_stream(reinterpret_cast<T*>(tab[u]), regs[u]);
         } else {
-          T cur = *reinterpret_cast<const T*>(tab[u]);
-          accumulate_chunk<VEC>(cur, regs[u], t.value_kind);
-          *reinterpret_cast<T*>(tab[u]) = cur;
+          if constexpr (VEC % 4 == 0) {
+            T cur = *reinterpret_cast<const T*>(tab[u]);
+            float* a = reinterpret_cast<float*>(&cur);
+            const float* b = reinterpret_cast<const float*>(&regs[u]);
+#pragma unroll
+            for (int e = 0; e < VEC / 4; ++e) a[e] += b[e];
+            *reinterpret_cast<T*>(tab[u]) = cur;
+          }
         }
       }
     }
@@ -550,6 +540,21 @@ template <int MODE, int VEC = 0, bool INDEXED = false>
 __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
                                                uint32_t slot, uint32_t lane,
                                                uint32_t row_index = 0) {
+  if constexpr (MODE == 2) {
+    if (t.value_kind > kValueF32) {
+      // the rarer element types: one row after the other, all lanes on one row
+      uint32_t todo = __ballot_sync(0xFFFFFFFFu, slot != kNoSlot);
+      while (todo) {
+        const uint32_t r = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r);
+        const uint32_t at = INDEXED ? __shfl_sync(0xFFFFFFFFu, row_index, r) : r;
+        warp_accumulate_row(row_ptr(t, s), batch_rows + uint64_t(at) * t.row_bytes, t.row_bytes,
+                            t.value_kind, lane);
+      }
+      return;
+    }
+  }
   if constexpr (VEC != 0) {
     // the fixed-width instantiations serve pure-HBM tables only
     warp_move_rows_vec<VEC, MODE, INDEXED, true>(t, batch_rows, slot, lane, row_index);

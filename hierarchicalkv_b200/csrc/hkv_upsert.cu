@@ -848,36 +848,7 @@ __global__ void __launch_bounds__(kMutateBlock)
           for (uint32_t c = lane; c < t.row_bytes; c += 32) dst[c] = src[c];
         }
       } else if (accumulate) {
-        // one element per lane and step, in the row's own element type
-        switch (t.value_kind) {
-          case kValueF64:
-            for (uint32_t c = lane; c < t.row_bytes / 8; c += 32)
-              reinterpret_cast<double*>(row)[c] += reinterpret_cast<const double*>(batch_row)[c];
-            break;
-          case kValueI64:
-            for (uint32_t c = lane; c < t.row_bytes / 8; c += 32)
-              reinterpret_cast<uint64_t*>(row)[c] += reinterpret_cast<const uint64_t*>(batch_row)[c];
-            break;
-          case kValueI32:
-            for (uint32_t c = lane; c < t.row_bytes / 4; c += 32)
-              reinterpret_cast<uint32_t*>(row)[c] += reinterpret_cast<const uint32_t*>(batch_row)[c];
-            break;
-          case kValueF16:
-            for (uint32_t c = lane; c < t.row_bytes / 2; c += 32)
-              reinterpret_cast<__half*>(row)[c] = __hadd(
-                  reinterpret_cast<__half*>(row)[c], reinterpret_cast<const __half*>(batch_row)[c]);
-            break;
-          case kValueBF16:
-            for (uint32_t c = lane; c < t.row_bytes / 2; c += 32)
-              reinterpret_cast<__nv_bfloat16*>(row)[c] =
-                  __hadd(reinterpret_cast<__nv_bfloat16*>(row)[c],
-                         reinterpret_cast<const __nv_bfloat16*>(batch_row)[c]);
-            break;
-          default:
-            for (uint32_t c = lane; c < t.row_bytes / 4; c += 32)
-              reinterpret_cast<float*>(row)[c] += reinterpret_cast<const float*>(batch_row)[c];
-            break;
-        }
+        warp_accumulate_row(row, batch_row, t.row_bytes, t.value_kind, lane);
       }
     }
     if (lane == 0 &&

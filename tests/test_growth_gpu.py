@@ -158,3 +158,44 @@ def test_large_rehash_keeps_rows_and_scores():
     k, _, _ = t.export_batch()
     assert k.size == before and np.unique(k).size == before
     t.close()
+
+
+def test_dynamic_max_capacity_like_the_reference():
+    """tests/dynamic_max_capacity_test.cc.cu of the reference, scaled down:
+    insert_and_evict (LRU) fills a growing table to load factor 0.98, then
+    set_max_capacity + reserve double it, again and again; at the end every key
+    ever inserted is either in the table or was handed back as evicted, with its
+    own row."""
+    LRU = 0
+    dim, n = 4, 10000
+    max_cap, uplimit = 1 << 14, 1 << 17
+    t = ProductTable(1 << 12, dim, LRU, max_capacity=max_cap,
+                     max_hbm_for_vectors=uplimit * dim * 4)
+    seen = {}
+    offset = 0
+    while True:
+        keys = np.arange(offset, offset + n, dtype=np.uint64)
+        rows = np.repeat(keys.astype(np.float32)[:, None], dim, axis=1)
+        ek, ev, _ = t.insert_and_evict(keys, rows, use_counter=False)
+        offset += n
+        for k, v in zip(ek.tolist(), ev):
+            assert np.all(v == np.float32(k))
+            seen[k] = True
+        if t.size() / t.capacity() >= 0.98:
+            assert t.size() >= int(max_cap * 0.98)
+            max_cap *= 2
+            if max_cap > uplimit:
+                break
+            t.set_max_capacity(max_cap)
+            t.reserve(max_cap)
+            assert t.capacity() == max_cap
+            assert t.size() / t.capacity() <= 0.5
+        assert offset <= 4 * uplimit, "walked too many keys without finishing"
+    k, v, _ = t.export_batch()
+    assert np.all(v == k.astype(np.float32)[:, None])
+    for key in k.tolist():
+        seen[key] = True
+    assert t.capacity() * 2 == max_cap
+    assert len(seen) >= int(t.capacity() * 0.98)
+    assert len(seen) == offset           # nothing was lost: resident or returned as evicted
+    t.close()
