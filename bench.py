@@ -110,6 +110,9 @@ class ProductArm:
     def find(self, keys, values, founds):
         self.t.find(keys.numel(), keys, values, founds)
 
+    def find_ptr(self, keys, ptrs, founds):
+        self.t.find_ptr(keys.numel(), keys, ptrs, founds)
+
     def size(self):
         return self.t.size()
 
@@ -160,6 +163,7 @@ class ReferenceArm:
         self.lib.ref_insert_or_assign.argtypes = [P, U, P, P, P, P, ctypes.c_int]
         self.lib.ref_find_or_insert.argtypes = [P, U, P, P, P, P, ctypes.c_int]
         self.lib.ref_find.argtypes = [P, U, P, P, P, P, P]
+        self.lib.ref_find_ptr.argtypes = [P, U, P, P, P, P, P, ctypes.c_int]
         self.lib.ref_export_batch.argtypes = [P, U, U, P, P, P, P, P]
         self.lib.ref_size.argtypes = [P, P, ctypes.POINTER(U)]
         self.lib.ref_capacity.argtypes = [P, ctypes.POINTER(U)]
@@ -192,6 +196,10 @@ class ReferenceArm:
     def find(self, keys, values, founds):
         self._chk(self.lib.ref_find(self.h, keys.numel(), keys.data_ptr(), values.data_ptr(),
                                     founds.data_ptr(), None, self._s()))
+
+    def find_ptr(self, keys, ptrs, founds):
+        self._chk(self.lib.ref_find_ptr(self.h, keys.numel(), keys.data_ptr(), ptrs.data_ptr(),
+                                        founds.data_ptr(), None, self._s(), 1))
 
     def size(self):
         o = ctypes.c_uint64(0)
@@ -400,6 +408,10 @@ def hybrid_ops(arm_cls, batch: int, reps: int = 5) -> dict:
     t_ms = time_steps(lambda i: arm.find(qs[i % 4], out, f), reps, 3)
     hits = float(f.float().mean().item())
     result = {"b_kv_s": round(batch * reps / (t_ms / 1e3) / BINARY_BILLION, 4)}
+    # find*: row addresses instead of rows (nothing crosses the host link)
+    ptrs = torch.empty(batch, dtype=torch.int64, device="cuda")
+    tp_ms = time_steps(lambda i: arm.find_ptr(qs[i % 4], ptrs, f), reps, 3)
+    result["find_ptr_b_kv_s"] = round(batch * reps / (tp_ms / 1e3) / BINARY_BILLION, 4)
     if hasattr(arm, "promote_hot_buckets"):
         # the warm-up pass of the workload: the buckets the queries hit most move into HBM
         t0 = time.perf_counter()
