@@ -137,7 +137,9 @@ struct hkv_table {
   hkv_allocator alloc{};
   bool own_allocator = true;
   std::atomic<uint64_t> global_epoch{hkv::kIgnoredEpoch};
-  unsigned long long* d_scratch = nullptr;  // counters for size / count overloads
+  // counters for size / count overloads: an allocation of their own, so that a
+  // doubling of the table in the middle of a call does not move them
+  unsigned long long* d_scratch = nullptr;
   StreamGroupLock lock;
   int device = 0;
   void* meta_block = nullptr;  // digests + keys + scores + sizes + status
@@ -362,7 +364,6 @@ struct Planes {
   void* meta_block = nullptr;
   void* values_hbm = nullptr;
   void* host_rows = nullptr;
-  unsigned long long* d_scratch = nullptr;
 };
 
 void free_planes(hkv_table* t, Planes& p) {
@@ -407,7 +408,6 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
     v.scores = reinterpret_cast<uint64_t*>(mb + off_scores);
     v.bucket_sizes = reinterpret_cast<int32_t*>(mb + off_sizes);
     v.status = reinterpret_cast<uint32_t*>(mb + off_status);
-    p.d_scratch = reinterpret_cast<unsigned long long*>(mb + off_status + 64);
     HKV_CUDA(cudaMemsetAsync(mb + off_status, 0, 256, stream));
     v.bucket_map = mapped ? reinterpret_cast<uint32_t*>(mb + off_map) : nullptr;
     v.bucket_heat = mapped ? reinterpret_cast<uint32_t*>(mb + off_heat) : nullptr;
@@ -541,7 +541,6 @@ void reserve(hkv_table* t, uint64_t new_capacity, cudaStream_t s) {
     t->view = grown;
     t->meta_block = fresh.meta_block;
     t->host_rows = fresh.host_rows;
-    t->d_scratch = fresh.d_scratch;
     free_planes(t, old);
   }
   t->reach_max_capacity.store(t->view.capacity * 2 > t->opt.max_capacity);
@@ -689,7 +688,13 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
       allocate_planes(t, buckets, v, planes, nullptr);
       t->meta_block = planes.meta_block;
       t->host_rows = planes.host_rows;
-      t->d_scratch = planes.d_scratch;
+      void* scratch = nullptr;
+      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &scratch, 256, 0) != 0 || scratch == nullptr) {
+        cudaGetLastError();
+        throw HkvError{HKV_ERR_CUDA, "device allocation of the counters failed"};
+      }
+      t->d_scratch = static_cast<unsigned long long*>(scratch);
+      HKV_CUDA(cudaMemset(scratch, 0, 256));
       HKV_CUDA(cudaDeviceSynchronize());
     } catch (...) {
       hkv_table_destroy(t);
@@ -705,6 +710,7 @@ int hkv_table_destroy(hkv_table* t) {
     DeviceGuard dg(t->device);
     cudaDeviceSynchronize();
     if (t->meta_block) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->meta_block);
+    if (t->d_scratch) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->d_scratch);
     if (t->view.values_hbm) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->view.values_hbm);
     if (t->host_rows) t->alloc.free(t->alloc.ctx, HKV_MEM_PINNED, t->host_rows);
     delete t;
