@@ -113,6 +113,9 @@ class ProductArm:
     def find_ptr(self, keys, ptrs, founds):
         self.t.find_ptr(keys.numel(), keys, ptrs, founds)
 
+    def accum_or_assign(self, keys, deltas, flags):
+        self.t.accum_or_assign(keys.numel(), keys, deltas, flags)
+
     def size(self):
         return self.t.size()
 
@@ -164,6 +167,7 @@ class ReferenceArm:
         self.lib.ref_find_or_insert.argtypes = [P, U, P, P, P, P, ctypes.c_int]
         self.lib.ref_find.argtypes = [P, U, P, P, P, P, P]
         self.lib.ref_find_ptr.argtypes = [P, U, P, P, P, P, P, ctypes.c_int]
+        self.lib.ref_accum_or_assign.argtypes = [P, U, P, P, P, P, P]
         self.lib.ref_export_batch.argtypes = [P, U, U, P, P, P, P, P]
         self.lib.ref_size.argtypes = [P, P, ctypes.POINTER(U)]
         self.lib.ref_capacity.argtypes = [P, ctypes.POINTER(U)]
@@ -196,6 +200,10 @@ class ReferenceArm:
     def find(self, keys, values, founds):
         self._chk(self.lib.ref_find(self.h, keys.numel(), keys.data_ptr(), values.data_ptr(),
                                     founds.data_ptr(), None, self._s()))
+
+    def accum_or_assign(self, keys, deltas, flags):
+        self._chk(self.lib.ref_accum_or_assign(self.h, keys.numel(), keys.data_ptr(),
+                                               deltas.data_ptr(), flags.data_ptr(), None, self._s()))
 
     def find_ptr(self, keys, ptrs, founds):
         self._chk(self.lib.ref_find_ptr(self.h, keys.numel(), keys.data_ptr(), ptrs.data_ptr(),
@@ -760,6 +768,16 @@ def main():
         t_ms = time_steps(lambda i: arm.insert_or_assign(queries[i % 2], vals[i % 2]), reps, 3)
         ops["insert_or_assign_all_hit"] = {"b_kv_s": per_kv(t_ms, batch * reps),
                                            "achieved_gbs": UPSERT_HIT_BYTES(row) * batch * reps / (t_ms / 1e3) / 1e9}
+        # accum_or_assign, all keys present, every flag "accumulate" (3R + 161 bytes per key);
+        # the call has no unique_key argument: both arms must tolerate repeated keys
+        if hasattr(arm, "accum_or_assign"):
+            deltas = torch.rand((batch, dim), device="cuda") * 1e-3
+            acc = torch.ones(batch, dtype=torch.bool, device="cuda")
+            t_ms = time_steps(lambda i: arm.accum_or_assign(queries[i % 2], deltas, acc), reps, 3)
+            ops["accum_or_assign_all_hit"] = {"b_kv_s": per_kv(t_ms, batch * reps),
+                                              "achieved_gbs": (3 * row + 161) * batch * reps / (t_ms / 1e3) / 1e9}
+            for i in range(2):      # the rows are functions of the keys again for what follows
+                arm.insert_or_assign(queries[i], vals[i])
         # insert_or_assign, all keys new (every insert evicts at load factor 1)
         newk = [mixed_keys((1 << 52) + key_base + i * batch, batch, "cuda") for i in range(reps + 3)]
         newv = rows_for(newk[0], dim)

@@ -129,8 +129,10 @@ __global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
       slot_out[i] = found ? static_cast<uint32_t>(row_slot(t, slot)) : kNoSlot;
       index_out[i] = static_cast<uint32_t>(i);
     }
-    // hybrid tables (they never run the VEC != 0 instantiations): hits per bucket
-    if (VEC == 0 && FORM != 3 && found && t.bucket_heat != nullptr) {
+    // hybrid tables (they never run the VEC != 0 instantiations): hits per
+    // bucket, sampled (every fourth key of a batch) to keep the atomics on the
+    // hot buckets' counters cheap -- the promotion only ranks buckets
+    if (VEC == 0 && FORM != 3 && found && t.bucket_heat != nullptr && (uint32_t(i) & 3u) == 0) {
       atomicAdd(t.bucket_heat + (slot >> 7), 1u);
     }
   }

@@ -44,6 +44,15 @@ struct MutateArgs {
   // accum_flags[row_index[i]], and the number of keys is read on the device.
   const uint32_t* row_index = nullptr;
   const uint64_t* n_device = nullptr;
+  // accum_or_assign on batches that may repeat a key: the fast kernel handles
+  // every accumulating key whose slot it can lock and appends the batch index
+  // of the others (assigning keys, and keys whose slot another occurrence holds
+  // at that moment) to deferred_list; the serialising kernel then walks that
+  // list (index_list / index_count).
+  uint32_t* deferred_list = nullptr;
+  unsigned int* deferred_count = nullptr;
+  const uint32_t* index_list = nullptr;
+  const unsigned int* index_count = nullptr;
 };
 
 void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values, bool* founds,

@@ -50,6 +50,7 @@ enum Result : uint32_t {
   kNeedEvict = 6,         // bucket has no free slot, goes to phase 3
   kMiss = 7,              // not found and the operation does not insert
   kFoundNoLock = 8,       // found, operation leaves the slot alone
+  kDeferred = 9,          // left to the serialising kernel (accum_or_assign with repeats)
 };
 
 constexpr uint32_t kModeValid = 1u;
@@ -273,6 +274,7 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
   uint32_t mode = 0;
   Address a{0, 0, 0};
   uint32_t my_row = 0;  // INDEXED: this key's row in the source rank's buffer
+  bool defer_me = false;
   uint8_t* const batch_rows = INDEXED ? args.values : args.values + base * t.row_bytes;
   if (i < n) {
     key = args.keys[i];
@@ -285,8 +287,14 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
         desired = desired_score(strategy, args.scores, in_score, args.epoch);
       }
       if (OP == kOpAccumOrAssign) {
-        mode |= args.accum_flags[INDEXED ? uint64_t(my_row) : i] ? kModeLockOnHit
-                                                                  : kModeInsertOnMiss;
+        const bool is_accum = args.accum_flags[INDEXED ? uint64_t(my_row) : i];
+        mode |= is_accum ? kModeLockOnHit : kModeInsertOnMiss;
+        // a batch that may repeat keys: two occurrences of a new key must not
+        // both insert it, so assigning keys go to the serialising kernel
+        if (!INDEXED && args.deferred_list != nullptr && !is_accum) {
+          mode = 0;
+          defer_me = true;
+        }
       } else if (op_inserts(OP)) {
         mode |= kModeLockOnHit | kModeInsertOnMiss;
       } else {
@@ -361,12 +369,14 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
     uint32_t slot = kNoSlot;
     if (pmode & kModeValid) {
       uint32_t hit_pos = 255u;
+      bool met_lock = false;  // a candidate slot was LOCKED: it may hold this very key
       uint32_t m = mask_j & 0xFFFFu;
       if (m) {
         uint32_t pos = pl.sub * 16u + (__ffs(m) - 1);
         if (first_j == want) {
           hit_pos = pos;
         } else {
+          met_lock = first_j == t.locked_key;
           m &= m - 1;
           while (m) {
             pos = pl.sub * 16u + (__ffs(m) - 1);
@@ -378,6 +388,7 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
               hit_pos = pos;
               break;
             }
+            met_lock |= seen == t.locked_key;
           }
         }
       }
@@ -387,6 +398,9 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
         const uint32_t pos = __shfl_sync(gmask, hit_pos, src);
         result = lock_on_hit ? kDuplicate : kFoundNoLock;
         slot = uint32_t(slot0) + pos;
+      } else if (OP == kOpAccumOrAssign && !INDEXED && args.deferred_list != nullptr &&
+                 __ballot_sync(gmask, met_lock)) {
+        result = kDeferred;  // another occurrence of the key may hold that slot right now
       } else if (!(pmode & kModeInsertOnMiss)) {
         result = kMiss;
       } else if (pmode & kModeBucketFull) {
@@ -420,6 +434,18 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
     if ((pl.lane >> 2) == uint32_t(j)) {
       my_result = r;
       my_slot = s;
+    }
+  }
+
+  if (OP == kOpAccumOrAssign && !INDEXED && args.deferred_list != nullptr) {
+    const uint32_t later = __ballot_sync(full, defer_me || my_result == kDeferred);
+    if (later) {
+      unsigned int first = 0;
+      if (pl.lane == 0) first = atomicAdd(args.deferred_count, __popc(later));
+      first = __shfl_sync(full, first, 0);
+      if ((later >> pl.lane) & 1u) {
+        args.deferred_list[first + __popc(later & lane_lt)] = static_cast<uint32_t>(i);
+      }
     }
   }
 
@@ -639,13 +665,14 @@ __global__ void __launch_bounds__(kMutateBlock)
   const uint32_t lane = threadIdx.x & 31u;
   const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const uint64_t base = warp * 32u;
-  const uint64_t n = args.n;
+  // with an index list the kernel walks the listed batch positions only
+  const uint64_t n = args.index_list != nullptr ? uint64_t(*args.index_count) : args.n;
   if (base >= n) return;
   const int strategy = args.strategy;
   const uint32_t count = uint32_t(min(uint64_t(32), n - base));
 
   for (uint32_t q = 0; q < count; ++q) {
-    const uint64_t i = base + q;
+    const uint64_t i = args.index_list != nullptr ? uint64_t(args.index_list[base + q]) : base + q;
     const uint64_t key = args.keys[i];
     if (is_reserved(t, key)) {
       if (lane == 0 &&
@@ -1120,6 +1147,31 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
   if (unique_key) {
     auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
     kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+  } else if (OP == kOpAccumOrAssign && args.n < (1ull << 32)) {
+    // Repeated keys are allowed.  The fast kernel serves every accumulating
+    // key whose slot it can lock; assigning keys and keys whose slot another
+    // occurrence held at that moment are listed and served by the serialising
+    // kernel afterwards (an empty list costs one launch that exits at once).
+    uint8_t* work = nullptr;
+    if (cudaMallocAsync(reinterpret_cast<void**>(&work), args.n * sizeof(uint32_t) + 256, stream) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+      return;
+    }
+    unsigned int* count = reinterpret_cast<unsigned int*>(work);
+    uint32_t* list = reinterpret_cast<uint32_t*>(work + 256);
+    cudaMemsetAsync(count, 0, sizeof(unsigned int), stream);
+    MutateArgs fast = args;
+    fast.deferred_list = list;
+    fast.deferred_count = count;
+    auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
+    kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, fast);
+    MutateArgs rest = args;
+    rest.index_list = list;
+    rest.index_count = count;
+    mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, rest);
+    cudaFreeAsync(work, stream);
   } else {
     mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
   }

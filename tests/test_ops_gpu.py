@@ -370,6 +370,50 @@ def test_repeated_keys_in_one_batch_non_unique():
     t.close()
 
 
+def test_accum_or_assign_with_repeated_keys():
+    """accum_or_assign has no unique_key argument in the reference: a batch may
+    repeat keys.  Every delta of a resident key must arrive exactly once
+    (integer-valued floats: the sum does not depend on the order), a new key that
+    occurs several times is inserted once, and (assign, hit) / (accum, miss)
+    stay no-ops."""
+    cap, dim = 128 * 64, 8
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    rng = np.random.default_rng(12)
+    keys = unique_keys(5000, seed=13)
+    resident, fresh = keys[:3000], keys[3000:]
+    base = rng.integers(-20, 20, size=(3000, dim)).astype(np.float32)
+    t.insert_or_assign(resident, base, np.arange(1, 3001, dtype=np.uint64))
+    # a Zipf-like batch: few keys many times, many keys once or twice
+    times = np.minimum(rng.zipf(1.5, size=3000), 300)
+    batch = np.repeat(resident, times)
+    new_dup = np.repeat(fresh[:500], 3)                     # new keys, three occurrences each
+    lost = fresh[500:1000]                                   # accumulate on keys that are absent
+    all_keys = np.concatenate([batch, new_dup, lost, resident[:400]])
+    flags = np.concatenate([np.ones(batch.size, bool), np.zeros(new_dup.size, bool),
+                            np.ones(lost.size, bool), np.zeros(400, bool)])
+    deltas = rng.integers(-5, 5, size=(all_keys.size, dim)).astype(np.float32)
+    deltas[batch.size:batch.size + new_dup.size] = np.repeat(values_for(fresh[:500], dim), 3, axis=0)
+    order = rng.permutation(all_keys.size)
+    all_keys, flags, deltas = all_keys[order], flags[order], np.ascontiguousarray(deltas[order])
+    sc = np.arange(10001, 10001 + all_keys.size, dtype=np.uint64)
+    t.accum_or_assign(all_keys, deltas, flags, sc)
+    assert t.t.device_status() == 0
+    assert t.size() == 3500
+    want = base.copy()
+    idx = {int(k): i for i, k in enumerate(resident)}
+    for k, f, d in zip(all_keys.tolist(), flags.tolist(), deltas):
+        if f and k in idx:
+            want[idx[k]] += d
+    v, f, _ = t.find(resident)
+    assert f.all()
+    np.testing.assert_array_equal(v, want)
+    v, f, _ = t.find(fresh[:500])
+    assert f.all()
+    np.testing.assert_array_equal(v, values_for(fresh[:500], dim))
+    assert not t.contains(lost).any()
+    t.close()
+
+
 def test_same_bucket_contention_unique_batch():
     """Every key of the batch targets one of two buckets (adversarial for the
     slot CAS protocol): capacity is respected, nothing is lost or duplicated."""
