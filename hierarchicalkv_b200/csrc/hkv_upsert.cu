@@ -274,6 +274,12 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
   uint32_t mode = 0;
   Address a{0, 0, 0};
   uint32_t my_row = 0;  // INDEXED: this key's row in the source rank's buffer
+  // Batches that may repeat a key (unique_key == false): this kernel only
+  // serves keys it finds and can lock.  A key that meets a LOCKED candidate
+  // slot (another occurrence may hold it) and every key that would have to be
+  // inserted (two occurrences must not both insert it) is appended to
+  // args.deferred_list for the serialising kernel that runs next.
+  const bool tolerant = !INDEXED && args.deferred_list != nullptr;
   bool defer_me = false;
   uint8_t* const batch_rows = INDEXED ? args.values : args.values + base * t.row_bytes;
   if (i < n) {
@@ -291,7 +297,7 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
         mode |= is_accum ? kModeLockOnHit : kModeInsertOnMiss;
         // a batch that may repeat keys: two occurrences of a new key must not
         // both insert it, so assigning keys go to the serialising kernel
-        if (!INDEXED && args.deferred_list != nullptr && !is_accum) {
+        if (tolerant && !is_accum) {
           mode = 0;
           defer_me = true;
         }
@@ -398,9 +404,9 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
         const uint32_t pos = __shfl_sync(gmask, hit_pos, src);
         result = lock_on_hit ? kDuplicate : kFoundNoLock;
         slot = uint32_t(slot0) + pos;
-      } else if (OP == kOpAccumOrAssign && !INDEXED && args.deferred_list != nullptr &&
-                 __ballot_sync(gmask, met_lock)) {
-        result = kDeferred;  // another occurrence of the key may hold that slot right now
+      } else if (tolerant &&
+                 (__ballot_sync(gmask, met_lock) != 0 || (pmode & kModeInsertOnMiss) != 0)) {
+        result = kDeferred;
       } else if (!(pmode & kModeInsertOnMiss)) {
         result = kMiss;
       } else if (pmode & kModeBucketFull) {
@@ -437,7 +443,7 @@ __global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutat
     }
   }
 
-  if (OP == kOpAccumOrAssign && !INDEXED && args.deferred_list != nullptr) {
+  if (tolerant) {
     const uint32_t later = __ballot_sync(full, defer_me || my_result == kDeferred);
     if (later) {
       unsigned int first = 0;
@@ -1147,9 +1153,9 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
   if (unique_key) {
     auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
     kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
-  } else if (OP == kOpAccumOrAssign && args.n < (1ull << 32)) {
-    // Repeated keys are allowed.  The fast kernel serves every accumulating
-    // key whose slot it can lock; assigning keys and keys whose slot another
+  } else if (OP != kOpFindOrInsertPtr && OP != kOpLockKeys && args.n < (1ull << 32)) {
+    // Repeated keys are allowed.  The fast kernel serves every key it finds
+    // and can lock; keys that have to be inserted and keys whose slot another
     // occurrence held at that moment are listed and served by the serialising
     // kernel afterwards (an empty list costs one launch that exits at once).
     uint8_t* work = nullptr;
