@@ -842,6 +842,9 @@ def main():
         "metric": "find B-KV/s at LF=1.0, dim=64 (n/s/2^30), all keys present",
         "value": round(value, 4),
         "unit": "B-KV/s",
+        # the same figure in decimal units (keys per second / 1e9); B-KV/s divides by 2^30 as the
+        # reference's benchmark does (benchmark/merlin_hashtable_benchmark.cc.cu:415-417)
+        "value_gkeys_per_s_decimal": round(value * BINARY_BILLION / 1e9, 4),
         "n_gpus": launched_world,
         "steps": args.steps,
         "warmup": args.warmup,
