@@ -30,7 +30,8 @@ constexpr int kPasses = 8;               // passes to cover a warp's 32 keys
 constexpr uint32_t kNoSlot = 0xFFFFFFFFu;
 constexpr uint64_t kMaxScore = 0xFFFFFFFFFFFFFFFFull;
 constexpr uint64_t kIgnoredEpoch = 0xFFFFFFFFFFFFFFFFull;
-constexpr uint32_t kSpinLimit = 1u << 16;  // bound of every device-side wait
+constexpr uint32_t kSpinLimit = 1u << 22;    // polls of one slot before a wait gives up (about a second)
+constexpr uint32_t kRescanLimit = 1u << 20;  // bucket rescans of the serialising kernels (about a second)
 
 // Bits of the per-table device status word.
 constexpr uint32_t kStatusLockTimeout = 1u;   // a bounded slot wait ran out

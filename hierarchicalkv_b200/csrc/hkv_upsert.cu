@@ -706,7 +706,7 @@ __global__ void __launch_bounds__(kMutateBlock)
     uint64_t victim_score = 0;
     uint32_t attempts = 0;
     while (result == kInitial) {
-      if (++attempts > kSpinLimit) {
+      if (++attempts > kRescanLimit) {
         if (lane == 0) atomicOr(t.status, kStatusLockTimeout);
         result = kRefused;
         break;
@@ -1036,7 +1036,7 @@ __global__ void __launch_bounds__(kMutateBlock)
     uint64_t victim = 0;
     uint32_t attempts = 0;
     while (result == kInitial) {
-      if (++attempts > kSpinLimit) {
+      if (++attempts > kRescanLimit) {
         if (lane == 0) atomicOr(t.status, kStatusLockTimeout);
         result = kRefused;
         break;
