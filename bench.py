@@ -880,7 +880,7 @@ def main():
                      "unit": "GB/s", "frac": round(achieved_gbs / peak, 4),
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the same
                      # kernel on the same number of keys, 1/8-size table
-                     # (profiles/find_kernel_c2_small.md); bytes per launch
+                     # (the committed ncu summary of find_kernel); bytes per launch
                      "traffic": 530_030_592 if args.impl == "product" else None,
                      "peak_source": peak_src,
                      "algorithmic_bytes_per_key": FIND_HIT_BYTES(row),

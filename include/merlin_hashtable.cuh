@@ -14,7 +14,8 @@
 // are evaluated by small kernels in this header over the table's planes
 // (hkv_get_view); everything else runs inside the library.
 //
-// Differences a caller can observe are listed in INTEGRATION.md.
+// Differences a caller can observe are listed in the integration notes shipped
+// with the library.
 #pragma once
 
 #include <cuda_bf16.h>
