@@ -116,6 +116,15 @@ class ProductArm:
     def accum_or_assign(self, keys, deltas, flags):
         self.t.accum_or_assign(keys.numel(), keys, deltas, flags)
 
+    def assign(self, keys, values):
+        self.t.assign(keys.numel(), keys, values)
+
+    def contains(self, keys, founds):
+        self.t.contains(keys.numel(), keys, founds)
+
+    def find_or_insert_ptr(self, keys, ptrs, founds):
+        self.t.find_or_insert_ptr(keys.numel(), keys, ptrs, founds)
+
     def size(self):
         return self.t.size()
 
@@ -168,6 +177,9 @@ class ReferenceArm:
         self.lib.ref_find.argtypes = [P, U, P, P, P, P, P]
         self.lib.ref_find_ptr.argtypes = [P, U, P, P, P, P, P, ctypes.c_int]
         self.lib.ref_accum_or_assign.argtypes = [P, U, P, P, P, P, P]
+        self.lib.ref_assign.argtypes = [P, U, P, P, P, P, ctypes.c_int]
+        self.lib.ref_contains.argtypes = [P, U, P, P, P]
+        self.lib.ref_find_or_insert_ptr.argtypes = [P, U, P, P, P, P, P, ctypes.c_int]
         self.lib.ref_export_batch.argtypes = [P, U, U, P, P, P, P, P]
         self.lib.ref_size.argtypes = [P, P, ctypes.POINTER(U)]
         self.lib.ref_capacity.argtypes = [P, ctypes.POINTER(U)]
@@ -200,6 +212,19 @@ class ReferenceArm:
     def find(self, keys, values, founds):
         self._chk(self.lib.ref_find(self.h, keys.numel(), keys.data_ptr(), values.data_ptr(),
                                     founds.data_ptr(), None, self._s()))
+
+    def assign(self, keys, values):
+        self._chk(self.lib.ref_assign(self.h, keys.numel(), keys.data_ptr(), values.data_ptr(), None,
+                                      self._s(), 1))
+
+    def contains(self, keys, founds):
+        self._chk(self.lib.ref_contains(self.h, keys.numel(), keys.data_ptr(), founds.data_ptr(),
+                                        self._s()))
+
+    def find_or_insert_ptr(self, keys, ptrs, founds):
+        self._chk(self.lib.ref_find_or_insert_ptr(self.h, keys.numel(), keys.data_ptr(),
+                                                  ptrs.data_ptr(), founds.data_ptr(), None,
+                                                  self._s(), 1))
 
     def accum_or_assign(self, keys, deltas, flags):
         self._chk(self.lib.ref_accum_or_assign(self.h, keys.numel(), keys.data_ptr(),
@@ -238,7 +263,9 @@ class ReferenceArm:
 
     def insert_and_evict(self, keys, values, scores, ek, ev, es, counter):
         self._chk(self.lib.ref_insert_and_evict(self.h, keys.numel(), keys.data_ptr(),
-                                                values.data_ptr(), scores.data_ptr(), ek.data_ptr(),
+                                                values.data_ptr(),
+                                                scores.data_ptr() if scores is not None else None,
+                                                ek.data_ptr(),
                                                 ev.data_ptr(), es.data_ptr(), counter.data_ptr(),
                                                 self._s(), 1))
 
@@ -553,6 +580,95 @@ def embedding_step_ops(sharded, rank: int, world: int, batch: int, dim: int, bar
     }
 
 
+API_ORDER = ["insert_or_assign", "find", "find_or_insert", "assign", "find_ptr",
+             "find_or_insert_ptr", "insert_and_evict", "export_batch", "export_batch_if", "contains"]
+
+
+def api_table(arm, capacity: int, dim: int, batch: int, reps: int = 3) -> dict:
+    """Every API of the reference's benchmark program at load factors 0.50,
+    0.75 and 1.00, with that program's batches: 60 % keys that are in the table
+    and 40 % keys that are not (benchmark/benchmark_util.cuh:136-177 of the
+    reference), LRU, B-KV/s = keys / second / 2^30.  Timed with CUDA events,
+    median of `reps` batches after one warm-up batch; the lookups run before the
+    calls that insert, which raise the load factor by a few percent."""
+    out = {}
+    g = torch.Generator(device="cuda")
+    g.manual_seed(23)
+    inserted = 0
+    fresh_counter = [1 << 54]
+    vals_out = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+    founds = torch.empty(batch, dtype=torch.bool, device="cuda")
+    ptrs = torch.empty(batch, dtype=torch.int64, device="cuda")
+    ek = torch.empty(batch, dtype=torch.int64, device="cuda")
+    ev = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+    es = torch.empty(batch, dtype=torch.int64, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+
+    def mixed_batch():
+        """60 % resident keys, 40 % keys nobody has seen"""
+        hit = int(batch * 0.6)
+        off = int(torch.randint(0, max(1, capacity - 4 * batch), (1,), generator=g, device="cuda").item())
+        off = off // 128 * 128
+        present = arm.export_keys(off, min(capacity - off, 4 * batch))
+        while present.numel() < hit:                      # sparse table: widen the window
+            present = arm.export_keys(0, capacity)
+        present = present[torch.randperm(present.numel(), generator=g, device="cuda")[:hit]]
+        fresh = mixed_keys(fresh_counter[0], batch - hit, "cuda")
+        fresh_counter[0] += batch
+        keys = torch.cat([present, fresh])
+        return keys[torch.randperm(batch, generator=g, device="cuda")].contiguous()
+
+    def timed(fn):
+        samples = []
+        for r in range(reps + 1):
+            keys = mixed_batch()
+            rows = rows_for(keys, dim)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn(keys, rows)
+            b.record()
+            torch.cuda.synchronize()
+            if r:
+                samples.append(a.elapsed_time(b))
+        return round(batch / (statistics.median(samples) / 1e3) / BINARY_BILLION, 3)
+
+    for lf in (0.5, 0.75, 1.0):
+        while arm.size() < lf * capacity - 0.0005 * capacity and inserted < 2.5 * capacity:
+            keys = mixed_keys(inserted, batch, "cuda")
+            arm.insert_or_assign(keys, rows_for(keys, dim))
+            inserted += batch
+        row = {"load_factor_reached": round(arm.size() / capacity, 4)}
+        window = min(capacity, int(batch / max(lf, 1e-6) * 0.995))
+
+        def export_all(keys, rows):
+            counter.zero_()
+            arm.export_batch(window, 0, counter, ek, ev, es)
+
+        def export_if(keys, rows):
+            counter.zero_()
+            arm.export_if_score_below((1 << 63) - 1, window, counter, ek, ev, es)
+
+        row["find"] = timed(lambda k, v: arm.find(k, vals_out, founds))
+        row["find_ptr"] = timed(lambda k, v: arm.find_ptr(k, ptrs, founds))
+        row["contains"] = timed(lambda k, v: arm.contains(k, founds))
+        row["export_batch"] = timed(export_all)
+        row["export_batch_if"] = timed(export_if)
+        row["assign"] = timed(lambda k, v: arm.assign(k, v))
+        row["insert_or_assign"] = timed(lambda k, v: arm.insert_or_assign(k, v))
+        row["find_or_insert"] = timed(lambda k, v: arm.find_or_insert(k, v))
+        row["find_or_insert_ptr"] = timed(lambda k, v: arm.find_or_insert_ptr(k, ptrs, founds))
+
+        def evict(keys, rows):
+            counter.zero_()
+            arm.insert_and_evict(keys, rows, None, ek, ev, es, counter)
+
+        row["insert_and_evict"] = timed(evict)
+        row["load_factor_after"] = round(arm.size() / capacity, 4)
+        out["%.2f" % lf] = row
+    return out
+
+
 def cpu_baseline(dim: int, batch: int, seconds_budget: float = 20.0) -> dict:
     """The CPU restatement (oracle/hkv_oracle.cpp) on all host threads, on a
     bounded sample: a 1/8-size table filled to the same load factor, then
@@ -612,6 +728,9 @@ def main():
     ap.add_argument("--load-factor", type=float, default=1.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ops", action="store_true", help="skip the secondary operations")
+    ap.add_argument("--api-table", action="store_true",
+                    help="instead of the JSON line of the headline workload: every API of the "
+                         "reference's benchmark program at load factors 0.50 / 0.75 / 1.00")
     ap.add_argument("--nccl-routing", action="store_true",
                     help="N > 1: route with NCCL all-to-all instead of the fused peer-memory kernels")
     args = ap.parse_args()
@@ -651,6 +770,22 @@ def main():
             return
     else:
         arm = ProductArm(capacity, dim, hbm_bytes)
+
+    if args.api_table:
+        if world > 1:
+            raise SystemExit("--api-table is a single-GPU mode")
+        table = api_table(arm, capacity, dim, batch)
+        print(json.dumps({"impl": args.impl, "unit": "B-KV/s (keys / second / 2^30)",
+                          "config": {"workload": "capacity %d, dim %d fp32, LRU, batch %d, 60 %% resident "
+                                                 "/ 40 %% new keys per batch" % (capacity, dim, batch)},
+                          "api_table": table}))
+        hdr = ["load factor"] + API_ORDER
+        print("| " + " | ".join(hdr) + " |", file=sys.stderr)
+        print("|" + "---:|" * len(hdr), file=sys.stderr)
+        for lf, row in table.items():
+            print("| " + " | ".join([lf] + ["%.3f" % row[a] for a in API_ORDER]) + " |", file=sys.stderr)
+        arm.close()
+        return
 
     # One shard of `capacity` slots per GPU (weak scaling: per-GPU table and
     # per-GPU batch stay fixed as N grows).  With N > 1 the table is sharded by

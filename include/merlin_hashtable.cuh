@@ -143,6 +143,23 @@ __device__ __forceinline__ const uint8_t* view_row(const hkv_table_view& v, uint
                             : v.values_host + (slot - v.hbm_slots) * v.row_bytes;
 }
 
+// One row, all 32 lanes: 16-byte chunks when the row size and both addresses
+// allow it, else elements of `elem` bytes.
+__device__ __forceinline__ void copy_row(uint8_t* dst, const uint8_t* src, uint64_t row_bytes,
+                                         uint32_t lane, uint32_t elem) {
+  if (((row_bytes | reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) == 0) {
+    for (uint64_t b = uint64_t(lane) * 16; b < row_bytes; b += 32 * 16) {
+      *reinterpret_cast<uint4*>(dst + b) = *reinterpret_cast<const uint4*>(src + b);
+    }
+  } else if (elem == 4) {
+    for (uint64_t b = uint64_t(lane) * 4; b < row_bytes; b += 32 * 4) {
+      *reinterpret_cast<uint32_t*>(dst + b) = *reinterpret_cast<const uint32_t*>(src + b);
+    }
+  } else {
+    for (uint64_t b = lane; b < row_bytes; b += 32) dst[b] = src[b];
+  }
+}
+
 // export_batch_if<PredFunctor>: one warp per 32 consecutive slots, ballot,
 // one ticket range per warp, rows copied by the whole warp.
 template <class K, class V, class S, template <typename, typename> class PredFunctor>
@@ -186,9 +203,7 @@ __global__ void export_if_kernel(const hkv_table_view v, const K pattern, const 
         left &= left - 1;
         const uint8_t* row = view_row(v, offset + tile * 32 + src);
         uint8_t* dst = reinterpret_cast<uint8_t*>(out_values) + (at + rank) * v.row_bytes;
-        for (uint64_t b = lane * sizeof(V); b < v.row_bytes; b += 32 * sizeof(V)) {
-          *reinterpret_cast<V*>(dst + b) = *reinterpret_cast<const V*>(row + b);
-        }
+        copy_row(dst, row, v.row_bytes, lane, sizeof(V));
         ++rank;
       }
     }
