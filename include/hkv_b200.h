@@ -13,9 +13,10 @@
  * nv::merlin::HashTable<K,V,S,Strategy> in include/merlin_hashtable.cuh is a
  * thin wrapper over these functions.
  *
- * Key type: 64-bit (uint64_t or int64_t bit pattern).  Score type: uint64_t.
- * Value rows are opaque bytes of `dim * value_size` except in
- * hkv_accum_or_assign, which adds float32 elements.
+ * Key type: 64-bit (uint64_t or int64_t bit pattern).  Score type: uint64_t
+ * (uint32_t with the Customized strategy, see hkv_options.score_size).  Value
+ * rows are opaque bytes of `dim * value_size` except in hkv_accum_or_assign,
+ * which adds elements of the type hkv_options.value_kind names.
  */
 #ifndef HKV_B200_H_
 #define HKV_B200_H_
@@ -81,7 +82,8 @@ typedef struct hkv_options {
   int32_t reserved_key_start_bit; /* 0..62 */
   uint64_t num_of_buckets_per_alloc;
   int32_t api_lock;
-  int32_t table_mode; /* 0 kThroughput; 1 kMemory is rejected */
+  int32_t table_mode; /* 0 kThroughput; 1 kMemory: dual-bucket table (insert_or_assign of unique
+                         keys, find and the whole-table scans only, as in the reference) */
   /* template parameters of HashTable<K,V,S,Strategy> */
   int32_t evict_strategy; /* hkv_evict_strategy */
   uint32_t value_size;    /* sizeof(V) */
@@ -163,8 +165,9 @@ HKV_API int hkv_insert_and_evict_count(hkv_table* table, uint64_t n, const uint6
                                        uint64_t* evicted_scores, hkv_stream stream, int unique_key,
                                        int ignore_evict_strategy, uint64_t* evicted_count);
 
-/* HashTable::accum_or_assign, include/merlin_hashtable.cuh:1589-1680
- * (float32 elements) */
+/* HashTable::accum_or_assign, include/merlin_hashtable.cuh:1589-1680.  Adds
+ * elements of hkv_options.value_kind.  A batch may repeat keys, as in the
+ * reference (the call has no unique_key argument there). */
 HKV_API int hkv_accum_or_assign(hkv_table* table, uint64_t n, const uint64_t* keys,
                                 const void* value_or_deltas, const bool* accum_or_assigns,
                                 const uint64_t* scores, hkv_stream stream,
@@ -393,9 +396,11 @@ HKV_API int hkv_upsert_routed(hkv_table* table, int op, uint32_t world, uint32_t
                               hkv_stream stream);
 
 /* hkv_accum_or_assign for batches the caller guarantees to hold each key once
- * (the sharded table de-duplicates before routing): runs the probe kernel the
- * other insert-like operations use instead of the reference's key-scanning
- * tile kernel (include/merlin/core_kernels/accum_or_assign.cuh:83-174). */
+ * (the sharded table de-duplicates before routing): one launch of the probe
+ * kernel the other insert-like operations use, without the second pass that
+ * serves repeated and newly inserted keys one after the other.  The reference
+ * has a single, key-scanning tile kernel here
+ * (include/merlin/core_kernels/accum_or_assign.cuh:83-174). */
 HKV_API int hkv_accum_or_assign_unique(hkv_table* table, uint64_t n, const uint64_t* keys,
                                        const void* value_or_deltas, const bool* accum_or_assigns,
                                        const uint64_t* scores, hkv_stream stream,
