@@ -22,6 +22,11 @@ constexpr int kFindBlock = 128;
 #define HKV_FIND_MIN_BLOCKS 8
 #endif
 constexpr int kFindMinBlocks = HKV_FIND_MIN_BLOCKS;  // resident blocks per SM asked of the compiler
+#ifndef HKV_FIND_LIGHT_MIN_BLOCKS
+#define HKV_FIND_LIGHT_MIN_BLOCKS 10
+#endif
+// the forms that move no rows (find*, contains, the probe step of the hybrid find)
+constexpr int kFindLightMinBlocks = HKV_FIND_LIGHT_MIN_BLOCKS;
 
 // Probes the 32 keys of a warp.  Returns in the owner lane the global slot of
 // its key, or kNoSlot.
@@ -97,7 +102,9 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
 //         index: the first step of find on a table whose rows partly live in
 //         host memory
 template <int FORM, int VEC>
-__global__ void __launch_bounds__(kFindBlock, kFindMinBlocks)
+__global__ void __launch_bounds__(kFindBlock, (FORM == 1 || FORM == 3 || FORM == 4)
+                                                  ? kFindLightMinBlocks
+                                                  : kFindMinBlocks)
     find_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
                 uint8_t* __restrict__ values, void** __restrict__ ptrs, bool* __restrict__ founds,
                 uint64_t* __restrict__ scores, uint64_t* __restrict__ missed_keys,
