@@ -38,6 +38,10 @@ constexpr int kMutateBlock = 128;
 // latency: 8 blocks (64 registers, a few spilled values) measured 13 % faster
 // than 5 blocks (96 registers, no spills) and faster than 10 or 12.
 constexpr int kMutateMinBlocks = HKV_MUTATE_MIN_BLOCKS;
+#ifndef HKV_MUTATE_LIGHT_MIN_BLOCKS
+#define HKV_MUTATE_LIGHT_MIN_BLOCKS 8
+#endif
+constexpr int kMutateLightMinBlocks = HKV_MUTATE_LIGHT_MIN_BLOCKS;
 constexpr uint32_t kEvictIterLimit = 1u << 16;  // iterations of the full-bucket loop per warp
 
 enum Result : uint32_t {
@@ -250,8 +254,18 @@ __device__ __forceinline__ void warp_copy_one_row(const TableView& t, uint8_t* d
 // INDEXED is the routed form of the key-hash sharded table: the batch is one
 // source rank's inbox segment, the number of keys is read from device memory
 // and key i's row is row args.row_index[i] of the source rank's buffer.
+// Resident blocks per SM asked of the compiler: the forms that move no rows
+// can afford more of them, insert_and_evict (evicted rows, tickets) fewer.
+__host__ __device__ constexpr int mutate_min_blocks(int op) {
+  return op == kOpInsertAndEvict ? kMutateMinBlocks - 2
+         : (op == kOpFindOrInsertPtr || op == kOpAssignScores || op == kOpFindAndUpdate ||
+            op == kOpLockKeys)
+             ? kMutateLightMinBlocks
+             : kMutateMinBlocks;
+}
+
 template <int OP, int VEC, bool INDEXED>
-__global__ void __launch_bounds__(kMutateBlock, OP == kOpInsertAndEvict ? kMutateMinBlocks - 2 : kMutateMinBlocks)
+__global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
     mutate_kernel(const TableView t, const MutateArgs args) {
   static_assert(!INDEXED || OP == kOpInsertOrAssign || OP == kOpFindOrInsert ||
                     OP == kOpAccumOrAssign,
