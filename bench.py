@@ -389,9 +389,13 @@ def present_batches(arm, capacity: int, batch: int, count: int, seed: int):
     return out
 
 
-def time_steps(fn, steps: int, warmup: int, barrier=None):
+def time_steps(fn, steps: int, warmup: int, barrier=None, join=None):
+    """`join` (optional) makes the timing stream wait for work `fn` queued on
+    other streams; it runs before the end event is recorded."""
     for i in range(warmup):
         fn(i)
+    if join:
+        join()
     torch.cuda.synchronize()
     if barrier:
         barrier()
@@ -400,6 +404,8 @@ def time_steps(fn, steps: int, warmup: int, barrier=None):
     start.record()
     for i in range(steps):
         fn(warmup + i)
+    if join:
+        join()
     end.record()
     torch.cuda.synchronize()
     if barrier:
@@ -731,6 +737,9 @@ def main():
     ap.add_argument("--api-table", action="store_true",
                     help="instead of the JSON line of the headline workload: every API of the "
                          "reference's benchmark program at load factors 0.50 / 0.75 / 1.00")
+    ap.add_argument("--lanes", type=int, default=2,
+                    help="N > 1: peer workspaces the fused find rotates through (1: no overlap of "
+                         "one batch's routing with the previous batch's lookup)")
     ap.add_argument("--nccl-routing", action="store_true",
                     help="N > 1: route with NCCL all-to-all instead of the fused peer-memory kernels")
     args = ap.parse_args()
@@ -819,15 +828,20 @@ def main():
     fused = False
     if sharded is not None and not args.nccl_routing:
         try:
-            ws = sharded.enable_fused_find(batch, dim)
+            ws = sharded.enable_fused_find(batch, dim, lanes=args.lanes)
             out_vals, founds = ws.out_values, ws.out_founds     # results land in peer-visible buffers
             fused = True
         except Exception as e:  # no peer mappings on this box: route with NCCL instead
             if rank == 0:
                 print(f"fused routing unavailable ({e}); using NCCL all-to-all", file=sys.stderr)
 
-    def do_find(keys):
-        if fused:
+    pipelined = fused and args.lanes > 1
+    last_result = [out_vals, founds]
+
+    def do_find(keys, pipeline=True):
+        if pipelined and pipeline:   # batch k + 1 is routed while the owners serve batch k
+            last_result[0], last_result[1], _ = sharded.find_fused_async(batch, keys)
+        elif fused:
             sharded.find_fused(batch, keys)
         elif sharded is not None:
             sharded.find(batch, keys, out_vals, founds)
@@ -840,13 +854,17 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms = time_steps(step, args.steps, args.warmup, barrier)
+    join = sharded.join_lanes if pipelined else None
+    ms = time_steps(step, args.steps, args.warmup, barrier, join)
     clocks = sampler.stop() if rank == 0 else None
+    out_vals, founds = last_result
 
     # correctness of what was timed: every key found, rows as generated
     last = queries[(args.warmup + args.steps - 1) % n_query_sets]
     assert bool(founds.all()), "timed find missed keys that are in the table"
     assert torch.equal(out_vals, rows_for(last, dim)), "timed find returned wrong rows"
+    if fused:
+        out_vals, founds = ws.out_values, ws.out_founds     # what the unpipelined call fills
 
     if dist:
         tms = torch.tensor([ms], device="cuda")
@@ -866,7 +884,7 @@ def main():
 
     def e2e_step(i):
         d_keys.copy_(h_keys[i % n_query_sets], non_blocking=True)
-        do_find(d_keys)
+        do_find(d_keys, pipeline=False)     # the copies dominate: one lane, results read right away
         h_vals.copy_(out_vals, non_blocking=True)
         h_founds.copy_(founds, non_blocking=True)
 
@@ -998,6 +1016,8 @@ def main():
             "sharding": ("key-hash sharded, owner = Murmur3(key) % N, one shard of this size per GPU; "
                          + ("every batch routed over peer memory: keys stored into the owners' inboxes, "
                             "hit rows stored by the lookup kernel into the requester's buffer (NVLink)"
+                            + ("; %d workspaces in rotation, batch k + 1 routed while batch k is served"
+                               % args.lanes if pipelined else "")
                             if fused else
                             "every batch routed by NCCL all-to-all: keys out, rows and flags back"))
             if world > 1 else ("single table" if launched_world == 1 else

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kFindBlock, (FORM == 1 || FORM == 3 || FORM ==
 // while the next buckets are being probed -- lookup and transfer are one kernel.
 template <int VEC>
 __global__ void __launch_bounds__(kFindBlock)
-    find_routed_kernel(const TableView t, const uint32_t blocks_per_segment, const uint32_t world,
+    find_routed_kernel(const TableView t, const uint32_t world,
                        const uint32_t first_segment, const uint64_t segment_capacity, const uint64_t* __restrict__ inbox_keys,
                        const uint32_t* __restrict__ inbox_origin,
                        const uint64_t* __restrict__ inbox_counts, const PeerPtrs out_values,
@@ -178,14 +178,15 @@ __global__ void __launch_bounds__(kFindBlock)
   // The key counts are only known on the device, so the grid covers every
   // segment's full capacity and blocks beyond a segment's count leave at once.
   const ProbeLane pl = probe_lane();
-  // Owners walk the source ranks in a rotated order (rank r starts with r + 1),
-  // so at any moment the owners store into different requesters instead of
-  // all converging on the same GPU's ingress.
-  const uint32_t turn = blockIdx.x / blocks_per_segment;
+  // Consecutive blocks serve different source ranks (block b: the b % world-th
+  // rank after this one), so at every moment an owner stores into all
+  // requesters at once -- its own buffer included -- instead of saturating one
+  // NVLink destination while its HBM idles, and no requester's ingress has all
+  // owners converging on it.
+  const uint32_t turn = blockIdx.x % world;
   uint32_t seg = turn + first_segment;
   seg = seg >= world ? seg - world : seg;
-  const uint64_t base =
-      uint64_t(blockIdx.x - turn * blocks_per_segment) * kFindBlock + (threadIdx.x & ~31u);
+  const uint64_t base = uint64_t(blockIdx.x / world) * kFindBlock + (threadIdx.x & ~31u);
   const uint64_t count = inbox_counts[seg];
   if (base >= count) return;
   uint8_t* values_of = nullptr;
@@ -356,7 +357,7 @@ void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
   const uint64_t per_segment = (segment_capacity + kFindBlock - 1) / kFindBlock;
   auto kernel = fast_rows(t) ? find_routed_kernel<16> : find_routed_kernel<0>;
   kernel<<<static_cast<unsigned>(per_segment * world), kFindBlock, 0, stream>>>(
-      t, static_cast<uint32_t>(per_segment), world, (my_rank + 1) % world, segment_capacity,
+      t, world, (my_rank + 1) % world, segment_capacity,
       inbox_keys, inbox_origin,
       inbox_counts, out_values, out_founds);
 }

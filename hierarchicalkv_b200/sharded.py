@@ -240,20 +240,36 @@ class ShardedHashTable:
             sc_back = self._all_to_all(sc, route.recv_counts, route.send_counts)
             self.ops.scatter_rows(sc_back, where, scores)
 
-    def enable_fused_find(self, max_batch: int, dim: int, dtype: torch.dtype = torch.float32):
-        """Allocates the peer-visible inbox and result buffers find_fused needs."""
-        self.peer = PeerWorkspace(self.group, max_batch, dim, dtype)
+    def enable_fused_find(self, max_batch: int, dim: int, dtype: torch.dtype = torch.float32,
+                          lanes: int = 1):
+        """Allocates the peer-visible inbox and result buffers find_fused needs.
+        With ``lanes`` > 1 it allocates that many independent sets (each with its
+        own stream, flags and epoch) for find_fused_async, which rotates through
+        them so the routing of one batch overlaps the lookup of the previous one."""
+        self.lanes = [PeerWorkspace(self.group, max_batch, dim, dtype) for _ in range(max(1, lanes))]
+        self.lane_streams = [torch.cuda.Stream() for _ in self.lanes]
+        self.lane_events = [None for _ in self.lanes]
+        self._next_lane = 0
+        self.peer = self.lanes[0]
         return self.peer
+
+    def share_workspace(self, other: "ShardedHashTable") -> None:
+        """Uses the peer workspaces (and lane streams) `other` allocated: several
+        sharded tables of one process can serve their fused calls from one set."""
+        self.lanes, self.lane_streams = other.lanes, other.lane_streams
+        self.lane_events = other.lane_events
+        self._next_lane = 0
+        self.peer = other.peer
 
     # -- fused paths: routing, lookup / update and transfer without NCCL ----------
     def _chk_shard(self, rc: int) -> None:
         if rc:
             raise RuntimeError((self.ops.lib.hkv_shard_last_error() or b"").decode())
 
-    def _route_p2p(self, n, keys) -> None:
+    def _route_p2p(self, n, keys, w=None) -> None:
         """Groups the batch by owner and stores keys and batch indices straight
         into the owners' inboxes over NVLink."""
-        w = self.peer
+        w = w or self.peer
         if n > w.max_batch:
             raise ValueError("batch larger than the workspace")
         self._chk_shard(self.ops.lib.hkv_shard_route_keys_p2p(
@@ -261,33 +277,63 @@ class ShardedHashTable:
             ctypes.byref(w.peers["inbox_keys"]), ctypes.byref(w.peers["inbox_origin"]),
             ctypes.byref(w.peers["inbox_counts"]), w.scratch.data_ptr(), _stream_ptr()))
 
-    def _peer_barrier(self, max_polls: int) -> None:
-        w = self.peer
+    def _peer_barrier(self, max_polls: int, w=None) -> None:
+        w = w or self.peer
         w.epoch += 1
         self._chk_shard(self.ops.lib.hkv_shard_barrier(
             self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
             w.scratch[16:].data_ptr(), max_polls, _stream_ptr()))
 
-    def find_fused(self, n, keys, max_polls: int = 50_000_000):
+    def find_fused(self, n, keys, max_polls: int = 50_000_000, lane: int = 0):
         """HashTable::find over all shards with lookup and transfer fused: keys
         are grouped by owner and stored straight into the owners' inboxes, every
         owner runs ONE lookup kernel over what arrived and stores hit rows and
         found flags straight into the requesters' result buffers over NVLink.
         No NCCL call and no host synchronisation; two bounded peer barriers.
         Returns views (rows, found flags) of this rank's result buffers, valid
-        until the next call; rows of misses keep their previous content."""
-        w = self.peer
+        until the next call on the same lane; rows of misses keep their previous
+        content."""
+        w = self.lanes[lane]
         lib = self.ops.lib
-        self._route_p2p(n, keys)
-        self._peer_barrier(max_polls)
+        self._route_p2p(n, keys, w)
+        self._peer_barrier(max_polls, w)
         rc = lib.hkv_find_routed(self.local.handle, self.world, self.rank, w.max_batch,
                                  w.local["inbox_keys"], w.local["inbox_origin"],
                                  w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
                                  ctypes.byref(w.peers["out_founds"]), _stream_ptr())
         if rc:
             raise RuntimeError((lib.hkv_last_error() or b"").decode())
-        self._peer_barrier(max_polls)
+        self._peer_barrier(max_polls, w)
         return w.out_values[:n], w.out_founds[:n]
+
+    def find_fused_async(self, n, keys, max_polls: int = 50_000_000):
+        """find_fused on the next lane's own stream: returns (rows, found flags,
+        event) at once; the results are complete when the event has fired
+        (``torch.cuda.current_stream().wait_event(event)``).  Every rank must make
+        the same sequence of calls.  Consecutive calls use different lanes, so
+        the grouping, the key stores and the barriers of batch k + 1 run while
+        the owners still serve batch k.  To keep that overlap, issue batch k + 1
+        BEFORE waiting for batch k: each call first makes its lane wait for
+        everything already queued on the caller's stream (the producer of
+        ``keys``, and the consumer of the lane's previous results)."""
+        lane = self._next_lane
+        self._next_lane = (lane + 1) % len(self.lanes)
+        s = self.lane_streams[lane]
+        s.wait_stream(torch.cuda.current_stream())
+        keys.record_stream(s)
+        with torch.cuda.stream(s):
+            rows, founds = self.find_fused(n, keys, max_polls, lane)
+            done = torch.cuda.Event()
+            done.record(s)
+        self.lane_events[lane] = done
+        return rows, founds, done
+
+    def join_lanes(self) -> None:
+        """Makes the caller's stream wait for every lane's last find_fused_async."""
+        cur = torch.cuda.current_stream()
+        for e in self.lane_events:
+            if e is not None:
+                cur.wait_event(e)
 
     _ROUTED_OPS = {"insert_or_assign": 0, "find_or_insert": 1, "accum_or_assign": 2}
 

@@ -170,12 +170,40 @@ def _nccl_worker(rank, world, port, dim, cap):
         assert np.array_equal(got[ef].view(np.uint32), ev[ef].view(np.uint32))
         assert np.all(got[~ef] == -3.0)
         assert st.peer.status() == 0
+    # the same lookups through two workspaces in rotation: batch k + 1 is issued
+    # before batch k is waited for, and every batch still gets its own answers
+    stp = ShardedHashTable(st.local)
+    stp.enable_fused_find(max_batch=q.size, dim=dim, lanes=2)
+    batches = [np.roll(q, 131 * i)[: q.size - 64 * i] for i in range(5)]
+    dev_batches = [to_dev(b) for b in batches]
+    for w_ in stp.lanes:
+        w_.out_values.fill_(-3.0)
+    torch.cuda.synchronize()
+
+    def check(i, res):
+        rows, flags, done = res
+        torch.cuda.current_stream().wait_event(done)
+        got, gf = rows.cpu().numpy(), flags.cpu().numpy()
+        ev, ef, _ = glob.find(batches[i])
+        assert np.array_equal(gf, ef)
+        assert np.array_equal(got[ef].view(np.uint32), ev[ef].view(np.uint32))
+
+    prev = None
+    for i, b in enumerate(dev_batches):
+        res = stp.find_fused_async(batches[i].size, b)
+        if prev is not None:
+            check(i - 1, prev)
+        prev = res
+    check(len(batches) - 1, prev)
+    stp.join_lanes()
+    torch.cuda.synchronize()
+    assert all(w_.status() == 0 for w_ in stp.lanes)
     # fused update path on an LRU table: rows travel straight between the ranks' buffers
     t2 = hkv.HashTable(hkv.EvictStrategy.kLru)
     t2.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
                                  dim=dim))
     st2 = ShardedHashTable(t2)
-    st2.peer = st.peer                       # same workspace
+    st2.share_workspace(st)                  # same workspace
     w = st2.peer
     both = keys[30000:33000]                 # every rank sends the same keys: all of them collide
     own = keys[33000 + rank * 1500: 33000 + (rank + 1) * 1500]
