@@ -248,6 +248,9 @@ class ShardedHashTable:
         them so the routing of one batch overlaps the lookup of the previous one."""
         self.lanes = [PeerWorkspace(self.group, max_batch, dim, dtype) for _ in range(max(1, lanes))]
         self.lane_streams = [torch.cuda.Stream() for _ in self.lanes]
+        # routing and barriers of the next batch must not queue behind the blocks
+        # of the previous batch's lookup: they run on streams of higher priority
+        self.lane_streams_hi = [torch.cuda.Stream(priority=-1) for _ in self.lanes]
         self.lane_events = [None for _ in self.lanes]
         self._next_lane = 0
         self.peer = self.lanes[0]
@@ -257,6 +260,7 @@ class ShardedHashTable:
         """Uses the peer workspaces (and lane streams) `other` allocated: several
         sharded tables of one process can serve their fused calls from one set."""
         self.lanes, self.lane_streams = other.lanes, other.lane_streams
+        self.lane_streams_hi = other.lane_streams_hi
         self.lane_events = other.lane_events
         self._next_lane = 0
         self.peer = other.peer
@@ -307,7 +311,7 @@ class ShardedHashTable:
         return w.out_values[:n], w.out_founds[:n]
 
     def find_fused_async(self, n, keys, max_polls: int = 50_000_000):
-        """find_fused on the next lane's own stream: returns (rows, found flags,
+        """find_fused on the next lane's own streams: returns (rows, found flags,
         event) at once; the results are complete when the event has fired
         (``torch.cuda.current_stream().wait_event(event)``).  Every rank must make
         the same sequence of calls.  Consecutive calls use different lanes, so
@@ -318,13 +322,28 @@ class ShardedHashTable:
         ``keys``, and the consumer of the lane's previous results)."""
         lane = self._next_lane
         self._next_lane = (lane + 1) % len(self.lanes)
-        s = self.lane_streams[lane]
-        s.wait_stream(torch.cuda.current_stream())
-        keys.record_stream(s)
-        with torch.cuda.stream(s):
-            rows, founds = self.find_fused(n, keys, max_polls, lane)
+        w = self.lanes[lane]
+        lib = self.ops.lib
+        hi, lo = self.lane_streams_hi[lane], self.lane_streams[lane]
+        hi.wait_stream(torch.cuda.current_stream())
+        keys.record_stream(hi)
+        with torch.cuda.stream(hi):
+            self._route_p2p(n, keys, w)
+            self._peer_barrier(max_polls, w)
+        lo.wait_stream(hi)
+        with torch.cuda.stream(lo):
+            rc = lib.hkv_find_routed(self.local.handle, self.world, self.rank, w.max_batch,
+                                     w.local["inbox_keys"], w.local["inbox_origin"],
+                                     w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
+                                     ctypes.byref(w.peers["out_founds"]), _stream_ptr())
+            if rc:
+                raise RuntimeError((lib.hkv_last_error() or b"").decode())
+        hi.wait_stream(lo)
+        with torch.cuda.stream(hi):
+            self._peer_barrier(max_polls, w)
             done = torch.cuda.Event()
-            done.record(s)
+            done.record(hi)
+        rows, founds = w.out_values[:n], w.out_founds[:n]
         self.lane_events[lane] = done
         return rows, founds, done
 
