@@ -129,10 +129,21 @@ __global__ void __launch_bounds__(kBlock)
       key[q] = 0;
       owner[q] = 0;
       rank[q] = 0;
-      if (i < n) {
+      const bool have = i < n;
+      if (have) {
         key[q] = keys[i];
         owner[q] = owner_of(key[q], world);
-        rank[q] = atomicAdd(&local[owner[q]], 1u);
+      }
+      // one shared-memory atomic per owner and warp, not per key: with few
+      // ranks all keys of a tile would otherwise queue on a handful of counters
+      const uint32_t same = __match_any_sync(0xFFFFFFFFu, have ? owner[q] : kMaxWorld);
+      if (have) {
+        const uint32_t lane = threadIdx.x & 31u;
+        const uint32_t leader = __ffs(same) - 1;
+        uint32_t first = 0;
+        if (lane == leader) first = atomicAdd(&local[owner[q]], uint32_t(__popc(same)));
+        first = __shfl_sync(same, first, leader);
+        rank[q] = first + __popc(same & ((1u << lane) - 1u));
       }
     }
     __syncthreads();

@@ -260,6 +260,47 @@ def test_two_nccl_ranks_match_one_global_oracle():
     mp.spawn(_nccl_worker, args=(2, port, 8, 128 * 256), nprocs=2, join=True)
 
 
+@pytest.mark.parametrize("world,n", [(2, 100000), (8, 4097), (16, 33), (3, 1), (5, 0)])
+def test_route_keys_into_the_owners_inboxes(world, n):
+    """The sending side of the fused routing on one GPU: `world` inboxes in
+    this GPU's memory stand in for the peers'.  Segment `me` of owner r's inbox
+    must hold exactly the keys r owns, each with its batch index, and r's count
+    for `me` must say how many."""
+    import ctypes
+
+    from hierarchicalkv_b200.sharded import CudaOps, _PeerPtrs
+
+    lib = CudaOps().lib
+    me = world - 1
+    cap_seg = max(32, (n + 31) // 32 * 32)
+    keys = unique_keys(max(n, 1), seed=world * 1000 + n)[:n]
+    d_keys = to_dev(keys) if n else torch.zeros(1, dtype=torch.int64, device="cuda")
+    inbox_k = [torch.full((world * cap_seg,), -1, dtype=torch.int64, device="cuda") for _ in range(world)]
+    inbox_o = [torch.full((world * cap_seg,), -1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    inbox_c = [torch.full((16,), -1, dtype=torch.int64, device="cuda") for _ in range(world)]
+    pk, po, pc = _PeerPtrs(), _PeerPtrs(), _PeerPtrs()
+    for r in range(world):
+        pk.p[r], po.p[r], pc.p[r] = inbox_k[r].data_ptr(), inbox_o[r].data_ptr(), inbox_c[r].data_ptr()
+    cursors = torch.zeros(32, dtype=torch.int64, device="cuda")
+    for rep in range(2):                      # the cursors are reset by the call itself
+        rc = lib.hkv_shard_route_keys_p2p(n, d_keys.data_ptr(), world, me, cap_seg, ctypes.byref(pk),
+                                          ctypes.byref(po), ctypes.byref(pc), cursors.data_ptr(), None)
+        assert rc == 0, (lib.hkv_shard_last_error() or b"").decode()
+        torch.cuda.synchronize()
+        owner = (fmix64(keys) % np.uint64(world)).astype(np.int64) if n else np.zeros(0, dtype=np.int64)
+        for r in range(world):
+            want_idx = np.nonzero(owner == r)[0]
+            cnt = int(inbox_c[r][me].item())
+            assert cnt == want_idx.size
+            seg_k = to_np_u64(inbox_k[r][me * cap_seg: me * cap_seg + cnt])
+            seg_o = inbox_o[r][me * cap_seg: me * cap_seg + cnt].cpu().numpy().astype(np.int64)
+            assert np.array_equal(np.sort(seg_o), want_idx)          # every index once
+            assert np.array_equal(seg_k, keys[seg_o])                # next to its own key
+            # nothing outside this rank's segment was touched
+            rest = torch.cat([inbox_o[r][: me * cap_seg], inbox_o[r][me * cap_seg + cnt:]])
+            assert bool((rest == -1).all())
+
+
 def _routed_call(lib, table, op, world, my_rank, cap_seg, inbox_keys, inbox_origin, counts, bufs,
                  flags=None):
     import ctypes
