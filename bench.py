@@ -113,6 +113,10 @@ class ProductArm:
     def find_ptr(self, keys, ptrs, founds):
         self.t.find_ptr(keys.numel(), keys, ptrs, founds)
 
+    def find_host(self, host_keys, host_values, host_founds):
+        """Batch in pinned host memory: chunked copies and lookups that overlap."""
+        self.t.find_host(host_keys.numel(), host_keys, host_values, host_founds)
+
     def accum_or_assign(self, keys, deltas, flags):
         self.t.accum_or_assign(keys.numel(), keys, deltas, flags)
 
@@ -737,6 +741,9 @@ def main():
     ap.add_argument("--api-table", action="store_true",
                     help="instead of the JSON line of the headline workload: every API of the "
                          "reference's benchmark program at load factors 0.50 / 0.75 / 1.00")
+    ap.add_argument("--staged-e2e", action="store_true",
+                    help="end-to-end loop with the caller staging the batch (copy keys in, find, copy "
+                         "rows out) instead of the host-buffer entry point")
     ap.add_argument("--lanes", type=int, default=2,
                     help="N > 1: peer workspaces the fused find rotates through (1: no overlap of "
                          "one batch's routing with the previous batch's lookup)")
@@ -882,7 +889,12 @@ def main():
     h_founds = torch.empty(batch, dtype=torch.bool).pin_memory()
     d_keys = torch.empty(batch, dtype=torch.int64, device="cuda")
 
+    host_call = sharded is None and hasattr(arm, "find_host") and not args.staged_e2e
+
     def e2e_step(i):
+        if host_call:       # the library's own host-buffer entry point (chunked, overlapped)
+            arm.find_host(h_keys[i % n_query_sets], h_vals, h_founds)
+            return
         d_keys.copy_(h_keys[i % n_query_sets], non_blocking=True)
         do_find(d_keys, pipeline=False)     # the copies dominate: one lane, results read right away
         h_vals.copy_(out_vals, non_blocking=True)
@@ -895,6 +907,8 @@ def main():
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         e2e_ms = float(tms.item())
     assert bool(h_founds.all())
+    last_e2e = queries[(3 + e2e_steps - 1) % n_query_sets]
+    assert torch.equal(h_vals.cuda(), rows_for(last_e2e, dim)), "end-to-end find returned wrong rows"
     e2e_value = batch * e2e_steps * world / (e2e_ms / 1e3) / BINARY_BILLION
 
     # ---- the other operations of the workload (not part of `value`) -----------
@@ -1026,7 +1040,10 @@ def main():
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 4), "unit": "B-KV/s",
                 "h2d_bytes_per_step": batch * 8, "d2h_bytes_per_step": batch * row + batch,
-                "steps": e2e_steps},
+                "steps": e2e_steps,
+                "call": ("find_host: keys, rows and flags in pinned host memory, chunks staged on two "
+                         "alternating streams inside the call" if host_call else
+                         "copy keys to the device, find, copy rows and flags back (the caller stages)")},
         # N > 1: count, offsets and place kernels of the router, the lookup, three row scatters
         # fused: route, publish counts, barrier, lookup, barrier
         "gpu_launches": args.steps * ((5 if fused else arm.launches_per_find + 6) if world > 1

@@ -148,6 +148,20 @@ struct hkv_table {
   // capacity cannot double below max_capacity
   // (reach_max_capacity_, include/merlin_hashtable.cuh:1064, 3508-3538)
   std::atomic<bool> reach_max_capacity{true};
+  // hkv_find_host: two sets of device staging buffers and the two streams that
+  // alternate over the chunks of a host-resident batch; created on first use
+  struct HostStage {
+    std::mutex mu;
+    cudaStream_t stream[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaEvent_t start = nullptr;
+    uint64_t chunk = 0;        // keys per chunk
+    uint8_t* block = nullptr;  // one allocation, carved below
+    uint64_t* keys[2] = {nullptr, nullptr};
+    uint8_t* rows[2] = {nullptr, nullptr};
+    uint64_t* scores[2] = {nullptr, nullptr};
+    bool* founds[2] = {nullptr, nullptr};
+  } stage;
 };
 
 namespace {
@@ -713,6 +727,12 @@ int hkv_table_destroy(hkv_table* t) {
     if (t->d_scratch) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->d_scratch);
     if (t->view.values_hbm) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->view.values_hbm);
     if (t->host_rows) t->alloc.free(t->alloc.ctx, HKV_MEM_PINNED, t->host_rows);
+    if (t->stage.block) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->stage.block);
+    for (int i = 0; i < 2; ++i) {
+      if (t->stage.stream[i]) cudaStreamDestroy(t->stage.stream[i]);
+      if (t->stage.done[i]) cudaEventDestroy(t->stage.done[i]);
+    }
+    if (t->stage.start) cudaEventDestroy(t->stage.start);
     delete t;
   });
 }
@@ -943,6 +963,95 @@ int hkv_find(hkv_table* t, uint64_t n, const uint64_t* keys, void* values, bool*
     }
     ls.done();
     check_launch();
+  });
+}
+
+namespace {
+
+// Creates the staging state of hkv_find_host on first use.  A chunk carries
+// about 32 MiB of rows: large enough for the copy engines to run at the rate of
+// the host link, small enough that the first rows leave after a few dozen
+// microseconds of lookup.
+void prepare_stage(hkv_table* t) {
+  hkv_table::HostStage& st = t->stage;
+  if (st.block != nullptr) return;
+  const uint64_t row_bytes = t->view.row_bytes;
+  uint64_t chunk = (32ull << 20) / (row_bytes ? row_bytes : 1);
+  chunk = chunk > (1ull << 17) ? (1ull << 17) : chunk;
+  chunk = chunk < 4096 ? 4096 : chunk;
+  chunk &= ~uint64_t(255);
+  auto up = [](uint64_t x) { return (x + 255) / 256 * 256; };
+  const uint64_t per_set = up(chunk * 8) + up(chunk * row_bytes) + up(chunk * 8) + up(chunk);
+  void* block = nullptr;
+  if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &block, 2 * per_set, 0) != 0 || block == nullptr) {
+    cudaGetLastError();
+    throw HkvError{HKV_ERR_CUDA, "hkv_find_host: out of device memory for the staging buffers"};
+  }
+  for (int i = 0; i < 2; ++i) {
+    HKV_CUDA(cudaStreamCreateWithFlags(&st.stream[i], cudaStreamNonBlocking));
+    HKV_CUDA(cudaEventCreateWithFlags(&st.done[i], cudaEventDisableTiming));
+    uint8_t* at = static_cast<uint8_t*>(block) + i * per_set;
+    st.keys[i] = reinterpret_cast<uint64_t*>(at);
+    at += up(chunk * 8);
+    st.rows[i] = at;
+    at += up(chunk * row_bytes);
+    st.scores[i] = reinterpret_cast<uint64_t*>(at);
+    at += up(chunk * 8);
+    st.founds[i] = reinterpret_cast<bool*>(at);
+  }
+  HKV_CUDA(cudaEventCreateWithFlags(&st.start, cudaEventDisableTiming));
+  st.chunk = chunk;
+  st.block = static_cast<uint8_t*>(block);
+}
+
+}  // namespace
+
+int hkv_find_host(hkv_table* t, uint64_t n, const uint64_t* host_keys, void* host_values,
+                  bool* host_founds, uint64_t* host_scores, hkv_stream stream) {
+  return guarded([&] {
+    if (n == 0) return;
+    HKV_CHECK(host_keys != nullptr && host_values != nullptr && host_founds != nullptr,
+              "hkv_find_host: keys, values and founds must not be null");
+    HKV_CHECK(host_scores == nullptr || t->opt.score_size == 8,
+              "hkv_find_host: scores are returned for 64-bit scores only");
+    DeviceGuard dg(t->device);
+    cudaStream_t user = static_cast<cudaStream_t>(stream);
+    hkv_table::HostStage& st = t->stage;
+    std::lock_guard<std::mutex> hold(st.mu);   // one batch at a time owns the staging buffers
+    prepare_stage(t);
+    const uint64_t row_bytes = t->view.row_bytes;
+    // everything below starts after what the caller queued before the call ...
+    HKV_CUDA(cudaEventRecord(st.start, user));
+    for (int i = 0; i < 2; ++i) HKV_CUDA(cudaStreamWaitEvent(st.stream[i], st.start, 0));
+    uint64_t c = 0;
+    for (uint64_t off = 0; off < n; off += st.chunk, ++c) {
+      const int b = static_cast<int>(c & 1);
+      const uint64_t m = n - off < st.chunk ? n - off : st.chunk;
+      cudaStream_t cs = st.stream[b];
+      // keys in, lookup, rows out: on the chunk's stream; the other stream does
+      // the same for the neighbouring chunk, so one chunk's lookup and key copy
+      // run under the other's row copy and the host link never idles
+      HKV_CUDA(cudaMemcpyAsync(st.keys[b], host_keys + off, m * 8, cudaMemcpyHostToDevice, cs));
+      HKV_CUDA(cudaMemsetAsync(st.rows[b], 0, m * row_bytes, cs));   // rows of misses: zero
+      const int rc = hkv_find(t, m, st.keys[b], st.rows[b], st.founds[b],
+                              host_scores ? st.scores[b] : nullptr, cs);
+      if (rc != HKV_OK) throw HkvError{rc, g_last_error};
+      // flags and scores leave first and the rows last: a small copy queued
+      // behind the rows would wait for the NEXT chunk's rows on the shared
+      // copy engine, and this stream's next chunk would wait with it
+      HKV_CUDA(cudaMemcpyAsync(host_founds + off, st.founds[b], m, cudaMemcpyDeviceToHost, cs));
+      if (host_scores) {
+        HKV_CUDA(cudaMemcpyAsync(host_scores + off, st.scores[b], m * 8, cudaMemcpyDeviceToHost,
+                                 cs));
+      }
+      HKV_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(host_values) + off * row_bytes, st.rows[b],
+                               m * row_bytes, cudaMemcpyDeviceToHost, cs));
+    }
+    // ... and what the caller queues after it starts when both streams are done
+    for (int i = 0; i < 2; ++i) {
+      HKV_CUDA(cudaEventRecord(st.done[i], st.stream[i]));
+      HKV_CUDA(cudaStreamWaitEvent(user, st.done[i], 0));
+    }
   });
 }
 

@@ -144,6 +144,7 @@ _SIGNATURES = {
     "hkv_assign_scores": [_P, _U64, _P, _P, _P, _INT],
     "hkv_assign_values": [_P, _U64, _P, _P, _P, _INT],
     "hkv_find": [_P, _U64, _P, _P, _P, _P, _P],
+    "hkv_find_host": [_P, _U64, _P, _P, _P, _P, _P],
     "hkv_find_missed": [_P, _U64, _P, _P, _P, _P, _P, _P, _P],
     "hkv_find_ptr": [_P, _U64, _P, _P, _P, _P, _P, _INT],
     "hkv_find_and_update": [_P, _U64, _P, _P, _P, _P, _P, _INT],
@@ -397,6 +398,14 @@ class HashTable:
     # -- read-like ----------------------------------------------------------
     def find(self, n, keys, values, founds, scores=None, stream=None) -> None:
         self._call("hkv_find", n, _ptr(keys), _ptr(values), _ptr(founds), _ptr(scores),
+                   _stream(stream))
+
+    def find_host(self, n, keys, values, founds, scores=None, stream=None) -> None:
+        """find for a batch in host memory (CPU tensors, pinned for asynchronous
+        copies): chunks of the batch alternate over two internal streams, so the
+        key copies and lookups run under the row copies.  The host buffers are
+        complete once `stream` has passed the call; rows of misses are zero."""
+        self._call("hkv_find_host", n, _ptr(keys), _ptr(values), _ptr(founds), _ptr(scores),
                    _stream(stream))
 
     def find_missed(self, n, keys, values, missed_keys, missed_indices, missed_size,

@@ -205,6 +205,20 @@ HKV_API int hkv_assign_values(hkv_table* table, uint64_t n, const uint64_t* keys
 /* HashTable::find, include/merlin_hashtable.cuh:2464-2577 */
 HKV_API int hkv_find(hkv_table* table, uint64_t n, const uint64_t* keys, void* values,
                      bool* founds, uint64_t* scores, hkv_stream stream);
+/* HashTable::find, include/merlin_hashtable.cuh:2464-2577, for batches that live in HOST memory
+ * (the reference wants every batch buffer GPU-accessible, include/merlin_hashtable.cuh:216-221, and
+ * leaves the staging to the caller).  The batch is cut into chunks of about 32 MiB of rows that
+ * alternate over two internal streams and two sets of staging buffers: key copy, lookup and row
+ * copy of neighbouring chunks overlap, so the call runs at the rate of the host link.  All of it
+ * is ordered after what `stream` holds at the call and before what is queued on `stream`
+ * afterwards; the host buffers are complete once `stream` has reached that point.  Pinned
+ * host memory gives asynchronous copies, pageable memory works but blocks per chunk.  Rows of keys
+ * that are not in the table come back as zero bytes (hkv_find leaves them untouched).  Scores
+ * (optional) for tables with 64-bit scores.  Calls on one table take turns.  Not for use
+ * inside a stream capture. */
+HKV_API int hkv_find_host(hkv_table* table, uint64_t n, const uint64_t* host_keys,
+                          void* host_values, bool* host_founds, uint64_t* host_scores,
+                          hkv_stream stream);
 /* HashTable::find (missed-keys form), include/merlin_hashtable.cuh:2600-2705 */
 HKV_API int hkv_find_missed(hkv_table* table, uint64_t n, const uint64_t* keys, void* values,
                             uint64_t* missed_keys, int* missed_indices, int* missed_size,

@@ -603,6 +603,19 @@ class HashTable : public HashTableBase<K, V, S> {
     detail::rethrow(hkv_find(table_, n, u(keys), values, founds, w(scores), stream));
   }
 
+  /**
+   * @brief find for a batch that lives in host memory (not in the reference,
+   * whose batch buffers must be GPU-accessible): the batch is staged through
+   * the device in chunks whose copies and lookups overlap.  `keys`, `values`,
+   * `founds` (and `scores`, 64-bit scores only) are host pointers, pinned for
+   * asynchronous copies; they are complete once `stream` has passed the call.
+   * Rows of keys that are not in the table are zero-filled.
+   */
+  void find_host(const size_type n, const key_type* keys, value_type* values, bool* founds,
+                 score_type* scores = nullptr, cudaStream_t stream = 0) const {
+    detail::rethrow(hkv_find_host(table_, n, u(keys), values, founds, w(scores), stream));
+  }
+
   void find(const size_type n, const key_type* keys, value_type* values, key_type* missed_keys,
             int* missed_indices, int* missed_size, score_type* scores = nullptr,
             cudaStream_t stream = 0) const override {

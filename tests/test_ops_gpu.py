@@ -895,3 +895,49 @@ def test_bounded_wait_on_a_slot_that_stays_locked():
     assert t.contains(late).all() and t.contains(held).all()
     assert t.t.device_status() == 0
     t.close()
+
+
+@pytest.mark.parametrize("dim,n,pinned", [(8, 300_000, True), (64, 140_001, True), (8, 5000, False),
+                                          (200, 9000, True)])
+def test_find_host_matches_find(dim, n, pinned):
+    """hkv_find_host: a batch in host memory goes through the device in chunks
+    on two alternating streams; found flags, rows and scores are those of find
+    (the CPU oracle's), rows of misses are zero, ragged last chunks included."""
+    import torch
+
+    cap = 1 << 19
+    p = ProductTable(cap, dim, CUSTOMIZED)
+    o = OracleTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(n + n // 3, seed=dim * 7 + n)
+    present = keys[:n]
+    sc = np.arange(1, n + 1, dtype=np.uint64) * np.uint64(3)
+    for x in (p, o):
+        x.insert_or_assign(present, values_for(present, dim), sc)
+    rng = np.random.default_rng(5)
+    q = keys[rng.permutation(keys.size)]           # a quarter of them are misses
+    want_v, want_f, want_s = o.find(q)
+
+    def host(t):
+        return t.pin_memory() if pinned else t
+
+    hk = host(torch.from_numpy(q.view(np.int64).copy()))
+    hv = host(torch.full((q.size, dim), 7.0, dtype=torch.float32))
+    hf = host(torch.zeros(q.size, dtype=torch.bool))
+    hs = host(torch.zeros(q.size, dtype=torch.int64))
+    for rep in range(2):                            # the staging buffers are reused
+        p.t.find_host(q.size, hk, hv, hf, hs)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(hf.numpy(), want_f)
+        got = hv.numpy()
+        np.testing.assert_array_equal(got[want_f], want_v[want_f])
+        assert np.all(got[~want_f] == 0.0)
+        np.testing.assert_array_equal(hs.numpy().view(np.uint64)[want_f], want_s[want_f])
+        hv.fill_(7.0)
+    # without scores, a short batch and an empty one
+    hv.fill_(7.0)
+    p.t.find_host(100, hk, hv, hf)
+    p.t.find_host(0, hk, hv, hf)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(hf.numpy()[:100], want_f[:100])
+    assert np.all(hv.numpy()[100:] == 7.0)
+    p.close()
