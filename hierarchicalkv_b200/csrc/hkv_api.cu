@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <condition_variable>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -138,8 +139,13 @@ struct hkv_table {
   bool own_allocator = true;
   std::atomic<uint64_t> global_epoch{hkv::kIgnoredEpoch};
   // counters for size / count overloads: an allocation of their own, so that a
-  // doubling of the table in the middle of a call does not move them
+  // doubling of the table in the middle of a call does not move them.  Readers
+  // on different streams overlap, so every call that returns a count leases a
+  // counter of its own (CounterLease) until its stream has been synchronised.
   unsigned long long* d_scratch = nullptr;
+  std::mutex counter_mu;
+  std::condition_variable counter_cv;
+  uint64_t counter_free = ~0ull;  // bit k set: counter k is free
   StreamGroupLock lock;
   int device = 0;
   void* meta_block = nullptr;  // digests + keys + scores + sizes + status
@@ -194,6 +200,34 @@ struct DeviceGuard {
   ~DeviceGuard() {
     if (prev >= 0) cudaSetDevice(prev);
   }
+};
+
+// One of the table's 64 device counters, held by one call from its memset to
+// the end of the stream synchronisation that reads it back.  A 65th concurrent
+// call waits for a counter to come back.
+constexpr int kCounters = 64;
+class CounterLease {
+ public:
+  explicit CounterLease(hkv_table* t) : t_(t) {
+    std::unique_lock<std::mutex> hold(t->counter_mu);
+    t->counter_cv.wait(hold, [&] { return t->counter_free != 0; });
+    index_ = __builtin_ctzll(t->counter_free);
+    t->counter_free &= ~(1ull << index_);
+  }
+  CounterLease(const CounterLease&) = delete;
+  CounterLease& operator=(const CounterLease&) = delete;
+  ~CounterLease() {
+    {
+      std::lock_guard<std::mutex> hold(t_->counter_mu);
+      t_->counter_free |= 1ull << index_;
+    }
+    t_->counter_cv.notify_one();
+  }
+  unsigned long long* get() const { return t_->d_scratch + index_; }
+
+ private:
+  hkv_table* t_;
+  int index_;
 };
 
 struct LockScope {
@@ -507,11 +541,11 @@ uint64_t promote_hot_buckets(hkv_table* t, cudaStream_t s) {
 // fast_load_factor, include/merlin_hashtable.cuh:3796-3828: the load the table
 // would have after `delta` more keys, estimated from the first 1024 buckets.
 float fast_load_factor(hkv_table* t, uint64_t delta, cudaStream_t s) {
-  unsigned long long* ctr = nullptr;
+  CounterLease lease(t);
+  unsigned long long* ctr = lease.get();
   uint64_t sampled = 0, capacity = 0;
   {
     LockScope ls(t, kReader, s);
-    ctr = t->d_scratch + 5;
     sampled = t->view.buckets < 1024 ? t->view.buckets : 1024;
     capacity = t->view.capacity;
     HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
@@ -703,12 +737,13 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
       t->meta_block = planes.meta_block;
       t->host_rows = planes.host_rows;
       void* scratch = nullptr;
-      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &scratch, 256, 0) != 0 || scratch == nullptr) {
+      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &scratch, kCounters * 8, 0) != 0 ||
+          scratch == nullptr) {
         cudaGetLastError();
         throw HkvError{HKV_ERR_CUDA, "device allocation of the counters failed"};
       }
       t->d_scratch = static_cast<unsigned long long*>(scratch);
-      HKV_CUDA(cudaMemset(scratch, 0, 256));
+      HKV_CUDA(cudaMemset(scratch, 0, kCounters * 8));
       HKV_CUDA(cudaDeviceSynchronize());
     } catch (...) {
       hkv_table_destroy(t);
@@ -798,7 +833,8 @@ int hkv_insert_and_evict_count(hkv_table* t, uint64_t n, const uint64_t* keys, c
     if (n == 0) return;
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    unsigned long long* ctr = t->d_scratch + 1;
+    CounterLease lease(t);
+    unsigned long long* ctr = lease.get();
     HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
     int rc = hkv_insert_and_evict(t, n, keys, values, scores, evicted_keys, evicted_values,
                                   evicted_scores, reinterpret_cast<uint64_t*>(ctr), stream,
@@ -1209,7 +1245,8 @@ int hkv_erase_if(hkv_table* t, int predicate, uint64_t pattern, uint64_t thresho
     if (predicate < HKV_PRED_ALL || predicate > HKV_PRED_SCORE_LESS_EQ) {
       throw HkvError{HKV_ERR_INVALID_ARG, "unknown predicate"};
     }
-    unsigned long long* ctr = t->d_scratch + 4;
+    CounterLease lease(t);
+    unsigned long long* ctr = lease.get();
     {
       LockScope ls(t, kInserter, s);
       HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));
@@ -1239,17 +1276,22 @@ int hkv_export_batch_if(hkv_table* t, int predicate, uint64_t pattern, uint64_t 
                         uint64_t n, uint64_t offset, uint64_t* d_counter, uint64_t* keys,
                         void* values, uint64_t* scores, hkv_stream stream) {
   return guarded([&] {
-    Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (predicate < HKV_PRED_ALL || predicate > HKV_PRED_SCORE_LESS_EQ) {
       throw HkvError{HKV_ERR_INVALID_ARG, "unknown predicate"};
     }
+    // The window is clamped before anything is sized by it: "export everything"
+    // callers pass a huge n.  The capacity read here can only be smaller than
+    // the one the kernel sees (tables never shrink).
+    {
+      const uint64_t capacity = t->view.capacity;
+      n = offset < capacity ? (n < capacity - offset ? n : capacity - offset) : 0;
+    }
+    Scores scores_w(t, scores, n, stream, true);
     LockScope ls(t, kReader, s);
     HKV_CUDA(cudaMemsetAsync(d_counter, 0, sizeof(uint64_t), s));
-    if (offset < t->view.capacity) {
-      const uint64_t left = t->view.capacity - offset;
-      if (n > left) n = left;
+    if (n > 0 && offset < t->view.capacity) {
       hkv::launch_export(view_for(t, values), predicate, pattern, threshold, n, offset,
                          reinterpret_cast<unsigned long long*>(d_counter), keys, values, scores_w.get(),
                          s);
@@ -1270,7 +1312,8 @@ int hkv_export_batch_count(hkv_table* t, uint64_t n, uint64_t offset, uint64_t* 
   return guarded([&] {
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    unsigned long long* ctr = t->d_scratch + 2;
+    CounterLease lease(t);
+    unsigned long long* ctr = lease.get();
     int rc = hkv_export_batch(t, n, offset, reinterpret_cast<uint64_t*>(ctr), keys, values,
                               scores, stream);
     if (rc != HKV_OK) throw HkvError{rc, g_last_error};
@@ -1302,7 +1345,8 @@ int hkv_size(hkv_table* t, hkv_stream stream, uint64_t* size) {
   return guarded([&] {
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    unsigned long long* ctr = t->d_scratch;
+    CounterLease lease(t);
+    unsigned long long* ctr = lease.get();
     {
       LockScope ls(t, kReader, s);
       HKV_CUDA(cudaMemsetAsync(ctr, 0, sizeof(*ctr), s));

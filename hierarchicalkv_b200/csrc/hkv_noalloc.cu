@@ -8,7 +8,9 @@
 // regular hkv_size keeps its partial result in scratch memory that belongs to
 // the table; this variant keeps its partial sums in a fixed array that is part
 // of the library image, so the call itself never asks CUDA (or any library
-// that allocates, torch included) for memory.
+// that allocates, torch included) for device memory.  On the host side the
+// table's API lock may create one CUDA event the first time it sees a stream,
+// and a failing call builds its error message as a std::string.
 //
 // The price is a fixed ceiling: the array has room for one partial sum per
 // 1024 buckets of a table with at most kNoAllocMaxBuckets buckets.  Every GPU
@@ -92,31 +94,42 @@ int hkv_size_no_alloc(hkv_table* table, hkv_stream stream, uint64_t* size) {
   if (table == nullptr || size == nullptr) {
     return fail(HKV_ERR_INVALID_ARG, "hkv_size_no_alloc: table and size must not be null");
   }
+  // The reader lock comes first: a doubling of the table on another thread
+  // replaces (and frees) the planes the view points at, and it cannot run
+  // between hkv_external_begin and hkv_external_end.
+  if (hkv_external_begin(table, 0, stream) != HKV_OK) {
+    return fail(HKV_ERR_RUNTIME, "hkv_size_no_alloc: cannot join the table's readers");
+  }
+  int rc = HKV_OK;
+  int previous = -1;
+  int device = -1;
+  unsigned long long* scratch = nullptr;
   hkv_table_view view{};
   if (hkv_get_view(table, &view) != HKV_OK) {
-    return fail(HKV_ERR_RUNTIME, "hkv_size_no_alloc: cannot read the table's view");
+    rc = fail(HKV_ERR_RUNTIME, "hkv_size_no_alloc: cannot read the table's view");
+  } else if (view.buckets > kNoAllocMaxBuckets) {
+    rc = fail(HKV_ERR_INVALID_ARG,
+              "hkv_size_no_alloc: the table has " + std::to_string(view.buckets) +
+                  " buckets, the fixed scratch array serves at most " +
+                  std::to_string(kNoAllocMaxBuckets) + "; use hkv_size");
   }
-  if (view.buckets > kNoAllocMaxBuckets) {
-    return fail(HKV_ERR_INVALID_ARG,
-                "hkv_size_no_alloc: the table has " + std::to_string(view.buckets) +
-                    " buckets, the fixed scratch array serves at most " +
-                    std::to_string(kNoAllocMaxBuckets) + "; use hkv_size");
+  cudaError_t e = cudaSuccess;
+  if (rc == HKV_OK) {
+    cudaPointerAttributes attr{};
+    e = cudaPointerGetAttributes(&attr, view.bucket_sizes);
+    if (e != cudaSuccess || attr.device < 0 || attr.device >= kMaxDevices) {
+      cudaGetLastError();
+      rc = fail(HKV_ERR_CUDA, "hkv_size_no_alloc: cannot tell which device owns the table");
+    } else {
+      device = attr.device;
+      cudaGetDevice(&previous);
+      if (previous != device) cudaSetDevice(device);
+    }
   }
-  cudaPointerAttributes attr{};
-  cudaError_t e = cudaPointerGetAttributes(&attr, view.bucket_sizes);
-  if (e != cudaSuccess || attr.device < 0 || attr.device >= kMaxDevices) {
-    cudaGetLastError();
-    return fail(HKV_ERR_CUDA, "hkv_size_no_alloc: cannot tell which device owns the table");
-  }
-  int previous = -1;
-  cudaGetDevice(&previous);
-  if (previous != attr.device) cudaSetDevice(attr.device);
-  int rc = HKV_OK;
-  unsigned long long* scratch = nullptr;
-  {
+  if (rc == HKV_OK) {
     // first call on this device: resolve the array's device address
     std::lock_guard<std::mutex> guard(g_setup_mutex);
-    if (g_scratch_addr[attr.device] == nullptr) {
+    if (g_scratch_addr[device] == nullptr) {
       void* p = nullptr;
       e = cudaGetSymbolAddress(&p, g_size_scratch);
       if (e != cudaSuccess || p == nullptr) {
@@ -124,24 +137,30 @@ int hkv_size_no_alloc(hkv_table* table, hkv_stream stream, uint64_t* size) {
         rc = fail(HKV_ERR_CUDA, std::string("hkv_size_no_alloc: cudaGetSymbolAddress: ") +
                                     cudaGetErrorString(e));
       } else {
-        g_scratch_addr[attr.device] = static_cast<unsigned long long*>(p);
+        g_scratch_addr[device] = static_cast<unsigned long long*>(p);
       }
     }
-    scratch = g_scratch_addr[attr.device];
+    scratch = g_scratch_addr[device];
   }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (rc == HKV_OK) {
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int blocks = static_cast<int>((view.buckets + kBucketsPerBlock - 1) / kBucketsPerBlock);
-    unsigned long long host_total = 0;
-    hkv_external_begin(table, 0, stream);  // a reader, like hkv_size
     size_partials_kernel<<<blocks, 256, 0, s>>>(view.bucket_sizes, view.buckets, scratch);
     size_total_kernel<<<1, 256, 0, s>>>(scratch, blocks, scratch + kNoAllocMaxBlocks);
     e = cudaGetLastError();
-    hkv_external_end(table, 0, stream);
-    if (e == cudaSuccess) {
-      e = cudaMemcpyAsync(&host_total, scratch + kNoAllocMaxBlocks, sizeof(host_total),
-                          cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) {
+      rc = fail(HKV_ERR_CUDA, std::string("hkv_size_no_alloc: launch: ") + cudaGetErrorString(e));
     }
+  }
+  // every path leaves the readers again; the kernels above are ordered before
+  // whatever an inserter enqueues afterwards
+  if (hkv_external_end(table, 0, stream) != HKV_OK && rc == HKV_OK) {
+    rc = fail(HKV_ERR_RUNTIME, "hkv_size_no_alloc: cannot leave the table's readers");
+  }
+  if (rc == HKV_OK) {
+    unsigned long long host_total = 0;
+    e = cudaMemcpyAsync(&host_total, scratch + kNoAllocMaxBlocks, sizeof(host_total),
+                        cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) {
       rc = fail(HKV_ERR_CUDA, std::string("hkv_size_no_alloc: ") + cudaGetErrorString(e));
@@ -149,7 +168,7 @@ int hkv_size_no_alloc(hkv_table* table, hkv_stream stream, uint64_t* size) {
       *size = host_total;
     }
   }
-  if (previous >= 0 && previous != attr.device) cudaSetDevice(previous);
+  if (previous >= 0 && previous != device) cudaSetDevice(previous);
   return rc;
 }
 

@@ -275,8 +275,12 @@ HKV_API uint64_t hkv_max_bucket_size(const hkv_table* table);
  * allocation, monitoring threads that must not cause the device-wide
  * synchronisation an allocation implies).  The partial sums live in a fixed
  * array inside the library image instead of scratch memory obtained at run
- * time, so the call issues no cudaMalloc / cudaFree and calls no allocating
- * library routine.  Limits and rules:
+ * time, so the call obtains no device memory: no cudaMalloc / cudaFree, no
+ * stream-ordered allocation, no library routine that allocates on the device.
+ * (Host side, two small things remain: with api_lock on, the first call that
+ * uses a new stream makes the table's lock create one CUDA event for that
+ * stream, and a failing call builds its error message as a string.)  Limits
+ * and rules:
  *   - tables of at most 4,194,304 buckets (2^29 slots); larger ones are
  *     rejected with HKV_ERR_INVALID_ARG -- use hkv_size for them;
  *   - every GPU that loads the library holds the array (about 32 KiB) until
