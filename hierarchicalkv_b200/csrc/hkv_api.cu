@@ -148,7 +148,7 @@ struct hkv_table {
   uint64_t counter_free = ~0ull;  // bit k set: counter k is free
   StreamGroupLock lock;
   int device = 0;
-  void* meta_block = nullptr;  // digests + keys + scores + sizes + status
+  void* meta_block = nullptr;  // digests + slot lines (keys, scores) + sizes + status
   void* host_rows = nullptr;   // host address of the pinned value rows
   // reserve() and the automatic growth of the insert-like calls stop once the
   // capacity cannot double below max_capacity
@@ -403,8 +403,8 @@ hkv::MutateArgs base_args(hkv_table* t, uint64_t n, const uint64_t* keys, const 
   return a;
 }
 
-// The planes of one table size: a metadata block (digests | keys | scores |
-// bucket sizes | status) and the value rows, whole buckets in HBM while
+// The planes of one table size: a metadata block (digests | slot lines of keys
+// and scores | bucket sizes | status) and the value rows, whole buckets in HBM while
 // max_hbm_for_vectors lasts and the rest in mapped pinned host memory (a static
 // split by bucket index, as include/merlin/core_kernels.cuh:204-232 does per
 // slice).
@@ -434,9 +434,8 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
   try {
     auto align256 = [](uint64_t x) { return (x + 255) & ~255ull; };
     const uint64_t off_digests = 0;
-    const uint64_t off_keys = align256(off_digests + capacity);
-    const uint64_t off_scores = align256(off_keys + capacity * 8);
-    const uint64_t off_sizes = align256(off_scores + capacity * 8);
+    const uint64_t off_lines = align256(off_digests + capacity);
+    const uint64_t off_sizes = align256(off_lines + capacity * 16);
     const uint64_t off_status = align256(off_sizes + buckets * 4);
     uint64_t hbm_buckets = t->opt.max_hbm_for_vectors / (row_bytes * hkv::kBucketSlots);
     if (hbm_buckets > buckets) hbm_buckets = buckets;
@@ -452,8 +451,7 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
     }
     uint8_t* mb = static_cast<uint8_t*>(p.meta_block);
     v.digests = mb + off_digests;
-    v.keys = reinterpret_cast<uint64_t*>(mb + off_keys);
-    v.scores = reinterpret_cast<uint64_t*>(mb + off_scores);
+    v.slot_lines = reinterpret_cast<uint64_t*>(mb + off_lines);
     v.bucket_sizes = reinterpret_cast<int32_t*>(mb + off_sizes);
     v.status = reinterpret_cast<uint32_t*>(mb + off_status);
     HKV_CUDA(cudaMemsetAsync(mb + off_status, 0, 256, stream));
@@ -1414,8 +1412,8 @@ int hkv_get_view(const hkv_table* t, hkv_table_view* view) {
   return guarded([&] {
     const hkv::TableView& v = t->view;
     view->digests = v.digests;
-    view->keys = v.keys;
-    view->scores = v.scores;
+    view->keys = v.slot_lines;
+    view->scores = v.slot_lines + hkv::kLineSlots;
     view->values_hbm = v.values_hbm;
     view->values_host = v.values_host;
     view->bucket_sizes = v.bucket_sizes;

@@ -58,7 +58,7 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
     first_key[j] = 0;
     if (cand[j]) {
       const uint32_t pos = pl.sub * 16u + (__ffs(cand[j]) - 1);
-      first_key[j] = ld_meta_u64(t.keys + (uint64_t(bkt[j]) << 7) + pos);
+      first_key[j] = ld_meta_u64(key_ptr(t, (uint64_t(bkt[j]) << 7) + pos));
     }
   }
   uint32_t my_slot = kNoSlot;
@@ -77,7 +77,7 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
         while (m) {
           pos = pl.sub * 16u + (__ffs(m) - 1);
           m &= m - 1;
-          if (ld_meta_u64(t.keys + (uint64_t(bkt[j]) << 7) + pos) == want) {
+          if (ld_meta_u64(key_ptr(t, (uint64_t(bkt[j]) << 7) + pos)) == want) {
             hit_slot = (bkt[j] << 7) + pos;
             break;
           }
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kFindBlock, (FORM == 1 || FORM == 3 || FORM ==
   if (i < n) {
     if (FORM != 2) founds[i] = found;
     if (FORM == 1) ptrs[i] = found ? row_ptr(t, slot) : nullptr;
-    if (FORM != 3 && scores != nullptr && found) scores[i] = t.scores[slot];
+    if (FORM != 3 && scores != nullptr && found) scores[i] = *score_ptr(t, slot);
     if (FORM == 4) {
       // where the row lives (kNoSlot sorts behind every real place)
       slot_out[i] = found ? static_cast<uint32_t>(row_slot(t, slot)) : kNoSlot;
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(kFindBlock)
   const bool found = slot != kNoSlot;
   if (i < n) {
     founds[i] = found;
-    if (scores != nullptr && found) scores[i] = t.scores[slot];
+    if (scores != nullptr && found) scores[i] = *score_ptr(t, slot);
   }
   if (values != nullptr) warp_move_rows<0>(t, values + base * t.row_bytes, slot, pl.lane);
 }

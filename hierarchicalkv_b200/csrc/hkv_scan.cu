@@ -55,8 +55,8 @@ __global__ void __launch_bounds__(kScanBlock)
     uint64_t score = 0;
     bool live = false;
     if (rel < n) {
-      key = __ldcs(t.keys + slot);
-      score = __ldcs(t.scores + slot);
+      key = __ldcs(key_ptr(t, slot));
+      score = __ldcs(score_ptr(t, slot));
       live = keep(t, pred, key, score, pattern, threshold);
     }
     const uint32_t votes = __ballot_sync(0xFFFFFFFFu, live);
@@ -95,8 +95,8 @@ __global__ void __launch_bounds__(kScanBlock)
   unsigned long long local = 0;
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < t.capacity;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    const uint64_t key = __ldcs(t.keys + slot);
-    const uint64_t score = __ldcs(t.scores + slot);
+    const uint64_t key = __ldcs(key_ptr(t, slot));
+    const uint64_t score = __ldcs(score_ptr(t, slot));
     local += keep(t, pred, key, score, pattern, threshold) ? 1 : 0;
   }
   for (int o = 16; o > 0; o >>= 1) local += __shfl_down_sync(0xFFFFFFFFu, local, o);
@@ -112,12 +112,12 @@ __global__ void __launch_bounds__(kScanBlock)
   unsigned long long local = 0;
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < t.capacity;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    const uint64_t key = t.keys[slot];
-    const uint64_t score = t.scores[slot];
+    const uint64_t key = *key_ptr(t, slot);
+    const uint64_t score = *score_ptr(t, slot);
     if (keep(t, pred, key, score, pattern, threshold)) {
-      t.keys[slot] = t.reclaim_key;
+      *key_ptr(t, slot) = t.reclaim_key;
       t.digests[slot] = static_cast<uint8_t>(t.reclaim_digest);
-      t.scores[slot] = 0;
+      *score_ptr(t, slot) = 0;
       atomicSub(t.bucket_sizes + (slot >> 7), 1);
       ++local;
     }
@@ -139,18 +139,18 @@ __global__ void __launch_bounds__(kScanBlock)
 }
 
 __global__ void __launch_bounds__(kScanBlock) clear_kernel(const TableView t) {
-  // one thread per 16 slots: a 16-byte digest store, 8 key and 8 score pairs
+  // one thread per 16 slots: a 16-byte digest store and two slot lines
   const uint64_t groups = t.capacity / 16;
   for (uint64_t g = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < groups;
        g += uint64_t(gridDim.x) * blockDim.x) {
     const uint32_t d = t.empty_digest4;
     reinterpret_cast<uint4*>(t.digests)[g] = make_uint4(d, d, d, d);
-    ulonglong2* k = reinterpret_cast<ulonglong2*>(t.keys + g * 16);
-    ulonglong2* s = reinterpret_cast<ulonglong2*>(t.scores + g * 16);
+    // slots 16g .. 16g+15 are two slot lines: 8 keys, 8 scores, 8 keys, 8 scores
+    ulonglong2* w = reinterpret_cast<ulonglong2*>(t.slot_lines + g * 32);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      k[q] = make_ulonglong2(t.empty_key, t.empty_key);
-      s[q] = make_ulonglong2(0ull, 0ull);
+    for (int q = 0; q < 16; ++q) {
+      const bool key_half = ((q >> 2) & 1) == 0;
+      w[q] = key_half ? make_ulonglong2(t.empty_key, t.empty_key) : make_ulonglong2(0ull, 0ull);
     }
     if ((g & 7u) == 0) t.bucket_sizes[g >> 3] = 0;
   }
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(kRehashBlock)
   const uint32_t below = (1u << lane) - 1u;
   for (uint64_t b = blockIdx.x; b < src.buckets; b += gridDim.x) {
     const uint64_t slot = b * kBucketSlots + threadIdx.x;
-    const uint64_t key = src.keys[slot];
+    const uint64_t key = *key_ptr(src, slot);
     const bool live = !is_reserved(src, key);
     const Address a = locate(dst, key);
     const bool high = live && a.bucket != b;
@@ -191,9 +191,9 @@ __global__ void __launch_bounds__(kRehashBlock)
     uint64_t to = 0;
     if (live) {
       to = a.bucket * kBucketSlots + rank;
-      dst.keys[to] = key;
+      *key_ptr(dst, to) = key;
       dst.digests[to] = static_cast<uint8_t>(a.digest);
-      dst.scores[to] = src.scores[slot];
+      *score_ptr(dst, to) = *score_ptr(src, slot);
     }
     if (threadIdx.x < 2) {
       uint32_t total = 0;

@@ -137,12 +137,24 @@ __device__ __forceinline__ bool hit_score_assign(int strategy, const uint64_t* s
   }
 }
 
-__device__ __forceinline__ void ld_scores16(const uint64_t* p, uint64_t (&s)[16]) {
+// Score scan of one bucket by the 8 lanes of a group.  A bucket's scores are
+// the second halves (64 bytes) of its 16 slot lines.  In step q the lanes 0-3
+// of the group read the score half of line 2q and the lanes 4-7 that of line
+// 2q + 1, 16 bytes each, so every load instruction of a group covers two
+// 64-byte segments completely.  A lane ends up with the 16 scores
+//   s[2q + e] = score of bucket position scan_pos(sub, 2q + e).
+__device__ __forceinline__ uint32_t scan_pos(uint32_t sub, uint32_t b) {
+  return ((b & ~1u) + (sub >> 2)) * kLineSlots + (sub & 3u) * 2u + (b & 1u);
+}
+
+__device__ __forceinline__ void ld_scores16(const TableView& t, uint64_t bucket, uint32_t sub,
+                                            uint64_t (&s)[16]) {
+  const uint64_t* mine = score_ptr(t, (bucket << 7) + (sub >> 2) * kLineSlots) + (sub & 3u) * 2u;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];"
                  : "=l"(s[2 * q]), "=l"(s[2 * q + 1])
-                 : "l"(p + 2 * q)
+                 : "l"(mine + q * 32)
                  : "memory");
   }
 }
@@ -173,7 +185,9 @@ __device__ __forceinline__ constexpr bool op_writes_row_on_insert(int op) {
 }
 
 // Minimum score of a full bucket and its first position, computed by the 8
-// lanes of a group from one coalesced 1-KiB read of the score line.
+// lanes of a group from the bucket's 1 KiB of scores.  Within a lane the
+// positions grow with the index, so the first minimum in the lane is the one
+// at the lowest position; across lanes the lowest position wins.
 __device__ __forceinline__ void lane_min16(const uint64_t (&s)[16], uint64_t* ms, uint32_t* mp) {
   *ms = s[0];
   *mp = 0;
@@ -192,7 +206,7 @@ __device__ __forceinline__ void group_reduce_min(uint32_t gmask, uint32_t sub, u
   const uint32_t ghi = __reduce_min_sync(gmask, hi);
   const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
   const uint32_t glo = __reduce_min_sync(gmask, lo);
-  const uint32_t cand = (hi == ghi && lo == glo) ? sub * 16u + mp : 255u;
+  const uint32_t cand = (hi == ghi && lo == glo) ? scan_pos(sub, mp) : 255u;
   *gpos = __reduce_min_sync(gmask, cand);
   *gmin = (uint64_t(ghi) << 32) | glo;
 }
@@ -200,7 +214,7 @@ __device__ __forceinline__ void group_reduce_min(uint32_t gmask, uint32_t sub, u
 __device__ __forceinline__ void group_min_score(const TableView& t, const ProbeLane& pl,
                                                 uint32_t bucket, uint64_t* gmin, uint32_t* gpos) {
   uint64_t s[16];
-  ld_scores16(t.scores + (uint64_t(bucket) << 7) + pl.sub * 16u, s);
+  ld_scores16(t, bucket, pl.sub, s);
   uint64_t ms;
   uint32_t mp;
   lane_min16(s, &ms, &mp);
@@ -355,9 +369,13 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
         const uint32_t cand = match16(dg[j], replicate4(tgt));
         masks[j] = cand | (match16(dg[j], t.empty_digest4) << 16);
         if (cand) {
-          uint64_t* kp = t.keys + (uint64_t(b) << 7) + pl.sub * 16u + (__ffs(cand) - 1);
+          uint64_t* kp = key_ptr(t, (uint64_t(b) << 7) + pl.sub * 16u + (__ffs(cand) - 1));
           first_key[j] = (m & kModeLockOnHit) ? cas_relaxed(kp, want, t.locked_key)
                                               : ld_relaxed(kp);
+          // the slot's score shares the key's line: with its sector on the way
+          // into L2 the score store that follows the lock merges there instead
+          // of becoming a read-modify-write in DRAM
+          if (OP != kOpAssignValues && (m & kModeLockOnHit)) prefetch_l2(kp + kLineSlots);
         }
       }
     }
@@ -401,7 +419,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
           while (m) {
             pos = pl.sub * 16u + (__ffs(m) - 1);
             m &= m - 1;
-            uint64_t* kp = t.keys + slot0 + pos;
+            uint64_t* kp = key_ptr(t, slot0 + pos);
             const uint64_t seen = lock_on_hit ? cas_relaxed(kp, want, t.locked_key)
                                               : ld_relaxed(kp);
             if (seen == want) {
@@ -437,7 +455,9 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
           const uint32_t pos = (start + gd) & (kBucketSlots - 1);
           bool won = false;
           if (d == gd) {
-            won = cas_relaxed(t.keys + slot0 + pos, t.empty_key, t.locked_key) == t.empty_key;
+            uint64_t* kp = key_ptr(t, slot0 + pos);
+            won = cas_relaxed(kp, t.empty_key, t.locked_key) == t.empty_key;
+            prefetch_l2(kp + kLineSlots);
             em &= ~(1u << (pos & 15u));
           }
           if (__ballot_sync(gmask, won)) {
@@ -479,13 +499,13 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
     const bool holds_lock = my_result == kDuplicate || my_result == kOccupiedEmpty;
     if (my_result == kOccupiedEmpty) {
       st_u8_cg(t.digests + my_slot, a.digest);
-      st_relaxed(t.scores + my_slot, inserted_score(strategy, in_score, desired));
+      st_relaxed(score_ptr(t, my_slot), inserted_score(strategy, in_score, desired));
       atomicAdd(t.bucket_sizes + a.bucket, 1);
     }
     if (my_result == kDuplicate && OP != kOpAssignValues) {
       const bool needs_old = strategy == kLfu || strategy == kEpochLfu ||
                              (OP == kOpFindAndUpdate && args.scores_out != nullptr);
-      const uint64_t old_score = needs_old ? ld_relaxed(t.scores + my_slot) : 0;
+      const uint64_t old_score = needs_old ? ld_relaxed(score_ptr(t, my_slot)) : 0;
       uint64_t ns = 0;
       bool write;
       if (op_inserts(OP) || OP == kOpLockKeys) {
@@ -493,7 +513,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
       } else {
         write = hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
       }
-      if (write) st_relaxed(t.scores + my_slot, ns);
+      if (write) st_relaxed(score_ptr(t, my_slot), ns);
       if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
         args.scores_out[i] = write ? ns : old_score;
       }
@@ -516,7 +536,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
                                       my_row);
     }
     __syncwarp();
-    if (holds_lock && !keep_locked) st_release(t.keys + my_slot, key);
+    if (holds_lock && !keep_locked) st_release(key_ptr(t, my_slot), key);
   }
 
   // ---- phase 4: full buckets ----------------------------------------------------------
@@ -572,14 +592,14 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
           my_result = kRefused;
         } else {
           const uint32_t slot = (my_bucket << 7) + my_pos;
-          uint64_t* kp = t.keys + slot;
+          uint64_t* kp = key_ptr(t, slot);
           // one round trip: swapping LOCKED in returns the victim; over a slot
           // that is already LOCKED the swap changes nothing
           victim = exch_acquire(kp, t.locked_key);
           if (victim == t.locked_key) {
             wait_on = kp;
           } else {
-            uint64_t* sp = t.scores + slot;
+            uint64_t* sp = score_ptr(t, slot);
             if (ld_relaxed(sp) > my_min) {
               st_release(kp, victim);  // the slot was refreshed in between: scan again
             } else {
@@ -639,7 +659,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
                                         my_row);
       }
       __syncwarp();
-      if (placed && !(OP == kOpFindOrInsertPtr && keep_locked)) st_release(t.keys + my_slot, key);
+      if (placed && !(OP == kOpFindOrInsertPtr && keep_locked)) st_release(key_ptr(t, my_slot), key);
       pending &= ~__ballot_sync(full, placed || refused_now);
       // the warp holds no lock now: lanes that met a foreign lock poll it (bounded)
       if (wait_on != nullptr) {
@@ -664,7 +684,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
       if (args.ptrs != nullptr) args.ptrs[i] = has_slot ? row_ptr(t, my_slot) : nullptr;
       if (args.founds != nullptr) args.founds[i] = my_result == kDuplicate;
       if (args.locked_key_ptrs != nullptr) {
-        args.locked_key_ptrs[i] = has_slot ? t.keys + my_slot : nullptr;
+        args.locked_key_ptrs[i] = has_slot ? key_ptr(t, my_slot) : nullptr;
       }
     }
   }
@@ -712,7 +732,6 @@ __global__ void __launch_bounds__(kMutateBlock)
     const bool lock_on_hit = OP == kOpAccumOrAssign ? is_accum : true;
     const bool insert_on_miss = OP == kOpAccumOrAssign ? !is_accum : op_inserts(OP);
     const uint64_t slot0 = a.bucket << 7;
-    uint64_t* key_line = t.keys + slot0;
 
     uint32_t result = kInitial;
     uint32_t pos = 0;
@@ -728,7 +747,7 @@ __global__ void __launch_bounds__(kMutateBlock)
       // lane l looks at slots l, l+32, l+64, l+96
       uint64_t k4[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) k4[c] = ld_acquire(key_line + c * 32 + lane);
+      for (int c = 0; c < 4; ++c) k4[c] = ld_acquire(key_ptr(t, slot0 + c * 32 + lane));
       uint32_t eq = 0, locked = 0, empty = 0;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -742,7 +761,7 @@ __global__ void __launch_bounds__(kMutateBlock)
         const uint32_t p = __shfl_sync(full, (__ffs(eq) - 1) * 32 + lane, src);
         uint32_t ok = 1;
         if (lock_on_hit) {
-          if (lane == src) ok = cas_acquire(key_line + p, key, t.locked_key) == key ? 1u : 0u;
+          if (lane == src) ok = cas_acquire(key_ptr(t, slot0 + p), key, t.locked_key) == key ? 1u : 0u;
           ok = __shfl_sync(full, ok, src);
         }
         if (ok) {
@@ -773,7 +792,7 @@ __global__ void __launch_bounds__(kMutateBlock)
       if (gbest != 255u) {
         const uint32_t p = (a.start + gbest) & (kBucketSlots - 1);
         uint32_t ok = 0;
-        if (lane == 0) ok = cas_acquire(key_line + p, t.empty_key, t.locked_key) == t.empty_key;
+        if (lane == 0) ok = cas_acquire(key_ptr(t, slot0 + p), t.empty_key, t.locked_key) == t.empty_key;
         ok = __shfl_sync(full, ok, 0);
         if (ok) {
           result = kOccupiedEmpty;
@@ -784,7 +803,7 @@ __global__ void __launch_bounds__(kMutateBlock)
       // full bucket: minimum score, first position on ties
       uint64_t s4[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) s4[c] = ld_relaxed(t.scores + slot0 + c * 32 + lane);
+      for (int c = 0; c < 4; ++c) s4[c] = ld_relaxed(score_ptr(t, slot0 + c * 32 + lane));
       uint64_t ms = s4[0];
       uint32_t mp = lane;
 #pragma unroll
@@ -808,10 +827,10 @@ __global__ void __launch_bounds__(kMutateBlock)
       }
       uint32_t code = 0;
       if (lane == 0) {
-        uint64_t* kp = key_line + gpos;
+        uint64_t* kp = key_ptr(t, slot0 + gpos);
         const uint64_t v = ld_relaxed(kp);
         if (v != t.locked_key && cas_acquire(kp, v, t.locked_key) == v) {
-          if (ld_relaxed(t.scores + slot0 + gpos) > gmin) {
+          if (ld_relaxed(score_ptr(t, slot0 + gpos)) > gmin) {
             st_release(kp, v);
           } else {
             victim = v;
@@ -856,16 +875,16 @@ __global__ void __launch_bounds__(kMutateBlock)
       if (lane == 0) {
         if (fresh) {
           st_u8_cg(t.digests + slot, a.digest);
-          st_relaxed(t.scores + slot, inserted_score(strategy, in_score, desired));
+          st_relaxed(score_ptr(t, slot), inserted_score(strategy, in_score, desired));
           if (result != kEvict) atomicAdd(t.bucket_sizes + a.bucket, 1);
         } else if (OP != kOpAssignValues) {
-          const uint64_t old_score = ld_relaxed(t.scores + slot);
+          const uint64_t old_score = ld_relaxed(score_ptr(t, slot));
           uint64_t ns = 0;
           const bool write =
               (op_inserts(OP) || OP == kOpLockKeys)
                   ? hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns)
                   : hit_score_assign(strategy, args.scores, in_score, args.epoch, old_score, &ns);
-          if (write) st_relaxed(t.scores + slot, ns);
+          if (write) st_relaxed(score_ptr(t, slot), ns);
           if (OP == kOpFindAndUpdate && args.scores_out != nullptr) {
             args.scores_out[i] = write ? ns : old_score;
           }
@@ -903,7 +922,7 @@ __global__ void __launch_bounds__(kMutateBlock)
       if (args.ptrs != nullptr) args.ptrs[i] = holds_lock ? row_ptr(t, slot) : nullptr;
       if (args.founds != nullptr) args.founds[i] = result == kDuplicate;
       if (args.locked_key_ptrs != nullptr) {
-        args.locked_key_ptrs[i] = holds_lock ? t.keys + slot : nullptr;
+        args.locked_key_ptrs[i] = holds_lock ? key_ptr(t, slot) : nullptr;
       }
     }
     __syncwarp();
@@ -911,7 +930,7 @@ __global__ void __launch_bounds__(kMutateBlock)
         (OP == kOpFindOrInsertPtr || OP == kOpLockKeys) && args.locked_key_ptrs != nullptr;
     if (holds_lock && !keep_locked && lane == 0) {
       __threadfence();
-      st_release(key_line + pos, key);
+      st_release(key_ptr(t, slot0 + pos), key);
     }
     __syncwarp();
   }
@@ -947,11 +966,11 @@ __global__ void __launch_bounds__(kMutateBlock)
   while (m) {
     const uint32_t pos = lane * 4 + (__ffs(m) - 1);
     m &= m - 1;
-    if (cas_acquire(t.keys + slot0 + pos, key, t.locked_key) == key) {
+    if (cas_acquire(key_ptr(t, slot0 + pos), key, t.locked_key) == key) {
       st_u8_cg(t.digests + slot0 + pos, t.reclaim_digest);
-      st_relaxed(t.scores + slot0 + pos, 0);
+      st_relaxed(score_ptr(t, slot0 + pos), 0);
       atomicSub(t.bucket_sizes + a.bucket, 1);
-      st_release(t.keys + slot0 + pos, t.reclaim_key);
+      st_release(key_ptr(t, slot0 + pos), t.reclaim_key);
       break;
     }
   }
@@ -980,7 +999,7 @@ __device__ __forceinline__ BucketScan scan_bucket_keys(const TableView& t, uint6
   BucketScan r{0, 0, 0};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    const uint64_t k = ld_acquire(t.keys + slot0 + c * 32 + lane);
+    const uint64_t k = ld_acquire(key_ptr(t, slot0 + c * 32 + lane));
     r.eq |= (k == key) ? (1u << c) : 0u;
     r.locked |= (k == t.locked_key) ? (1u << c) : 0u;
     r.empty |= (k == t.empty_key) ? (1u << c) : 0u;
@@ -1008,7 +1027,7 @@ __device__ __forceinline__ void bucket_min_score(const TableView& t, uint64_t sl
   uint32_t mp = 255u;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    const uint64_t s = ld_relaxed(t.scores + slot0 + c * 32 + lane);
+    const uint64_t s = ld_relaxed(score_ptr(t, slot0 + c * 32 + lane));
     if (mp == 255u || s < ms) {
       ms = s;
       mp = c * 32 + lane;
@@ -1066,7 +1085,7 @@ __global__ void __launch_bounds__(kMutateBlock)
         const uint32_t mine = (__ffs(w == 0 ? s0.eq : s1.eq) - 1) * 32 + lane;
         const uint32_t p = __shfl_sync(full, mine, src);
         uint32_t ok = 0;
-        if (lane == src) ok = cas_acquire(t.keys + slot0[w] + p, key, t.locked_key) == key;
+        if (lane == src) ok = cas_acquire(key_ptr(t, slot0[w] + p), key, t.locked_key) == key;
         if (__shfl_sync(full, ok, src)) {
           result = kDuplicate;
           which = w;
@@ -1091,7 +1110,7 @@ __global__ void __launch_bounds__(kMutateBlock)
         const uint32_t p = (start[w] + d) & (kBucketSlots - 1);
         uint32_t ok = 0;
         if (lane == 0) {
-          ok = cas_acquire(t.keys + slot0[w] + p, t.empty_key, t.locked_key) == t.empty_key;
+          ok = cas_acquire(key_ptr(t, slot0[w] + p), t.empty_key, t.locked_key) == t.empty_key;
         }
         if (__shfl_sync(full, ok, 0)) {
           result = kOccupiedEmpty;
@@ -1116,10 +1135,10 @@ __global__ void __launch_bounds__(kMutateBlock)
       }
       uint32_t code = 0;
       if (lane == 0) {
-        uint64_t* kp = t.keys + slot0[w] + gpos;
+        uint64_t* kp = key_ptr(t, slot0[w] + gpos);
         const uint64_t v = ld_relaxed(kp);
         if (v != t.locked_key && cas_acquire(kp, v, t.locked_key) == v) {
-          if (ld_relaxed(t.scores + slot0[w] + gpos) > gmin) {
+          if (ld_relaxed(score_ptr(t, slot0[w] + gpos)) > gmin) {
             st_release(kp, v);  // refreshed in between: scan again
           } else {
             victim = v;
@@ -1139,14 +1158,14 @@ __global__ void __launch_bounds__(kMutateBlock)
     const uint32_t slot = uint32_t(slot0[which]) + pos;
     if (lane == 0) {
       if (result == kDuplicate) {
-        const uint64_t old_score = ld_relaxed(t.scores + slot);
+        const uint64_t old_score = ld_relaxed(score_ptr(t, slot));
         uint64_t ns = 0;
         if (hit_score_upsert(strategy, args.scores, in_score, desired, old_score, &ns)) {
-          st_relaxed(t.scores + slot, ns);
+          st_relaxed(score_ptr(t, slot), ns);
         }
       } else {
         st_u8_cg(t.digests + slot, a.first.digest);
-        st_relaxed(t.scores + slot, inserted_score(strategy, in_score, desired));
+        st_relaxed(score_ptr(t, slot), inserted_score(strategy, in_score, desired));
         if (result != kEvict) atomicAdd(t.bucket_sizes + bucket[which], 1);
       }
     }
@@ -1154,10 +1173,16 @@ __global__ void __launch_bounds__(kMutateBlock)
     __syncwarp();
     if (lane == 0) {
       __threadfence();
-      st_release(t.keys + slot, key);
+      st_release(key_ptr(t, slot), key);
     }
     __syncwarp();
   }
+}
+
+template <int OP>
+void launch_fast(const TableView& t, const MutateArgs& args, uint64_t blocks, cudaStream_t stream) {
+  auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
+  kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
 }
 
 template <int OP>
@@ -1165,8 +1190,7 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
   const uint64_t warps = (args.n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kMutateBlock - 1) / kMutateBlock;
   if (unique_key) {
-    auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
-    kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+    launch_fast<OP>(t, args, blocks, stream);
   } else if (OP != kOpFindOrInsertPtr && OP != kOpLockKeys && args.n < (1ull << 32)) {
     // Repeated keys are allowed.  The fast kernel serves every key it finds
     // and can lock; keys that have to be inserted and keys whose slot another
@@ -1185,8 +1209,7 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
     MutateArgs fast = args;
     fast.deferred_list = list;
     fast.deferred_count = count;
-    auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, false> : mutate_kernel<OP, 0, false>;
-    kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, fast);
+    launch_fast<OP>(t, fast, blocks, stream);
     MutateArgs rest = args;
     rest.index_list = list;
     rest.index_count = count;

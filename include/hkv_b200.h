@@ -119,10 +119,16 @@ typedef enum hkv_predicate {
 /* Raw view of the table's planes for header-side kernels that evaluate a
  * user-templated functor (export_batch_if<PredFunctor>, for_each).  Valid
  * until the table is destroyed. */
+#define HKV_SLOT_WORD(slot) \
+  ((((uint64_t)(slot) >> 3) << 4) | ((uint64_t)(slot) & 7u))
 typedef struct hkv_table_view {
   uint8_t* digests;      /* [buckets][128] */
-  uint64_t* keys;        /* [buckets][128] */
-  uint64_t* scores;      /* [buckets][128] */
+  /* Keys and scores share one plane of 128-byte lines: a line holds the keys
+   * of 8 consecutive slots followed by their 8 scores (a slot's lock word and
+   * its score are written together by every update, so they sit in one line).
+   * Index both arrays with HKV_SLOT_WORD(slot), never with the slot itself. */
+  uint64_t* keys;        /* key of slot s:   keys[HKV_SLOT_WORD(s)]   */
+  uint64_t* scores;      /* score of slot s: scores[HKV_SLOT_WORD(s)] (scores == keys + 8) */
   uint8_t* values_hbm;   /* rows of row slots [0, hbm_slots) */
   uint8_t* values_host;  /* rows of row slots [hbm_slots, capacity), mapped pinned */
   int32_t* bucket_sizes; /* [buckets] */

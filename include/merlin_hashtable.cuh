@@ -178,8 +178,8 @@ __global__ void export_if_kernel(const hkv_table_view v, const K pattern, const 
     S score = 0;
     bool live = false;
     if (rel < n) {
-      key = static_cast<K>(v.keys[slot]);
-      score = static_cast<S>(v.scores[slot]);
+      key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
+      score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
       live = !view_is_reserved(v, static_cast<uint64_t>(key)) && pred(key, score, pattern, threshold);
     }
     const uint32_t votes = __ballot_sync(0xFFFFFFFFu, live);
@@ -217,8 +217,8 @@ __global__ void size_if_kernel(const hkv_table_view v, const K pattern, const S 
   unsigned long long local = 0;
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < v.capacity;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    K key = static_cast<K>(v.keys[slot]);
-    S score = static_cast<S>(v.scores[slot]);
+    K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
+    S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
     if (!view_is_reserved(v, static_cast<uint64_t>(key)) && pred(key, score, pattern, threshold)) {
       ++local;
     }
@@ -238,12 +238,12 @@ __global__ void erase_if_kernel(const hkv_table_view v, const K pattern, const S
   unsigned long long local = 0;
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < v.capacity;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    K key = static_cast<K>(v.keys[slot]);
-    S score = static_cast<S>(v.scores[slot]);
+    K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
+    S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
     if (!view_is_reserved(v, static_cast<uint64_t>(key)) && pred(key, score, pattern, threshold)) {
-      v.keys[slot] = v.reclaim_key;
+      v.keys[HKV_SLOT_WORD(slot)] = v.reclaim_key;
       v.digests[slot] = reclaim_digest;
-      v.scores[slot] = 0;
+      v.scores[HKV_SLOT_WORD(slot)] = 0;
       atomicSub(v.bucket_sizes + (slot >> 7), 1);
       ++local;
     }
@@ -287,8 +287,8 @@ __global__ void export_if_v2_kernel(const hkv_table_view v, PredFunctor pred, co
   for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += uint64_t(gridDim.x) * blockDim.x) {
     const uint64_t slot = offset + i;
-    const K key = static_cast<K>(v.keys[slot]);
-    const S score = static_cast<S>(v.scores[slot]);
+    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
+    const S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
     const V* value = reinterpret_cast<const V*>(view_row(v, slot));
     bool match = pred.template operator()<G>(key, value, score, g);
     match = match && !view_is_reserved(v, static_cast<uint64_t>(key));
@@ -324,8 +324,8 @@ __global__ void erase_if_v2_kernel(const hkv_table_view v, PredFunctor pred, con
   cg::thread_block_tile<G> g = cg::tiled_partition<G>(cg::this_thread_block());
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < n;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    const K key = static_cast<K>(v.keys[slot]);
-    const S score = static_cast<S>(v.scores[slot]);
+    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
+    const S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
     const V* value = reinterpret_cast<const V*>(view_row(v, slot));
     bool match = pred.template operator()<G>(key, value, score, g);
     match = match && !view_is_reserved(v, static_cast<uint64_t>(key));
@@ -336,9 +336,9 @@ __global__ void erase_if_v2_kernel(const hkv_table_view v, PredFunctor pred, con
       atomicSub(v.bucket_sizes + (slot >> 7), __popc(votes));
     }
     if (match) {
-      v.keys[slot] = v.reclaim_key;
+      v.keys[HKV_SLOT_WORD(slot)] = v.reclaim_key;
       v.digests[slot] = reclaim_digest;
-      v.scores[slot] = 0;
+      v.scores[HKV_SLOT_WORD(slot)] = 0;
     }
   }
 }
@@ -350,8 +350,8 @@ __global__ void for_each_kernel(const hkv_table_view v, ExecutionFunc f, const u
   for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += uint64_t(gridDim.x) * blockDim.x) {
     const uint64_t slot = first + i;
-    const K key = static_cast<K>(v.keys[slot]);
-    S* score = reinterpret_cast<S*>(v.scores + slot);
+    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
+    S* score = reinterpret_cast<S*>(v.scores + HKV_SLOT_WORD(slot));
     V* value = reinterpret_cast<V*>(const_cast<uint8_t*>(view_row(v, slot)));
     f.template operator()<G>(key, value, score, g);
   }

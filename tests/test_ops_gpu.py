@@ -820,9 +820,11 @@ def test_export_batch_slot_windows(offset, n):
     import torch
     from cuda.bindings import runtime as cudart
 
-    all_keys = np.zeros(cap, dtype=np.uint64)
-    cudart.cudaMemcpy(all_keys.ctypes.data, view.keys, cap * 8,
+    # keys and scores share 128-byte lines: 8 keys, then the 8 scores of the same slots
+    lines = np.zeros(cap * 2, dtype=np.uint64)
+    cudart.cudaMemcpy(lines.ctypes.data, view.keys, cap * 16,
                       cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+    all_keys = np.ascontiguousarray(lines.reshape(-1, 2, 8)[:, 0, :]).reshape(-1)
     lo, hi = min(offset, cap), min(offset + n, cap)
     window = all_keys[lo:hi]
     mask = np.uint64(0xFFFFFFFFFFFFFFFC)
