@@ -60,7 +60,6 @@ enum Result : uint32_t {
 constexpr uint32_t kModeValid = 1u;
 constexpr uint32_t kModeLockOnHit = 2u;
 constexpr uint32_t kModeInsertOnMiss = 4u;
-constexpr uint32_t kModeBucketFull = 8u;
 
 __device__ __forceinline__ bool op_inserts(int op) { return op <= kOpAccumOrAssign; }
 
@@ -300,6 +299,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
   uint64_t in_score = 0;
   uint64_t desired = 0;
   uint32_t mode = 0;
+  uint32_t bucket_full = 0;  // the key's bucket has no EMPTY slot left (inserting operations)
   Address a{0, 0, 0};
   uint32_t my_row = 0;  // INDEXED: this key's row in the source rank's buffer
   // Batches that may repeat a key (unique_key == false): this kernel only
@@ -334,7 +334,9 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
       } else {
         mode |= kModeLockOnHit;
       }
-      if (op_inserts(OP) && t.bucket_sizes[a.bucket] >= kBucketSlots) mode |= kModeBucketFull;
+      // kept out of `mode`: the digest loads of phase 1 are issued on `mode`
+      // and must not wait for this load
+      if (op_inserts(OP)) bucket_full = t.bucket_sizes[a.bucket] >= kBucketSlots ? 1u : 0u;
     }
   }
   const uint32_t my_bucket = uint32_t(a.bucket);
@@ -399,6 +401,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
     const uint32_t gmask = group_mask(pl.group);
     const uint32_t owner = pass_owner(j, pl.group);
     const uint32_t pmode = __shfl_sync(full, mode, owner);
+    const bool pfull = __shfl_sync(full, bucket_full, owner) != 0u;
     const uint32_t start = __shfl_sync(full, a.start, owner);
     const uint64_t want = __shfl_sync(full, key, owner);
     const uint64_t slot0 = uint64_t(__shfl_sync(full, my_bucket, owner)) << 7;
@@ -441,7 +444,7 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
         result = kDeferred;
       } else if (!(pmode & kModeInsertOnMiss)) {
         result = kMiss;
-      } else if (pmode & kModeBucketFull) {
+      } else if (pfull) {
         result = kNeedEvict;
       } else {
         uint32_t em = mask_j >> 16;

@@ -492,11 +492,24 @@ def test_memory_mode_dual_bucket_tables():
     q = keys[:at + 500]
     want = o.find(q)
     assert want[1][:at].all() and not want[1][at:].any()
-    for x in tables:
+    for x in list(tables):
         got = x.find(q)
-        np.testing.assert_array_equal(got[1], want[1])
-        np.testing.assert_array_equal(got[0][want[1]], want[0][want[1]])
-        np.testing.assert_array_equal(got[2][want[1]], want[2][want[1]])
+        who = type(x).__name__
+        both = want[1]
+        if x is r:
+            # The reference's own dual-bucket insert races with itself: on B200 about
+            # one run in three leaves one of the 7,000 keys counted by size() but not
+            # found again.  Its result is held to the oracle on every key it does
+            # find, and may miss a handful; product and oracle are held exactly.
+            lost = want[1] & ~got[1]
+            assert not (got[1] & ~want[1]).any() and lost.sum() <= 3, who
+            both = want[1] & got[1]
+            if lost.any():      # its table is no longer comparable: leave it out of what follows
+                tables = [y for y in tables if y is not r]
+        else:
+            np.testing.assert_array_equal(got[1], want[1], err_msg=who)
+        np.testing.assert_array_equal(got[0][both], want[0][both], err_msg=who)
+        np.testing.assert_array_equal(got[2][both], want[2][both], err_msg=who)
     # assignment of resident keys: new rows and scores, same size
     k = keys[1000:2000]
     sc = np.arange(50001, 51001, dtype=np.uint64)
