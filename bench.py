@@ -538,40 +538,135 @@ def churn_ops(arm_cls, batch: int) -> dict:
             "table": f"capacity {capacity}, dim {dim}, EpochLfu, load factor 1.0"}
 
 
-def embedding_step_ops(sharded, rank: int, world: int, batch: int, dim: int, barrier, dist) -> dict:
-    """One step of the key-hash sharded embedding table: every rank draws
+def zipf_keys(ranks: torch.Tensor) -> torch.Tensor:
+    """Zipf rank -> key through the splitmix bijection: hot keys spread over the owners."""
+    z = ranks + _s64(0x9E3779B97F4A7C15)
+    z = (z ^ _lsr(z, 30)) * _s64(0xBF58476D1CE4E5B9)
+    z = (z ^ _lsr(z, 27)) * _s64(0x94D049BB133111EB)
+    z = z ^ _lsr(z, 31)
+    return torch.where((z & -4) == -4, z & 0xFFFF, z)
+
+
+class EmbeddingStepper:
+    """find_or_insert (rows come back) followed by accum_or_assign of fp32
+    deltas for the same keys: the training step of the key-hash sharded
+    embedding table.  With several ranks both calls are the fused peer-memory
+    path (no NCCL call inside the step); with one rank they are the local
+    table's calls on the same buffers."""
+
+    def __init__(self, sharded, arm, rank, world, batch, dim, dist):
+        self.sharded, self.arm, self.rank, self.world, self.dim, self.dist = sharded, arm, rank, world, dim, dist
+        if sharded is not None:
+            self.buf, self.flags = sharded.peer.out_values, sharded.peer.out_founds
+        else:
+            self.buf = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+            self.flags = torch.empty(batch, dtype=torch.bool, device="cuda")
+
+    def step(self, keys, init_rows, deltas):
+        n = keys.numel()
+        self.buf[:n].copy_(init_rows[:n])                     # rows for the keys that are new
+        if self.sharded is not None:
+            self.sharded.upsert_fused("find_or_insert", n, keys)
+        else:
+            self.arm.t.find_or_insert(n, keys, self.buf)
+        # rows of all keys are now in the buffer; the "gradients" take their place
+        self.buf[:n].copy_(deltas[:n])
+        self.flags[:n].fill_(True)
+        if self.sharded is not None:
+            self.sharded.upsert_fused("accum_or_assign", n, keys, reuse_route=True)
+        else:
+            self.arm.t.accum_or_assign_unique(n, keys, self.buf, self.flags)
+
+    def lookup(self, keys):
+        """(rows, found flags) of keys every rank asks for."""
+        n = keys.numel()
+        if self.sharded is not None:
+            rows, founds = self.sharded.find_fused(n, keys)
+            torch.cuda.synchronize()
+            return rows.clone(), founds.clone()
+        rows = torch.zeros((n, self.dim), dtype=torch.float32, device="cuda")
+        founds = torch.zeros(n, dtype=torch.bool, device="cuda")
+        self.arm.find(keys, rows, founds)
+        torch.cuda.synchronize()
+        return rows, founds
+
+    def expected(self, sample, before_rows, before_found, steps):
+        """What `sample` (the same keys on every rank) must hold after `steps`
+        = [(sorted unique keys, init rows, deltas) of this rank, ...]: at each
+        owner the ranks' batches are applied one after the other starting with
+        rank owner + 1 (wrapping), fp32 sums in that order."""
+        world, dist = self.world, self.dist
+        val = before_rows.clone()
+        exists = before_found.clone()
+        owner = owner_of(sample, world)
+        idx = torch.arange(sample.numel(), device="cuda")
+        for keys, init_rows, deltas in steps:
+            pos = torch.searchsorted(keys, sample).clamp_(max=keys.numel() - 1)
+            present = keys[pos] == sample
+            mine = torch.cat([init_rows[pos], deltas[pos]], dim=1)
+            if dist:
+                all_present = torch.empty((world,) + present.shape, dtype=torch.bool, device="cuda")
+                all_rows = torch.empty((world,) + mine.shape, dtype=torch.float32, device="cuda")
+                dist.all_gather_into_tensor(all_present.view(torch.uint8), present.view(torch.uint8).contiguous())
+                dist.all_gather_into_tensor(all_rows, mine.contiguous())
+            else:
+                all_present, all_rows = present[None], mine[None]
+            turns = [(owner + 1 + t) % world for t in range(world)]
+            for src in turns:                                   # find_or_insert of every rank ...
+                here = all_present[src, idx]
+                fresh = here & ~exists
+                val[fresh] = all_rows[src, idx][fresh][:, :self.dim]
+                exists |= here
+            for src in turns:                                   # ... then accum_or_assign of every rank
+                here = all_present[src, idx]
+                val[here] = val[here] + all_rows[src, idx][here][:, self.dim:]
+        return val, exists
+
+
+def check_routed_updates(stepper, rank, world, dim, dist) -> int:
+    """A small seeded step before anything is timed: 4096 new keys that every
+    rank sends and 4096 new keys of its own per rank go through find_or_insert
+    and accum_or_assign; every rank then looks all of them up and compares bit
+    for bit with the rows the documented order of application gives."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(777 + rank)
+    both = mixed_keys(1 << 60, 4096, "cuda")
+    own = mixed_keys((1 << 60) + 4096 * (rank + 1), 4096, "cuda")
+    keys = torch.unique(torch.cat([both, own]))
+    init_rows = torch.rand((keys.numel(), dim), device="cuda", generator=g) * 2 - 1
+    deltas = (torch.rand((keys.numel(), dim), device="cuda", generator=g) * 2 - 1) * 1e-3
+    sample = torch.cat([mixed_keys((1 << 60) + 4096 * r, 4096, "cuda") for r in range(world + 1)])
+    before_rows, before_found = stepper.lookup(sample)
+    stepper.step(keys, init_rows, deltas)
+    torch.cuda.synchronize()
+    want, want_found = stepper.expected(sample, before_rows, before_found, [(keys, init_rows, deltas)])
+    rows, found = stepper.lookup(sample)
+    assert bool(found.all()) and bool(want_found.all()), "routed find_or_insert lost keys"
+    assert torch.equal(rows.view(torch.int32), want.view(torch.int32)), \
+        "routed find_or_insert / accum_or_assign: rows differ from the documented order of application"
+    return int(sample.numel())
+
+
+def embedding_step_ops(sharded, arm, rank: int, world: int, batch: int, dim: int, barrier, dist) -> dict:
+    """The step of the key-hash sharded embedding table: every rank draws
     `batch` Zipf(1.1) keys over a 2^34 key space, removes its own repeats, and
     runs find_or_insert (rows come back) followed by accum_or_assign of fp32
-    deltas U(-1e-3, 1e-3) for the same keys.  Routing, update and transfer are
-    the fused peer-memory path (no NCCL call inside the step)."""
+    deltas U(-1e-3, 1e-3) for the same keys.  After the timed steps the 2048
+    hottest keys (every rank sends them in nearly every step) are looked up and
+    compared bit for bit with a replay of all steps in the documented order."""
     g = torch.Generator(device="cuda")
     g.manual_seed(4321 + rank)
     reps, warm = 10, 3
-    ws = sharded.peer
-    batches = []
-    for _ in range(reps + warm):
-        ranks = zipf_ranks(batch, 1 << 34, 1.1, g)
-        # rank -> key through the splitmix bijection: hot keys spread over the owners
-        z = ranks + _s64(0x9E3779B97F4A7C15)
-        z = (z ^ _lsr(z, 30)) * _s64(0xBF58476D1CE4E5B9)
-        z = (z ^ _lsr(z, 27)) * _s64(0x94D049BB133111EB)
-        z = z ^ _lsr(z, 31)
-        z = torch.where((z & -4) == -4, z & 0xFFFF, z)
-        batches.append(torch.unique(z))
+    stepper = EmbeddingStepper(sharded, arm, rank, world, batch, dim, dist)
+    checked_keys = check_routed_updates(stepper, rank, world, dim, dist)
+    batches = [torch.unique(zipf_keys(zipf_ranks(batch, 1 << 34, 1.1, g))) for _ in range(reps + warm)]
     init_rows = torch.rand((batch, dim), device="cuda", generator=g) * 2 - 1
     deltas = (torch.rand((batch, dim), device="cuda", generator=g) * 2 - 1) * 1e-3
     unique_total = sum(int(b.numel()) for b in batches[warm:])
+    sample = zipf_keys(torch.arange(2048, dtype=torch.int64, device="cuda"))
+    before_rows, before_found = stepper.lookup(sample)
 
-    def step(i):
-        k = batches[i]
-        n = k.numel()
-        ws.out_values[:n].copy_(init_rows[:n])              # rows for the keys that are new
-        sharded.upsert_fused("find_or_insert", n, k)         # rows of all keys are now in the buffer
-        ws.out_values[:n].copy_(deltas[:n])                  # the "gradients"
-        ws.out_founds[:n].fill_(True)
-        sharded.upsert_fused("accum_or_assign", n, k)
-
-    ms = time_steps(step, reps, warm, barrier)
+    ms = time_steps(lambda i: stepper.step(batches[i], init_rows, deltas), reps, warm, barrier)
     if dist:
         t = torch.tensor([ms, float(unique_total)], device="cuda", dtype=torch.float64)
         dist.all_reduce(t[:1], op=dist.ReduceOp.MAX)
@@ -579,14 +674,24 @@ def embedding_step_ops(sharded, rank: int, world: int, batch: int, dim: int, bar
         ms, unique_all = float(t[0].item()), float(t[1].item())
     else:
         unique_all = float(unique_total)
-    assert sharded.peer.status() == 0
+    if sharded is not None:
+        assert sharded.peer.status() == 0
+    want, want_found = stepper.expected(sample, before_rows, before_found,
+                                        [(b, init_rows, deltas) for b in batches])
+    rows, found = stepper.lookup(sample)
+    assert torch.equal(found, want_found), "embedding step: hot keys missing afterwards"
+    assert torch.equal(rows[found].view(torch.int32), want[found].view(torch.int32)), \
+        "embedding step: rows of the hot keys differ from the replay of all steps"
     return {
         "b_kv_s_drawn": round(batch * reps * world / (ms / 1e3) / BINARY_BILLION, 4),
         "b_kv_s_unique": round(unique_all / (ms / 1e3) / BINARY_BILLION, 4),
         "ms_per_step": round(ms / reps, 4),
         "unique_fraction": round(unique_all / (batch * reps * world), 4),
-        "step": "find_or_insert + accum_or_assign, Zipf(1.1) over 2^34 keys, per-rank dedup, fused "
-                "peer-memory routing",
+        "checked": True,
+        "checked_rows": {"seeded_step_before_timing": checked_keys,
+                         "hot_keys_after_timed_steps": int(found.sum().item())},
+        "step": ("find_or_insert + accum_or_assign, Zipf(1.1) over 2^34 keys, per-rank dedup, "
+                 + ("fused peer-memory routing" if sharded is not None else "one rank: the local table's calls")),
     }
 
 
@@ -908,15 +1013,14 @@ def main():
         e2e_ms = float(tms.item())
     assert bool(h_founds.all())
     last_e2e = queries[(3 + e2e_steps - 1) % n_query_sets]
-    if sharded is None:
-        assert torch.equal(h_vals.cuda(), rows_for(last_e2e, dim)), "end-to-end find returned wrong rows"
+    assert torch.equal(h_vals.cuda(), rows_for(last_e2e, dim)), "end-to-end find returned wrong rows"
     e2e_value = batch * e2e_steps * world / (e2e_ms / 1e3) / BINARY_BILLION
 
     # ---- the other operations of the workload (not part of `value`) -----------
     ops = {}
-    if not args.no_ops and world > 1 and fused:
-        ops["sharded_embedding_step"] = embedding_step_ops(sharded, rank, world, batch, dim, barrier,
-                                                           dist)
+    if not args.no_ops and args.impl == "product" and (fused or world == 1):
+        ops["sharded_embedding_step"] = embedding_step_ops(sharded if fused else None, arm, rank,
+                                                           world, batch, dim, barrier, dist)
     if not args.no_ops and world == 1:
         reps = 10
 
@@ -980,8 +1084,9 @@ def main():
                                "achieved_gbs": (16 * win + (2 * row + 32) * exported) * 5 / (t_ms / 1e3) / 1e9}
         del xk, xs, xv
         for v in ops.values():
-            v["b_kv_s"] = round(v["b_kv_s"], 4)
-            v["achieved_gbs"] = round(v["achieved_gbs"], 1)
+            if "achieved_gbs" in v:
+                v["b_kv_s"] = round(v["b_kv_s"], 4)
+                v["achieved_gbs"] = round(v["achieved_gbs"], 1)
         try:
             ops["churn_epoch_lfu"] = churn_ops(type(arm), batch)
         except Exception as e:

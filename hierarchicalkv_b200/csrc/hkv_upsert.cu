@@ -278,18 +278,10 @@ __host__ __device__ constexpr int mutate_min_blocks(int op) {
 }
 
 template <int OP, int VEC, bool INDEXED>
-__global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
-    mutate_kernel(const TableView t, const MutateArgs args) {
-  static_assert(!INDEXED || OP == kOpInsertOrAssign || OP == kOpFindOrInsert ||
-                    OP == kOpAccumOrAssign,
-                "the routed form exists for the three operations the sharded table routes");
+__device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs& args,
+                                            const uint64_t base, const uint64_t n) {
   const uint32_t full = 0xFFFFFFFFu;
   const ProbeLane pl = probe_lane();
-  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const uint64_t base = warp * 32u;
-  uint64_t n = args.n;
-  if (INDEXED) n = min(n, *args.n_device);
-  if (base >= n) return;
   const uint64_t i = base + pl.lane;
   const int strategy = args.strategy;
   const uint32_t lane_lt = (1u << pl.lane) - 1u;
@@ -689,6 +681,28 @@ __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
       if (args.locked_key_ptrs != nullptr) {
         args.locked_key_ptrs[i] = has_slot ? key_ptr(t, my_slot) : nullptr;
       }
+    }
+  }
+}
+
+// The local form serves one warp of 32 consecutive keys per launched warp.  The
+// routed form learns the number of keys from device memory, so its grid is a
+// fixed number of resident blocks that stride over the segment.
+template <int OP, int VEC, bool INDEXED>
+__global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
+    mutate_kernel(const TableView t, const MutateArgs args) {
+  static_assert(!INDEXED || OP == kOpInsertOrAssign || OP == kOpFindOrInsert ||
+                    OP == kOpAccumOrAssign,
+                "the routed form exists for the three operations the sharded table routes");
+  const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (!INDEXED) {
+    if (warp * 32u < args.n) mutate_warp<OP, VEC, INDEXED>(t, args, warp * 32u, args.n);
+  } else {
+    const uint64_t n = min(args.n, *args.n_device);
+    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
+    for (uint64_t base = warp * 32u; base < n; base += stride) {
+      mutate_warp<OP, VEC, INDEXED>(t, args, base, n);
+      __syncwarp();  // the warp's columns of the parked probe results are reused
     }
   }
 }
@@ -1249,7 +1263,14 @@ void launch_routed_op(const TableView& t, MutateArgs args, uint32_t world, uint3
                       const PeerPtrs& values_of, const PeerPtrs& flags_of, cudaStream_t stream) {
   const uint64_t* keys0 = args.keys;
   const uint32_t* index0 = args.row_index;
-  const uint64_t blocks = (segment_capacity + kMutateBlock - 1) / kMutateBlock;
+  // the key counts are only known on the device: a grid of resident blocks
+  // strides over whatever arrived
+  int device = 0, sms = 148;
+  cudaGetDevice(&device);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const uint64_t resident = uint64_t(sms) * mutate_min_blocks(OP);
+  const uint64_t needed = (segment_capacity + kMutateBlock - 1) / kMutateBlock;
+  const uint64_t blocks = needed < resident ? needed : resident;
   auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, true> : mutate_kernel<OP, 0, true>;
   for (uint32_t turn = 0; turn < world; ++turn) {
     const uint32_t seg = (first_segment + turn) % world;

@@ -356,7 +356,8 @@ class ShardedHashTable:
 
     _ROUTED_OPS = {"insert_or_assign": 0, "find_or_insert": 1, "accum_or_assign": 2}
 
-    def upsert_fused(self, op: str, n, keys, max_polls: int = 50_000_000):
+    def upsert_fused(self, op: str, n, keys, max_polls: int = 50_000_000,
+                     reuse_route: bool = False):
         """insert_or_assign / find_or_insert / accum_or_assign over all shards
         with the update and the transfer fused.  The batch rows are the first n
         rows of this rank's peer-visible buffer ``peer.out_values`` (for
@@ -369,10 +370,17 @@ class ShardedHashTable:
         At each owner the requesting ranks' batches are applied one after the
         other, starting with rank owner + 1 (wrapping), so a key that several
         ranks send in one step behaves as if those ranks had called the table
-        in that order.  Needs a score-free strategy (kLru / kEpochLru)."""
+        in that order.  Needs a score-free strategy (kLru / kEpochLru).
+
+        ``reuse_route``: the keys are those of the previous upsert_fused call of
+        every rank (the update that follows a find_or_insert of the same
+        batch): the owners' inboxes still hold them and the routing is skipped;
+        the barrier stays, it tells the owners that the ranks' buffers carry
+        the new rows."""
         w = self.peer
         lib = self.ops.lib
-        self._route_p2p(n, keys)
+        if not reuse_route:
+            self._route_p2p(n, keys)
         self._peer_barrier(max_polls)
         rc = lib.hkv_upsert_routed(self.local.handle, self._ROUTED_OPS[op], self.world, self.rank,
                                    w.max_batch, w.local["inbox_keys"], w.local["inbox_origin"],
