@@ -63,6 +63,15 @@ def mixed_keys(start: int, n: int, device) -> torch.Tensor:
     return torch.where(reserved, z & 0xFFFF, z)
 
 
+def mixed_keys_at(counters: torch.Tensor) -> torch.Tensor:
+    """mixed_keys for arbitrary counter values (the same bijection)."""
+    z = counters + _s64(0x9E3779B97F4A7C15)
+    z = (z ^ _lsr(z, 30)) * _s64(0xBF58476D1CE4E5B9)
+    z = (z ^ _lsr(z, 27)) * _s64(0x94D049BB133111EB)
+    z = z ^ _lsr(z, 31)
+    return torch.where((z & -4) == -4, z & 0xFFFF, z)
+
+
 def owner_of(keys: torch.Tensor, world: int) -> torch.Tensor:
     """Murmur3 finaliser of the key modulo the world size: the shard that owns it."""
     k = keys
@@ -426,51 +435,145 @@ def zipf_ranks(n: int, population: int, alpha: float, generator) -> torch.Tensor
     return (x.floor().to(torch.int64) - 1).clamp_(0, population - 1)
 
 
-def hybrid_ops(arm_cls, batch: int, reps: int = 5) -> dict:
-    """The hybrid HBM + HMEM table in miniature (1/16 of its size, same
-    proportions): dim 128 fp32 rows, a quarter of them in HBM and the rest in
-    pinned host memory, queries Zipf(1.05) over the inserted keys with 90 %
-    hits.  Rows that live in host memory cross the host link on every find."""
-    capacity, dim = 8 << 20, 128
+def host_memory_available():
+    """Bytes of host memory this process may still take: MemAvailable, or what
+    the cgroup leaves if that is less; None when neither can be read."""
+    avail = None
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    avail = int(line.split()[1]) * 1024
+    except OSError:
+        pass
+    try:
+        with open("/sys/fs/cgroup/memory.max") as f:
+            limit = f.read().strip()
+        with open("/sys/fs/cgroup/memory.current") as f:
+            used = int(f.read().strip())
+        if limit != "max":
+            left = int(limit) - used
+            avail = left if avail is None else min(avail, left)
+    except (OSError, ValueError):
+        pass
+    return avail
+
+
+def host_link_gbs() -> float:
+    """Pinned host -> device copy rate of this box, GB/s (256 MiB, best of 3)."""
+    n = 256 << 20
+    src = torch.empty(n, dtype=torch.uint8).pin_memory()
+    dst = torch.empty(n, dtype=torch.uint8, device="cuda")
+    best = None
+    for _ in range(4):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        dst.copy_(src, non_blocking=True)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        best = ms if best is None else min(best, ms)
+    return n / (best / 1e3) / 1e9
+
+
+def hybrid_ops(arm_cls, batch: int, reps: int = 30) -> dict:
+    """The hybrid HBM + HMEM table: dim 128 fp32 rows, a quarter of them in HBM
+    and the rest in pinned host memory, filled to load factor 0.5, queries
+    Zipf(1.05) over the inserted keys with 90 % hits.  The stated size is 128 Mi
+    slots (16 GiB of rows in HBM, 48 GiB pinned); when the box refuses the pinned
+    allocation the capacity is halved until the table can be created, and every
+    attempt is reported.  Rows that live in host memory cross the host link on
+    every find."""
+    dim = 128
     row = dim * 4
-    arm = arm_cls(capacity, dim, capacity * row // 4)
-    keys = mixed_keys(1 << 58, capacity // 2, "cuda")
-    for b in range(0, keys.numel(), batch):
-        k = keys[b:b + batch]
+    attempts = []
+    arm = None
+    capacity = 128 << 20
+    host_free = host_memory_available()
+    while capacity >= (8 << 20):
+        pinned = capacity * row * 3 // 4
+        if host_free is not None and pinned > 0.6 * host_free:
+            # pinning most of what the host has left is how a box gets killed: not attempted
+            attempts.append({"capacity": capacity, "pinned_gib": round(pinned / 2**30, 1), "ok": False,
+                             "error": "skipped: above 60 %% of the %.0f GiB of host memory available"
+                                      % (host_free / 2**30)})
+            capacity //= 2
+            continue
+        try:
+            arm = arm_cls(capacity, dim, capacity * row // 4)
+            attempts.append({"capacity": capacity, "pinned_gib": round(capacity * row * 3 / 4 / 2**30, 1),
+                             "ok": True})
+            break
+        except Exception as e:
+            attempts.append({"capacity": capacity, "pinned_gib": round(capacity * row * 3 / 4 / 2**30, 1),
+                             "ok": False, "error": str(e)[:160]})
+            capacity //= 2
+    if arm is None:
+        return {"b_kv_s": None, "attempts": attempts}
+    filled = capacity // 2
+    for b in range(0, filled, batch):
+        k = mixed_keys((1 << 58) + b, min(batch, filled - b), "cuda")
         arm.insert_or_assign(k, rows_for(k, dim))
     torch.cuda.synchronize()
     g = torch.Generator(device="cuda")
     g.manual_seed(5)
-    perm = torch.randperm(keys.numel(), generator=g, device="cuda")
+    # Zipf rank -> inserted key through a fixed bijection of the counter range
+    mult, n_q = 2654435761, 4
     qs = []
-    for i in range(4):
-        hot = keys[perm[zipf_ranks(batch, keys.numel(), 1.05, g)]]
+    for i in range(n_q):
+        ranks = zipf_ranks(batch, filled, 1.05, g)
+        hot = mixed_keys_at((1 << 58) + (ranks * mult) % filled)
         fresh = mixed_keys((1 << 59) + i * batch, batch, "cuda")
         miss = torch.rand(batch, device="cuda", generator=g) < 0.1
         qs.append(torch.where(miss, fresh, hot).contiguous())
     out = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
     f = torch.empty(batch, dtype=torch.bool, device="cuda")
-    t_ms = time_steps(lambda i: arm.find(qs[i % 4], out, f), reps, 3)
+    t_ms = time_steps(lambda i: arm.find(qs[i % n_q], out, f), reps, 3)
     hits = float(f.float().mean().item())
+    last = qs[(reps + 2) % n_q]
+    assert torch.equal(out[f], rows_for(last, dim)[f]), "hybrid find returned wrong rows"
     result = {"b_kv_s": round(batch * reps / (t_ms / 1e3) / BINARY_BILLION, 4)}
-    # find*: row addresses instead of rows (nothing crosses the host link)
+    # find*: row addresses instead of rows (nothing crosses the host link); the addresses
+    # also tell which rows live in host memory
     ptrs = torch.empty(batch, dtype=torch.int64, device="cuda")
-    tp_ms = time_steps(lambda i: arm.find_ptr(qs[i % 4], ptrs, f), reps, 3)
+    tp_ms = time_steps(lambda i: arm.find_ptr(qs[i % n_q], ptrs, f), reps, 3)
     result["find_ptr_b_kv_s"] = round(batch * reps / (tp_ms / 1e3) / BINARY_BILLION, 4)
+    link = host_link_gbs()
+
+    def host_rows_per_batch():
+        """distinct host-resident rows one batch reads (product arm: from the row addresses)"""
+        if not hasattr(arm, "t") or not hasattr(arm.t, "view"):
+            return None
+        v = arm.t.view()
+        lo = int(v.values_host or 0)
+        hi = lo + (int(v.capacity) - int(v.hbm_slots)) * row
+        arm.find_ptr(qs[0], ptrs, f)
+        torch.cuda.synchronize()
+        p = ptrs[f]
+        return int(torch.unique(p[(p >= lo) & (p < hi)]).numel())
+
+    host_rows = host_rows_per_batch()
+    result.update({"host_rows_per_batch": host_rows, "host_link_gbs": round(link, 1)})
+    if host_rows:
+        result["host_link_fraction"] = round(host_rows * row * reps / (t_ms / 1e3) / 1e9 / link, 3)
     if hasattr(arm, "promote_hot_buckets"):
         # the warm-up pass of the workload: the buckets the queries hit most move into HBM
         t0 = time.perf_counter()
         moved = arm.promote_hot_buckets()
         torch.cuda.synchronize()
         promote_ms = (time.perf_counter() - t0) * 1e3
-        t2_ms = time_steps(lambda i: arm.find(qs[i % 4], out, f), reps, 3)
-        assert torch.equal(out[f], rows_for(qs[(reps + 2) % 4], dim)[f]), "rows changed by the promotion"
+        t2_ms = time_steps(lambda i: arm.find(qs[i % n_q], out, f), reps, 3)
+        assert torch.equal(out[f], rows_for(last, dim)[f]), "rows changed by the promotion"
+        after = host_rows_per_batch()
         result.update({"b_kv_s_after_promotion": round(batch * reps / (t2_ms / 1e3) / BINARY_BILLION, 4),
-                       "buckets_promoted": int(moved), "promotion_ms": round(promote_ms, 1)})
+                       "buckets_promoted": int(moved), "promotion_ms": round(promote_ms, 1),
+                       "host_rows_per_batch_after_promotion": after})
     arm.close()
     return {**result,
-            "hit_rate": round(hits, 3),
-            "table": f"capacity {capacity}, dim {dim}, load factor 0.5, 25 % of the rows in HBM, 75 % in pinned host memory",
+            "hit_rate": round(hits, 3), "timed_batches": reps, "attempts": attempts,
+            "table": f"capacity {capacity}, dim {dim}, load factor 0.5, 25 % of the rows in HBM "
+                     f"({capacity * row // 4 >> 30} GiB), 75 % in pinned host memory "
+                     f"({capacity * row * 3 // 4 >> 30} GiB)",
             "queries": "Zipf(1.05) over the inserted keys, 10 % fresh keys; duplicates inside a batch kept"}
 
 
@@ -821,11 +924,24 @@ def cpu_baseline(dim: int, batch: int, seconds_budget: float = 20.0) -> dict:
         reps += 1
         best = dt if best is None else min(best, dt)
     assert f.all()
+    # the metric's second operation on the same sample: insert_or_assign of keys that are
+    # all present (the assign path), same threads
+    upd_reps, upd_spent, upd_best = 0, 0.0, None
+    while upd_spent < 4.0 and upd_reps < 10:
+        t.set_clock((64 + upd_reps) << 22)
+        t1 = time.time()
+        t.insert_or_assign(q, vals, threads=threads)
+        dt = time.time() - t1
+        upd_spent += dt
+        upd_reps += 1
+        upd_best = dt if upd_best is None else min(upd_best, dt)
     return {"value": q.size / best / BINARY_BILLION, "unit": "B-KV/s (n/s/2^30)",
             "cores": threads, "kind": "port",
+            "insert_or_assign_value": round(q.size / upd_best / BINARY_BILLION, 5),
             "sample": f"find, all hits, {q.size} keys x {reps} reps (best), table of "
                       f"{capacity} slots (1/8 of the workload) at load factor "
-                      f"{t.size() / capacity:.3f}, dim {dim}"}
+                      f"{t.size() / capacity:.3f}, dim {dim}; insert_or_assign_value: the same "
+                      f"keys through insert_or_assign (all present), {upd_reps} reps (best)"}
 
 
 # ---------------------------------------------------------------------------

@@ -147,6 +147,17 @@ struct hkv_table {
   std::condition_variable counter_cv;
   uint64_t counter_free = ~0ull;  // bit k set: counter k is free
   StreamGroupLock lock;
+  // Scratch the operations reuse instead of allocating per call: [0] the
+  // deferred-key list of batches that may repeat keys and the sort buffers of
+  // the hybrid find, [1] and [2] widened copies of 32-bit score arrays.
+  struct Workspace {
+    std::mutex mu;
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    cudaStream_t stream = nullptr;   // stream of the last user
+    cudaEvent_t done = nullptr;      // end of the last user's work
+    bool used = false;
+  } workspace[3];
   int device = 0;
   void* meta_block = nullptr;  // digests + slot lines (keys, scores) + sizes + status
   void* host_rows = nullptr;   // host address of the pinned value rows
@@ -228,6 +239,81 @@ class CounterLease {
  private:
   hkv_table* t_;
   int index_;
+};
+
+// Scratch memory for the work one call enqueues on `stream`.  The table's
+// workspace serves it when the previous user ran on the same stream (stream
+// order protects the memory) or has finished; it grows on demand and is never
+// returned before the table is destroyed.  A call that finds the workspace
+// busy on another stream (concurrent readers) gets a stream-ordered allocation
+// of its own instead.  The host mutex is held while the call enqueues.
+class WorkspaceLease {
+ public:
+  WorkspaceLease(hkv_table* t, int which, size_t bytes, cudaStream_t stream)
+      : t_(t), ws_(t->workspace[which]), stream_(stream) {
+    if (bytes == 0) return;
+    ws_.mu.lock();
+    locked_ = true;
+    const bool busy_elsewhere =
+        ws_.used && ws_.stream != stream && cudaEventQuery(ws_.done) != cudaSuccess;
+    if (busy_elsewhere) {
+      ws_.mu.unlock();
+      locked_ = false;
+      if (cudaMallocAsync(&own_, bytes, stream) != cudaSuccess) {
+        cudaGetLastError();
+        own_ = nullptr;   // the caller falls back to its scratch-free form
+      }
+      return;
+    }
+    if (bytes > ws_.bytes) {
+      if (ws_.ptr != nullptr) {
+        if (ws_.used) cudaEventSynchronize(ws_.done);
+        t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, ws_.ptr);
+        ws_.ptr = nullptr;
+        ws_.bytes = 0;
+      }
+      const size_t want = bytes + bytes / 2 + 4096;
+      void* p = nullptr;
+      if (t->alloc.alloc(t->alloc.ctx, HKV_MEM_DEVICE, &p, want, 0) != 0 || p == nullptr) {
+        cudaGetLastError();
+        ws_.mu.unlock();
+        locked_ = false;
+        return;
+      }
+      ws_.ptr = p;
+      ws_.bytes = want;
+    }
+    if (ws_.done == nullptr &&
+        cudaEventCreateWithFlags(&ws_.done, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      ws_.mu.unlock();
+      locked_ = false;
+      return;
+    }
+    shared_ = ws_.ptr;
+  }
+  WorkspaceLease(const WorkspaceLease&) = delete;
+  WorkspaceLease& operator=(const WorkspaceLease&) = delete;
+  ~WorkspaceLease() {
+    if (own_ != nullptr) cudaFreeAsync(own_, stream_);
+    if (locked_) {
+      if (shared_ != nullptr) {
+        ws_.stream = stream_;
+        ws_.used = true;
+        cudaEventRecord(ws_.done, stream_);
+      }
+      ws_.mu.unlock();
+    }
+  }
+  void* get() const { return own_ != nullptr ? own_ : shared_; }
+
+ private:
+  hkv_table* t_;
+  hkv_table::Workspace& ws_;
+  cudaStream_t stream_;
+  void* own_ = nullptr;
+  void* shared_ = nullptr;
+  bool locked_ = false;
 };
 
 struct LockScope {
@@ -315,15 +401,23 @@ hkv::TableView view_for(const hkv_table* t, const void* a, const void* b = nullp
 // 64-bit scores this is the caller's pointer and nothing else.
 class Scores {
  public:
-  Scores(hkv_table* t, const uint64_t* user, uint64_t n, hkv_stream stream, bool is_output)
+  // `which`: the workspace the widened copy lives in (1, or 2 for a call's
+  // second score array)
+  Scores(hkv_table* t, const uint64_t* user, uint64_t n, hkv_stream stream, bool is_output,
+         int which = 1)
       : user_(const_cast<uint64_t*>(user)),
         n_(n),
         stream_(static_cast<cudaStream_t>(stream)),
         output_(is_output),
-        exceptions_(std::uncaught_exceptions()) {
+        exceptions_(std::uncaught_exceptions()),
+        guard_(t->device),
+        lease_(t, which, (user == nullptr || n == 0 || t->opt.score_size == 8) ? 0 : n * sizeof(uint64_t),
+               static_cast<cudaStream_t>(stream)) {
     if (user == nullptr || n == 0 || t->opt.score_size == 8) return;
-    DeviceGuard dg(t->device);
-    HKV_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&wide_), n * sizeof(uint64_t), stream_));
+    wide_ = static_cast<uint64_t*>(lease_.get());
+    if (wide_ == nullptr) {
+      throw HkvError{HKV_ERR_CUDA, "out of device memory for the widened score array"};
+    }
     hkv::launch_widen_scores(reinterpret_cast<const uint32_t*>(user), wide_, n, stream_);
   }
   Scores(const Scores&) = delete;
@@ -333,7 +427,6 @@ class Scores {
     if (output_ && std::uncaught_exceptions() == exceptions_) {
       hkv::launch_narrow_scores(wide_, reinterpret_cast<uint32_t*>(user_), n_, stream_);
     }
-    cudaFreeAsync(wide_, stream_);
   }
   uint64_t* get() const { return wide_ != nullptr ? wide_ : user_; }
 
@@ -344,6 +437,8 @@ class Scores {
   cudaStream_t stream_;
   bool output_;
   int exceptions_;
+  DeviceGuard guard_;      // the lease allocates on the table's device
+  WorkspaceLease lease_;   // released after the narrowing pass was enqueued
 };
 
 // Dual-bucket tables serve insert_or_assign and find and the whole-table scans;
@@ -607,8 +702,9 @@ void mutate(hkv_table* t, int op, hkv::MutateArgs& args, const void* batch_a, co
       reserve(t, t->view.capacity * 2, stream);
     }
   }
+  WorkspaceLease work(t, 0, hkv::mutate_workspace_bytes(op, args.n, unique_key), stream);
   LockScope ls(t, g, stream);
-  hkv::launch_mutate(op, view_for(t, batch_a, batch_b), args, unique_key, stream);
+  hkv::launch_mutate(op, view_for(t, batch_a, batch_b), args, unique_key, stream, work.get());
   ls.done();
   check_launch();
 }
@@ -761,6 +857,10 @@ int hkv_table_destroy(hkv_table* t) {
     if (t->view.values_hbm) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->view.values_hbm);
     if (t->host_rows) t->alloc.free(t->alloc.ctx, HKV_MEM_PINNED, t->host_rows);
     if (t->stage.block) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, t->stage.block);
+    for (auto& w : t->workspace) {
+      if (w.ptr) t->alloc.free(t->alloc.ctx, HKV_MEM_DEVICE, w.ptr);
+      if (w.done) cudaEventDestroy(w.done);
+    }
     for (int i = 0; i < 2; ++i) {
       if (t->stage.stream[i]) cudaStreamDestroy(t->stage.stream[i]);
       if (t->stage.done[i]) cudaEventDestroy(t->stage.done[i]);
@@ -804,7 +904,7 @@ int hkv_insert_and_evict(hkv_table* t, uint64_t n, const uint64_t* keys, const v
     refuse_in_memory_mode(t, "insert_and_evict");
     if (n == 0) return;
     Scores scores_w(t, scores, n, stream, false);
-    Scores evicted_scores_w(t, evicted_scores, n, stream, true);
+    Scores evicted_scores_w(t, evicted_scores, n, stream, true, 2);
     if (t->view.hbm_slots < t->view.capacity) {
       // include/merlin_hashtable.cuh:1384-1386
       throw HkvError{HKV_ERR_RUNTIME, "Only allow insert_and_evict in pure HBM mode."};
@@ -989,11 +1089,15 @@ int hkv_find(hkv_table* t, uint64_t n, const uint64_t* keys, void* values, bool*
     Scores scores_w(t, scores, n, stream, true);
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t work_bytes =
+        t->opt.table_mode == 1 ? 0 : hkv::find_workspace_bytes(t->view, n, values);
+    WorkspaceLease work(t, 0, work_bytes, s);
     LockScope ls(t, kReader, s);
     if (t->opt.table_mode == 1) {
       hkv::launch_dual_find(view_for(t, values), n, keys, values, founds, scores_w.get(), s);
     } else {
-      hkv::launch_find(view_for(t, values), n, keys, values, founds, scores_w.get(), s);
+      hkv::launch_find(view_for(t, values), n, keys, values, founds, scores_w.get(), s,
+                       work.get(), work_bytes);
     }
     ls.done();
     check_launch();

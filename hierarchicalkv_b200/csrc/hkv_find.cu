@@ -286,22 +286,32 @@ __global__ void __launch_bounds__(kFindBlock)
 }
 
 // find on a table with rows in pinned host memory: probe, sort by slot, gather.
-bool launch_find_hybrid(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
-                        bool* founds, uint64_t* scores, cudaStream_t stream) {
-  if (n < 4096 || n >= (1ull << 32)) return false;
+// Only the bits a row place can have are sorted (misses carry kNoSlot, whose
+// low bits are all ones: they end up behind or among the last places, and the
+// gather skips them by value).
+int hybrid_sort_bits(const TableView& t) {
+  int bits = 1;
+  while (bits < 32 && (1ull << bits) < t.capacity) ++bits;
+  return bits;
+}
+
+size_t hybrid_sort_temp_bytes(const TableView& t, uint64_t n) {
   size_t temp_bytes = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, temp_bytes, static_cast<uint32_t*>(nullptr),
                                   static_cast<uint32_t*>(nullptr), static_cast<uint32_t*>(nullptr),
-                                  static_cast<uint32_t*>(nullptr), static_cast<int>(n), 0, 32,
-                                  stream);
+                                  static_cast<uint32_t*>(nullptr), static_cast<int>(n), 0,
+                                  hybrid_sort_bits(t));
+  return temp_bytes;
+}
+
+bool launch_find_hybrid(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
+                        bool* founds, uint64_t* scores, cudaStream_t stream, void* scratch,
+                        size_t scratch_bytes) {
+  if (n < 4096 || n >= (1ull << 32) || scratch == nullptr) return false;
   const size_t arrays = ((n * sizeof(uint32_t)) + 255) & ~size_t(255);
-  uint8_t* work = nullptr;
-  // stream-ordered scratch: concurrent readers on other streams get their own
-  if (cudaMallocAsync(reinterpret_cast<void**>(&work), 4 * arrays + temp_bytes, stream) !=
-      cudaSuccess) {
-    cudaGetLastError();
-    return false;
-  }
+  size_t temp_bytes = hybrid_sort_temp_bytes(t, n);
+  if (4 * arrays + temp_bytes > scratch_bytes) return false;
+  uint8_t* work = static_cast<uint8_t*>(scratch);
   uint32_t* slot = reinterpret_cast<uint32_t*>(work);
   uint32_t* index = reinterpret_cast<uint32_t*>(work + arrays);
   uint32_t* slot_sorted = reinterpret_cast<uint32_t*>(work + 2 * arrays);
@@ -310,19 +320,24 @@ bool launch_find_hybrid(const TableView& t, uint64_t n, const uint64_t* keys, vo
   find_kernel<4, 0><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
       t, keys, n, nullptr, nullptr, founds, scores, nullptr, nullptr, nullptr, slot, index);
   cub::DeviceRadixSort::SortPairs(work + 4 * arrays, temp_bytes, slot, slot_sorted, index,
-                                  index_sorted, static_cast<int>(n), 0, 32, stream);
+                                  index_sorted, static_cast<int>(n), 0, hybrid_sort_bits(t), stream);
   gather_sorted_kernel<<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
       t, n, slot_sorted, index_sorted, static_cast<uint8_t*>(values));
-  cudaFreeAsync(work, stream);
   return true;
 }
 
 }  // namespace
 
+size_t find_workspace_bytes(const TableView& t, uint64_t n, const void* values) {
+  if (t.hbm_slots == t.capacity || values == nullptr || n < 4096 || n >= (1ull << 32)) return 0;
+  const size_t arrays = ((n * sizeof(uint32_t)) + 255) & ~size_t(255);
+  return 4 * arrays + hybrid_sort_temp_bytes(t, n);
+}
+
 void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values, bool* founds,
-                 uint64_t* scores, cudaStream_t stream) {
+                 uint64_t* scores, cudaStream_t stream, void* work, size_t work_bytes) {
   if (t.hbm_slots < t.capacity && values != nullptr &&
-      launch_find_hybrid(t, n, keys, values, founds, scores, stream)) {
+      launch_find_hybrid(t, n, keys, values, founds, scores, stream, work, work_bytes)) {
     return;
   }
   launch_form<0>(t, n, keys, values, nullptr, founds, scores, nullptr, nullptr, nullptr, stream);

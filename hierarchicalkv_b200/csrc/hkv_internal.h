@@ -55,8 +55,12 @@ struct MutateArgs {
   const unsigned int* index_count = nullptr;
 };
 
+// `work` / `work_bytes`: scratch for the sort of the hybrid find
+// (find_workspace_bytes; null: the one-kernel form runs instead).
 void launch_find(const TableView& t, uint64_t n, const uint64_t* keys, void* values, bool* founds,
-                 uint64_t* scores, cudaStream_t stream);
+                 uint64_t* scores, cudaStream_t stream, void* work = nullptr, size_t work_bytes = 0);
+// Scratch find needs for n keys on this table: 0 unless rows live in host memory.
+size_t find_workspace_bytes(const TableView& t, uint64_t n, const void* values);
 void launch_find_ptr(const TableView& t, uint64_t n, const uint64_t* keys, void** ptrs,
                      bool* founds, uint64_t* scores, cudaStream_t stream);
 void launch_find_missed(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
@@ -88,8 +92,12 @@ void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
 
 // unique_key == false selects the serialising kernel that tolerates repeated
 // keys inside one batch.
+// `work`: scratch of mutate_workspace_bytes(op, n, unique_key) bytes for the
+// list of keys the fast kernel leaves to the serialising one (null: batches
+// that may repeat keys run on the serialising kernel alone).
 void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool unique_key,
-                   cudaStream_t stream);
+                   cudaStream_t stream, void* work = nullptr);
+size_t mutate_workspace_bytes(int op, uint64_t n, bool unique_key);
 
 // insert_or_assign / find_or_insert / accum_or_assign over the inbox segments
 // of a key-hash sharded table: one launch per source rank, in the order

@@ -1203,7 +1203,8 @@ void launch_fast(const TableView& t, const MutateArgs& args, uint64_t blocks, cu
 }
 
 template <int OP>
-void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cudaStream_t stream) {
+void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cudaStream_t stream,
+               void* scratch) {
   const uint64_t warps = (args.n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kMutateBlock - 1) / kMutateBlock;
   if (unique_key) {
@@ -1213,10 +1214,8 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
     // and can lock; keys that have to be inserted and keys whose slot another
     // occurrence held at that moment are listed and served by the serialising
     // kernel afterwards (an empty list costs one launch that exits at once).
-    uint8_t* work = nullptr;
-    if (cudaMallocAsync(reinterpret_cast<void**>(&work), args.n * sizeof(uint32_t) + 256, stream) !=
-        cudaSuccess) {
-      cudaGetLastError();
+    uint8_t* work = static_cast<uint8_t*>(scratch);
+    if (work == nullptr) {
       mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
       return;
     }
@@ -1231,7 +1230,6 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
     rest.index_list = list;
     rest.index_count = count;
     mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, rest);
-    cudaFreeAsync(work, stream);
   } else {
     mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
   }
@@ -1239,20 +1237,25 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
 
 }  // namespace
 
+size_t mutate_workspace_bytes(int op, uint64_t n, bool unique_key) {
+  if (unique_key || op == kOpFindOrInsertPtr || op == kOpLockKeys || n >= (1ull << 32)) return 0;
+  return n * sizeof(uint32_t) + 256;   // counter | list of deferred batch positions
+}
+
 void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool unique_key,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, void* work) {
   if (args.n == 0) return;
   switch (op) {
-    case kOpInsertOrAssign: launch_op<kOpInsertOrAssign>(t, args, unique_key, stream); break;
-    case kOpFindOrInsert: launch_op<kOpFindOrInsert>(t, args, unique_key, stream); break;
-    case kOpInsertAndEvict: launch_op<kOpInsertAndEvict>(t, args, unique_key, stream); break;
-    case kOpFindOrInsertPtr: launch_op<kOpFindOrInsertPtr>(t, args, unique_key, stream); break;
-    case kOpAccumOrAssign: launch_op<kOpAccumOrAssign>(t, args, unique_key, stream); break;
-    case kOpAssign: launch_op<kOpAssign>(t, args, unique_key, stream); break;
-    case kOpAssignScores: launch_op<kOpAssignScores>(t, args, unique_key, stream); break;
-    case kOpAssignValues: launch_op<kOpAssignValues>(t, args, unique_key, stream); break;
-    case kOpFindAndUpdate: launch_op<kOpFindAndUpdate>(t, args, unique_key, stream); break;
-    case kOpLockKeys: launch_op<kOpLockKeys>(t, args, unique_key, stream); break;
+    case kOpInsertOrAssign: launch_op<kOpInsertOrAssign>(t, args, unique_key, stream, work); break;
+    case kOpFindOrInsert: launch_op<kOpFindOrInsert>(t, args, unique_key, stream, work); break;
+    case kOpInsertAndEvict: launch_op<kOpInsertAndEvict>(t, args, unique_key, stream, work); break;
+    case kOpFindOrInsertPtr: launch_op<kOpFindOrInsertPtr>(t, args, unique_key, stream, work); break;
+    case kOpAccumOrAssign: launch_op<kOpAccumOrAssign>(t, args, unique_key, stream, work); break;
+    case kOpAssign: launch_op<kOpAssign>(t, args, unique_key, stream, work); break;
+    case kOpAssignScores: launch_op<kOpAssignScores>(t, args, unique_key, stream, work); break;
+    case kOpAssignValues: launch_op<kOpAssignValues>(t, args, unique_key, stream, work); break;
+    case kOpFindAndUpdate: launch_op<kOpFindAndUpdate>(t, args, unique_key, stream, work); break;
+    case kOpLockKeys: launch_op<kOpLockKeys>(t, args, unique_key, stream, work); break;
     default: break;
   }
 }
