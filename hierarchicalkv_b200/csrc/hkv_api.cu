@@ -520,7 +520,7 @@ void free_planes(hkv_table* t, Planes& p) {
 // and clears the new table on `stream`.
 void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& p,
                      cudaStream_t stream) {
-  const uint64_t capacity = buckets * hkv::kBucketSlots;
+  const uint64_t capacity = buckets * v.bucket_slots;
   HKV_CHECK(capacity <= (1ull << 31), "capacity above 2^31 slots is not supported.");
   const uint64_t row_bytes = v.row_bytes;
   v.buckets = buckets;
@@ -532,7 +532,7 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
     const uint64_t off_lines = align256(off_digests + capacity);
     const uint64_t off_sizes = align256(off_lines + capacity * 16);
     const uint64_t off_status = align256(off_sizes + buckets * 4);
-    uint64_t hbm_buckets = t->opt.max_hbm_for_vectors / (row_bytes * hkv::kBucketSlots);
+    uint64_t hbm_buckets = t->opt.max_hbm_for_vectors / (row_bytes * v.bucket_slots);
     if (hbm_buckets > buckets) hbm_buckets = buckets;
     // a table with rows on both sides gets a bucket map and hit counters
     const bool mapped = hbm_buckets > 0 && hbm_buckets < buckets;
@@ -553,7 +553,7 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
     v.bucket_map = mapped ? reinterpret_cast<uint32_t*>(mb + off_map) : nullptr;
     v.bucket_heat = mapped ? reinterpret_cast<uint32_t*>(mb + off_heat) : nullptr;
 
-    v.hbm_slots = hbm_buckets * hkv::kBucketSlots;
+    v.hbm_slots = hbm_buckets * v.bucket_slots;
     v.values_hbm = nullptr;
     v.values_host = nullptr;
     if (v.hbm_slots > 0) {
@@ -596,7 +596,7 @@ uint64_t promote_hot_buckets(hkv_table* t, cudaStream_t s) {
   if (v.bucket_map == nullptr) return 0;
   LockScope ls(t, kInserter, s);
   const uint64_t buckets = v.buckets;
-  const uint32_t hbm_blocks = static_cast<uint32_t>(v.hbm_slots / hkv::kBucketSlots);
+  const uint32_t hbm_blocks = static_cast<uint32_t>(v.hbm_slots / v.bucket_slots);
   std::vector<uint32_t> map(buckets), heat(buckets);
   HKV_CUDA(cudaMemcpyAsync(map.data(), v.bucket_map, buckets * 4, cudaMemcpyDeviceToHost, s));
   HKV_CUDA(cudaMemcpyAsync(heat.data(), v.bucket_heat, buckets * 4, cudaMemcpyDeviceToHost, s));
@@ -650,7 +650,7 @@ float fast_load_factor(hkv_table* t, uint64_t delta, cudaStream_t s) {
   HKV_CUDA(cudaMemcpyAsync(&h, ctr, sizeof(h), cudaMemcpyDeviceToHost, s));
   HKV_CUDA(cudaStreamSynchronize(s));
   return static_cast<float>((delta * 1.0) / (capacity * 1.0) +
-                            (h * 1.0) / (hkv::kBucketSlots * sampled * 1.0));
+                            (h * 1.0) / (t->view.bucket_slots * sampled * 1.0));
 }
 
 // reserve, include/merlin_hashtable.cuh:3503-3545.  Each doubling builds the
@@ -740,8 +740,13 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
               "options.reserved_key_start_bit should >= 0 and <= 62.");
     HKV_CHECK(o.max_bucket_size != 0 && (o.max_bucket_size & (o.max_bucket_size - 1)) == 0,
               "Bucket size should be the pow of 2");
-    HKV_CHECK(o.max_bucket_size == hkv::kBucketSlots,
-              "only max_bucket_size == 128 is supported by this library.");
+    // the reference takes any power of two whose key and score lines are
+    // 128-byte aligned (include/merlin_hashtable.cuh:1032-1048); here a bucket
+    // holds 16 to 1024 slots, and dual-bucket tables keep the default 128
+    HKV_CHECK(o.max_bucket_size >= 16 && o.max_bucket_size <= hkv::kMaxBucketSlots,
+              "max_bucket_size should be a power of two between 16 and 1024.");
+    HKV_CHECK(o.table_mode == 0 || o.max_bucket_size == uint64_t(hkv::kBucketSlots),
+              "[MEMORY_MODE] dual-bucket tables need max_bucket_size == 128.");
     HKV_CHECK(o.num_of_buckets_per_alloc != 0 &&
                   (o.num_of_buckets_per_alloc & (o.num_of_buckets_per_alloc - 1)) == 0,
               "Then `num_of_buckets_per_alloc` should be the pow of 2");
@@ -780,16 +785,19 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
       const uint64_t max_size = o.init_capacity > o.max_capacity ? o.init_capacity : o.max_capacity;
       uint64_t buckets;
       if (o.init_capacity * 2 > max_size) {
-        buckets = 1 + (max_size - 1) / hkv::kBucketSlots;
+        buckets = 1 + (max_size - 1) / o.max_bucket_size;
       } else {
         buckets = 1;
-        while (buckets * hkv::kBucketSlots < o.init_capacity) buckets *= 2;
+        while (buckets * o.max_bucket_size < o.init_capacity) buckets *= 2;
       }
       const uint64_t row_bytes = o.dim * uint64_t(o.value_size);
       HKV_CHECK(row_bytes < (1ull << 24), "value rows above 16 MiB are not supported.");
       t->reach_max_capacity.store(o.init_capacity * 2 > o.max_capacity || o.table_mode == 1);
 
       hkv::TableView& v = t->view;
+      v.bucket_slots = uint32_t(o.max_bucket_size);
+      v.bucket_shift = 0;
+      while ((1u << v.bucket_shift) < v.bucket_slots) ++v.bucket_shift;
       v.row_bytes = uint32_t(row_bytes);
       v.vec_bytes = widest_vec(row_bytes);
       v.chunks_per_row = uint32_t(row_bytes / v.vec_bytes);
@@ -1252,6 +1260,9 @@ int hkv_find_routed(hkv_table* t, uint32_t world, uint32_t my_rank, uint64_t seg
     if (world == 0 || world > hkv::kMaxPeers || my_rank >= world) {
       throw HkvError{HKV_ERR_INVALID_ARG, "world size must be between 1 and 16"};
     }
+    if (!hkv::line_buckets(t->view)) {
+      throw HkvError{HKV_ERR_UNSUPPORTED, "the routed form needs max_bucket_size == 128"};
+    }
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     hkv::PeerPtrs ov{}, of{};
@@ -1292,9 +1303,11 @@ int hkv_upsert_routed(hkv_table* t, int op, uint32_t world, uint32_t my_rank,
       throw HkvError{HKV_ERR_INVALID_ARG, "segment_capacity must be a multiple of 32"};
     }
     check_strategy(t, t->opt.evict_strategy, nullptr);  // only the score-free strategies pass
-    if (t->view.hbm_slots < t->view.capacity || !t->reach_max_capacity.load()) {
+    if (t->view.hbm_slots < t->view.capacity || !t->reach_max_capacity.load() ||
+        !hkv::line_buckets(t->view)) {
       throw HkvError{HKV_ERR_UNSUPPORTED,
-                     "the routed form needs a pure-HBM table of fixed capacity"};
+                     "the routed form needs a pure-HBM table of fixed capacity with "
+                     "max_bucket_size == 128"};
     }
     DeviceGuard dg(t->device);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1526,6 +1539,7 @@ int hkv_get_view(const hkv_table* t, hkv_table_view* view) {
     view->hbm_slots = v.hbm_slots;
     view->bucket_map = v.bucket_map;
     view->row_bytes = v.row_bytes;
+    view->max_bucket_size = v.bucket_slots;
     view->empty_key = v.empty_key;
     view->reclaim_key = v.reclaim_key;
     view->locked_key = v.locked_key;

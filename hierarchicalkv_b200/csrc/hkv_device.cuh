@@ -36,7 +36,11 @@
 
 namespace hkv {
 
-constexpr int kBucketSlots = 128;        // slots per bucket (one digest line)
+// Slots per bucket of the tables the warp-parallel kernels serve (one digest
+// line).  Tables created with another max_bucket_size run the bucket-size
+// generic kernels (find_generic_kernel, mutate_serial_kernel).
+constexpr int kBucketSlots = 128;
+constexpr uint32_t kMaxBucketSlots = 1024;
 constexpr int kGroupLanes = 8;           // lanes that probe one bucket
 constexpr int kKeysPerPass = 4;          // buckets probed per warp instruction
 constexpr int kPasses = 8;               // passes to cover a warp's 32 keys
@@ -87,7 +91,9 @@ struct TableView {
   int32_t* bucket_sizes;
   uint32_t* status;       // device status word (kStatus* bits)
   uint64_t buckets;
-  uint64_t capacity;      // buckets * 128
+  uint64_t capacity;      // buckets * bucket_slots
+  uint32_t bucket_slots;  // slots per bucket: a power of two, 16 ... 1024 (128 by default)
+  uint32_t bucket_shift;  // log2(bucket_slots)
   uint64_t hbm_slots;
   uint32_t row_bytes;     // dim * sizeof(V)
   uint32_t vec_bytes;     // widest power-of-two access usable on a row
@@ -134,8 +140,8 @@ __device__ __forceinline__ Address locate(const TableView& t, uint64_t key) {
   const uint64_t h = fmix64(key);
   const uint64_t g = t.capacity_pow2 ? (h & (t.capacity - 1)) : (h % t.capacity);
   Address a;
-  a.bucket = g >> 7;
-  a.start = static_cast<uint32_t>(g) & (kBucketSlots - 1);
+  a.bucket = g >> t.bucket_shift;
+  a.start = static_cast<uint32_t>(g) & (t.bucket_slots - 1u);
   a.digest = static_cast<uint32_t>(h >> 32) & 0xFFu;
   return a;
 }
@@ -185,11 +191,15 @@ inline bool fast_rows(const TableView& t) {
   return t.vec_bytes == 16 && t.hbm_slots == t.capacity && t.bucket_map == nullptr;
 }
 
+// Host side: do the kernels built around the 128-byte digest line serve this table?
+inline bool line_buckets(const TableView& t) { return t.bucket_slots == uint32_t(kBucketSlots); }
+
 // Where slot's row lives: the slot itself, or its place in the row block the
 // bucket map assigns to the slot's bucket.
 __device__ __forceinline__ uint64_t row_slot(const TableView& t, uint64_t slot) {
   if (t.bucket_map == nullptr) return slot;
-  return (uint64_t(t.bucket_map[slot >> 7]) << 7) | (slot & (kBucketSlots - 1));
+  return (uint64_t(t.bucket_map[slot >> t.bucket_shift]) << t.bucket_shift) |
+         (slot & (t.bucket_slots - 1u));
 }
 
 __device__ __forceinline__ uint8_t* row_ptr_of_row_slot(const TableView& t, uint64_t rs) {
@@ -599,6 +609,31 @@ __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batc
     case 4: warp_move_rows_vec<4, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
     case 2: warp_move_rows_vec<2, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
     default: warp_move_rows_vec<1, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
+  }
+}
+
+// Copies one row with all 32 lanes (used for the few rows that do not follow
+// the warp's batch order, e.g. refused inputs leaving through the evicted
+// arrays).
+template <int VEC = 0>
+__device__ __forceinline__ void warp_copy_one_row(const TableView& t, uint8_t* dst,
+                                                  const uint8_t* src, uint32_t lane) {
+  const uint32_t vec = VEC != 0 ? uint32_t(VEC) : t.vec_bytes;
+  const uint32_t cpr = t.chunks_per_row;
+  if (vec == 16) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+  } else if (vec == 8) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
+  } else if (vec == 4) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
+  } else if (vec == 2) {
+    for (uint32_t c = lane; c < cpr; c += 32)
+      reinterpret_cast<uint16_t*>(dst)[c] = reinterpret_cast<const uint16_t*>(src)[c];
+  } else {
+    for (uint32_t c = lane; c < cpr; c += 32) dst[c] = src[c];
   }
 }
 

@@ -249,11 +249,77 @@ __global__ void __launch_bounds__(kFindBlock)
   if (values != nullptr) warp_move_rows<0>(t, values + base * t.row_bytes, slot, pl.lane);
 }
 
+// Lookups on a table whose buckets are not one 128-byte digest line
+// (max_bucket_size of 16 ... 1024 other than 128; the reference serves them
+// with its tile kernels, include/merlin/core_kernels/lookup.cuh:873-925): one
+// warp per key walks the bucket's digests four per lane and 128 per step,
+// verifies the candidates' keys and copies the row with all 32 lanes.  Same
+// forms as find_kernel.
+template <int FORM>
+__global__ void __launch_bounds__(kFindBlock)
+    find_generic_kernel(const TableView t, const uint64_t* __restrict__ keys, const uint64_t n,
+                        uint8_t* __restrict__ values, void** __restrict__ ptrs,
+                        bool* __restrict__ founds, uint64_t* __restrict__ scores,
+                        uint64_t* __restrict__ missed_keys, int* __restrict__ missed_indices,
+                        int* __restrict__ missed_size) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t i = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (i >= n) return;
+  const uint64_t key = keys[i];
+  uint32_t slot = kNoSlot;
+  if (!is_reserved(t, key)) {
+    const Address a = locate(t, key);
+    const uint64_t slot0 = a.bucket << t.bucket_shift;
+    const uint32_t pattern = replicate4(a.digest);
+    for (uint32_t first = 0; first < t.bucket_slots && slot == kNoSlot; first += 128u) {
+      const uint32_t at = first + lane * 4u;
+      uint32_t hit = kNoSlot;
+      if (at < t.bucket_slots) {
+        uint32_t m = match4(*reinterpret_cast<const uint32_t*>(t.digests + slot0 + at), pattern);
+        while (m) {
+          const uint32_t pos = at + (__ffs(m) - 1);
+          m &= m - 1;
+          if (ld_relaxed(key_ptr(t, slot0 + pos)) == key) {
+            hit = uint32_t(slot0) + pos;
+            break;
+          }
+        }
+      }
+      const uint32_t votes = __ballot_sync(0xFFFFFFFFu, hit != kNoSlot);
+      if (votes) slot = __shfl_sync(0xFFFFFFFFu, hit, __ffs(votes) - 1);
+    }
+  }
+  const bool found = slot != kNoSlot;
+  if (lane == 0) {
+    if (FORM != 2) founds[i] = found;
+    if (FORM == 1) ptrs[i] = found ? row_ptr(t, slot) : nullptr;
+    if (FORM != 3 && scores != nullptr && found) scores[i] = *score_ptr(t, slot);
+    if (FORM != 3 && found && t.bucket_heat != nullptr && (uint32_t(i) & 3u) == 0) {
+      atomicAdd(t.bucket_heat + (slot >> t.bucket_shift), 1u);
+    }
+    if (FORM == 2 && !found) {
+      const int at = atomicAdd(missed_size, 1);
+      missed_keys[at] = key;
+      missed_indices[at] = static_cast<int>(i);
+    }
+  }
+  if ((FORM == 0 || FORM == 2) && found && values != nullptr) {
+    warp_copy_one_row<0>(t, values + i * t.row_bytes, row_ptr(t, slot), lane);
+  }
+}
+
 template <int FORM>
 void launch_form(const TableView& t, uint64_t n, const uint64_t* keys, void* values, void** ptrs,
                  bool* founds, uint64_t* scores, uint64_t* missed_keys, int* missed_indices,
                  int* missed_size, cudaStream_t stream) {
   if (n == 0) return;
+  if (!line_buckets(t)) {
+    const uint64_t blocks = (n * 32 + kFindBlock - 1) / kFindBlock;
+    find_generic_kernel<FORM><<<static_cast<unsigned>(blocks), kFindBlock, 0, stream>>>(
+        t, keys, n, static_cast<uint8_t*>(values), ptrs, founds, scores, missed_keys,
+        missed_indices, missed_size);
+    return;
+  }
   const uint64_t warps = (n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kFindBlock - 1) / kFindBlock;
   auto kernel = fast_rows(t) ? find_kernel<FORM, 16> : find_kernel<FORM, 0>;
@@ -307,7 +373,7 @@ size_t hybrid_sort_temp_bytes(const TableView& t, uint64_t n) {
 bool launch_find_hybrid(const TableView& t, uint64_t n, const uint64_t* keys, void* values,
                         bool* founds, uint64_t* scores, cudaStream_t stream, void* scratch,
                         size_t scratch_bytes) {
-  if (n < 4096 || n >= (1ull << 32) || scratch == nullptr) return false;
+  if (n < 4096 || n >= (1ull << 32) || scratch == nullptr || !line_buckets(t)) return false;
   const size_t arrays = ((n * sizeof(uint32_t)) + 255) & ~size_t(255);
   size_t temp_bytes = hybrid_sort_temp_bytes(t, n);
   if (4 * arrays + temp_bytes > scratch_bytes) return false;
@@ -329,7 +395,10 @@ bool launch_find_hybrid(const TableView& t, uint64_t n, const uint64_t* keys, vo
 }  // namespace
 
 size_t find_workspace_bytes(const TableView& t, uint64_t n, const void* values) {
-  if (t.hbm_slots == t.capacity || values == nullptr || n < 4096 || n >= (1ull << 32)) return 0;
+  if (t.hbm_slots == t.capacity || values == nullptr || n < 4096 || n >= (1ull << 32) ||
+      !line_buckets(t)) {
+    return 0;
+  }
   const size_t arrays = ((n * sizeof(uint32_t)) + 255) & ~size_t(255);
   return 4 * arrays + hybrid_sort_temp_bytes(t, n);
 }

@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(kScanBlock)
       *key_ptr(t, slot) = t.reclaim_key;
       t.digests[slot] = static_cast<uint8_t>(t.reclaim_digest);
       *score_ptr(t, slot) = 0;
-      atomicSub(t.bucket_sizes + (slot >> 7), 1);
+      atomicSub(t.bucket_sizes + (slot >> t.bucket_shift), 1);
       ++local;
     }
   }
@@ -152,7 +152,9 @@ __global__ void __launch_bounds__(kScanBlock) clear_kernel(const TableView t) {
       const bool key_half = ((q >> 2) & 1) == 0;
       w[q] = key_half ? make_ulonglong2(t.empty_key, t.empty_key) : make_ulonglong2(0ull, 0ull);
     }
-    if ((g & 7u) == 0) t.bucket_sizes[g >> 3] = 0;
+    // the thread that clears a bucket's first 16 slots also clears its size
+    const uint64_t groups_per_bucket = t.bucket_slots / 16u;
+    if (g % groups_per_bucket == 0) t.bucket_sizes[g / groups_per_bucket] = 0;
   }
 }
 
@@ -164,18 +166,20 @@ __global__ void __launch_bounds__(kScanBlock) clear_kernel(const TableView t) {
 // (a compacted bucket; tombstones are dropped).  Lookups and inserts probe the
 // whole digest line, so any position inside the bucket is valid.  Rows are then
 // copied one per warp instruction group, coalesced.
-constexpr int kRehashBlock = kBucketSlots;
-constexpr int kRehashWarps = kRehashBlock / 32;
+// The block has max(32, bucket_slots) threads; thread i carries old slot i.
+constexpr int kRehashMaxWarps = kMaxBucketSlots / 32;
 
-__global__ void __launch_bounds__(kRehashBlock)
+__global__ void __launch_bounds__(kMaxBucketSlots)
     rehash_kernel(const TableView src, const TableView dst) {
-  __shared__ uint32_t side_count[2][kRehashWarps];
+  __shared__ uint32_t side_count[2][kRehashMaxWarps];
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t wid = threadIdx.x >> 5;
+  const uint32_t warps = blockDim.x >> 5;
   const uint32_t below = (1u << lane) - 1u;
   for (uint64_t b = blockIdx.x; b < src.buckets; b += gridDim.x) {
-    const uint64_t slot = b * kBucketSlots + threadIdx.x;
-    const uint64_t key = *key_ptr(src, slot);
+    const bool in_bucket = threadIdx.x < src.bucket_slots;
+    const uint64_t slot = b * src.bucket_slots + (in_bucket ? threadIdx.x : 0u);
+    const uint64_t key = in_bucket ? *key_ptr(src, slot) : src.empty_key;
     const bool live = !is_reserved(src, key);
     const Address a = locate(dst, key);
     const bool high = live && a.bucket != b;
@@ -190,15 +194,14 @@ __global__ void __launch_bounds__(kRehashBlock)
     for (uint32_t w = 0; w < wid; ++w) rank += side_count[high ? 1 : 0][w];
     uint64_t to = 0;
     if (live) {
-      to = a.bucket * kBucketSlots + rank;
+      to = a.bucket * dst.bucket_slots + rank;
       *key_ptr(dst, to) = key;
       dst.digests[to] = static_cast<uint8_t>(a.digest);
       *score_ptr(dst, to) = *score_ptr(src, slot);
     }
     if (threadIdx.x < 2) {
       uint32_t total = 0;
-#pragma unroll
-      for (int w = 0; w < kRehashWarps; ++w) total += side_count[threadIdx.x][w];
+      for (uint32_t w = 0; w < warps; ++w) total += side_count[threadIdx.x][w];
       dst.bucket_sizes[b + threadIdx.x * src.buckets] = static_cast<int32_t>(total);
     }
     // rows: the warp walks its live lanes; all 32 lanes copy one row together
@@ -240,18 +243,18 @@ __global__ void __launch_bounds__(kScanBlock) decay_heat_kernel(const TableView 
 }
 
 // One block per pair (a, b) of buckets: the two buckets trade row blocks --
-// the 128 rows of each are copied to the other's place (16-byte chunks,
+// the rows of each are copied to the other's place (16-byte chunks,
 // coalesced; one of the two places is pinned host memory) and the map entries
 // are exchanged.  Runs under the exclusive lock.
 __global__ void __launch_bounds__(kScanBlock)
     swap_row_blocks_kernel(const TableView t, const uint32_t* __restrict__ pairs,
                            const uint64_t n_pairs) {
-  const uint64_t block_bytes = uint64_t(kBucketSlots) * t.row_bytes;
+  const uint64_t block_bytes = uint64_t(t.bucket_slots) * t.row_bytes;
   for (uint64_t p = blockIdx.x; p < n_pairs; p += gridDim.x) {
     const uint32_t a = pairs[2 * p], b = pairs[2 * p + 1];
     const uint32_t place_a = t.bucket_map[a], place_b = t.bucket_map[b];
-    uint8_t* rows_a = row_ptr_of_row_slot(t, uint64_t(place_a) << 7);
-    uint8_t* rows_b = row_ptr_of_row_slot(t, uint64_t(place_b) << 7);
+    uint8_t* rows_a = row_ptr_of_row_slot(t, uint64_t(place_a) << t.bucket_shift);
+    uint8_t* rows_b = row_ptr_of_row_slot(t, uint64_t(place_b) << t.bucket_shift);
     if (t.row_bytes % 16 == 0) {
       for (uint64_t off = uint64_t(threadIdx.x) * 16; off < block_bytes;
            off += uint64_t(blockDim.x) * 16) {
@@ -360,7 +363,8 @@ void launch_narrow_scores(const uint64_t* in, uint32_t* out, uint64_t n, cudaStr
 }
 
 void launch_rehash(const TableView& src, const TableView& dst, cudaStream_t stream) {
-  rehash_kernel<<<scan_grid(1, src.buckets), kRehashBlock, 0, stream>>>(src, dst);
+  const unsigned threads = src.bucket_slots < 32u ? 32u : src.bucket_slots;
+  rehash_kernel<<<scan_grid(1, src.buckets), threads, 0, stream>>>(src, dst);
 }
 
 }  // namespace hkv

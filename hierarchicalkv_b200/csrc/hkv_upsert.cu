@@ -220,31 +220,6 @@ __device__ __forceinline__ void group_min_score(const TableView& t, const ProbeL
   group_reduce_min(group_mask(pl.group), pl.sub, ms, mp, gmin, gpos);
 }
 
-// Copies one row with all 32 lanes (used for the few rows that do not follow
-// the warp's batch order, e.g. refused inputs leaving through the evicted
-// arrays).
-template <int VEC = 0>
-__device__ __forceinline__ void warp_copy_one_row(const TableView& t, uint8_t* dst,
-                                                  const uint8_t* src, uint32_t lane) {
-  const uint32_t vec = VEC != 0 ? uint32_t(VEC) : t.vec_bytes;
-  const uint32_t cpr = t.chunks_per_row;
-  if (vec == 16) {
-    for (uint32_t c = lane; c < cpr; c += 32)
-      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
-  } else if (vec == 8) {
-    for (uint32_t c = lane; c < cpr; c += 32)
-      reinterpret_cast<uint2*>(dst)[c] = reinterpret_cast<const uint2*>(src)[c];
-  } else if (vec == 4) {
-    for (uint32_t c = lane; c < cpr; c += 32)
-      reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
-  } else if (vec == 2) {
-    for (uint32_t c = lane; c < cpr; c += 32)
-      reinterpret_cast<uint16_t*>(dst)[c] = reinterpret_cast<const uint16_t*>(src)[c];
-  } else {
-    for (uint32_t c = lane; c < cpr; c += 32) dst[c] = src[c];
-  }
-}
-
 // One warp serves 32 keys.
 //   phase 0  own key: hash, bucket, digest, incoming score, bucket fill
 //   phase 1  all eight digest lines in flight, then all first candidates: a
@@ -748,7 +723,9 @@ __global__ void __launch_bounds__(kMutateBlock)
     const bool is_accum = OP == kOpAccumOrAssign ? args.accum_flags[i] : false;
     const bool lock_on_hit = OP == kOpAccumOrAssign ? is_accum : true;
     const bool insert_on_miss = OP == kOpAccumOrAssign ? !is_accum : op_inserts(OP);
-    const uint64_t slot0 = a.bucket << 7;
+    const uint64_t slot0 = a.bucket << t.bucket_shift;
+    const uint32_t bucket_slots = t.bucket_slots;
+    const uint32_t steps = (bucket_slots + 31u) >> 5;  // 32 slots per step, at most 32 steps
 
     uint32_t result = kInitial;
     uint32_t pos = 0;
@@ -761,16 +738,16 @@ __global__ void __launch_bounds__(kMutateBlock)
         result = kRefused;
         break;
       }
-      // lane l looks at slots l, l+32, l+64, l+96
-      uint64_t k4[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) k4[c] = ld_acquire(key_ptr(t, slot0 + c * 32 + lane));
+      // lane l looks at slots l, l + 32, l + 64, ... (bit c of the masks: step c)
       uint32_t eq = 0, locked = 0, empty = 0;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        eq |= (k4[c] == key) ? (1u << c) : 0u;
-        locked |= (k4[c] == t.locked_key) ? (1u << c) : 0u;
-        empty |= (k4[c] == t.empty_key) ? (1u << c) : 0u;
+      for (uint32_t c = 0; c < steps; ++c) {
+        const uint32_t at = c * 32u + lane;
+        if (at < bucket_slots) {
+          const uint64_t k = ld_acquire(key_ptr(t, slot0 + at));
+          eq |= (k == key) ? (1u << c) : 0u;
+          locked |= (k == t.locked_key) ? (1u << c) : 0u;
+          empty |= (k == t.empty_key) ? (1u << c) : 0u;
+        }
       }
       const uint32_t any_eq = __ballot_sync(full, eq != 0);
       if (any_eq) {
@@ -797,17 +774,16 @@ __global__ void __launch_bounds__(kMutateBlock)
         break;
       }
       // first EMPTY slot in probe order from a.start
-      uint32_t best = 255u;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      uint32_t best = kNoSlot;
+      for (uint32_t c = 0; c < steps; ++c) {
         if ((empty >> c) & 1u) {
-          const uint32_t d = (uint32_t(c) * 32u + lane - a.start) & (kBucketSlots - 1);
+          const uint32_t d = (c * 32u + lane - a.start) & (bucket_slots - 1u);
           best = min(best, d);
         }
       }
       const uint32_t gbest = __reduce_min_sync(full, best);
-      if (gbest != 255u) {
-        const uint32_t p = (a.start + gbest) & (kBucketSlots - 1);
+      if (gbest != kNoSlot) {
+        const uint32_t p = (a.start + gbest) & (bucket_slots - 1u);
         uint32_t ok = 0;
         if (lane == 0) ok = cas_acquire(key_ptr(t, slot0 + p), t.empty_key, t.locked_key) == t.empty_key;
         ok = __shfl_sync(full, ok, 0);
@@ -818,23 +794,25 @@ __global__ void __launch_bounds__(kMutateBlock)
         continue;
       }
       // full bucket: minimum score, first position on ties
-      uint64_t s4[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) s4[c] = ld_relaxed(score_ptr(t, slot0 + c * 32 + lane));
-      uint64_t ms = s4[0];
-      uint32_t mp = lane;
-#pragma unroll
-      for (int c = 1; c < 4; ++c) {
-        if (s4[c] < ms) {
-          ms = s4[c];
-          mp = c * 32 + lane;
+      uint64_t ms = kMaxScore;
+      uint32_t mp = kNoSlot;
+      for (uint32_t c = 0; c < steps; ++c) {
+        const uint32_t at = c * 32u + lane;
+        if (at < bucket_slots) {
+          const uint64_t sc = ld_relaxed(score_ptr(t, slot0 + at));
+          if (mp == kNoSlot || sc < ms) {
+            ms = sc;
+            mp = at;
+          }
         }
       }
-      const uint32_t hi = uint32_t(ms >> 32);
+      // lanes beyond a small bucket hold no score: they take no part in the minimum
+      const bool has = mp != kNoSlot;
+      const uint32_t hi = has ? uint32_t(ms >> 32) : 0xFFFFFFFFu;
       const uint32_t ghi = __reduce_min_sync(full, hi);
-      const uint32_t lo = hi == ghi ? uint32_t(ms) : 0xFFFFFFFFu;
+      const uint32_t lo = (has && hi == ghi) ? uint32_t(ms) : 0xFFFFFFFFu;
       const uint32_t glo = __reduce_min_sync(full, lo);
-      const uint32_t cp = (hi == ghi && lo == glo) ? mp : 255u;
+      const uint32_t cp = (has && hi == ghi && lo == glo) ? mp : kNoSlot;
       const uint32_t gpos = __reduce_min_sync(full, cp);
       const uint64_t gmin = (uint64_t(ghi) << 32) | glo;
       const bool refuse = (OP == kOpFindOrInsertPtr) ? (desired <= gmin) : (desired < gmin);
@@ -977,19 +955,28 @@ __global__ void __launch_bounds__(kMutateBlock)
   const uint64_t key = keys[warp];
   if (is_reserved(t, key)) return;
   const Address a = locate(t, key);
-  const uint64_t slot0 = a.bucket << 7;
-  const uint32_t d4 = reinterpret_cast<const uint32_t*>(t.digests + slot0)[lane];
-  uint32_t m = match4(d4, replicate4(a.digest));
-  while (m) {
-    const uint32_t pos = lane * 4 + (__ffs(m) - 1);
-    m &= m - 1;
-    if (cas_acquire(key_ptr(t, slot0 + pos), key, t.locked_key) == key) {
-      st_u8_cg(t.digests + slot0 + pos, t.reclaim_digest);
-      st_relaxed(score_ptr(t, slot0 + pos), 0);
-      atomicSub(t.bucket_sizes + a.bucket, 1);
-      st_release(key_ptr(t, slot0 + pos), t.reclaim_key);
-      break;
+  const uint64_t slot0 = a.bucket << t.bucket_shift;
+  // four digests per lane, 128 slots per step
+  for (uint32_t first = 0; first < t.bucket_slots; first += 128u) {
+    const uint32_t at = first + lane * 4u;
+    bool erased = false;
+    if (at < t.bucket_slots) {
+      const uint32_t d4 = *reinterpret_cast<const uint32_t*>(t.digests + slot0 + at);
+      uint32_t m = match4(d4, replicate4(a.digest));
+      while (m) {
+        const uint32_t pos = at + (__ffs(m) - 1);
+        m &= m - 1;
+        if (cas_acquire(key_ptr(t, slot0 + pos), key, t.locked_key) == key) {
+          st_u8_cg(t.digests + slot0 + pos, t.reclaim_digest);
+          st_relaxed(score_ptr(t, slot0 + pos), 0);
+          atomicSub(t.bucket_sizes + a.bucket, 1);
+          st_release(key_ptr(t, slot0 + pos), t.reclaim_key);
+          erased = true;
+          break;
+        }
+      }
     }
+    if (__any_sync(0xFFFFFFFFu, erased)) break;
   }
 }
 
@@ -1207,7 +1194,12 @@ void launch_op(const TableView& t, const MutateArgs& args, bool unique_key, cuda
                void* scratch) {
   const uint64_t warps = (args.n + 31) / 32;
   const uint64_t blocks = (warps * 32 + kMutateBlock - 1) / kMutateBlock;
-  if (unique_key) {
+  if (!line_buckets(t)) {
+    // buckets that are not one 128-byte digest line: the serialising kernel
+    // walks buckets of any size (the reference's own fallback for them are its
+    // tile kernels, e.g. include/merlin/core_kernels/upsert.cuh:1233-1305)
+    mutate_serial_kernel<OP><<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+  } else if (unique_key) {
     launch_fast<OP>(t, args, blocks, stream);
   } else if (OP != kOpFindOrInsertPtr && OP != kOpLockKeys && args.n < (1ull << 32)) {
     // Repeated keys are allowed.  The fast kernel serves every key it finds

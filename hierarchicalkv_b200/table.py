@@ -95,6 +95,7 @@ class TableView(ctypes.Structure):
         ("locked_key", ctypes.c_uint64),
         ("reserved_mask", ctypes.c_uint64),
         ("reserved_value", ctypes.c_uint64),
+        ("max_bucket_size", ctypes.c_uint64),
     ]
 
 

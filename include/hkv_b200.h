@@ -71,7 +71,7 @@ typedef struct hkv_options {
   uint64_t init_capacity;
   uint64_t max_capacity;
   uint64_t max_hbm_for_vectors; /* bytes; 0 puts every value row in pinned host memory */
-  uint64_t max_bucket_size;     /* only 128 is supported */
+  uint64_t max_bucket_size;     /* a power of two, 16 ... 1024; 128 runs the tuned kernels */
   uint64_t dim;
   float max_load_factor;
   int32_t block_size;
@@ -122,7 +122,7 @@ typedef enum hkv_predicate {
 #define HKV_SLOT_WORD(slot) \
   ((((uint64_t)(slot) >> 3) << 4) | ((uint64_t)(slot) & 7u))
 typedef struct hkv_table_view {
-  uint8_t* digests;      /* [buckets][128] */
+  uint8_t* digests;      /* [buckets][max_bucket_size] */
   /* Keys and scores share one plane of 128-byte lines: a line holds the keys
    * of 8 consecutive slots followed by their 8 scores (a slot's lock word and
    * its score are written together by every update, so they sit in one line).
@@ -132,14 +132,15 @@ typedef struct hkv_table_view {
   uint8_t* values_hbm;   /* rows of row slots [0, hbm_slots) */
   uint8_t* values_host;  /* rows of row slots [hbm_slots, capacity), mapped pinned */
   int32_t* bucket_sizes; /* [buckets] */
-  uint32_t* bucket_map;  /* null, or [buckets]: the row of slot s is row slot
-                            bucket_map[s / 128] * 128 + s % 128 (hybrid tables) */
+  uint32_t* bucket_map;  /* null, or [buckets]: with B = max_bucket_size the row of slot s is
+                            row slot bucket_map[s / B] * B + s % B (hybrid tables) */
   uint64_t buckets;
   uint64_t capacity;
   uint64_t hbm_slots;
   uint64_t row_bytes;
   uint64_t empty_key, reclaim_key, locked_key;
   uint64_t reserved_mask, reserved_value; /* reserved iff (key & mask) == value */
+  uint64_t max_bucket_size; /* slots per bucket: bucket of slot s is s / max_bucket_size */
 } hkv_table_view;
 
 /* Message of the last failing call on this thread. */

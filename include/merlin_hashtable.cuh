@@ -138,7 +138,10 @@ __device__ __forceinline__ bool view_is_reserved(const hkv_table_view& v, uint64
 }
 
 __device__ __forceinline__ const uint8_t* view_row(const hkv_table_view& v, uint64_t slot) {
-  if (v.bucket_map != nullptr) slot = (uint64_t(v.bucket_map[slot >> 7]) << 7) | (slot & 127u);
+  if (v.bucket_map != nullptr) {
+    const uint64_t b = v.max_bucket_size;
+    slot = uint64_t(v.bucket_map[slot / b]) * b + slot % b;
+  }
   return slot < v.hbm_slots ? v.values_hbm + slot * v.row_bytes
                             : v.values_host + (slot - v.hbm_slots) * v.row_bytes;
 }
@@ -244,7 +247,7 @@ __global__ void erase_if_kernel(const hkv_table_view v, const K pattern, const S
       v.keys[HKV_SLOT_WORD(slot)] = v.reclaim_key;
       v.digests[slot] = reclaim_digest;
       v.scores[HKV_SLOT_WORD(slot)] = 0;
-      atomicSub(v.bucket_sizes + (slot >> 7), 1);
+      atomicSub(v.bucket_sizes + slot / v.max_bucket_size, 1);
       ++local;
     }
   }
@@ -332,8 +335,8 @@ __global__ void erase_if_v2_kernel(const hkv_table_view v, PredFunctor pred, con
     const uint32_t votes = g.ballot(match);
     if (g.thread_rank() == 0 && votes) {
       atomicAdd(d_counter, static_cast<unsigned long long>(__popc(votes)));
-      // G divides 128: a tile never straddles two buckets
-      atomicSub(v.bucket_sizes + (slot >> 7), __popc(votes));
+      // G divides the bucket size (a power of two >= 16): a tile never straddles two buckets
+      atomicSub(v.bucket_sizes + slot / v.max_bucket_size, __popc(votes));
     }
     if (match) {
       v.keys[HKV_SLOT_WORD(slot)] = v.reclaim_key;
@@ -774,7 +777,8 @@ class HashTable : public HashTableBase<K, V, S> {
     if (rc == HKV_OK && err == cudaSuccess) {
       const uint8_t reclaim_digest = static_cast<uint8_t>(Murmur3HashHost(v.reclaim_key) >> 32);
       const uint64_t n = v.capacity;
-      detail::dispatch_tile(options_.dim, n, [&](auto tile) {
+      // a tile must not straddle two buckets: its size is capped by the bucket size
+      detail::dispatch_tile(std::min<uint64_t>(options_.dim, v.max_bucket_size), n, [&](auto tile) {
         detail::erase_if_v2_kernel<K, V, S, PredFunctor, decltype(tile)::value>
             <<<detail::tile_scan_blocks(n), 128, 0, stream>>>(v, pred, n, reclaim_digest, d_count);
       });

@@ -19,6 +19,7 @@
 #include <string>
 
 #include "merlin_hashtable.cuh"
+#include "merlin_localfile.hpp"
 
 #ifndef REF_STRATEGY
 #define REF_STRATEGY 0
@@ -112,9 +113,18 @@ REF_API int ref_create(uint64_t init_capacity, uint64_t max_capacity,
     o.max_bucket_size = max_bucket_size;
     o.reserved_key_start_bit = reserved_key_start_bit;
     o.api_lock = api_lock != 0;
-    // One allocation for all buckets' metadata instead of one per bucket.
+    // One allocation for all buckets instead of one per bucket.  The reference
+    // places whole allocations in HBM while max_hbm_for_vectors lasts
+    // (include/merlin/core_kernels.cuh:204-232), so a table whose rows only
+    // partly fit gets allocations small enough for the HBM share to be used.
     size_t buckets = 1;
     while (buckets * 2 * max_bucket_size <= init_capacity) buckets *= 2;
+    const uint64_t row_bytes = dim * sizeof(V);
+    while (buckets > 1 && max_hbm_for_vectors > 0 &&
+           max_hbm_for_vectors < init_capacity * row_bytes &&
+           buckets * max_bucket_size * row_bytes > max_hbm_for_vectors) {
+      buckets /= 2;
+    }
     o.num_of_buckets_per_alloc = buckets;
     auto* t = new Table();
     try {
@@ -192,6 +202,34 @@ REF_API int ref_set_max_capacity(void* t, uint64_t new_max_capacity) {
     g_err = e.what();
     return -1;
   }
+}
+
+// save / load through the reference's own LocalKVFile
+// (include/merlin_localfile.hpp:44-158): <prefix>.keys / .values / .scores.
+REF_API int ref_save(void* t, const char* prefix, uint64_t max_workspace_size,
+                     cudaStream_t stream, uint64_t* saved) {
+  return guarded([&] {
+    nv::merlin::LocalKVFile<K, V, S> file;
+    const std::string p(prefix);
+    if (!file.open(p + ".keys", p + ".values", p + ".scores", "wb")) {
+      throw std::runtime_error("cannot open " + p + ".* for writing");
+    }
+    *saved = static_cast<Table*>(t)->save(&file, max_workspace_size, stream);
+    file.close();
+  });
+}
+
+REF_API int ref_load(void* t, const char* prefix, uint64_t max_workspace_size,
+                     cudaStream_t stream, uint64_t* loaded) {
+  return guarded([&] {
+    nv::merlin::LocalKVFile<K, V, S> file;
+    const std::string p(prefix);
+    if (!file.open(p + ".keys", p + ".values", p + ".scores", "rb")) {
+      throw std::runtime_error("cannot open " + p + ".* for reading");
+    }
+    *loaded = static_cast<Table*>(t)->load(&file, max_workspace_size, stream);
+    file.close();
+  });
 }
 
 REF_API int ref_destroy(void* t) {

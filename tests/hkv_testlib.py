@@ -79,6 +79,7 @@ def bucket_of(keys: np.ndarray, capacity: int) -> np.ndarray:
 # ---------------------------------------------------------------------------
 _ORACLE_SIGS = {
     "orc_create": ([_U64, _U64, _U64, ctypes.c_uint32, _INT, _INT], _P),
+    "orc_create_sized": ([_U64, _U64, _U64, ctypes.c_uint32, _INT, _INT, _INT], _P),
     "orc_destroy": ([_P], None),
     "orc_reserve": ([_P, _U64], None),
     "orc_set_max_capacity": ([_P, _U64], _INT),
@@ -142,12 +143,13 @@ class OracleTable:
 
     def __init__(self, capacity: int, dim: int, strategy: int = 0, reserved_key_start_bit: int = 0,
                  max_capacity: Optional[int] = None, value_size: int = 4,
-                 max_load_factor: Optional[float] = None, memory_mode: bool = False):
+                 max_load_factor: Optional[float] = None, memory_mode: bool = False,
+                 max_bucket_size: int = 128):
         self.lib = load_oracle()
         self.dim = dim
         self.strategy = strategy
-        self.h = self.lib.orc_create(capacity, max_capacity or capacity, dim, value_size, strategy,
-                                     reserved_key_start_bit)
+        self.h = self.lib.orc_create_sized(capacity, max_capacity or capacity, dim, value_size,
+                                           strategy, reserved_key_start_bit, max_bucket_size)
         if max_load_factor is not None:
             self.lib.orc_set_max_load_factor(self.h, max_load_factor)
         if memory_mode:
@@ -284,7 +286,7 @@ class ProductTable:
 
     def __init__(self, capacity, dim, strategy=0, reserved_key_start_bit=0, max_capacity=None,
                  max_hbm_for_vectors=None, api_lock=True, max_load_factor=None,
-                 memory_mode=False):
+                 memory_mode=False, max_bucket_size=128):
         import torch
         import hierarchicalkv_b200 as hkv
 
@@ -299,7 +301,7 @@ class ProductTable:
         self.t.init(hkv.HashTableOptions(
             init_capacity=capacity, max_capacity=max_capacity or capacity,
             max_hbm_for_vectors=hbm, dim=dim, reserved_key_start_bit=reserved_key_start_bit,
-            api_lock=api_lock, **extra))
+            api_lock=api_lock, max_bucket_size=max_bucket_size, **extra))
 
     def reserve(self, new_capacity):
         self.t.reserve(new_capacity, self.torch.cuda.current_stream().cuda_stream)
@@ -490,6 +492,8 @@ def load_ref(strategy: int, private: bool = False) -> ctypes.CDLL:
         "ref_destroy": [_P],
         "ref_create_growable": [_U64, _U64, _U64, _U64, ctypes.c_float, ctypes.POINTER(_P)],
         "ref_reserve": [_P, _U64, _P],
+        "ref_save": [_P, ctypes.c_char_p, _U64, _P, ctypes.POINTER(_U64)],
+        "ref_load": [_P, ctypes.c_char_p, _U64, _P, ctypes.POINTER(_U64)],
         "ref_set_max_capacity": [_P, _U64],
         "ref_create_memory_mode": [_U64, _U64, ctypes.POINTER(_P)],
         "ref_set_global_epoch": [_P, _U64],
@@ -532,7 +536,7 @@ class RefTable:
 
     def __init__(self, capacity, dim, strategy=0, reserved_key_start_bit=0, max_capacity=None,
                  max_hbm_for_vectors=None, api_lock=True, max_load_factor=None,
-                 memory_mode=False):
+                 memory_mode=False, max_bucket_size=128):
         import torch
 
         self.torch = torch
@@ -548,12 +552,25 @@ class RefTable:
             self._chk(self.lib.ref_create_growable(capacity, max_capacity or capacity, hbm, dim,
                                                    max_load_factor, ctypes.byref(self.h)))
         else:
-            self._chk(self.lib.ref_create(capacity, max_capacity or capacity, hbm, dim, 128,
-                                          reserved_key_start_bit, int(api_lock),
+            self._chk(self.lib.ref_create(capacity, max_capacity or capacity, hbm, dim,
+                                          max_bucket_size, reserved_key_start_bit, int(api_lock),
                                           ctypes.byref(self.h)))
 
     def reserve(self, new_capacity):
         self._chk(self.lib.ref_reserve(self.h, new_capacity, self._s()))
+
+    def save(self, prefix: str, max_workspace_size: int = 1 << 20) -> int:
+        """HashTable::save into <prefix>.keys / .values / .scores with the reference's LocalKVFile"""
+        out = _U64(0)
+        self._chk(self.lib.ref_save(self.h, prefix.encode(), max_workspace_size, self._s(),
+                                    ctypes.byref(out)))
+        return out.value
+
+    def load(self, prefix: str, max_workspace_size: int = 1 << 20) -> int:
+        out = _U64(0)
+        self._chk(self.lib.ref_load(self.h, prefix.encode(), max_workspace_size, self._s(),
+                                    ctypes.byref(out)))
+        return out.value
 
     def set_max_capacity(self, new_max_capacity):
         rc = self.lib.ref_set_max_capacity(self.h, new_max_capacity)

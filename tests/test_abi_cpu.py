@@ -54,7 +54,10 @@ def test_each_declaration_cites_the_reference():
     (dict(reserved_key_start_bit=63), hkv.MerlinException, "reserved_key_start_bit"),
     (dict(reserved_key_start_bit=-1), hkv.MerlinException, "reserved_key_start_bit"),
     (dict(max_bucket_size=100), hkv.MerlinException, "pow of 2"),
-    (dict(max_bucket_size=256), hkv.MerlinException, "128"),
+    (dict(max_bucket_size=8), hkv.MerlinException, "between 16 and 1024"),
+    (dict(max_bucket_size=2048, init_capacity=4096, max_capacity=4096), hkv.MerlinException,
+     "between 16 and 1024"),
+    (dict(table_mode=1, max_bucket_size=256), hkv.MerlinException, "max_bucket_size == 128"),
     (dict(num_of_buckets_per_alloc=3), hkv.MerlinException, "num_of_buckets_per_alloc"),
     (dict(init_capacity=128, max_capacity=128, num_of_buckets_per_alloc=2), hkv.MerlinException,
      "num_of_buckets_per_alloc"),
