@@ -149,7 +149,9 @@ struct hkv_table {
   StreamGroupLock lock;
   // Scratch the operations reuse instead of allocating per call: [0] the
   // deferred-key list of batches that may repeat keys and the sort buffers of
-  // the hybrid find, [1] and [2] widened copies of 32-bit score arrays.
+  // the hybrid find, [1] and [2] widened copies of 32-bit score arrays, [3]
+  // the request chains of the routed updates (kept in its all-empty state
+  // between calls, so it has a workspace of its own).
   struct Workspace {
     std::mutex mu;
     void* ptr = nullptr;
@@ -157,7 +159,10 @@ struct hkv_table {
     cudaStream_t stream = nullptr;   // stream of the last user
     cudaEvent_t done = nullptr;      // end of the last user's work
     bool used = false;
-  } workspace[3];
+  } workspace[4];
+  // shape of the last routed update: another shape lays the scratch out anew
+  uint32_t routed_world = 0;
+  uint64_t routed_segment_capacity = 0;
   int device = 0;
   void* meta_block = nullptr;  // digests + slot lines (keys, scores) + sizes + status
   void* host_rows = nullptr;   // host address of the pinned value rows
@@ -263,6 +268,7 @@ class WorkspaceLease {
         cudaGetLastError();
         own_ = nullptr;   // the caller falls back to its scratch-free form
       }
+      fresh_ = true;
       return;
     }
     if (bytes > ws_.bytes) {
@@ -282,6 +288,7 @@ class WorkspaceLease {
       }
       ws_.ptr = p;
       ws_.bytes = want;
+      fresh_ = true;
     }
     if (ws_.done == nullptr &&
         cudaEventCreateWithFlags(&ws_.done, cudaEventDisableTiming) != cudaSuccess) {
@@ -306,10 +313,13 @@ class WorkspaceLease {
     }
   }
   void* get() const { return own_ != nullptr ? own_ : shared_; }
+  // the memory was obtained by this lease: nothing an earlier call left is in it
+  bool fresh() const { return fresh_; }
 
  private:
   hkv_table* t_;
   hkv_table::Workspace& ws_;
+  bool fresh_ = false;
   cudaStream_t stream_;
   void* own_ = nullptr;
   void* shared_ = nullptr;
@@ -1316,11 +1326,30 @@ int hkv_upsert_routed(hkv_table* t, int op, uint32_t world, uint32_t my_rank,
       pv.p[r] = values->p[r];
       pf.p[r] = accum_flags != nullptr ? accum_flags->p[r] : nullptr;
     }
-    hkv::MutateArgs a = base_args(t, 0, inbox_keys, nullptr, nullptr, false);
-    a.row_index = inbox_origin;
+    if (segment_capacity > (1ull << hkv::kRowTagShift)) {
+      throw HkvError{HKV_ERR_INVALID_ARG, "segment_capacity above 2^28 keys"};
+    }
+    hkv::MutateArgs a = base_args(t, 0, nullptr, nullptr, nullptr, false);
+    hkv::RoutedArgs r;
+    r.world = world;
+    r.first_segment = (my_rank + 1) % world;
+    r.segment_capacity = segment_capacity;
+    r.inbox_keys = inbox_keys;
+    r.inbox_origin = inbox_origin;
+    r.inbox_counts = inbox_counts;
+    r.values_of = pv;
+    r.flags_of = pf;
+    WorkspaceLease work(t, 3, hkv::routed_workspace_bytes(world, segment_capacity), s);
+    if (work.get() == nullptr) {
+      throw HkvError{HKV_ERR_CUDA, "out of device memory for the request chains of the routed update"};
+    }
+    const bool same_shape =
+        t->routed_world == world && t->routed_segment_capacity == segment_capacity;
+    t->routed_world = world;
+    t->routed_segment_capacity = segment_capacity;
+    hkv::prepare_routed_workspace(t->view, r, work.get(), work.fresh() || !same_shape, s);
     LockScope ls(t, kInserter, s);
-    hkv::launch_mutate_routed(kernel_op, t->view, a, world, (my_rank + 1) % world,
-                              segment_capacity, inbox_counts, pv, pf, s);
+    hkv::launch_mutate_routed(kernel_op, t->view, a, r, s);
     ls.done();
     check_launch();
   });

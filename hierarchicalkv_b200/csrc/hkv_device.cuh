@@ -45,6 +45,8 @@ constexpr int kGroupLanes = 8;           // lanes that probe one bucket
 constexpr int kKeysPerPass = 4;          // buckets probed per warp instruction
 constexpr int kPasses = 8;               // passes to cover a warp's 32 keys
 constexpr uint32_t kNoSlot = 0xFFFFFFFFu;
+constexpr uint32_t kRowTagShift = 28;              // routed form: row tag = rank << 28 | row
+constexpr uint32_t kRowTagMask = (1u << kRowTagShift) - 1u;
 constexpr uint64_t kMaxScore = 0xFFFFFFFFFFFFFFFFull;
 constexpr uint64_t kIgnoredEpoch = 0xFFFFFFFFFFFFFFFFull;
 constexpr uint32_t kSpinLimit = 1u << 22;    // polls of one slot before a wait gives up (about a second)
@@ -443,22 +445,31 @@ __device__ __forceinline__ void warp_accumulate_row(uint8_t* row, const uint8_t*
 // MODE 2: table += batch, float32 elements (needs VEC % 4 == 0); the other
 //         element types go through warp_accumulate_rows
 //
-// INDEXED: the batch rows are not the warp's 32 consecutive rows; lane r holds
-// in `row_index` which row of `batch_rows` belongs to it.  `batch_rows` may
-// then be another GPU's memory and is accessed with plain loads and stores.
+// INDEXED (the routed form of the sharded table): the batch rows are not the
+// warp's 32 consecutive rows.  Lane r holds in `row_index` a row tag: bits
+// 28-31 name the source rank, bits 0-27 the row in that rank's batch buffer,
+// whose address is bases[rank].  Those buffers may be other GPUs' memory and
+// are accessed with plain loads and stores.
 //
 // PURE: every row is in HBM at its slot's own place (no host rows, no bucket
 // map), which the launcher checks before it picks such an instantiation.
 template <int VEC, int MODE, bool INDEXED = false, bool PURE = false>
 __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* batch_rows,
                                                    uint32_t slot, uint32_t lane,
-                                                   uint32_t row_index = 0) {
+                                                   uint32_t row_index = 0,
+                                                   uint8_t* const* bases = nullptr) {
   using T = typename VecType<VEC>::type;
-  constexpr int U = (VEC == 16) ? 8 : 4;  // chunks in flight per lane
+  // Chunks in flight per lane.  Accumulation holds two values per chunk (the
+  // delta and the stored chunk: both are loaded before anything is written, so
+  // the stored chunks of a pass arrive together instead of one after the
+  // other) and the routed form keeps a second address per chunk: four instead
+  // of eight for those.
+  constexpr int U = (VEC == 16 && MODE != 2 && !INDEXED) ? 8 : 4;
   const uint32_t cpr = t.chunks_per_row;
   const uint32_t total = cpr * 32u;
   for (uint32_t base = 0; base < total; base += 32u * U) {
     T regs[U];
+    T stored[MODE == 2 ? U : 1];
     uint8_t* tab[U];
     uint8_t* bat[U];
     bool ok[U];
@@ -475,7 +486,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
                               : row_ptr_of_row_slot(t, rs)) + off;
       if (INDEXED) {
         const uint32_t at = __shfl_sync(0xFFFFFFFFu, row_index, r & 31u);
-        bat[u] = batch_rows + uint64_t(at) * t.row_bytes + off;
+        bat[u] = bases[at >> kRowTagShift] + uint64_t(at & kRowTagMask) * t.row_bytes + off;
       }
       if (ok[u]) {
         if (MODE == 0) {
@@ -485,6 +496,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
         } else {
           regs[u] = ld_stream(reinterpret_cast<const T*>(batch_rows + size_t(c) * VEC));
         }
+        if (MODE == 2) stored[MODE == 2 ? u : 0] = *reinterpret_cast<const T*>(tab[u]);
       }
     }
 #pragma unroll
@@ -501,7 +513,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
           st_stream(reinterpret_cast<T*>(tab[u]), regs[u]);
         } else {
           if constexpr (VEC % 4 == 0) {
-            T cur = *reinterpret_cast<const T*>(tab[u]);
+            T cur = stored[MODE == 2 ? u : 0];
             float* a = reinterpret_cast<float*>(&cur);
             const float* b = reinterpret_cast<const float*>(&regs[u]);
 #pragma unroll
@@ -580,7 +592,8 @@ __device__ __forceinline__ void warp_gather_rows_to(const TableView& t, uint8_t*
 template <int MODE, int VEC = 0, bool INDEXED = false>
 __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
                                                uint32_t slot, uint32_t lane,
-                                               uint32_t row_index = 0) {
+                                               uint32_t row_index = 0,
+                                               uint8_t* const* bases = nullptr) {
   if constexpr (MODE == 2) {
     if (t.value_kind > kValueF32) {
       // the rarer element types: one row after the other, all lanes on one row
@@ -590,25 +603,27 @@ __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batc
         todo &= todo - 1;
         const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r);
         const uint32_t at = INDEXED ? __shfl_sync(0xFFFFFFFFu, row_index, r) : r;
-        warp_accumulate_row(row_ptr(t, s), batch_rows + uint64_t(at) * t.row_bytes, t.row_bytes,
-                            t.value_kind, lane);
+        const uint8_t* delta = INDEXED ? bases[at >> kRowTagShift] +
+                                             uint64_t(at & kRowTagMask) * t.row_bytes
+                                       : batch_rows + uint64_t(at) * t.row_bytes;
+        warp_accumulate_row(row_ptr(t, s), delta, t.row_bytes, t.value_kind, lane);
       }
       return;
     }
   }
   if constexpr (VEC != 0) {
     // the fixed-width instantiations serve pure-HBM tables only
-    warp_move_rows_vec<VEC, MODE, INDEXED, true>(t, batch_rows, slot, lane, row_index);
+    warp_move_rows_vec<VEC, MODE, INDEXED, true>(t, batch_rows, slot, lane, row_index, bases);
     return;
   }
   // vec_bytes is warp-uniform; the host lowers it when a batch pointer is
   // less aligned than the rows.
   switch (t.vec_bytes) {
-    case 16: warp_move_rows_vec<16, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
-    case 8: warp_move_rows_vec<8, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
-    case 4: warp_move_rows_vec<4, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
-    case 2: warp_move_rows_vec<2, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
-    default: warp_move_rows_vec<1, MODE, INDEXED>(t, batch_rows, slot, lane, row_index); break;
+    case 16: warp_move_rows_vec<16, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    case 8: warp_move_rows_vec<8, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    case 4: warp_move_rows_vec<4, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    case 2: warp_move_rows_vec<2, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    default: warp_move_rows_vec<1, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
   }
 }
 

@@ -100,14 +100,38 @@ void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool uniq
 size_t mutate_workspace_bytes(int op, uint64_t n, bool unique_key);
 
 // insert_or_assign / find_or_insert / accum_or_assign over the inbox segments
-// of a key-hash sharded table: one launch per source rank, in the order
-// first_segment, first_segment + 1, ... (wrapping), so that keys requested by
-// several ranks are applied one rank after the other.  args.keys / row_index
-// point at segment 0; values_of / flags_of give each source rank's buffers.
-void launch_mutate_routed(int op, const TableView& t, const MutateArgs& args, uint32_t world,
-                          uint32_t first_segment, uint64_t segment_capacity,
-                          const uint64_t* inbox_counts, const PeerPtrs& values_of,
-                          const PeerPtrs& flags_of, cudaStream_t stream);
+// of a key-hash sharded table (segment s: the keys source rank s sent, each
+// with the row it has in that rank's batch buffer).  A key that several ranks
+// sent is applied as if those ranks had called the table one after the other
+// in the order first_segment, first_segment + 1, ... (wrapping): the requests
+// for one key are chained in a scratch hash table first, the first rank in
+// that order serves the key in the warp-parallel kernel and applies the other
+// ranks' requests behind its own while it holds the slot.
+struct RoutedArgs {
+  uint32_t world = 0;
+  uint32_t first_segment = 0;
+  uint64_t segment_capacity = 0;       // a multiple of 32, at most 2^28
+  const uint64_t* inbox_keys = nullptr;
+  const uint32_t* inbox_origin = nullptr;
+  const uint64_t* inbox_counts = nullptr;
+  PeerPtrs values_of{};                // each source rank's batch rows
+  PeerPtrs flags_of{};                 // accum_or_assign: each source rank's flags
+  // grouping scratch (routed_workspace_bytes): an open-addressing set of the
+  // inbox's keys, the head of each key's request chain, and per inbox entry
+  // the next request for the same key and the set slot of its key
+  uint64_t* set_keys = nullptr;
+  uint32_t* set_head = nullptr;
+  uint32_t* next = nullptr;
+  uint32_t* set_slot = nullptr;
+  uint32_t set_bits = 0;               // log2 of the set's size
+};
+size_t routed_workspace_bytes(uint32_t world, uint64_t segment_capacity);
+// Carves `work` into the scratch arrays of `r`; `fresh`: the memory is new and
+// is put into the all-empty state the calls leave behind.
+void prepare_routed_workspace(const TableView& t, RoutedArgs& r, void* work, bool fresh,
+                              cudaStream_t stream);
+void launch_mutate_routed(int op, const TableView& t, const MutateArgs& args, const RoutedArgs& r,
+                          cudaStream_t stream);
 
 void launch_unlock_keys(const TableView& t, uint64_t n, uint64_t** locked_key_ptrs,
                         const uint64_t* keys, bool* success, cudaStream_t stream);

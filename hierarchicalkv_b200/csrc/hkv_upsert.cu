@@ -252,9 +252,49 @@ __host__ __device__ constexpr int mutate_min_blocks(int op) {
              : kMutateMinBlocks;
 }
 
+// What the routed form knows about the tile a warp serves.
+constexpr uint32_t kMaxRequests = 16;     // requests for one key in one call: one per rank
+constexpr uint32_t kNoEntry = 0xFFFFFFFFu;
+struct RoutedWarp {
+  const RoutedArgs* r;
+  uint32_t segment;                        // source rank of the tile's keys
+  uint8_t* const* values_of;               // shared-memory copies of the ranks' buffers
+  const bool* const* flags_of;
+  uint32_t (*requests)[kMutateBlock];      // per thread: its key's requests in turn order
+};
+
+// Turn of source rank `segment`: the owner applies rank first_segment first.
+__device__ __forceinline__ uint32_t turn_of(const RoutedArgs& r, uint32_t segment) {
+  return segment >= r.first_segment ? segment - r.first_segment
+                                    : segment + r.world - r.first_segment;
+}
+__device__ __forceinline__ uint32_t segment_of(const RoutedArgs& r, uint32_t turn) {
+  const uint32_t s = turn + r.first_segment;
+  return s >= r.world ? s - r.world : s;
+}
+
+// Requests `from` .. `count - 1` of each lane's key that are selected by
+// `which` (bit r: request r), one after the other: MODE 0 copies the slot's row
+// into the requesting rank's buffer, MODE 2 adds that rank's row to the slot's.
+// All lanes call it; a lane without a slot passes kNoSlot.
+template <int MODE, int VEC>
+__device__ __forceinline__ void serve_requests(const TableView& t, const RoutedWarp* rw,
+                                               uint32_t slot, uint32_t from, uint32_t count,
+                                               uint32_t which, uint32_t lane) {
+  const uint32_t most = __reduce_max_sync(0xFFFFFFFFu, slot != kNoSlot ? count : 0u);
+  for (uint32_t q = 0; q < most; ++q) {
+    const bool mine = slot != kNoSlot && q >= from && q < count && ((which >> q) & 1u);
+    if (__ballot_sync(0xFFFFFFFFu, mine) == 0) continue;
+    const uint32_t tag = mine ? rw->requests[q][threadIdx.x] : 0u;
+    warp_move_rows<MODE, VEC, true>(t, nullptr, mine ? slot : kNoSlot, lane, tag, rw->values_of);
+    __syncwarp();  // request q + 1 of a key sees what request q did to its row
+  }
+}
+
 template <int OP, int VEC, bool INDEXED>
 __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs& args,
-                                            const uint64_t base, const uint64_t n) {
+                                            const uint64_t base, const uint64_t n,
+                                            const RoutedWarp* rw = nullptr) {
   const uint32_t full = 0xFFFFFFFFu;
   const ProbeLane pl = probe_lane();
   const uint64_t i = base + pl.lane;
@@ -268,7 +308,12 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
   uint32_t mode = 0;
   uint32_t bucket_full = 0;  // the key's bucket has no EMPTY slot left (inserting operations)
   Address a{0, 0, 0};
-  uint32_t my_row = 0;  // INDEXED: this key's row in the source rank's buffer
+  uint32_t my_row = 0;  // INDEXED: tag of the row this key is written from / read into
+  // INDEXED: the requests for this key (this lane's own and those of the ranks
+  // whose turn comes later): how many, which of them accumulate (bit r: request
+  // r), and the first that assigns (kMaxRequests: none)
+  uint32_t n_requests = 1, accumulating = 0, first_assign = kMaxRequests;
+  uint8_t* const* const bases = INDEXED ? rw->values_of : nullptr;
   // Batches that may repeat a key (unique_key == false): this kernel only
   // serves keys it finds and can lock.  A key that meets a LOCKED candidate
   // slot (another occurrence may hold it) and every key that would have to be
@@ -276,19 +321,73 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
   // args.deferred_list for the serialising kernel that runs next.
   const bool tolerant = !INDEXED && args.deferred_list != nullptr;
   bool defer_me = false;
-  uint8_t* const batch_rows = INDEXED ? args.values : args.values + base * t.row_bytes;
-  if (i < n) {
-    key = args.keys[i];
-    if (INDEXED) my_row = args.row_index[i];
+  uint8_t* const batch_rows = INDEXED ? nullptr : args.values + base * t.row_bytes;
+  bool serves = true;  // INDEXED: this lane is the first in turn order to ask for its key
+  if (INDEXED && i < n) {
+    // This lane's inbox entry and the chain of all requests for its key.  The
+    // lane whose rank comes first in turn order serves the key; it keeps the
+    // chain, sorted by turn, in its column of rw->requests as turn << 28 | row.
+    const RoutedArgs& r = *rw->r;
+    const uint64_t entry = uint64_t(rw->segment) * r.segment_capacity + i;
+    key = r.inbox_keys[entry];
+    const uint32_t my_turn = turn_of(r, rw->segment);
     if (!is_reserved(t, key)) {
+      n_requests = 0;
+      uint32_t hops = 0;
+      for (uint32_t e = r.set_head[r.set_slot[entry]]; e != kNoEntry && hops < 4 * kMaxRequests;
+           e = r.next[e], ++hops) {
+        const uint32_t seg = uint32_t(e / r.segment_capacity);
+        const uint32_t turn = turn_of(r, seg);
+        if (turn < my_turn || (turn == my_turn && e < entry)) serves = false;
+        if (n_requests < kMaxRequests) {
+          // insertion into the sorted column
+          const uint32_t word = (turn << kRowTagShift) | r.inbox_origin[e];
+          uint32_t at = n_requests++;
+          while (at > 0 && rw->requests[at - 1][threadIdx.x] > word) {
+            rw->requests[at][threadIdx.x] = rw->requests[at - 1][threadIdx.x];
+            --at;
+          }
+          rw->requests[at][threadIdx.x] = word;
+        }
+      }
+      if (n_requests == 0) serves = false;  // cannot happen: the chain holds this entry
+    }
+  }
+  if (i < n) {
+    if (!INDEXED) key = args.keys[i];
+    if (!is_reserved(t, key) && serves) {
       mode = kModeValid;
       a = locate(t, key);
       if (args.scores != nullptr) in_score = args.scores[i];
       if (op_inserts(OP) || OP == kOpLockKeys) {
         desired = desired_score(strategy, args.scores, in_score, args.epoch);
       }
-      if (OP == kOpAccumOrAssign) {
-        const bool is_accum = args.accum_flags[INDEXED ? uint64_t(my_row) : i];
+      if (INDEXED) {
+        // rows are named by rank << 28 | row
+        const RoutedArgs& r = *rw->r;
+        for (uint32_t q = 0; q < n_requests; ++q) {
+          const uint32_t word = rw->requests[q][threadIdx.x];
+          const uint32_t tag =
+              (segment_of(r, word >> kRowTagShift) << kRowTagShift) | (word & kRowTagMask);
+          rw->requests[q][threadIdx.x] = tag;
+          if (OP == kOpAccumOrAssign) {
+            const bool is_accum = rw->flags_of[tag >> kRowTagShift][tag & kRowTagMask];
+            if (is_accum) accumulating |= 1u << q;
+            else if (first_assign == kMaxRequests) first_assign = q;
+          }
+        }
+        // insert_or_assign: the last rank's row is what stays; find_or_insert: the
+        // first rank's row is inserted; accum_or_assign: the first assigning rank's
+        my_row = rw->requests[OP == kOpInsertOrAssign ? n_requests - 1
+                              : (OP == kOpAccumOrAssign && first_assign != kMaxRequests)
+                                  ? first_assign
+                                  : 0][threadIdx.x];
+      }
+      if (OP == kOpAccumOrAssign && INDEXED) {
+        if (accumulating) mode |= kModeLockOnHit;
+        if (first_assign != kMaxRequests) mode |= kModeInsertOnMiss;
+      } else if (OP == kOpAccumOrAssign) {
+        const bool is_accum = args.accum_flags[i];
         mode |= is_accum ? kModeLockOnHit : kModeInsertOnMiss;
         // a batch that may repeat keys: two occurrences of a new key must not
         // both insert it, so assigning keys go to the serialising kernel
@@ -491,19 +590,34 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
     if (OP == kOpInsertOrAssign || OP == kOpInsertAndEvict || OP == kOpAssign ||
         OP == kOpAssignValues) {
       warp_move_rows<1, VEC, INDEXED>(t, batch_rows, holds_lock ? my_slot : kNoSlot, pl.lane,
-                                      my_row);
+                                      my_row, bases);
     } else if (OP == kOpFindOrInsert) {
       warp_move_rows<0, VEC, INDEXED>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot,
-                                      pl.lane, my_row);
+                                      pl.lane, my_row, bases);
       warp_move_rows<1, VEC, INDEXED>(t, batch_rows,
                                       my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane,
-                                      my_row);
-    } else if (OP == kOpAccumOrAssign) {
-      warp_move_rows<2, VEC, INDEXED>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot,
-                                      pl.lane, my_row);
-      warp_move_rows<1, VEC, INDEXED>(t, batch_rows,
-                                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane,
-                                      my_row);
+                                      my_row, bases);
+      if constexpr (INDEXED) {
+        // the ranks whose turn comes later find the key: they get the row
+        __syncwarp();
+        serve_requests<0, VEC>(t, rw, holds_lock ? my_slot : kNoSlot, 1u, n_requests, ~0u, pl.lane);
+      }
+    } else if (OP == kOpAccumOrAssign && !INDEXED) {
+      warp_move_rows<2, VEC, false>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot,
+                                    pl.lane, my_row);
+      warp_move_rows<1, VEC, false>(t, batch_rows,
+                                    my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane,
+                                    my_row);
+    } else if constexpr (OP == kOpAccumOrAssign && INDEXED) {
+      // a key that was there: every accumulating request adds, in turn order; a
+      // new key: the first assigning request's row went in (my_row), the
+      // accumulating requests behind it add
+      warp_move_rows<1, VEC, true>(t, batch_rows, my_result == kOccupiedEmpty ? my_slot : kNoSlot,
+                                   pl.lane, my_row, bases);
+      __syncwarp();
+      serve_requests<2, VEC>(t, rw, holds_lock ? my_slot : kNoSlot,
+                             my_result == kDuplicate ? 0u : first_assign + 1u, n_requests,
+                             accumulating, pl.lane);
     }
     __syncwarp();
     if (holds_lock && !keep_locked) st_release(key_ptr(t, my_slot), key);
@@ -626,7 +740,16 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
       }
       if (op_writes_row_on_insert(OP)) {
         warp_move_rows<1, VEC, INDEXED>(t, batch_rows, placed ? my_slot : kNoSlot, pl.lane,
-                                        my_row);
+                                        my_row, bases);
+      }
+      if constexpr (INDEXED && OP == kOpFindOrInsert) {
+        __syncwarp();
+        serve_requests<0, VEC>(t, rw, placed ? my_slot : kNoSlot, 1u, n_requests, ~0u, pl.lane);
+      }
+      if constexpr (INDEXED && OP == kOpAccumOrAssign) {
+        __syncwarp();
+        serve_requests<2, VEC>(t, rw, placed ? my_slot : kNoSlot, first_assign + 1u, n_requests,
+                               accumulating, pl.lane);
       }
       __syncwarp();
       if (placed && !(OP == kOpFindOrInsertPtr && keep_locked)) st_release(key_ptr(t, my_slot), key);
@@ -660,25 +783,124 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
   }
 }
 
-// The local form serves one warp of 32 consecutive keys per launched warp.  The
-// routed form learns the number of keys from device memory, so its grid is a
-// fixed number of resident blocks that stride over the segment.
 template <int OP, int VEC, bool INDEXED>
 __global__ void __launch_bounds__(kMutateBlock, mutate_min_blocks(OP))
     mutate_kernel(const TableView t, const MutateArgs args) {
-  static_assert(!INDEXED || OP == kOpInsertOrAssign || OP == kOpFindOrInsert ||
-                    OP == kOpAccumOrAssign,
-                "the routed form exists for the three operations the sharded table routes");
+  static_assert(!INDEXED, "the routed form is mutate_routed_kernel");
   const uint64_t warp = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  if (!INDEXED) {
-    if (warp * 32u < args.n) mutate_warp<OP, VEC, INDEXED>(t, args, warp * 32u, args.n);
-  } else {
-    const uint64_t n = min(args.n, *args.n_device);
-    const uint64_t stride = uint64_t(gridDim.x) * blockDim.x;
-    for (uint64_t base = warp * 32u; base < n; base += stride) {
-      mutate_warp<OP, VEC, INDEXED>(t, args, base, n);
-      __syncwarp();  // the warp's columns of the parked probe results are reused
+  if (warp * 32u < args.n) mutate_warp<OP, VEC, false>(t, args, warp * 32u, args.n);
+}
+
+// ---- the routed form ------------------------------------------------------------
+//
+// Tiles of 128 inbox entries of one segment; tile k belongs to the k % world-th
+// rank in turn order, so a block reads from (and, for find_or_insert, writes
+// to) all source ranks in rotation.  The key counts live in device memory: the
+// grid is a fixed number of resident blocks that stride over the tiles.
+__device__ __forceinline__ uint64_t routed_tiles(const RoutedArgs& r) {
+  uint64_t most = 0;
+  for (uint32_t s = 0; s < r.world; ++s) most = max(most, r.inbox_counts[s]);
+  most = min(most, r.segment_capacity);
+  return ((most + kMutateBlock - 1) / kMutateBlock) * r.world;
+}
+
+// Chains the requests for one key: every inbox entry enters its key into the
+// scratch set (linear probing from the top bits of the key's hash, which the
+// table's own addressing does not use) and pushes itself onto the key's chain.
+__global__ void __launch_bounds__(kMutateBlock)
+    routed_group_kernel(const TableView t, const RoutedArgs r) {
+  const uint64_t tiles = routed_tiles(r);
+  const uint32_t set_mask = (1u << r.set_bits) - 1u;
+  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const uint32_t seg = segment_of(r, uint32_t(tile % r.world));
+    const uint64_t i = (tile / r.world) * kMutateBlock + threadIdx.x;
+    if (i >= r.inbox_counts[seg] || i >= r.segment_capacity) continue;
+    const uint64_t entry = uint64_t(seg) * r.segment_capacity + i;
+    const uint64_t key = r.inbox_keys[entry];
+    if (is_reserved(t, key)) continue;
+    uint32_t at = uint32_t(fmix64(key) >> (64 - r.set_bits));
+    // the set has at least twice as many places as the inbox has entries
+    for (uint32_t probe = 0; probe <= set_mask; ++probe, at = (at + 1u) & set_mask) {
+      const uint64_t seen = atomicCAS(reinterpret_cast<unsigned long long*>(r.set_keys + at),
+                                      (unsigned long long)t.empty_key, (unsigned long long)key);
+      if (seen == t.empty_key || seen == key) break;
     }
+    r.set_slot[entry] = at;
+    r.next[entry] = atomicExch(r.set_head + at, uint32_t(entry));
+  }
+}
+
+// Leaves the scratch set empty again for the next call.
+__global__ void __launch_bounds__(kMutateBlock)
+    routed_ungroup_kernel(const TableView t, const RoutedArgs r) {
+  const uint64_t tiles = routed_tiles(r);
+  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const uint32_t seg = segment_of(r, uint32_t(tile % r.world));
+    const uint64_t i = (tile / r.world) * kMutateBlock + threadIdx.x;
+    if (i >= r.inbox_counts[seg] || i >= r.segment_capacity) continue;
+    const uint64_t entry = uint64_t(seg) * r.segment_capacity + i;
+    if (is_reserved(t, r.inbox_keys[entry])) continue;
+    const uint32_t at = r.set_slot[entry];
+    r.set_keys[at] = t.empty_key;
+    r.set_head[at] = kNoEntry;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    routed_fill_kernel(uint64_t* set_keys, uint32_t* set_head, uint64_t places, uint64_t empty_key) {
+  for (uint64_t p = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; p < places;
+       p += uint64_t(gridDim.x) * blockDim.x) {
+    set_keys[p] = empty_key;
+    set_head[p] = kNoEntry;
+  }
+}
+
+// Walking the request chains and serving them costs registers the local form
+// does not need: five resident blocks per SM (about 100 registers) instead of
+// eight keep the routed form free of large spills; its pace is set by the
+// peer-memory accesses anyway.
+#ifndef HKV_ROUTED_MIN_BLOCKS
+#define HKV_ROUTED_MIN_BLOCKS 5
+#endif
+constexpr int kRoutedMinBlocks = HKV_ROUTED_MIN_BLOCKS;
+
+template <int OP, int VEC>
+__global__ void __launch_bounds__(kMutateBlock, kRoutedMinBlocks)
+    mutate_routed_kernel(const TableView t, const MutateArgs args, const RoutedArgs r) {
+  static_assert(OP == kOpInsertOrAssign || OP == kOpFindOrInsert || OP == kOpAccumOrAssign,
+                "the routed form exists for the three operations the sharded table routes");
+  __shared__ uint8_t* sm_values[kMaxPeers];
+  __shared__ const bool* sm_flags[kMaxPeers];
+  __shared__ uint32_t sm_requests[kMaxRequests][kMutateBlock];
+  // a copy in shared memory: the warps reach the arguments through a pointer,
+  // which would otherwise put the whole parameter block into local memory
+  __shared__ RoutedArgs sm_r;
+  if (threadIdx.x < kMaxPeers) {
+    sm_values[threadIdx.x] = static_cast<uint8_t*>(r.values_of.p[threadIdx.x]);
+    sm_flags[threadIdx.x] = static_cast<const bool*>(r.flags_of.p[threadIdx.x]);
+  }
+  if (threadIdx.x == 0) {
+    sm_r.world = r.world;
+    sm_r.first_segment = r.first_segment;
+    sm_r.segment_capacity = r.segment_capacity;
+    sm_r.inbox_keys = r.inbox_keys;
+    sm_r.inbox_origin = r.inbox_origin;
+    sm_r.inbox_counts = r.inbox_counts;
+    sm_r.set_keys = r.set_keys;
+    sm_r.set_head = r.set_head;
+    sm_r.next = r.next;
+    sm_r.set_slot = r.set_slot;
+    sm_r.set_bits = r.set_bits;
+  }
+  __syncthreads();
+  const uint64_t tiles = routed_tiles(r);
+  RoutedWarp rw{&sm_r, 0, sm_values, sm_flags, sm_requests};
+  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    rw.segment = segment_of(r, uint32_t(tile % r.world));
+    const uint64_t base = (tile / r.world) * kMutateBlock + (threadIdx.x & ~31u);
+    const uint64_t n = min(r.inbox_counts[rw.segment], r.segment_capacity);
+    if (base < n) mutate_warp<OP, VEC, true>(t, args, base, n, &rw);
+    __syncwarp();  // the warp's columns of the parked results and requests are reused
   }
 }
 
@@ -1253,50 +1475,60 @@ void launch_mutate(int op, const TableView& t, const MutateArgs& args, bool uniq
 }
 
 template <int OP>
-void launch_routed_op(const TableView& t, MutateArgs args, uint32_t world, uint32_t first_segment,
-                      uint64_t segment_capacity, const uint64_t* inbox_counts,
-                      const PeerPtrs& values_of, const PeerPtrs& flags_of, cudaStream_t stream) {
-  const uint64_t* keys0 = args.keys;
-  const uint32_t* index0 = args.row_index;
-  // the key counts are only known on the device: a grid of resident blocks
-  // strides over whatever arrived
+void launch_routed_op(const TableView& t, const MutateArgs& args, const RoutedArgs& r,
+                      cudaStream_t stream) {
+  // the key counts are only known on the device: grids of resident blocks
+  // stride over whatever arrived
   int device = 0, sms = 148;
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-  const uint64_t resident = uint64_t(sms) * mutate_min_blocks(OP);
-  const uint64_t needed = (segment_capacity + kMutateBlock - 1) / kMutateBlock;
-  const uint64_t blocks = needed < resident ? needed : resident;
-  auto kernel = fast_rows(t) ? mutate_kernel<OP, 16, true> : mutate_kernel<OP, 0, true>;
-  for (uint32_t turn = 0; turn < world; ++turn) {
-    const uint32_t seg = (first_segment + turn) % world;
-    args.keys = keys0 + uint64_t(seg) * segment_capacity;
-    args.row_index = index0 + uint64_t(seg) * segment_capacity;
-    args.n = segment_capacity;
-    args.n_device = inbox_counts + seg;
-    args.values = static_cast<uint8_t*>(values_of.p[seg]);
-    args.accum_flags = static_cast<const bool*>(flags_of.p[seg]);
-    kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, args);
+  const uint64_t tiles = ((r.segment_capacity + kMutateBlock - 1) / kMutateBlock) * r.world;
+  const uint64_t resident = uint64_t(sms) * kRoutedMinBlocks;
+  const unsigned blocks = static_cast<unsigned>(tiles < resident ? tiles : resident);
+  const unsigned scan_blocks = static_cast<unsigned>(tiles < uint64_t(sms) * 16 ? tiles : sms * 16);
+  routed_group_kernel<<<scan_blocks, kMutateBlock, 0, stream>>>(t, r);
+  auto kernel = fast_rows(t) ? mutate_routed_kernel<OP, 16> : mutate_routed_kernel<OP, 0>;
+#ifndef HKV_EXP_SKIP_B
+  kernel<<<blocks, kMutateBlock, 0, stream>>>(t, args, r);
+#endif
+  routed_ungroup_kernel<<<scan_blocks, kMutateBlock, 0, stream>>>(t, r);
+}
+
+size_t routed_workspace_bytes(uint32_t world, uint64_t segment_capacity) {
+  const uint64_t entries = uint64_t(world) * segment_capacity;
+  uint32_t bits = 10;
+  while (bits < 31 && (1ull << bits) < 2 * entries) ++bits;
+  const uint64_t places = 1ull << bits;
+  return places * sizeof(uint64_t) + places * sizeof(uint32_t) + 2 * entries * sizeof(uint32_t) + 1024;
+}
+
+void prepare_routed_workspace(const TableView& t, RoutedArgs& r, void* work, bool fresh,
+                              cudaStream_t stream) {
+  const uint64_t entries = uint64_t(r.world) * r.segment_capacity;
+  uint32_t bits = 10;
+  while (bits < 31 && (1ull << bits) < 2 * entries) ++bits;
+  const uint64_t places = 1ull << bits;
+  uint8_t* at = static_cast<uint8_t*>(work);
+  r.set_keys = reinterpret_cast<uint64_t*>(at);
+  at += places * sizeof(uint64_t);
+  r.set_head = reinterpret_cast<uint32_t*>(at);
+  at += places * sizeof(uint32_t);
+  r.next = reinterpret_cast<uint32_t*>(at);
+  at += entries * sizeof(uint32_t);
+  r.set_slot = reinterpret_cast<uint32_t*>(at);
+  r.set_bits = bits;
+  if (fresh) {
+    routed_fill_kernel<<<1184, 256, 0, stream>>>(r.set_keys, r.set_head, places, t.empty_key);
   }
 }
 
-void launch_mutate_routed(int op, const TableView& t, const MutateArgs& args, uint32_t world,
-                          uint32_t first_segment, uint64_t segment_capacity,
-                          const uint64_t* inbox_counts, const PeerPtrs& values_of,
-                          const PeerPtrs& flags_of, cudaStream_t stream) {
-  if (segment_capacity == 0 || world == 0) return;
+void launch_mutate_routed(int op, const TableView& t, const MutateArgs& args, const RoutedArgs& r,
+                          cudaStream_t stream) {
+  if (r.segment_capacity == 0 || r.world == 0) return;
   switch (op) {
-    case kOpInsertOrAssign:
-      launch_routed_op<kOpInsertOrAssign>(t, args, world, first_segment, segment_capacity,
-                                          inbox_counts, values_of, flags_of, stream);
-      break;
-    case kOpFindOrInsert:
-      launch_routed_op<kOpFindOrInsert>(t, args, world, first_segment, segment_capacity,
-                                        inbox_counts, values_of, flags_of, stream);
-      break;
-    case kOpAccumOrAssign:
-      launch_routed_op<kOpAccumOrAssign>(t, args, world, first_segment, segment_capacity,
-                                         inbox_counts, values_of, flags_of, stream);
-      break;
+    case kOpInsertOrAssign: launch_routed_op<kOpInsertOrAssign>(t, args, r, stream); break;
+    case kOpFindOrInsert: launch_routed_op<kOpFindOrInsert>(t, args, r, stream); break;
+    case kOpAccumOrAssign: launch_routed_op<kOpAccumOrAssign>(t, args, r, stream); break;
     default: break;
   }
 }
