@@ -107,11 +107,14 @@ class ProductArm:
                                          max_hbm_for_vectors=hbm_bytes, dim=dim))
         self.dim = dim
 
-    def insert_or_assign(self, keys, values):
-        self.t.insert_or_assign(keys.numel(), keys, values)
+    def insert_or_assign(self, keys, values, unique_key=True):
+        self.t.insert_or_assign(keys.numel(), keys, values, unique_key=unique_key)
 
     def find_or_insert(self, keys, values):
         self.t.find_or_insert(keys.numel(), keys, values)
+
+    def erase(self, keys):
+        self.t.erase(keys.numel(), keys)
 
     def promote_hot_buckets(self):
         return self.t.promote_hot_buckets()
@@ -200,6 +203,7 @@ class ReferenceArm:
         self.lib.ref_set_global_epoch.argtypes = [P, U]
         self.lib.ref_insert_and_evict.argtypes = [P, U, P, P, P, P, P, P, P, P, ctypes.c_int]
         self.lib.ref_export_batch_if.argtypes = [P, ctypes.c_int, U, U, U, U, P, P, P, P, P]
+        self.lib.ref_erase.argtypes = [P, U, P, P]
         self.h = P()
         self._chk(self.lib.ref_create(capacity, capacity, hbm_bytes, dim, 128, 0, 1,
                                       ctypes.byref(self.h)))
@@ -214,9 +218,13 @@ class ReferenceArm:
     def _s():
         return torch.cuda.current_stream().cuda_stream or None
 
-    def insert_or_assign(self, keys, values):
+    def insert_or_assign(self, keys, values, unique_key=True):
         self._chk(self.lib.ref_insert_or_assign(self.h, keys.numel(), keys.data_ptr(),
-                                                values.data_ptr(), None, self._s(), 1))
+                                                values.data_ptr(), None, self._s(),
+                                                1 if unique_key else 0))
+
+    def erase(self, keys):
+        self._chk(self.lib.ref_erase(self.h, keys.numel(), keys.data_ptr(), self._s()))
 
     def find_or_insert(self, keys, values):
         self._chk(self.lib.ref_find_or_insert(self.h, keys.numel(), keys.data_ptr(),
@@ -799,7 +807,8 @@ def embedding_step_ops(sharded, arm, rank: int, world: int, batch: int, dim: int
 
 
 API_ORDER = ["insert_or_assign", "find", "find_or_insert", "assign", "find_ptr",
-             "find_or_insert_ptr", "insert_and_evict", "export_batch", "export_batch_if", "contains"]
+             "find_or_insert_ptr", "insert_and_evict", "export_batch", "export_batch_if", "contains",
+             "insert_or_assign_repeats_allowed", "erase"]
 
 
 def api_table(arm, capacity: int, dim: int, batch: int, reps: int = 3) -> dict:
@@ -882,6 +891,16 @@ def api_table(arm, capacity: int, dim: int, batch: int, reps: int = 3) -> dict:
             arm.insert_and_evict(keys, rows, None, ek, ev, es, counter)
 
         row["insert_and_evict"] = timed(evict)
+        # Not in the reference's program: the same batches with unique_key = false, and erase.
+        # Product arm only: with these two columns the reference arm's run did not end within
+        # 20 minutes on this table (its other ten columns take under a minute), so its kernels
+        # are not run for them.
+        if arm.name == "product":
+            row["insert_or_assign_repeats_allowed"] = timed(
+                lambda k, v: arm.insert_or_assign(k, v, unique_key=False))
+            row["erase"] = timed(lambda k, v: arm.erase(k))
+        else:
+            row["insert_or_assign_repeats_allowed"] = row["erase"] = None
         row["load_factor_after"] = round(arm.size() / capacity, 4)
         out["%.2f" % lf] = row
     return out
@@ -1020,7 +1039,8 @@ def main():
         print("| " + " | ".join(hdr) + " |", file=sys.stderr)
         print("|" + "---:|" * len(hdr), file=sys.stderr)
         for lf, row in table.items():
-            print("| " + " | ".join([lf] + ["%.3f" % row[a] for a in API_ORDER]) + " |", file=sys.stderr)
+            print("| " + " | ".join([lf] + ["-" if row[a] is None else "%.3f" % row[a]
+                                            for a in API_ORDER]) + " |", file=sys.stderr)
         arm.close()
         return
 

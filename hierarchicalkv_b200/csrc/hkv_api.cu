@@ -556,7 +556,9 @@ void allocate_planes(hkv_table* t, uint64_t buckets, hkv::TableView& v, Planes& 
     }
     uint8_t* mb = static_cast<uint8_t*>(p.meta_block);
     v.digests = mb + off_digests;
-    v.slot_lines = reinterpret_cast<uint64_t*>(mb + off_lines);
+    // keys | scores, or lines of 8 keys + 8 scores: the same 16 bytes per slot
+    v.key_words = reinterpret_cast<uint64_t*>(mb + off_lines);
+    v.score_words = v.line_mask ? v.key_words + hkv::kLineSlots : v.key_words + capacity;
     v.bucket_sizes = reinterpret_cast<int32_t*>(mb + off_sizes);
     v.status = reinterpret_cast<uint32_t*>(mb + off_status);
     HKV_CUDA(cudaMemsetAsync(mb + off_status, 0, 256, stream));
@@ -773,6 +775,8 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
     HKV_CHECK(o.evict_strategy >= HKV_LRU && o.evict_strategy <= HKV_CUSTOMIZED,
               "unknown evict strategy");
     HKV_CHECK(o.dim > 0 && o.value_size > 0, "dim and value_size must be positive");
+    HKV_CHECK(o.slot_layout == HKV_SLOT_PLANES || o.slot_layout == HKV_SLOT_LINES,
+              "hkv_options.slot_layout should be HKV_SLOT_PLANES or HKV_SLOT_LINES.");
 
     auto* t = new hkv_table();
     try {
@@ -805,6 +809,7 @@ int hkv_table_create(const hkv_options* options, const hkv_allocator* allocator,
       t->reach_max_capacity.store(o.init_capacity * 2 > o.max_capacity || o.table_mode == 1);
 
       hkv::TableView& v = t->view;
+      v.line_mask = o.slot_layout == HKV_SLOT_LINES ? ~uint64_t(0) : 0;
       v.bucket_slots = uint32_t(o.max_bucket_size);
       v.bucket_shift = 0;
       while ((1u << v.bucket_shift) < v.bucket_slots) ++v.bucket_shift;
@@ -1558,8 +1563,9 @@ int hkv_get_view(const hkv_table* t, hkv_table_view* view) {
   return guarded([&] {
     const hkv::TableView& v = t->view;
     view->digests = v.digests;
-    view->keys = v.slot_lines;
-    view->scores = v.slot_lines + hkv::kLineSlots;
+    view->keys = v.key_words;
+    view->scores = v.score_words;
+    view->slot_word_mask = v.line_mask;
     view->values_hbm = v.values_hbm;
     view->values_host = v.values_host;
     view->bucket_sizes = v.bucket_sizes;

@@ -4,23 +4,30 @@
 //
 // Storage is flat structure-of-arrays (one allocation per plane):
 //   digests      [buckets][128]  u8    one 128-byte line per bucket
-//   slot_lines   [buckets][16][16] u64  16 lines of 128 bytes per bucket: line l
-//                                       holds the keys of slots 8l .. 8l+7 and,
-//                                       behind them, the scores of the same
-//                                       slots; the key doubles as the slot lock
+//   keys, scores [buckets][128]  u64   the key doubles as the slot lock; two
+//                                       layouts, chosen when the table is made:
+//       planes (default)  one array of keys, one of scores
+//       lines             16 lines of 128 bytes per bucket, line l holding the
+//                         keys of slots 8l .. 8l+7 and behind them the scores
+//                         of the same slots
 //   values       [buckets*128][row_bytes]   HBM part, then pinned-host part
 //   bucket_sizes [buckets]       i32
 //
-// Why a slot's key and score share a line: every operation that locks a slot
-// also writes its score.  An 8-byte store into a 32-byte sector that is not in
-// L2 is a read-modify-write in DRAM at a random address; measured on B200 on
-// the 64 Mi-slot table it cost as much as the whole 256-byte row write
-// (73 us per 1 Mi keys of a 239 us update).  With the score in the line the
-// lock's compare-and-swap has just opened, and a prefetch of its sector issued
-// together with the compare-and-swap, the score store merges in L2 and the
-// line is written back once (172 us for the same update).  Scanning a
-// bucket's 128 scores reads the second half of 16 lines instead of 8 whole
-// lines, which costs a full-bucket insert about a sixth more.
+// What the two layouts trade (measured on B200, 64 Mi-slot table, 1 Mi-key
+// batches).  Every operation that locks a slot also writes its score.  With
+// separate planes that 8-byte store goes into a 32-byte sector that is not in
+// L2: a read-modify-write in DRAM at a random address, as expensive as the
+// whole 256-byte row write (73 us of a 239 us update of present keys).  With
+// the score in the line the lock's compare-and-swap has just opened, and a
+// prefetch of its sector issued with the compare-and-swap, the store merges in
+// L2 and the line is written back once: updates of present keys and inserts
+// into free slots run a quarter faster (insert_or_assign of present keys 3.96
+// -> 4.95 B-KV/s).  The price: a bucket's 128 scores are the second halves of
+// 16 lines instead of 8 whole lines, which makes every eviction's score scan
+// dearer (inserts that all evict 1.81 -> 1.55 B-KV/s), and the keys a lookup
+// verifies are spread over twice the address range (find 8.2 -> 7.9, contains
+// 20.3 -> 17.9 B-KV/s).  Tables that mostly update resident keys want lines,
+// tables that mostly look up or churn want planes.
 //
 // Semantics follow the reference (NVIDIA-Merlin/HierarchicalKV):
 //   hash / bucket / start / digest  include/merlin/utils.cuh:137-145,
@@ -81,7 +88,9 @@ enum ValueKind : uint32_t {
 
 struct TableView {
   uint8_t* digests;
-  uint64_t* slot_lines;   // keys and scores, see key_ptr / score_ptr
+  uint64_t* key_words;    // keys and scores: see key_ptr / score_ptr
+  uint64_t* score_words;
+  uint64_t line_mask;     // ~0: keys and scores share 128-byte lines; 0: separate planes
   uint8_t* values_hbm;    // rows of row slots [0, hbm_slots)
   uint8_t* values_host;   // rows of row slots [hbm_slots, capacity), pinned+mapped
   // Hybrid tables only (else null): bucket b keeps its 128 rows in row block
@@ -148,6 +157,17 @@ __device__ __forceinline__ Address locate(const TableView& t, uint64_t key) {
   return a;
 }
 
+// The same for the kernels that only serve 128-slot buckets: constant shifts.
+__device__ __forceinline__ Address locate_line(const TableView& t, uint64_t key) {
+  const uint64_t h = fmix64(key);
+  const uint64_t g = t.capacity_pow2 ? (h & (t.capacity - 1)) : (h % t.capacity);
+  Address a;
+  a.bucket = g >> 7;
+  a.start = static_cast<uint32_t>(g) & (kBucketSlots - 1);
+  a.digest = static_cast<uint32_t>(h >> 32) & 0xFFu;
+  return a;
+}
+
 // Dual-bucket addressing (TableMode::kMemory of the reference,
 // include/merlin/core_kernels/dual_bucket_utils.cuh:31-65): a key may live in
 // one of two buckets, chosen from the low and the high half of its hash; the
@@ -175,17 +195,23 @@ __device__ __forceinline__ DualAddress locate_dual(const TableView& t, uint64_t 
   return d;
 }
 
-// Key and score of a slot: line (slot >> 3) of the slot-line plane, 16 words
-// each: words 0-7 the keys of the line's 8 slots, words 8-15 their scores.
+// Key and score of a slot.  Planes: word `slot` of the key array and of the
+// score array.  Lines: line slot / 8 holds 16 words, 0-7 the keys of its 8
+// slots and 8-15 their scores; score_words points 8 words behind key_words.
 constexpr uint32_t kLineSlots = 8;
-__host__ __device__ __forceinline__ uint64_t slot_line_word(uint64_t slot) {
-  return ((slot >> 3) << 4) | (slot & 7u);
+__host__ __device__ __forceinline__ uint64_t slot_word(const TableView& t, uint64_t slot) {
+  return slot + ((slot & ~uint64_t(7)) & t.line_mask);
 }
 __host__ __device__ __forceinline__ uint64_t* key_ptr(const TableView& t, uint64_t slot) {
-  return t.slot_lines + slot_line_word(slot);
+  return t.key_words + slot_word(t, slot);
 }
 __host__ __device__ __forceinline__ uint64_t* score_ptr(const TableView& t, uint64_t slot) {
-  return t.slot_lines + slot_line_word(slot) + kLineSlots;
+  return t.score_words + slot_word(t, slot);
+}
+// Key at position pos of 128-slot bucket b.
+__device__ __forceinline__ uint64_t* key_ptr_in_line_bucket(const TableView& t, uint32_t bucket,
+                                                            uint32_t pos) {
+  return key_ptr(t, (uint64_t(bucket) << 7) + pos);
 }
 
 // Host side: may the kernels specialised for 16-byte chunks of pure-HBM rows run?
@@ -291,21 +317,38 @@ __device__ __forceinline__ uint64_t policy_keep() {
   return p;
 }
 
+#ifndef HKV_DIGEST_HINT
+#define HKV_DIGEST_HINT 1
+#endif
+#ifndef HKV_KEY_HINT
+#define HKV_KEY_HINT 1
+#endif
 __device__ __forceinline__ uint4 ld_meta_v4(const void* p) {
   uint4 v;
+#if HKV_DIGEST_HINT
   asm volatile("ld.global.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p), "l"(policy_keep())
                : "memory");
+#else
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+#endif
   return v;
 }
 
 __device__ __forceinline__ uint64_t ld_meta_u64(const uint64_t* p) {
   uint64_t v;
+#if HKV_KEY_HINT
   asm volatile("ld.global.L1::no_allocate.L2::cache_hint.u64 %0, [%1], %2;"
                : "=l"(v)
                : "l"(p), "l"(policy_keep())
                : "memory");
+#else
+  asm volatile("ld.global.L1::no_allocate.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+#endif
   return v;
 }
 

@@ -23,7 +23,7 @@ constexpr int kFindBlock = 128;
 #endif
 constexpr int kFindMinBlocks = HKV_FIND_MIN_BLOCKS;  // resident blocks per SM asked of the compiler
 #ifndef HKV_FIND_LIGHT_MIN_BLOCKS
-#define HKV_FIND_LIGHT_MIN_BLOCKS 10
+#define HKV_FIND_LIGHT_MIN_BLOCKS 8
 #endif
 // the forms that move no rows (find*, contains, the probe step of the hybrid find)
 constexpr int kFindLightMinBlocks = HKV_FIND_LIGHT_MIN_BLOCKS;
@@ -58,7 +58,7 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
     first_key[j] = 0;
     if (cand[j]) {
       const uint32_t pos = pl.sub * 16u + (__ffs(cand[j]) - 1);
-      first_key[j] = ld_meta_u64(key_ptr(t, (uint64_t(bkt[j]) << 7) + pos));
+      first_key[j] = ld_meta_u64(key_ptr_in_line_bucket(t, bkt[j], pos));
     }
   }
   uint32_t my_slot = kNoSlot;
@@ -77,7 +77,7 @@ __device__ __forceinline__ uint32_t warp_probe_readonly(const TableView& t, cons
         while (m) {
           pos = pl.sub * 16u + (__ffs(m) - 1);
           m &= m - 1;
-          if (ld_meta_u64(key_ptr(t, (uint64_t(bkt[j]) << 7) + pos)) == want) {
+          if (ld_meta_u64(key_ptr_in_line_bucket(t, bkt[j], pos)) == want) {
             hit_slot = (bkt[j] << 7) + pos;
             break;
           }
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(kFindBlock, (FORM == 1 || FORM == 3 || FORM ==
     valid = !is_reserved(t, key);
   }
   Address a{0, 0, 0};
-  if (valid) a = locate(t, key);
+  if (valid) a = locate_line(t, key);
 
   const uint32_t slot = warp_probe_readonly(t, pl, key, valid, a);
   const bool found = slot != kNoSlot;
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kFindBlock)
     valid = !is_reserved(t, key);
   }
   Address a{0, 0, 0};
-  if (valid) a = locate(t, key);
+  if (valid) a = locate_line(t, key);
   const uint32_t slot = warp_probe_readonly(t, pl, key, valid, a);
   if (present) founds_of[origin] = slot != kNoSlot ? 1 : 0;
   warp_gather_rows_to<VEC>(t, values_of, origin, slot, pl.lane);

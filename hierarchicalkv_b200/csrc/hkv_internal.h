@@ -20,6 +20,7 @@ enum MutateOp : int {
   kOpAssignValues = 7,     // HashTable::assign_values
   kOpFindAndUpdate = 8,    // HashTable::find_and_update
   kOpLockKeys = 9,         // HashTable::lock_keys
+  kOpErase = 10,           // HashTable::erase
 };
 
 struct MutateArgs {

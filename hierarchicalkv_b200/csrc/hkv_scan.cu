@@ -139,18 +139,19 @@ __global__ void __launch_bounds__(kScanBlock)
 }
 
 __global__ void __launch_bounds__(kScanBlock) clear_kernel(const TableView t) {
-  // one thread per 16 slots: a 16-byte digest store and two slot lines
+  // one thread per 16 slots: a 16-byte digest store, 16 keys and 16 scores
   const uint64_t groups = t.capacity / 16;
   for (uint64_t g = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; g < groups;
        g += uint64_t(gridDim.x) * blockDim.x) {
     const uint32_t d = t.empty_digest4;
     reinterpret_cast<uint4*>(t.digests)[g] = make_uint4(d, d, d, d);
-    // slots 16g .. 16g+15 are two slot lines: 8 keys, 8 scores, 8 keys, 8 scores
-    ulonglong2* w = reinterpret_cast<ulonglong2*>(t.slot_lines + g * 32);
+    // slots 16g .. 16g+15, two at a time (an even slot's words are 16-byte aligned
+    // in both layouts)
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      const bool key_half = ((q >> 2) & 1) == 0;
-      w[q] = key_half ? make_ulonglong2(t.empty_key, t.empty_key) : make_ulonglong2(0ull, 0ull);
+    for (int q = 0; q < 8; ++q) {
+      const uint64_t slot = g * 16 + 2 * q;
+      *reinterpret_cast<ulonglong2*>(key_ptr(t, slot)) = make_ulonglong2(t.empty_key, t.empty_key);
+      *reinterpret_cast<ulonglong2*>(score_ptr(t, slot)) = make_ulonglong2(0ull, 0ull);
     }
     // the thread that clears a bucket's first 16 slots also clears its size
     const uint64_t groups_per_bucket = t.bucket_slots / 16u;

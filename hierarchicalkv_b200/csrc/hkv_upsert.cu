@@ -43,6 +43,7 @@ constexpr int kMutateMinBlocks = HKV_MUTATE_MIN_BLOCKS;
 #endif
 constexpr int kMutateLightMinBlocks = HKV_MUTATE_LIGHT_MIN_BLOCKS;
 constexpr uint32_t kEvictIterLimit = 1u << 16;  // iterations of the full-bucket loop per warp
+constexpr uint32_t kHeldLockWaits = 1u << 12;   // polls (about a millisecond) before a lock counts as held
 
 enum Result : uint32_t {
   kInitial = 0,
@@ -136,11 +137,12 @@ __device__ __forceinline__ bool hit_score_assign(int strategy, const uint64_t* s
   }
 }
 
-// Score scan of one bucket by the 8 lanes of a group.  A bucket's scores are
-// the second halves (64 bytes) of its 16 slot lines.  In step q the lanes 0-3
-// of the group read the score half of line 2q and the lanes 4-7 that of line
-// 2q + 1, 16 bytes each, so every load instruction of a group covers two
-// 64-byte segments completely.  A lane ends up with the 16 scores
+// Score scan of one bucket by the 8 lanes of a group.  In step q the lanes 0-3
+// of the group read the scores of positions 16q .. 16q + 7 and the lanes 4-7
+// those of positions 16q + 8 .. 16q + 15, 16 bytes (two scores) each: with
+// separate planes a group reads 128 contiguous bytes per instruction, with
+// shared lines the 64-byte score halves of two neighbouring lines.  A lane
+// ends up with the 16 scores
 //   s[2q + e] = score of bucket position scan_pos(sub, 2q + e).
 __device__ __forceinline__ uint32_t scan_pos(uint32_t sub, uint32_t b) {
   return ((b & ~1u) + (sub >> 2)) * kLineSlots + (sub & 3u) * 2u + (b & 1u);
@@ -148,12 +150,14 @@ __device__ __forceinline__ uint32_t scan_pos(uint32_t sub, uint32_t b) {
 
 __device__ __forceinline__ void ld_scores16(const TableView& t, uint64_t bucket, uint32_t sub,
                                             uint64_t (&s)[16]) {
-  const uint64_t* mine = score_ptr(t, (bucket << 7) + (sub >> 2) * kLineSlots) + (sub & 3u) * 2u;
+  // positions scan_pos(sub, 2q) for q = 0 .. 7 are 16 slots apart
+  const uint64_t* mine = score_ptr(t, (bucket << 7) + scan_pos(sub, 0));
+  const uint64_t step = 16u + (16u & t.line_mask);   // words between them
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];"
                  : "=l"(s[2 * q]), "=l"(s[2 * q + 1])
-                 : "l"(mine + q * 32)
+                 : "l"(mine + q * step)
                  : "memory");
   }
 }
@@ -247,7 +251,7 @@ __device__ __forceinline__ void group_min_score(const TableView& t, const ProbeL
 __host__ __device__ constexpr int mutate_min_blocks(int op) {
   return op == kOpInsertAndEvict ? kMutateMinBlocks - 2
          : (op == kOpFindOrInsertPtr || op == kOpAssignScores || op == kOpFindAndUpdate ||
-            op == kOpLockKeys)
+            op == kOpLockKeys || op == kOpErase)
              ? kMutateLightMinBlocks
              : kMutateMinBlocks;
 }
@@ -357,7 +361,7 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
     if (!INDEXED) key = args.keys[i];
     if (!is_reserved(t, key) && serves) {
       mode = kModeValid;
-      a = locate(t, key);
+      a = locate_line(t, key);
       if (args.scores != nullptr) in_score = args.scores[i];
       if (op_inserts(OP) || OP == kOpLockKeys) {
         desired = desired_score(strategy, args.scores, in_score, args.epoch);
@@ -437,13 +441,16 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
         const uint32_t cand = match16(dg[j], replicate4(tgt));
         masks[j] = cand | (match16(dg[j], t.empty_digest4) << 16);
         if (cand) {
-          uint64_t* kp = key_ptr(t, (uint64_t(b) << 7) + pl.sub * 16u + (__ffs(cand) - 1));
+          uint64_t* kp = key_ptr_in_line_bucket(t, b, pl.sub * 16u + (__ffs(cand) - 1));
           first_key[j] = (m & kModeLockOnHit) ? cas_relaxed(kp, want, t.locked_key)
                                               : ld_relaxed(kp);
-          // the slot's score shares the key's line: with its sector on the way
-          // into L2 the score store that follows the lock merges there instead
-          // of becoming a read-modify-write in DRAM
-          if (OP != kOpAssignValues && (m & kModeLockOnHit)) prefetch_l2(kp + kLineSlots);
+          // with the score's sector on the way into L2 the score store that
+          // follows the lock merges there instead of becoming a read-modify-write
+          // in DRAM (shared lines: the sector is in the line the lock has just
+          // opened; separate planes: a second random access, still cheaper)
+          if (OP != kOpAssignValues && (m & kModeLockOnHit)) {
+            prefetch_l2(score_ptr(t, (uint64_t(b) << 7) + pl.sub * 16u + (__ffs(cand) - 1)));
+          }
         }
       }
     }
@@ -524,9 +531,8 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
           const uint32_t pos = (start + gd) & (kBucketSlots - 1);
           bool won = false;
           if (d == gd) {
-            uint64_t* kp = key_ptr(t, slot0 + pos);
-            won = cas_relaxed(kp, t.empty_key, t.locked_key) == t.empty_key;
-            prefetch_l2(kp + kLineSlots);
+            won = cas_relaxed(key_ptr(t, slot0 + pos), t.empty_key, t.locked_key) == t.empty_key;
+            prefetch_l2(score_ptr(t, slot0 + pos));
             em &= ~(1u << (pos & 15u));
           }
           if (__ballot_sync(gmask, won)) {
@@ -571,7 +577,7 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
       st_relaxed(score_ptr(t, my_slot), inserted_score(strategy, in_score, desired));
       atomicAdd(t.bucket_sizes + a.bucket, 1);
     }
-    if (my_result == kDuplicate && OP != kOpAssignValues) {
+    if (my_result == kDuplicate && OP != kOpAssignValues && OP != kOpErase) {
       const bool needs_old = strategy == kLfu || strategy == kEpochLfu ||
                              (OP == kOpFindAndUpdate && args.scores_out != nullptr);
       const uint64_t old_score = needs_old ? ld_relaxed(score_ptr(t, my_slot)) : 0;
@@ -620,7 +626,18 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
                              accumulating, pl.lane);
     }
     __syncwarp();
-    if (holds_lock && !keep_locked) st_release(key_ptr(t, my_slot), key);
+    if (OP == kOpErase) {
+      // the slot becomes a tombstone: RECLAIM key, reclaim digest, score 0, size - 1
+      // (include/merlin/core_kernels.cuh:680-734)
+      if (my_result == kDuplicate) {
+        st_u8_cg(t.digests + my_slot, t.reclaim_digest);
+        st_relaxed(score_ptr(t, my_slot), 0);
+        atomicSub(t.bucket_sizes + a.bucket, 1);
+        st_release(key_ptr(t, my_slot), t.reclaim_key);
+      }
+    } else if (holds_lock && !keep_locked) {
+      st_release(key_ptr(t, my_slot), key);
+    }
   }
 
   // ---- phase 4: full buckets ----------------------------------------------------------
@@ -986,10 +1003,26 @@ __global__ void __launch_bounds__(kMutateBlock)
         }
         continue;
       }
+      // Somebody holds a slot of this bucket; it may be writing this very key.
+      // A kernel holds a slot for microseconds, so the slot is waited for.  A
+      // slot that stays locked (a key held through lock_keys or the pointer form
+      // of find_or_insert) would starve the bucket: after kHeldLockWaits polls
+      // a locked slot is passed over if its digest, stable by then, belongs to
+      // another key.  A held slot with this key's own digest (one in 256)
+      // cannot be told from this key and is waited for to the bound.
       if (__ballot_sync(full, locked != 0)) {
-        // somebody is writing a slot of this bucket; it may be this very key
-        __nanosleep(128);
-        continue;
+        bool may_be_mine = attempts <= kHeldLockWaits;
+        for (uint32_t c = 0; c < steps && !may_be_mine; ++c) {
+          if ((locked >> c) & 1u) {
+            uint32_t d;
+            asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(d) : "l"(t.digests + slot0 + c * 32u + lane));
+            may_be_mine = d == a.digest || d == (t.empty_digest4 & 0xFFu) || d == t.reclaim_digest;
+          }
+        }
+        if (__ballot_sync(full, may_be_mine)) {
+          __nanosleep(128);
+          continue;
+        }
       }
       if (!insert_on_miss) {
         result = kMiss;
@@ -1167,8 +1200,9 @@ __global__ void unlock_keys_kernel(const TableView t, uint64_t n, uint64_t** loc
   if (success != nullptr) success[i] = ok;
 }
 
-// erase: tombstone = RECLAIM key, reclaim digest, score 0, size - 1
-// (core_kernels.cuh:680-734).
+// erase on tables whose buckets are not one 128-byte digest line (the others
+// run mutate_kernel<kOpErase>): one warp per key; tombstone = RECLAIM key,
+// reclaim digest, score 0, size - 1 (core_kernels.cuh:680-734).
 __global__ void __launch_bounds__(kMutateBlock)
     erase_kernel(const TableView t, uint64_t n, const uint64_t* keys) {
   const uint32_t lane = threadIdx.x & 31u;
@@ -1548,6 +1582,15 @@ void launch_unlock_keys(const TableView& t, uint64_t n, uint64_t** locked_key_pt
 
 void launch_erase(const TableView& t, uint64_t n, const uint64_t* keys, cudaStream_t stream) {
   if (n == 0) return;
+  if (line_buckets(t)) {
+    // 32 keys per warp on the 8-lane digest probe, like every other keyed operation
+    MutateArgs args;
+    args.keys = keys;
+    args.n = n;
+    const uint64_t fast_blocks = (((n + 31) / 32) * 32 + kMutateBlock - 1) / kMutateBlock;
+    launch_fast<kOpErase>(t, args, fast_blocks, stream);
+    return;
+  }
   const uint64_t blocks = (n * 32 + kMutateBlock - 1) / kMutateBlock;
   erase_kernel<<<static_cast<unsigned>(blocks), kMutateBlock, 0, stream>>>(t, n, keys);
 }

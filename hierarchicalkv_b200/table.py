@@ -72,6 +72,7 @@ class _Options(ctypes.Structure):
         ("value_size", ctypes.c_uint32),
         ("score_size", ctypes.c_uint32),
         ("value_kind", ctypes.c_uint32),
+        ("slot_layout", ctypes.c_uint32),
     ]
 
 
@@ -96,7 +97,12 @@ class TableView(ctypes.Structure):
         ("reserved_mask", ctypes.c_uint64),
         ("reserved_value", ctypes.c_uint64),
         ("max_bucket_size", ctypes.c_uint64),
+        ("slot_word_mask", ctypes.c_uint64),
     ]
+
+    def slot_word(self, slot: int) -> int:
+        """HKV_SLOT_WORD: index of slot's key in `keys` and of its score in `scores`"""
+        return slot + ((slot & ~7) & self.slot_word_mask)
 
 
 @dataclasses.dataclass
@@ -118,6 +124,9 @@ class HashTableOptions:
     num_of_buckets_per_alloc: int = 1
     api_lock: bool = True
     table_mode: int = 0
+    # not in the reference: 0 separate key and score arrays, 1 keys and scores of 8
+    # slots share a 128-byte line (hkv_slot_layout)
+    slot_layout: int = 0
 
 
 def library_path() -> str:
@@ -299,7 +308,8 @@ class HashTable:
             evict_strategy=int(self.evict_strategy),
             value_size=_VALUE_SIZES[self.value_dtype],
             score_size=8 if self.score_dtype == torch.int64 else 4,
-            value_kind=_VALUE_KINDS.get(self.value_dtype, 0))
+            value_kind=_VALUE_KINDS.get(self.value_dtype, 0),
+            slot_layout=int(getattr(options, "slot_layout", 0)))
         h = ctypes.c_void_p()
         rc = self._lib.hkv_table_create(ctypes.byref(o), None, ctypes.byref(h))
         if rc:

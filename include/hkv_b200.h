@@ -90,7 +90,18 @@ typedef struct hkv_options {
   uint32_t score_size;    /* sizeof(S): 8, or 4 with HKV_CUSTOMIZED; with 4 every `scores` array of
                              this header holds uint32 values (the pointer type stays uint64_t*) */
   uint32_t value_kind;    /* hkv_value_kind: what accum_or_assign adds */
+  /* Not in the reference.  Where a slot's key and score live (hkv_slot_layout):
+   * HKV_SLOT_PLANES, the default, keeps an array of keys and an array of
+   * scores; HKV_SLOT_LINES puts the keys of 8 consecutive slots and their 8
+   * scores into one 128-byte line, so the score store every update makes lands
+   * in the line its lock has just opened.  Measured on B200 (64 Mi slots, dim
+   * 64): lines make updates of resident keys and inserts into free slots about
+   * a quarter faster, evicting inserts a sixth slower, find 4 % and contains /
+   * find* 12 % slower.  Results are identical. */
+  uint32_t slot_layout;
 } hkv_options;
+
+typedef enum hkv_slot_layout { HKV_SLOT_PLANES = 0, HKV_SLOT_LINES = 1 } hkv_slot_layout;
 
 /* Element type of V.  Rows are opaque bytes to every operation except
  * accum_or_assign, which adds elements as V's operator+= does in the reference
@@ -119,16 +130,15 @@ typedef enum hkv_predicate {
 /* Raw view of the table's planes for header-side kernels that evaluate a
  * user-templated functor (export_batch_if<PredFunctor>, for_each).  Valid
  * until the table is destroyed. */
-#define HKV_SLOT_WORD(slot) \
-  ((((uint64_t)(slot) >> 3) << 4) | ((uint64_t)(slot) & 7u))
+#define HKV_SLOT_WORD(view, slot) \
+  ((uint64_t)(slot) + (((uint64_t)(slot) & ~(uint64_t)7) & (view).slot_word_mask))
 typedef struct hkv_table_view {
   uint8_t* digests;      /* [buckets][max_bucket_size] */
-  /* Keys and scores share one plane of 128-byte lines: a line holds the keys
-   * of 8 consecutive slots followed by their 8 scores (a slot's lock word and
-   * its score are written together by every update, so they sit in one line).
-   * Index both arrays with HKV_SLOT_WORD(slot), never with the slot itself. */
-  uint64_t* keys;        /* key of slot s:   keys[HKV_SLOT_WORD(s)]   */
-  uint64_t* scores;      /* score of slot s: scores[HKV_SLOT_WORD(s)] (scores == keys + 8) */
+  /* Index both arrays with HKV_SLOT_WORD(view, slot), never with the slot itself:
+   * with HKV_SLOT_LINES a 128-byte line holds the keys of 8 consecutive slots
+   * followed by their 8 scores (scores == keys + 8 then). */
+  uint64_t* keys;        /* key of slot s:   keys[HKV_SLOT_WORD(view, s)]   */
+  uint64_t* scores;      /* score of slot s: scores[HKV_SLOT_WORD(view, s)] */
   uint8_t* values_hbm;   /* rows of row slots [0, hbm_slots) */
   uint8_t* values_host;  /* rows of row slots [hbm_slots, capacity), mapped pinned */
   int32_t* bucket_sizes; /* [buckets] */
@@ -141,6 +151,7 @@ typedef struct hkv_table_view {
   uint64_t empty_key, reclaim_key, locked_key;
   uint64_t reserved_mask, reserved_value; /* reserved iff (key & mask) == value */
   uint64_t max_bucket_size; /* slots per bucket: bucket of slot s is s / max_bucket_size */
+  uint64_t slot_word_mask;  /* all ones with HKV_SLOT_LINES, else 0 (HKV_SLOT_WORD) */
 } hkv_table_view;
 
 /* Message of the last failing call on this thread. */

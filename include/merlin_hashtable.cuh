@@ -64,7 +64,7 @@ struct MemoryPoolOptions {
   size_t max_pending = 16;
 };
 
-// merlin_hashtable.cuh:103-136, field for field
+// merlin_hashtable.cuh:103-136, field for field (plus slot_layout at the end)
 struct HashTableOptions {
   size_t init_capacity = 0;
   size_t max_capacity = 0;
@@ -83,6 +83,10 @@ struct HashTableOptions {
   TableMode table_mode = TableMode::kThroughput;
   MemoryPoolOptions device_memory_pool;
   MemoryPoolOptions host_memory_pool;
+  // Not in the reference (hkv_slot_layout): 0 keeps keys and scores in separate
+  // arrays, 1 puts the keys of 8 slots and their scores into one 128-byte line,
+  // which makes updates of resident keys faster and lookups and evictions slower.
+  int slot_layout = 0;
 };
 
 // merlin_hashtable.cuh:173-179
@@ -181,8 +185,8 @@ __global__ void export_if_kernel(const hkv_table_view v, const K pattern, const 
     S score = 0;
     bool live = false;
     if (rel < n) {
-      key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
-      score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
+      key = static_cast<K>(v.keys[HKV_SLOT_WORD(v, slot)]);
+      score = static_cast<S>(v.scores[HKV_SLOT_WORD(v, slot)]);
       live = !view_is_reserved(v, static_cast<uint64_t>(key)) && pred(key, score, pattern, threshold);
     }
     const uint32_t votes = __ballot_sync(0xFFFFFFFFu, live);
@@ -220,8 +224,8 @@ __global__ void size_if_kernel(const hkv_table_view v, const K pattern, const S 
   unsigned long long local = 0;
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < v.capacity;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
-    S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
+    K key = static_cast<K>(v.keys[HKV_SLOT_WORD(v, slot)]);
+    S score = static_cast<S>(v.scores[HKV_SLOT_WORD(v, slot)]);
     if (!view_is_reserved(v, static_cast<uint64_t>(key)) && pred(key, score, pattern, threshold)) {
       ++local;
     }
@@ -241,12 +245,12 @@ __global__ void erase_if_kernel(const hkv_table_view v, const K pattern, const S
   unsigned long long local = 0;
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < v.capacity;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
-    S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
+    K key = static_cast<K>(v.keys[HKV_SLOT_WORD(v, slot)]);
+    S score = static_cast<S>(v.scores[HKV_SLOT_WORD(v, slot)]);
     if (!view_is_reserved(v, static_cast<uint64_t>(key)) && pred(key, score, pattern, threshold)) {
-      v.keys[HKV_SLOT_WORD(slot)] = v.reclaim_key;
+      v.keys[HKV_SLOT_WORD(v, slot)] = v.reclaim_key;
       v.digests[slot] = reclaim_digest;
-      v.scores[HKV_SLOT_WORD(slot)] = 0;
+      v.scores[HKV_SLOT_WORD(v, slot)] = 0;
       atomicSub(v.bucket_sizes + slot / v.max_bucket_size, 1);
       ++local;
     }
@@ -290,8 +294,8 @@ __global__ void export_if_v2_kernel(const hkv_table_view v, PredFunctor pred, co
   for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += uint64_t(gridDim.x) * blockDim.x) {
     const uint64_t slot = offset + i;
-    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
-    const S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
+    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(v, slot)]);
+    const S score = static_cast<S>(v.scores[HKV_SLOT_WORD(v, slot)]);
     const V* value = reinterpret_cast<const V*>(view_row(v, slot));
     bool match = pred.template operator()<G>(key, value, score, g);
     match = match && !view_is_reserved(v, static_cast<uint64_t>(key));
@@ -327,8 +331,8 @@ __global__ void erase_if_v2_kernel(const hkv_table_view v, PredFunctor pred, con
   cg::thread_block_tile<G> g = cg::tiled_partition<G>(cg::this_thread_block());
   for (uint64_t slot = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; slot < n;
        slot += uint64_t(gridDim.x) * blockDim.x) {
-    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
-    const S score = static_cast<S>(v.scores[HKV_SLOT_WORD(slot)]);
+    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(v, slot)]);
+    const S score = static_cast<S>(v.scores[HKV_SLOT_WORD(v, slot)]);
     const V* value = reinterpret_cast<const V*>(view_row(v, slot));
     bool match = pred.template operator()<G>(key, value, score, g);
     match = match && !view_is_reserved(v, static_cast<uint64_t>(key));
@@ -339,9 +343,9 @@ __global__ void erase_if_v2_kernel(const hkv_table_view v, PredFunctor pred, con
       atomicSub(v.bucket_sizes + slot / v.max_bucket_size, __popc(votes));
     }
     if (match) {
-      v.keys[HKV_SLOT_WORD(slot)] = v.reclaim_key;
+      v.keys[HKV_SLOT_WORD(v, slot)] = v.reclaim_key;
       v.digests[slot] = reclaim_digest;
-      v.scores[HKV_SLOT_WORD(slot)] = 0;
+      v.scores[HKV_SLOT_WORD(v, slot)] = 0;
     }
   }
 }
@@ -353,8 +357,8 @@ __global__ void for_each_kernel(const hkv_table_view v, ExecutionFunc f, const u
   for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += uint64_t(gridDim.x) * blockDim.x) {
     const uint64_t slot = first + i;
-    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(slot)]);
-    S* score = reinterpret_cast<S*>(v.scores + HKV_SLOT_WORD(slot));
+    const K key = static_cast<K>(v.keys[HKV_SLOT_WORD(v, slot)]);
+    S* score = reinterpret_cast<S*>(v.scores + HKV_SLOT_WORD(v, slot));
     V* value = reinterpret_cast<V*>(const_cast<uint8_t*>(view_row(v, slot)));
     f.template operator()<G>(key, value, score, g);
   }
@@ -506,6 +510,7 @@ class HashTable : public HashTableBase<K, V, S> {
     o.evict_strategy = Strategy;
     o.value_size = sizeof(V);
     o.value_kind = detail::value_kind_of<V>();
+    o.slot_layout = static_cast<uint32_t>(options.slot_layout);
     o.score_size = sizeof(S);
     hkv_allocator bridge{allocator, detail::alloc_trampoline, detail::free_trampoline};
     detail::rethrow(hkv_table_create(&o, allocator ? &bridge : nullptr, &table_));

@@ -286,9 +286,12 @@ class ProductTable:
 
     def __init__(self, capacity, dim, strategy=0, reserved_key_start_bit=0, max_capacity=None,
                  max_hbm_for_vectors=None, api_lock=True, max_load_factor=None,
-                 memory_mode=False, max_bucket_size=128):
+                 memory_mode=False, max_bucket_size=128, slot_layout=None):
         import torch
         import hierarchicalkv_b200 as hkv
+
+        if slot_layout is None:     # HKV_TEST_SLOT_LAYOUT=1 runs the whole suite on shared lines
+            slot_layout = int(os.environ.get("HKV_TEST_SLOT_LAYOUT", "0"))
 
         self.torch = torch
         self.dim = dim
@@ -301,7 +304,7 @@ class ProductTable:
         self.t.init(hkv.HashTableOptions(
             init_capacity=capacity, max_capacity=max_capacity or capacity,
             max_hbm_for_vectors=hbm, dim=dim, reserved_key_start_bit=reserved_key_start_bit,
-            api_lock=api_lock, max_bucket_size=max_bucket_size, **extra))
+            api_lock=api_lock, max_bucket_size=max_bucket_size, slot_layout=slot_layout, **extra))
 
     def reserve(self, new_capacity):
         self.t.reserve(new_capacity, self.torch.cuda.current_stream().cuda_stream)

@@ -73,13 +73,15 @@ def test_find_with_missed_keys_over_bucket_sizes(bucket, load_factor, placement)
             x.close()
 
 
-@pytest.mark.parametrize("bucket", [16, 32, 64, 256, 1024])
-def test_every_operation_on_other_bucket_sizes(bucket):
+@pytest.mark.parametrize("bucket,slot_layout", [(16, 0), (32, 1), (64, 0), (256, 1), (1024, 0),
+                                                (128, 0), (128, 1)])
+def test_every_operation_on_other_bucket_sizes(bucket, slot_layout):
     """insert_or_assign with eviction, find_or_insert, assign, accum_or_assign,
-    erase, insert_and_evict, export, size and a doubling of the capacity on
-    tables whose buckets are not 128 slots: product against the CPU oracle."""
+    erase, insert_and_evict, export and size on tables whose buckets are not 128
+    slots, and on both slot layouts (keys and scores in separate arrays, or
+    sharing 128-byte lines): product against the CPU oracle."""
     cap = bucket * 96
-    p = ProductTable(cap, 8, CUSTOMIZED, max_bucket_size=bucket)
+    p = ProductTable(cap, 8, CUSTOMIZED, max_bucket_size=bucket, slot_layout=slot_layout)
     o = OracleTable(cap, 8, CUSTOMIZED, max_bucket_size=bucket)
     assert p.t.max_bucket_size() == bucket and p.bucket_count() == o.bucket_count() == 96
     keys = unique_keys(3 * cap, seed=2000 + bucket)

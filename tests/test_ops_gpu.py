@@ -105,6 +105,46 @@ def test_find_or_insert_ptr_then_unlock_keys():
     t.close()
 
 
+def test_held_locks_do_not_starve_batches_that_may_repeat_keys():
+    """Keys held through lock_keys stay LOCKED for as long as the caller likes.
+    A batch with unique_key=False goes through the serialising kernel, which
+    waits for locked slots because one of them may be an earlier occurrence of
+    its own key; a slot that stays locked and carries another key's digest must
+    not keep the rest of its bucket from being served."""
+    import torch
+
+    cap, dim = 128, 4                       # one bucket: everything meets the held slots
+    t = ProductTable(cap, dim, CUSTOMIZED)
+    keys = unique_keys(100, seed=61)
+    t.insert_or_assign(keys[:40], values_for(keys[:40], dim), np.arange(1, 41, dtype=np.uint64))
+    n = 8
+    k = to_dev(keys[:n])
+    lk = torch.zeros(n, dtype=torch.int64, device="cuda")
+    ok = torch.zeros(n, dtype=torch.bool, device="cuda")
+    t.t.lock_keys(n, k, lk, ok)
+    torch.cuda.synchronize()
+    assert bool(ok.all())
+    # A held slot whose 8-bit digest equals the new key's cannot be told from an
+    # earlier occurrence of that key and is waited for to the bound (the key is
+    # then refused and the status word says so): keep such keys out of the batch.
+    from tests.hkv_testlib import fmix64
+
+    digest = lambda a: (fmix64(a) >> np.uint64(32)) & np.uint64(0xFF)
+    fresh = keys[40:100]
+    fresh = np.ascontiguousarray(fresh[~np.isin(digest(fresh), digest(keys[:n]))])
+    assert fresh.size >= 40
+    t.insert_or_assign(fresh, values_for(fresh, dim),
+                       np.arange(101, 101 + fresh.size, dtype=np.uint64), unique_key=False)
+    assert t.t.device_status() == 0         # nothing timed out
+    v, f, s = t.find(fresh)
+    assert f.all()
+    np.testing.assert_array_equal(v, values_for(fresh, dim))
+    t.t.unlock_keys(n, lk, k, ok)
+    torch.cuda.synchronize()
+    assert bool(ok.all()) and t.size() == 40 + fresh.size
+    t.close()
+
+
 def test_find_and_update_and_assign_values():
     import torch
 
@@ -833,11 +873,11 @@ def test_export_batch_slot_windows(offset, n):
     import torch
     from cuda.bindings import runtime as cudart
 
-    # keys and scores share 128-byte lines: 8 keys, then the 8 scores of the same slots
-    lines = np.zeros(cap * 2, dtype=np.uint64)
-    cudart.cudaMemcpy(lines.ctypes.data, view.keys, cap * 16,
+    # slot s's key is word view.slot_word(s) of view.keys (HKV_SLOT_WORD)
+    words = np.zeros(cap * 2, dtype=np.uint64)
+    cudart.cudaMemcpy(words.ctypes.data, view.keys, cap * (16 if view.slot_word_mask else 8),
                       cudart.cudaMemcpyKind.cudaMemcpyDeviceToHost)
-    all_keys = np.ascontiguousarray(lines.reshape(-1, 2, 8)[:, 0, :]).reshape(-1)
+    all_keys = words[[view.slot_word(s) for s in range(cap)]]
     lo, hi = min(offset, cap), min(offset + n, cap)
     window = all_keys[lo:hi]
     mask = np.uint64(0xFFFFFFFFFFFFFFFC)
@@ -879,16 +919,23 @@ def test_erase_if_built_in_predicates(pred, pattern, threshold):
 
 def test_bounded_wait_on_a_slot_that_stays_locked():
     """Every device-side wait has a limit.  Keys locked with lock_keys stay
-    LOCKED; a duplicate-tolerant insert into their bucket has to wait for
-    LOCKED slots, gives up after its bound, refuses the key and raises the
-    status bit -- no hang, and the table works again after unlock_keys."""
+    LOCKED; a duplicate-tolerant insert into their bucket has to wait for a
+    LOCKED slot that may hold its own key (same 8-bit digest), gives up after
+    its bound, refuses the key and raises the status bit -- no hang, and the
+    table works again after unlock_keys."""
     import torch
+
+    from tests.hkv_testlib import fmix64
 
     cap, dim = 128 * 4, 4
     t = ProductTable(cap, dim, CUSTOMIZED)
     pool = unique_keys(60000, seed=41)
     in_b0 = pool[bucket_of(pool, cap) == 0]
-    held, late = in_b0[:8], in_b0[8:12]
+    digest = (fmix64(in_b0) >> np.uint64(32)) & np.uint64(0xFF)
+    held = in_b0[:8]
+    # late keys that share a digest with a held key: they cannot be told from it
+    late = in_b0[8:][np.isin(digest[8:], digest[:8])][:4]
+    assert late.size == 4
     t.insert_or_assign(held, values_for(held, dim), np.arange(1, 9, dtype=np.uint64))
     k = to_dev(held)
     lk = torch.zeros(8, dtype=torch.int64, device="cuda")
