@@ -97,14 +97,16 @@ def rows_for(keys: torch.Tensor, dim: int) -> torch.Tensor:
 class ProductArm:
     name = "product"
 
-    def __init__(self, capacity: int, dim: int, hbm_bytes: int, strategy: int = 0):
+    def __init__(self, capacity: int, dim: int, hbm_bytes: int, strategy: int = 0,
+                 slot_layout: int = 0):
         import hierarchicalkv_b200 as hkv
         from hierarchicalkv_b200.build import build_library
 
         build_library()
         self.t = hkv.HashTable(hkv.EvictStrategy(strategy))
         self.t.init(hkv.HashTableOptions(init_capacity=capacity, max_capacity=capacity,
-                                         max_hbm_for_vectors=hbm_bytes, dim=dim))
+                                         max_hbm_for_vectors=hbm_bytes, dim=dim,
+                                         slot_layout=slot_layout))
         self.dim = dim
 
     def insert_or_assign(self, keys, values, unique_key=True):
@@ -585,6 +587,45 @@ def hybrid_ops(arm_cls, batch: int, reps: int = 30) -> dict:
             "queries": "Zipf(1.05) over the inserted keys, 10 % fresh keys; duplicates inside a batch kept"}
 
 
+def shared_lines_ops(capacity: int, dim: int, batch: int, load_factor: float) -> dict:
+    """The headline table once more with the other slot layout (hkv_options.
+    slot_layout = HKV_SLOT_LINES: the keys of 8 slots and their 8 scores share a
+    128-byte line), same fill, same kinds of batches: what the layout gives to
+    updates of resident keys and what it takes from lookups and evictions."""
+    row = dim * 4
+    arm = ProductArm(capacity, dim, capacity * row + (1 << 30), slot_layout=1)
+    fill_table(arm, capacity, dim, batch, load_factor, 0)
+    qs = present_batches(arm, capacity, batch, 4, seed=17)
+    vals = [rows_for(q, dim) for q in qs]
+    out = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+    f = torch.empty(batch, dtype=torch.bool, device="cuda")
+    reps = 10
+    kv = lambda ms, r=reps: round(batch * r / (ms / 1e3) / BINARY_BILLION, 4)
+    res = {"find_all_hit": kv(time_steps(lambda i: arm.find(qs[i % 4], out, f), 50, 5), 50)}
+    assert bool(f.all()) and torch.equal(out, vals[(50 + 5 - 1) % 4])
+    res["contains"] = kv(time_steps(lambda i: arm.contains(qs[i % 4], f), 50, 5), 50)
+    res["insert_or_assign_all_hit"] = kv(time_steps(lambda i: arm.insert_or_assign(qs[i % 4], vals[i % 4]), reps, 3))
+    res["assign_all_hit"] = kv(time_steps(lambda i: arm.assign(qs[i % 4], vals[i % 4]), reps, 3))
+    deltas = torch.rand((batch, dim), device="cuda") * 1e-3
+    acc = torch.ones(batch, dtype=torch.bool, device="cuda")
+    res["accum_or_assign_all_hit"] = kv(time_steps(lambda i: arm.accum_or_assign(qs[i % 4], deltas, acc), reps, 3))
+    mixk = []
+    for i in range(reps + 3):
+        span = min(8 * batch, capacity)
+        cur = arm.export_keys(((i * 7919) % max(1, (capacity - span) // 128 + 1)) * 128, span)
+        cur = cur[torch.randperm(cur.numel(), device="cuda")[: int(batch * 0.6)]]
+        fresh = mixed_keys((1 << 54) + i * batch, batch - cur.numel(), "cuda")
+        mixk.append(torch.cat([cur, fresh]).contiguous())
+    newv = rows_for(mixk[0], dim)
+    res["insert_or_assign_60_40"] = kv(time_steps(lambda i: arm.insert_or_assign(mixk[i], newv), reps, 3))
+    newk = [mixed_keys((1 << 52) + i * batch, batch, "cuda") for i in range(reps + 3)]
+    res["insert_or_assign_all_new"] = kv(time_steps(lambda i: arm.insert_or_assign(newk[i], newv), reps, 3))
+    arm.close()
+    res["unit"] = "B-KV/s"
+    res["table"] = "the headline table with slot_layout = HKV_SLOT_LINES"
+    return res
+
+
 def churn_ops(arm_cls, batch: int) -> dict:
     """The churn / eviction table: capacity 32 Mi, dim 32 fp32, EpochLfu,
     steady-state insert_and_evict at load factor 1.0 with batches that are 30 %
@@ -963,6 +1004,117 @@ def cpu_baseline(dim: int, batch: int, seconds_budget: float = 20.0) -> dict:
                       f"keys through insert_or_assign (all present), {upd_reps} reps (best)"}
 
 
+def kernel_case(name: str, batch: int) -> None:
+    """One kernel of the library on a small table (about 2 GiB on the device),
+    a few launches, nothing timed: the workload `ncu` is pointed at when a
+    kernel is profiled that the headline run does not launch, or not in
+    isolation.  `--kernel-case NAME`, NAME one of the keys of `cases` below."""
+    import hierarchicalkv_b200 as hkv
+
+    dim, capacity = 64, 8 << 20
+
+    def table(strategy=0, cap=capacity, **kw):
+        t = hkv.HashTable(hkv.EvictStrategy(strategy))
+        t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=kw.pop("max_capacity", cap),
+                                    max_hbm_for_vectors=kw.pop("hbm", cap * dim * 4 + (1 << 30)),
+                                    dim=dim, **kw))
+        return t
+
+    def fill(t, n_keys, start=0, **kw):
+        for b in range(0, n_keys, batch):
+            k = mixed_keys(start + b, min(batch, n_keys - b), "cuda")
+            t.insert_or_assign(k.numel(), k, rows_for(k, dim), **kw)
+        torch.cuda.synchronize()
+
+    out = torch.empty((batch, dim), dtype=torch.float32, device="cuda")
+    f = torch.empty(batch, dtype=torch.bool, device="cuda")
+    p = torch.empty(batch, dtype=torch.int64, device="cuda")
+    c = torch.zeros(1, dtype=torch.int64, device="cuda")
+
+    def present(t, n=batch):
+        return mixed_keys(capacity - 2 * n, n, "cuda")      # among the last keys inserted
+
+    def find_forms():
+        t = table(); fill(t, capacity)
+        q = present(t)
+        for _ in range(3):
+            t.find(batch, q, out, f); t.find_ptr(batch, q, p, f); t.contains(batch, q, f)
+
+    def updates_of_present_keys():
+        t = table(); fill(t, capacity)
+        q = present(t); v = rows_for(q, dim); acc = torch.ones(batch, dtype=torch.bool, device="cuda")
+        for _ in range(3):
+            t.insert_or_assign(batch, q, v); t.assign(batch, q, v)
+            t.accum_or_assign_unique(batch, q, v, acc); t.find_or_insert(batch, q, v)
+
+    def evicting_inserts():
+        t = table(); fill(t, capacity + capacity // 4)
+        for i in range(3):
+            k = mixed_keys((1 << 52) + i * batch, batch, "cuda")
+            t.insert_or_assign(batch, k, rows_for(k, dim))
+
+    def repeated_keys():      # the serialising kernel: new keys of a batch that may repeat keys
+        t = table(); fill(t, capacity // 2)
+        for i in range(3):
+            k = mixed_keys((1 << 52) + i * batch, batch, "cuda")
+            t.insert_or_assign(batch, k, rows_for(k, dim), unique_key=False)
+
+    def erase():
+        t = table(); fill(t, capacity)
+        for i in range(3):
+            t.erase(batch, mixed_keys(capacity - (i + 1) * batch, batch, "cuda"))
+
+    def rehash():
+        t = table(cap=capacity // 2, max_capacity=capacity, max_load_factor=0.99)
+        fill(t, capacity // 2 - batch)
+        t.reserve(capacity)
+
+    def size_if_and_export():
+        t = table(); fill(t, capacity)
+        k = torch.empty(capacity // 4, dtype=torch.int64, device="cuda")
+        sc = torch.empty_like(k)
+        v = torch.empty((capacity // 4, dim), dtype=torch.float32, device="cuda")
+        for _ in range(3):
+            t.size_if(1, 0, (1 << 62), c)
+            t.export_batch(capacity // 4, 0, c, k, v, sc)
+
+    def other_bucket_size():  # 256-slot buckets: the bucket-size generic kernels
+        t = table(4, max_bucket_size=256)
+        sc = torch.arange(1, batch + 1, dtype=torch.int64, device="cuda")
+        for b in range(0, capacity // 2, batch):
+            k = mixed_keys(b, batch, "cuda")
+            t.insert_or_assign(batch, k, rows_for(k, dim), sc + b)
+        q = mixed_keys(capacity // 4, batch, "cuda")
+        for _ in range(3):
+            t.find(batch, q, out, f)
+
+    def dual_bucket():
+        t = table(4, hbm=0, table_mode=1)
+        sc = torch.arange(1, batch + 1, dtype=torch.int64, device="cuda")
+        for b in range(0, capacity // 2, batch):
+            k = mixed_keys(b, batch, "cuda")
+            t.insert_or_assign(batch, k, rows_for(k, dim), sc + b)
+        q = mixed_keys(capacity // 4, batch, "cuda")
+        for _ in range(3):
+            t.find(batch, q, out, f)
+
+    def hybrid_promotion():   # rows half in HBM, half in pinned host memory
+        t = table(hbm=capacity * dim * 4 // 2); fill(t, capacity // 2)
+        q = mixed_keys(0, batch, "cuda")
+        for _ in range(4):
+            t.find(batch, q, out, f)
+        t.promote_hot_buckets()
+
+    cases = {fn.__name__: fn for fn in (find_forms, updates_of_present_keys, evicting_inserts,
+                                     repeated_keys, erase, rehash, size_if_and_export,
+                                     other_bucket_size, dual_bucket, hybrid_promotion)}
+    if name not in cases:
+        raise SystemExit("--kernel-case: one of " + ", ".join(cases))
+    cases[name]()
+    torch.cuda.synchronize()
+    print(json.dumps({"kernel_case": name, "ok": True}))
+
+
 # ---------------------------------------------------------------------------
 # main
 # ---------------------------------------------------------------------------
@@ -981,6 +1133,9 @@ def main():
     ap.add_argument("--api-table", action="store_true",
                     help="instead of the JSON line of the headline workload: every API of the "
                          "reference's benchmark program at load factors 0.50 / 0.75 / 1.00")
+    ap.add_argument("--kernel-case", default=None,
+                    help="run one small named workload (a few launches of one kernel family on a "
+                         "2 GiB table) and exit: what ncu is pointed at; see kernel_case()")
     ap.add_argument("--staged-e2e", action="store_true",
                     help="end-to-end loop with the caller staging the batch (copy keys in, find, copy "
                          "rows out) instead of the host-buffer entry point")
@@ -1015,6 +1170,13 @@ def main():
     capacity, dim, batch = args.capacity, args.dim, args.batch
     row = dim * 4
     hbm_bytes = capacity * row + (1 << 30)
+
+    if args.kernel_case:
+        from hierarchicalkv_b200.build import build_library
+
+        build_library()
+        kernel_case(args.kernel_case, batch)
+        return
 
     if args.impl == "reference":
         try:
@@ -1223,6 +1385,11 @@ def main():
             if "achieved_gbs" in v:
                 v["b_kv_s"] = round(v["b_kv_s"], 4)
                 v["achieved_gbs"] = round(v["achieved_gbs"], 1)
+        if args.impl == "product":
+            try:
+                ops["shared_lines_layout"] = shared_lines_ops(capacity, dim, batch, args.load_factor)
+            except Exception as e:
+                ops["shared_lines_layout"] = {"failed": str(e)[:200]}
         try:
             ops["churn_epoch_lfu"] = churn_ops(type(arm), batch)
         except Exception as e:
