@@ -17,7 +17,8 @@ CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libhkv_b200.so")
 
-SOURCES = ["hkv_api.cu", "hkv_find.cu", "hkv_upsert.cu", "hkv_scan.cu", "hkv_noalloc.cu", "hkv_shard.cu"]
+SOURCES = ["hkv_api.cu", "hkv_find.cu", "hkv_upsert.cu", "hkv_scan.cu", "hkv_noalloc.cu", "hkv_shard.cu",
+           "hkv_sharded.cu"]
 HEADERS = ["hkv_device.cuh", "hkv_internal.h"]
 
 NVCC_FLAGS = [

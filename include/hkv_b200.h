@@ -431,6 +431,73 @@ HKV_API int hkv_upsert_routed(hkv_table* table, int op, uint32_t world, uint32_t
                               const hkv_peer_ptrs* values, const hkv_peer_ptrs* accum_flags,
                               hkv_stream stream);
 
+/* ---- the sharded table's host side -----------------------------------------
+ * No counterpart in the reference.  One hkv_sharded per rank (one rank per GPU;
+ * ranks are processes, or threads of one process) wraps that rank's sub-table
+ * and owns its peer workspaces ("lanes": inbox of routed keys, barrier flags,
+ * batch / result buffers, allocated with cudaMalloc so that they can be shared).
+ * Set-up, once:
+ *   1. every rank: hkv_sharded_create;
+ *   2. ranks in different processes exchange hkv_sharded_ipc_handle of every
+ *      lane by any means they have (files, sockets, MPI, torch.distributed) and
+ *      call hkv_sharded_connect_ipc; threads of one process pass each other
+ *      hkv_sharded_workspace pointers, enable peer access and call
+ *      hkv_sharded_connect_pointers;
+ *   3. a barrier of the caller's own before the first operation (every rank's
+ *      workspace must be connected and its flags still zero).
+ * Every rank then makes the same sequence of calls.  The device-side barriers
+ * are bounded by max_polls: a rank that never arrives sets bit 0 of the lane's
+ * status word instead of hanging the others. */
+typedef struct hkv_sharded hkv_sharded;
+typedef struct hkv_ipc_handle {
+  unsigned char bytes[64]; /* a cudaIpcMemHandle_t */
+} hkv_ipc_handle;
+
+HKV_API int hkv_sharded_create(hkv_table* table, uint32_t world, uint32_t rank,
+                               uint64_t max_batch, uint32_t lanes, hkv_sharded** out);
+HKV_API int hkv_sharded_destroy(hkv_sharded* sharded);
+HKV_API uint32_t hkv_sharded_lanes(const hkv_sharded* sharded);
+HKV_API uint64_t hkv_sharded_max_batch(const hkv_sharded* sharded);
+HKV_API int hkv_sharded_ipc_handle(hkv_sharded* sharded, uint32_t lane, hkv_ipc_handle* handle);
+/* handles[world]: every rank's handle of this lane (this rank's own is ignored) */
+HKV_API int hkv_sharded_connect_ipc(hkv_sharded* sharded, uint32_t lane,
+                                    const hkv_ipc_handle* handles);
+HKV_API void* hkv_sharded_workspace(hkv_sharded* sharded, uint32_t lane);
+/* bases[world]: every rank's hkv_sharded_workspace of this lane, valid in this process */
+HKV_API int hkv_sharded_connect_pointers(hkv_sharded* sharded, uint32_t lane, void* const* bases);
+/* This rank's buffers of a lane: rows (max_batch x row bytes) are the results
+ * of find and the batch rows of the updates, flags (max_batch) the found flags
+ * of find and the accum_or_assigns of accum_or_assign. */
+HKV_API int hkv_sharded_buffers(hkv_sharded* sharded, uint32_t lane, void** rows, bool** flags);
+/* HashTable::find over all shards (include/merlin_hashtable.cuh:2464 per shard):
+ * keys are routed to their owners, every owner looks up what arrived and stores
+ * hit rows and found flags into the requesters' buffers of `lane`, row i for
+ * key i.  Rows of misses keep their previous content.  Enqueued on `stream`. */
+HKV_API int hkv_sharded_find(hkv_sharded* sharded, uint32_t lane, uint64_t n, const uint64_t* keys,
+                             uint32_t max_polls, hkv_stream stream);
+/* The same on the next lane's own streams (routing and barriers at high
+ * priority), so that the routing of batch k + 1 overlaps the lookup of batch
+ * k: returns at once with the lane it used; hkv_sharded_wait makes a stream
+ * wait for that lane's results.  Issue batch k + 1 before waiting for batch k. */
+HKV_API int hkv_sharded_find_async(hkv_sharded* sharded, uint64_t n, const uint64_t* keys,
+                                   uint32_t max_polls, hkv_stream stream, uint32_t* lane_used);
+HKV_API int hkv_sharded_wait(hkv_sharded* sharded, uint32_t lane, hkv_stream stream);
+/* insert_or_assign / find_or_insert / accum_or_assign over all shards
+ * (op: HKV_ROUTED_*; include/merlin_hashtable.cuh:1125, 1699, 1589 per shard).
+ * The batch rows are the first n rows of lane 0's buffers (accum_or_assign: its
+ * flags too); find_or_insert writes the stored rows of the hits back into
+ * them.  A key several ranks send is applied as if those ranks had called the
+ * table one after the other, starting with rank owner + 1 and wrapping.
+ * reuse_route != 0: `keys` are the keys of the previous hkv_sharded_upsert call
+ * on every rank (the update that follows a find_or_insert of the same batch);
+ * the inboxes still hold them and the routing is skipped. */
+HKV_API int hkv_sharded_upsert(hkv_sharded* sharded, int op, uint64_t n, const uint64_t* keys,
+                               int reuse_route, uint32_t max_polls, hkv_stream stream);
+/* bit 0: a peer barrier of this lane timed out.  Synchronises the stream. */
+HKV_API int hkv_sharded_status(hkv_sharded* sharded, uint32_t lane, hkv_stream stream,
+                               uint32_t* status);
+HKV_API const char* hkv_sharded_last_error(void);
+
 /* hkv_accum_or_assign for batches the caller guarantees to hold each key once
  * (the sharded table de-duplicates before routing): one launch of the probe
  * kernel the other insert-like operations use, without the second pass that
