@@ -7,10 +7,13 @@ table's own hash, include/merlin/utils.cuh:137-145 of the reference), and a
 batch is routed with an all-to-all over NVLink -- keys out, rows and found
 flags back -- around the local operation.
 
-One process per GPU; ``torch.distributed`` (NCCL) carries the exchange, the
-grouping by owner and the row permutations are CUDA kernels of
-libhkv_b200.so (csrc/hkv_shard.cu).  With a world of one rank the exchange is
-skipped and every call is exactly the local table's.
+One process per GPU.  Two routings: the fused one (find_fused, upsert_fused:
+keys, rows and flags travel over peer memory inside the library's own kernels;
+the host side is the library's C++ sharded table, csrc/hkv_sharded.cu, which
+this module only binds) and the plain one, where ``torch.distributed`` (NCCL)
+carries the exchange and the grouping by owner and the row permutations are
+CUDA kernels of libhkv_b200.so (csrc/hkv_shard.cu).  With a world of one rank
+the exchange is skipped and every call is exactly the local table's.
 """
 from __future__ import annotations
 
@@ -72,64 +75,60 @@ class _PeerPtrs(ctypes.Structure):
     _fields_ = [("p", ctypes.c_void_p * 16)]
 
 
+class _IpcHandle(ctypes.Structure):
+    """hkv_ipc_handle"""
+
+    _fields_ = [("bytes", ctypes.c_ubyte * 64)]
+
+
+class _DeviceBytes:
+    """A range of device memory torch can wrap without copying."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 2}
+
+
 class PeerWorkspace:
-    """Buffers every rank of the node can store into (torch symmetric memory,
-    i.e. CUDA peer mappings over NVLink): each rank's inbox of routed keys and
-    its batch / result buffers.  Used by ShardedHashTable.find_fused and
-    upsert_fused."""
+    """One lane of the sharded table's C++ host (hkv_sharded, csrc/hkv_sharded.cu):
+    this rank's inbox of routed keys and its batch / result buffers, which the
+    other ranks of the node store into over NVLink.  The object only holds
+    torch views of this rank's buffers; allocation, the mapping of the peers'
+    workspaces and the barrier epochs live in the library."""
 
-    MAX_WORLD = 16
-
-    def __init__(self, group, max_batch: int, dim: int, dtype: torch.dtype = torch.float32):
-        import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm
-
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
-        if self.world > self.MAX_WORLD:
-            raise ValueError("at most 16 ranks")
-        max_batch = (max_batch + 31) // 32 * 32   # inbox segments hold whole warps of keys
+    def __init__(self, lib, host, lane: int, max_batch: int, dim: int, dtype: torch.dtype):
+        self.lib, self.host, self.lane = lib, host, lane
         self.max_batch = max_batch
         self.dim = dim
         self.dtype = dtype
+        rows, flags = ctypes.c_void_p(), ctypes.c_void_p()
+        if lib.hkv_sharded_buffers(host, lane, ctypes.byref(rows), ctypes.byref(flags)):
+            raise RuntimeError((lib.hkv_sharded_last_error() or b"").decode())
         row_bytes = dim * torch.empty((), dtype=dtype).element_size()
-        self.row_bytes = row_bytes
-
-        def up(x):
-            return (x + 255) // 256 * 256
-
-        off = {}
-        at = 0
-        for name, size in (("inbox_keys", self.world * max_batch * 8),
-                           ("inbox_origin", self.world * max_batch * 4),
-                           ("inbox_counts", 16 * 8), ("flags", 16 * 4),
-                           ("out_founds", max_batch), ("out_values", max_batch * row_bytes)):
-            off[name] = at
-            at = up(at + size)
-        self.offsets = off
-        self.buf = symm.empty(at, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
-        self.buf.zero_()
-        self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
-        torch.cuda.synchronize()
-        dist.barrier(group)                       # every rank's flags are zero before the first use
-        bases = [int(p) for p in self.handle.buffer_ptrs]
-        self.peers = {}
-        for name in off:
-            pp = _PeerPtrs()
-            for r in range(self.world):
-                pp.p[r] = bases[r] + off[name]
-            self.peers[name] = pp
-        self.local = {name: bases[self.rank] + off[name] for name in off}
-        self.scratch = torch.zeros(32, dtype=torch.int64, device="cuda")   # cursors | status
-        self.epoch = 0
-        # views of this rank's result buffers
-        ov = self.buf[off["out_values"]: off["out_values"] + max_batch * row_bytes]
+        ov = torch.as_tensor(_DeviceBytes(rows.value, max_batch * row_bytes), device="cuda")
         self.out_values = ov.view(dtype).view(max_batch, dim)
-        self.out_founds = self.buf[off["out_founds"]: off["out_founds"] + max_batch].view(torch.bool)
+        self.out_founds = torch.as_tensor(_DeviceBytes(flags.value, max_batch),
+                                          device="cuda").view(torch.bool)
 
     def status(self) -> int:
         """Non-zero after a barrier timed out (a peer never arrived)."""
-        return int(self.scratch[16].item())
+        out = ctypes.c_uint32(0)
+        if self.lib.hkv_sharded_status(self.host, self.lane, _stream_ptr(), ctypes.byref(out)):
+            raise RuntimeError((self.lib.hkv_sharded_last_error() or b"").decode())
+        return out.value
+
+
+class LaneResult:
+    """Completion of one find_fused_async call."""
+
+    def __init__(self, table, lane: int, keys):
+        self._table, self.lane, self._keys = table, lane, keys   # the keys stay alive until waited for
+
+    def wait(self) -> None:
+        """Makes the current stream wait for the lane's results."""
+        self._table._chk_host(self._table.ops.lib.hkv_sharded_wait(self._table._host, self.lane,
+                                                                   _stream_ptr()))
+        self._keys = None
 
 
 class _Route:
@@ -242,154 +241,124 @@ class ShardedHashTable:
 
     def enable_fused_find(self, max_batch: int, dim: int, dtype: torch.dtype = torch.float32,
                           lanes: int = 1):
-        """Allocates the peer-visible inbox and result buffers find_fused needs.
-        With ``lanes`` > 1 it allocates that many independent sets (each with its
-        own stream, flags and epoch) for find_fused_async, which rotates through
-        them so the routing of one batch overlaps the lookup of the previous one."""
-        self.lanes = [PeerWorkspace(self.group, max_batch, dim, dtype) for _ in range(max(1, lanes))]
-        self.lane_streams = [torch.cuda.Stream() for _ in self.lanes]
-        # routing and barriers of the next batch must not queue behind the blocks
-        # of the previous batch's lookup: they run on streams of higher priority
-        self.lane_streams_hi = [torch.cuda.Stream(priority=-1) for _ in self.lanes]
-        self.lane_events = [None for _ in self.lanes]
-        self._next_lane = 0
+        """Creates the C++ host of the fused paths for this rank's sub-table
+        (hkv_sharded_create), lets the ranks exchange the CUDA IPC handles of
+        their workspaces and maps them.  With ``lanes`` > 1 there are that many
+        independent workspaces (own inbox, flags, epochs and streams) for
+        find_fused_async, which rotates through them so the routing of one
+        batch overlaps the lookup of the previous one.  A collective call."""
+        lib = self.ops.lib
+        host = ctypes.c_void_p()
+        self._chk_host(lib.hkv_sharded_create(self.local.handle, self.world, self.rank, max_batch,
+                                              max(1, lanes), ctypes.byref(host)))
+        self._host = host
+        n_lanes = lib.hkv_sharded_lanes(host)
+        if self.world > 1:
+            mine = []
+            for lane in range(n_lanes):
+                h = _IpcHandle()
+                self._chk_host(lib.hkv_sharded_ipc_handle(host, lane, ctypes.byref(h)))
+                mine.append(bytes(h.bytes))
+            everyone = [None] * self.world
+            self.dist.all_gather_object(everyone, mine, group=self.group)
+            for lane in range(n_lanes):
+                handles = (_IpcHandle * self.world)()
+                for r in range(self.world):
+                    ctypes.memmove(handles[r].bytes, everyone[r][lane], 64)
+                self._chk_host(lib.hkv_sharded_connect_ipc(host, lane, handles))
+            torch.cuda.synchronize()
+            self.dist.barrier(self.group)     # every rank's workspace is mapped, its flags still zero
+        cap = lib.hkv_sharded_max_batch(host)
+        self.lanes = [PeerWorkspace(lib, host, lane, cap, dim, dtype) for lane in range(n_lanes)]
+        self._pending = [None for _ in self.lanes]
         self.peer = self.lanes[0]
         return self.peer
 
     def share_workspace(self, other: "ShardedHashTable") -> None:
-        """Uses the peer workspaces (and lane streams) `other` allocated: several
-        sharded tables of one process can serve their fused calls from one set."""
-        self.lanes, self.lane_streams = other.lanes, other.lane_streams
-        self.lane_streams_hi = other.lane_streams_hi
-        self.lane_events = other.lane_events
-        self._next_lane = 0
-        self.peer = other.peer
+        """Gives this table fused paths shaped like `other`'s (a collective call:
+        every host belongs to one sub-table and has workspaces of its own)."""
+        self.enable_fused_find(other.peer.max_batch, other.peer.dim, other.peer.dtype,
+                               lanes=len(other.lanes))
+
+    def close_fused(self) -> None:
+        """Destroys the C++ host (call it on every rank, after a barrier of their own)."""
+        host = getattr(self, "_host", None)
+        if host:
+            self.ops.lib.hkv_sharded_destroy(host)
+            self._host = None
 
     # -- fused paths: routing, lookup / update and transfer without NCCL ----------
-    def _chk_shard(self, rc: int) -> None:
+    def _chk_host(self, rc: int) -> None:
         if rc:
-            raise RuntimeError((self.ops.lib.hkv_shard_last_error() or b"").decode())
-
-    def _route_p2p(self, n, keys, w=None) -> None:
-        """Groups the batch by owner and stores keys and batch indices straight
-        into the owners' inboxes over NVLink."""
-        w = w or self.peer
-        if n > w.max_batch:
-            raise ValueError("batch larger than the workspace")
-        self._chk_shard(self.ops.lib.hkv_shard_route_keys_p2p(
-            n, keys.data_ptr(), self.world, self.rank, w.max_batch,
-            ctypes.byref(w.peers["inbox_keys"]), ctypes.byref(w.peers["inbox_origin"]),
-            ctypes.byref(w.peers["inbox_counts"]), w.scratch.data_ptr(), _stream_ptr()))
-
-    def _peer_barrier(self, max_polls: int, w=None) -> None:
-        w = w or self.peer
-        w.epoch += 1
-        self._chk_shard(self.ops.lib.hkv_shard_barrier(
-            self.world, self.rank, ctypes.byref(w.peers["flags"]), w.epoch,
-            w.scratch[16:].data_ptr(), max_polls, _stream_ptr()))
+            raise RuntimeError((self.ops.lib.hkv_sharded_last_error() or b"").decode())
 
     def find_fused(self, n, keys, max_polls: int = 50_000_000, lane: int = 0):
-        """HashTable::find over all shards with lookup and transfer fused: keys
-        are grouped by owner and stored straight into the owners' inboxes, every
-        owner runs ONE lookup kernel over what arrived and stores hit rows and
-        found flags straight into the requesters' result buffers over NVLink.
-        No NCCL call and no host synchronisation; two bounded peer barriers.
-        Returns views (rows, found flags) of this rank's result buffers, valid
-        until the next call on the same lane; rows of misses keep their previous
-        content."""
+        """HashTable::find over all shards with lookup and transfer fused
+        (hkv_sharded_find): keys are grouped by owner and stored straight into
+        the owners' inboxes, every owner runs ONE lookup kernel over what
+        arrived and stores hit rows and found flags straight into the
+        requesters' result buffers over NVLink.  No NCCL call and no host
+        synchronisation; two bounded peer barriers.  Returns views (rows, found
+        flags) of this rank's result buffers, valid until the next call on the
+        same lane; rows of misses keep their previous content."""
         w = self.lanes[lane]
-        lib = self.ops.lib
-        self._route_p2p(n, keys, w)
-        self._peer_barrier(max_polls, w)
-        rc = lib.hkv_find_routed(self.local.handle, self.world, self.rank, w.max_batch,
-                                 w.local["inbox_keys"], w.local["inbox_origin"],
-                                 w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
-                                 ctypes.byref(w.peers["out_founds"]), _stream_ptr())
-        if rc:
-            raise RuntimeError((lib.hkv_last_error() or b"").decode())
-        self._peer_barrier(max_polls, w)
+        self._chk_host(self.ops.lib.hkv_sharded_find(self._host, lane, n, keys.data_ptr(), max_polls,
+                                                     _stream_ptr()))
         return w.out_values[:n], w.out_founds[:n]
 
     def find_fused_async(self, n, keys, max_polls: int = 50_000_000):
-        """find_fused on the next lane's own streams: returns (rows, found flags,
-        event) at once; the results are complete when the event has fired
-        (``torch.cuda.current_stream().wait_event(event)``).  Every rank must make
-        the same sequence of calls.  Consecutive calls use different lanes, so
-        the grouping, the key stores and the barriers of batch k + 1 run while
-        the owners still serve batch k.  To keep that overlap, issue batch k + 1
-        BEFORE waiting for batch k: each call first makes its lane wait for
-        everything already queued on the caller's stream (the producer of
-        ``keys``, and the consumer of the lane's previous results)."""
-        lane = self._next_lane
-        self._next_lane = (lane + 1) % len(self.lanes)
+        """find_fused on the next lane's own streams (hkv_sharded_find_async):
+        returns (rows, found flags, result) at once; ``result.wait()`` makes the
+        current stream wait for them.  Every rank must make the same sequence
+        of calls.  Consecutive calls use different lanes, so the grouping, the
+        key stores and the barriers of batch k + 1 run while the owners still
+        serve batch k.  To keep that overlap, issue batch k + 1 BEFORE waiting
+        for batch k: each call first makes its lane wait for everything
+        already queued on the caller's stream (the producer of ``keys``, and
+        the consumer of the lane's previous results)."""
+        used = ctypes.c_uint32(0)
+        self._chk_host(self.ops.lib.hkv_sharded_find_async(self._host, n, keys.data_ptr(), max_polls,
+                                                           _stream_ptr(), ctypes.byref(used)))
+        lane = used.value
         w = self.lanes[lane]
-        lib = self.ops.lib
-        hi, lo = self.lane_streams_hi[lane], self.lane_streams[lane]
-        hi.wait_stream(torch.cuda.current_stream())
-        keys.record_stream(hi)
-        with torch.cuda.stream(hi):
-            self._route_p2p(n, keys, w)
-            self._peer_barrier(max_polls, w)
-        lo.wait_stream(hi)
-        with torch.cuda.stream(lo):
-            rc = lib.hkv_find_routed(self.local.handle, self.world, self.rank, w.max_batch,
-                                     w.local["inbox_keys"], w.local["inbox_origin"],
-                                     w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
-                                     ctypes.byref(w.peers["out_founds"]), _stream_ptr())
-            if rc:
-                raise RuntimeError((lib.hkv_last_error() or b"").decode())
-        hi.wait_stream(lo)
-        with torch.cuda.stream(hi):
-            self._peer_barrier(max_polls, w)
-            done = torch.cuda.Event()
-            done.record(hi)
-        rows, founds = w.out_values[:n], w.out_founds[:n]
-        self.lane_events[lane] = done
-        return rows, founds, done
+        result = LaneResult(self, lane, keys)
+        self._pending[lane] = result
+        return w.out_values[:n], w.out_founds[:n], result
 
     def join_lanes(self) -> None:
         """Makes the caller's stream wait for every lane's last find_fused_async."""
-        cur = torch.cuda.current_stream()
-        for e in self.lane_events:
-            if e is not None:
-                cur.wait_event(e)
+        for lane, r in enumerate(self._pending):
+            if r is not None:
+                r.wait()
+                self._pending[lane] = None
 
     _ROUTED_OPS = {"insert_or_assign": 0, "find_or_insert": 1, "accum_or_assign": 2}
 
     def upsert_fused(self, op: str, n, keys, max_polls: int = 50_000_000,
                      reuse_route: bool = False):
         """insert_or_assign / find_or_insert / accum_or_assign over all shards
-        with the update and the transfer fused.  The batch rows are the first n
-        rows of this rank's peer-visible buffer ``peer.out_values`` (for
-        accum_or_assign the flags are ``peer.out_founds[:n]``): the caller
-        fills them before the call, the owners' kernels read new rows and deltas
-        from them and -- find_or_insert -- write the stored rows of the hits
-        back into them, all over NVLink.  No NCCL call, no host
-        synchronisation, no staging copy; two bounded peer barriers.
+        with the update and the transfer fused (hkv_sharded_upsert).  The batch
+        rows are the first n rows of this rank's peer-visible buffer
+        ``peer.out_values`` (for accum_or_assign the flags are
+        ``peer.out_founds[:n]``): the caller fills them before the call, the
+        owners' kernels read new rows and deltas from them and --
+        find_or_insert -- write the stored rows of the hits back into them, all
+        over NVLink.  No NCCL call, no host synchronisation, no staging copy;
+        two bounded peer barriers.
 
-        At each owner the requesting ranks' batches are applied one after the
-        other, starting with rank owner + 1 (wrapping), so a key that several
-        ranks send in one step behaves as if those ranks had called the table
-        in that order.  Needs a score-free strategy (kLru / kEpochLru).
+        A key that several ranks send in one step behaves as if those ranks had
+        called the table one after the other, starting with rank owner + 1
+        (wrapping).  Needs a score-free strategy (kLru / kEpochLru).
 
         ``reuse_route``: the keys are those of the previous upsert_fused call of
         every rank (the update that follows a find_or_insert of the same
         batch): the owners' inboxes still hold them and the routing is skipped;
         the barrier stays, it tells the owners that the ranks' buffers carry
         the new rows."""
-        w = self.peer
-        lib = self.ops.lib
-        if not reuse_route:
-            self._route_p2p(n, keys)
-        self._peer_barrier(max_polls)
-        rc = lib.hkv_upsert_routed(self.local.handle, self._ROUTED_OPS[op], self.world, self.rank,
-                                   w.max_batch, w.local["inbox_keys"], w.local["inbox_origin"],
-                                   w.local["inbox_counts"], ctypes.byref(w.peers["out_values"]),
-                                   ctypes.byref(w.peers["out_founds"]), _stream_ptr())
-        if rc:
-            raise RuntimeError((lib.hkv_last_error() or b"").decode())
-        self._peer_barrier(max_polls)
-        return w.out_values[:n]
+        self._chk_host(self.ops.lib.hkv_sharded_upsert(self._host, self._ROUTED_OPS[op], n,
+                                                       keys.data_ptr(), int(reuse_route), max_polls,
+                                                       _stream_ptr()))
+        return self.peer.out_values[:n]
 
     def insert_or_assign(self, n, keys, values, scores=None, stream=None) -> None:
         if n == 0:

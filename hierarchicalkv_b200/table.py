@@ -178,6 +178,22 @@ _SIGNATURES = {
     "hkv_find_routed": [_P, ctypes.c_uint32, ctypes.c_uint32, _U64, _P, _P, _P, _P, _P, _P],
     "hkv_upsert_routed": [_P, ctypes.c_int, ctypes.c_uint32, ctypes.c_uint32, _U64, _P, _P, _P, _P,
                           _P, _P],
+    "hkv_sharded_create": [_P, ctypes.c_uint32, ctypes.c_uint32, _U64, ctypes.c_uint32,
+                           ctypes.POINTER(_P)],
+    "hkv_sharded_destroy": [_P],
+    "hkv_sharded_lanes": [_P],
+    "hkv_sharded_max_batch": [_P],
+    "hkv_sharded_ipc_handle": [_P, ctypes.c_uint32, _P],
+    "hkv_sharded_connect_ipc": [_P, ctypes.c_uint32, _P],
+    "hkv_sharded_workspace": [_P, ctypes.c_uint32],
+    "hkv_sharded_connect_pointers": [_P, ctypes.c_uint32, _P],
+    "hkv_sharded_buffers": [_P, ctypes.c_uint32, ctypes.POINTER(_P), ctypes.POINTER(_P)],
+    "hkv_sharded_find": [_P, ctypes.c_uint32, _U64, _P, ctypes.c_uint32, _P],
+    "hkv_sharded_find_async": [_P, _U64, _P, ctypes.c_uint32, _P, ctypes.POINTER(ctypes.c_uint32)],
+    "hkv_sharded_wait": [_P, ctypes.c_uint32, _P],
+    "hkv_sharded_upsert": [_P, _INT, _U64, _P, _INT, ctypes.c_uint32, _P],
+    "hkv_sharded_status": [_P, ctypes.c_uint32, _P, ctypes.POINTER(ctypes.c_uint32)],
+    "hkv_sharded_last_error": [],
     "hkv_accum_or_assign_unique": [_P, _U64, _P, _P, _P, _P, _P, _INT],
     "hkv_size_no_alloc": [_P, _P, ctypes.POINTER(_U64)],
     "hkv_size_no_alloc_last_error": [],
@@ -196,6 +212,10 @@ _SIGNATURES = {
     "hkv_last_error": [],
 }
 _RESTYPES = {
+    "hkv_sharded_lanes": ctypes.c_uint32,
+    "hkv_sharded_max_batch": _U64,
+    "hkv_sharded_workspace": _P,
+    "hkv_sharded_last_error": ctypes.c_char_p,
     "hkv_capacity": _U64,
     "hkv_bucket_count": _U64,
     "hkv_dim": _U64,

@@ -182,7 +182,7 @@ def _nccl_worker(rank, world, port, dim, cap):
 
     def check(i, res):
         rows, flags, done = res
-        torch.cuda.current_stream().wait_event(done)
+        done.wait()
         got, gf = rows.cpu().numpy(), flags.cpu().numpy()
         ev, ef, _ = glob.find(batches[i])
         assert np.array_equal(gf, ef)
@@ -203,7 +203,7 @@ def _nccl_worker(rank, world, port, dim, cap):
     t2.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
                                  dim=dim))
     st2 = ShardedHashTable(t2)
-    st2.share_workspace(st)                  # same workspace
+    st2.share_workspace(st)                  # fused paths of the same shape
     w = st2.peer
     both = keys[30000:33000]                 # every rank sends the same keys: all of them collide
     own = keys[33000 + rank * 1500: 33000 + (rank + 1) * 1500]
