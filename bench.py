@@ -1105,9 +1105,38 @@ def kernel_case(name: str, batch: int) -> None:
             t.find(batch, q, out, f)
         t.promote_hot_buckets()
 
+    def routed_updates():     # the owner's side of the sharded updates, both source ranks' buffers local
+        import ctypes
+        from hierarchicalkv_b200.sharded import CudaOps, _PeerPtrs
+        t = table(); fill(t, capacity)
+        lib, world, per, segcap = CudaOps().lib, 2, batch // 4, batch
+        q = present(t)
+        inbox_k = torch.zeros(world * segcap, dtype=torch.int64, device="cuda")
+        inbox_o = torch.zeros(world * segcap, dtype=torch.int32, device="cuda")
+        counts = torch.zeros(16, dtype=torch.int64, device="cuda")
+        shared = 4096                                        # keys both ranks ask for
+        for s in range(world):
+            ks = torch.cat([q[:shared], q[shared + s * per: shared + (s + 1) * per]])
+            inbox_k[s * segcap: s * segcap + ks.numel()] = ks
+            inbox_o[s * segcap: s * segcap + ks.numel()] = torch.arange(ks.numel(), dtype=torch.int32,
+                                                                        device="cuda")
+            counts[s] = ks.numel()
+        bufs = [torch.rand((shared + per, dim), device="cuda") * 1e-3 for _ in range(world)]
+        flags = [torch.ones(shared + per, dtype=torch.bool, device="cuda") for _ in range(world)]
+        pv, pf = _PeerPtrs(), _PeerPtrs()
+        for r in range(world):
+            pv.p[r], pf.p[r] = bufs[r].data_ptr(), flags[r].data_ptr()
+        for _ in range(2):
+            for op in (1, 2, 0):                             # find_or_insert, accum_or_assign, insert_or_assign
+                rc = lib.hkv_upsert_routed(t.handle, op, world, 0, segcap, inbox_k.data_ptr(),
+                                           inbox_o.data_ptr(), counts.data_ptr(), ctypes.byref(pv),
+                                           ctypes.byref(pf), None)
+                if rc != 0:
+                    raise RuntimeError(lib.hkv_last_error())
+
     cases = {fn.__name__: fn for fn in (find_forms, updates_of_present_keys, evicting_inserts,
                                      repeated_keys, erase, rehash, size_if_and_export,
-                                     other_bucket_size, dual_bucket, hybrid_promotion)}
+                                     other_bucket_size, dual_bucket, hybrid_promotion, routed_updates)}
     if name not in cases:
         raise SystemExit("--kernel-case: one of " + ", ".join(cases))
     cases[name]()

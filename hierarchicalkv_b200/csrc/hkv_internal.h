@@ -119,12 +119,17 @@ struct RoutedArgs {
   PeerPtrs flags_of{};                 // accum_or_assign: each source rank's flags
   // grouping scratch (routed_workspace_bytes): an open-addressing set of the
   // inbox's keys, the head of each key's request chain, and per inbox entry
-  // the next request for the same key and the set slot of its key
+  // the next request for the same key and the set slot of its key; then what
+  // the resolving pass leaves for the serving pass: a plan word per entry and
+  // the later ranks' requests of every key as runs of a list array
   uint64_t* set_keys = nullptr;
   uint32_t* set_head = nullptr;
   uint32_t* next = nullptr;
   uint32_t* set_slot = nullptr;
   uint32_t set_bits = 0;               // log2 of the set's size
+  uint64_t* plan = nullptr;
+  uint32_t* lists = nullptr;
+  uint32_t* list_cursor = nullptr;     // zero between calls
 };
 size_t routed_workspace_bytes(uint32_t world, uint64_t segment_capacity);
 // Carves `work` into the scratch arrays of `r`; `fresh`: the memory is new and

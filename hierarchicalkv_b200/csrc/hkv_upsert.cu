@@ -259,11 +259,15 @@ __host__ __device__ constexpr int mutate_min_blocks(int op) {
 // What the routed form knows about the tile a warp serves.
 constexpr uint32_t kMaxRequests = 16;     // requests for one key in one call: one per rank
 constexpr uint32_t kNoEntry = 0xFFFFFFFFu;
+// The plan word of an inbox entry that serves its key: bits 0-4 the number of
+// requests, 5-20 which of them accumulate, 21-25 the first that assigns
+// (kMaxRequests: none), 26-57 where the later ranks' requests start in the
+// list array, bit 63 set.  Zero: the entry does nothing.
+constexpr uint32_t kPlanAccumShift = 5, kPlanAssignShift = 21, kPlanListShift = 26;
 struct RoutedWarp {
   const RoutedArgs* r;
   uint32_t segment;                        // source rank of the tile's keys
   uint8_t* const* values_of;               // shared-memory copies of the ranks' buffers
-  const bool* const* flags_of;
   uint32_t (*requests)[kMutateBlock];      // per thread: its key's requests in turn order
 };
 
@@ -281,8 +285,13 @@ __device__ __forceinline__ uint32_t segment_of(const RoutedArgs& r, uint32_t tur
 // `which` (bit r: request r), one after the other: MODE 0 copies the slot's row
 // into the requesting rank's buffer, MODE 2 adds that rank's row to the slot's.
 // All lanes call it; a lane without a slot passes kNoSlot.
+#ifdef HKV_SERVE_NOINLINE
+#define HKV_SERVE_INLINE __noinline__
+#else
+#define HKV_SERVE_INLINE __forceinline__
+#endif
 template <int MODE, int VEC>
-__device__ __forceinline__ void serve_requests(const TableView& t, const RoutedWarp* rw,
+__device__ HKV_SERVE_INLINE void serve_requests(const TableView& t, const RoutedWarp* rw,
                                                uint32_t slot, uint32_t from, uint32_t count,
                                                uint32_t which, uint32_t lane) {
   const uint32_t most = __reduce_max_sync(0xFFFFFFFFu, slot != kNoSlot ? count : 0u);
@@ -328,33 +337,29 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
   uint8_t* const batch_rows = INDEXED ? nullptr : args.values + base * t.row_bytes;
   bool serves = true;  // INDEXED: this lane is the first in turn order to ask for its key
   if (INDEXED && i < n) {
-    // This lane's inbox entry and the chain of all requests for its key.  The
-    // lane whose rank comes first in turn order serves the key; it keeps the
-    // chain, sorted by turn, in its column of rw->requests as turn << 28 | row.
+    // This lane's inbox entry and what routed_resolve_kernel planned for it:
+    // nothing (another rank's entry serves the key, or the key is reserved), or
+    // the number of requests for the key, which of them accumulate, the first
+    // that assigns, and where the requests of the later ranks are listed.  The
+    // lane keeps the requests, in turn order, in its column of rw->requests as
+    // rank << 28 | row.
     const RoutedArgs& r = *rw->r;
     const uint64_t entry = uint64_t(rw->segment) * r.segment_capacity + i;
     key = r.inbox_keys[entry];
-    const uint32_t my_turn = turn_of(r, rw->segment);
-    if (!is_reserved(t, key)) {
-      n_requests = 0;
-      uint32_t hops = 0;
-      for (uint32_t e = r.set_head[r.set_slot[entry]]; e != kNoEntry && hops < 4 * kMaxRequests;
-           e = r.next[e], ++hops) {
-        const uint32_t seg = uint32_t(e / r.segment_capacity);
-        const uint32_t turn = turn_of(r, seg);
-        if (turn < my_turn || (turn == my_turn && e < entry)) serves = false;
-        if (n_requests < kMaxRequests) {
-          // insertion into the sorted column
-          const uint32_t word = (turn << kRowTagShift) | r.inbox_origin[e];
-          uint32_t at = n_requests++;
-          while (at > 0 && rw->requests[at - 1][threadIdx.x] > word) {
-            rw->requests[at][threadIdx.x] = rw->requests[at - 1][threadIdx.x];
-            --at;
-          }
-          rw->requests[at][threadIdx.x] = word;
-        }
-      }
-      if (n_requests == 0) serves = false;  // cannot happen: the chain holds this entry
+    const uint64_t plan = r.plan[entry];
+    serves = plan != 0;
+    if (serves) {
+      n_requests = uint32_t(plan) & 31u;
+      accumulating = uint32_t(plan >> kPlanAccumShift) & 0xFFFFu;
+      first_assign = uint32_t(plan >> kPlanAssignShift) & 31u;
+      const uint32_t* later = r.lists + (uint32_t(plan >> kPlanListShift));
+      rw->requests[0][threadIdx.x] = (rw->segment << kRowTagShift) | r.inbox_origin[entry];
+      for (uint32_t q = 1; q < n_requests; ++q) rw->requests[q][threadIdx.x] = later[q - 1];
+      // nobody reads the scratch set after the resolving pass: the one entry
+      // that serves a key leaves the key's place empty for the next call
+      const uint32_t at = r.set_slot[entry];
+      r.set_keys[at] = t.empty_key;
+      r.set_head[at] = kNoEntry;
     }
   }
   if (i < n) {
@@ -367,19 +372,6 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
         desired = desired_score(strategy, args.scores, in_score, args.epoch);
       }
       if (INDEXED) {
-        // rows are named by rank << 28 | row
-        const RoutedArgs& r = *rw->r;
-        for (uint32_t q = 0; q < n_requests; ++q) {
-          const uint32_t word = rw->requests[q][threadIdx.x];
-          const uint32_t tag =
-              (segment_of(r, word >> kRowTagShift) << kRowTagShift) | (word & kRowTagMask);
-          rw->requests[q][threadIdx.x] = tag;
-          if (OP == kOpAccumOrAssign) {
-            const bool is_accum = rw->flags_of[tag >> kRowTagShift][tag & kRowTagMask];
-            if (is_accum) accumulating |= 1u << q;
-            else if (first_assign == kMaxRequests) first_assign = q;
-          }
-        }
         // insert_or_assign: the last rank's row is what stays; find_or_insert: the
         // first rank's row is inserted; accum_or_assign: the first assigning rank's
         my_row = rw->requests[OP == kOpInsertOrAssign ? n_requests - 1
@@ -598,11 +590,18 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
       warp_move_rows<1, VEC, INDEXED>(t, batch_rows, holds_lock ? my_slot : kNoSlot, pl.lane,
                                       my_row, bases);
     } else if (OP == kOpFindOrInsert) {
-      warp_move_rows<0, VEC, INDEXED>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot,
-                                      pl.lane, my_row, bases);
-      warp_move_rows<1, VEC, INDEXED>(t, batch_rows,
-                                      my_result == kOccupiedEmpty ? my_slot : kNoSlot, pl.lane,
-                                      my_row, bases);
+      if constexpr (INDEXED) {
+        // found rows come out, the rows of new keys go in: one pass (the routed
+        // form is short of registers; the local form is faster with two)
+        warp_move_rows<3, VEC, true>(
+            t, batch_rows,
+            (my_result == kDuplicate || my_result == kOccupiedEmpty) ? my_slot : kNoSlot, pl.lane,
+            my_row, bases, __ballot_sync(full, my_result == kOccupiedEmpty));
+      } else {
+        warp_move_rows<0, VEC>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
+        warp_move_rows<1, VEC>(t, batch_rows, my_result == kOccupiedEmpty ? my_slot : kNoSlot,
+                               pl.lane);
+      }
       if constexpr (INDEXED) {
         // the ranks whose turn comes later find the key: they get the row
         __syncwarp();
@@ -847,19 +846,63 @@ __global__ void __launch_bounds__(kMutateBlock)
   }
 }
 
-// Leaves the scratch set empty again for the next call.
+// Plans the serving pass, one thread per inbox entry: the entry whose rank comes
+// first in turn order among all requests for its key serves the key; it sorts
+// the chain by turn, reads the accumulate flags of accum_or_assign from the
+// requesting ranks, and leaves the later ranks' requests as one contiguous run
+// of the list array.  What the serving kernel then needs per entry is its plan
+// word (coalesced) and, for keys several ranks asked for, that run: the chain
+// walk with its dependent loads happens here, where nothing else waits for it.
 __global__ void __launch_bounds__(kMutateBlock)
-    routed_ungroup_kernel(const TableView t, const RoutedArgs r) {
+    routed_resolve_kernel(const TableView t, const RoutedArgs r, const bool with_flags) {
   const uint64_t tiles = routed_tiles(r);
   for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     const uint32_t seg = segment_of(r, uint32_t(tile % r.world));
     const uint64_t i = (tile / r.world) * kMutateBlock + threadIdx.x;
     if (i >= r.inbox_counts[seg] || i >= r.segment_capacity) continue;
     const uint64_t entry = uint64_t(seg) * r.segment_capacity + i;
-    if (is_reserved(t, r.inbox_keys[entry])) continue;
-    const uint32_t at = r.set_slot[entry];
-    r.set_keys[at] = t.empty_key;
-    r.set_head[at] = kNoEntry;
+    uint64_t plan = 0;
+    if (!is_reserved(t, r.inbox_keys[entry])) {
+      const uint32_t my_turn = turn_of(r, seg);
+      uint32_t words[kMaxRequests];  // turn << 28 | row, sorted
+      uint32_t n_requests = 0, hops = 0;
+      bool serves = true;
+      for (uint32_t e = r.set_head[r.set_slot[entry]];
+           e != kNoEntry && hops < 4 * kMaxRequests && serves; e = r.next[e], ++hops) {
+        const uint32_t turn = turn_of(r, uint32_t(e / r.segment_capacity));
+        if (turn < my_turn || (turn == my_turn && e < entry)) serves = false;
+        if (serves && n_requests < kMaxRequests) {
+          const uint32_t word = (turn << kRowTagShift) | r.inbox_origin[e];
+          uint32_t at = n_requests++;
+          while (at > 0 && words[at - 1] > word) {
+            words[at] = words[at - 1];
+            --at;
+          }
+          words[at] = word;
+        }
+      }
+      if (serves && n_requests > 0) {
+        uint32_t accumulating = 0, first_assign = kMaxRequests;
+        for (uint32_t q = 0; q < n_requests; ++q) {
+          // rows are named by rank << 28 | row from here on
+          const uint32_t rank = segment_of(r, words[q] >> kRowTagShift);
+          const uint32_t row = words[q] & kRowTagMask;
+          words[q] = (rank << kRowTagShift) | row;
+          if (with_flags) {
+            if (static_cast<const bool*>(r.flags_of.p[rank])[row]) accumulating |= 1u << q;
+            else if (first_assign == kMaxRequests) first_assign = q;
+          }
+        }
+        uint32_t list = 0;
+        if (n_requests > 1) {
+          list = atomicAdd(r.list_cursor, n_requests - 1);
+          for (uint32_t q = 1; q < n_requests; ++q) r.lists[list + q - 1] = words[q];
+        }
+        plan = (1ull << 63) | n_requests | (uint64_t(accumulating) << kPlanAccumShift) |
+               (uint64_t(first_assign) << kPlanAssignShift) | (uint64_t(list) << kPlanListShift);
+      }
+    }
+    r.plan[entry] = plan;
   }
 }
 
@@ -872,29 +915,33 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// Walking the request chains and serving them costs registers the local form
-// does not need: five resident blocks per SM (about 100 registers) instead of
-// eight keep the routed form free of large spills; its pace is set by the
-// peer-memory accesses anyway.
-#ifndef HKV_ROUTED_MIN_BLOCKS
-#define HKV_ROUTED_MIN_BLOCKS 5
+// Serving the later ranks' requests and addressing rows by rank and index cost
+// registers the local form does not need: fewer resident blocks per SM than
+// its eight keep the routed form free of large spills (its pace is set by the
+// peer-memory accesses anyway).  Measured per operation with both source
+// ranks' buffers local, 2 x 156 k keys: find_or_insert 151 / 176 / 184 us at
+// 4 / 5 / 6 blocks, accum_or_assign 211 / 223 / 207 us, insert_or_assign
+// 140 / 132 / 142 us.
+#ifdef HKV_ROUTED_MIN_BLOCKS
+__host__ __device__ constexpr int routed_min_blocks(int) { return HKV_ROUTED_MIN_BLOCKS; }
+#else
+__host__ __device__ constexpr int routed_min_blocks(int op) {
+  return op == kOpFindOrInsert ? 4 : op == kOpAccumOrAssign ? 6 : 5;
+}
 #endif
-constexpr int kRoutedMinBlocks = HKV_ROUTED_MIN_BLOCKS;
 
 template <int OP, int VEC>
-__global__ void __launch_bounds__(kMutateBlock, kRoutedMinBlocks)
+__global__ void __launch_bounds__(kMutateBlock, routed_min_blocks(OP))
     mutate_routed_kernel(const TableView t, const MutateArgs args, const RoutedArgs r) {
   static_assert(OP == kOpInsertOrAssign || OP == kOpFindOrInsert || OP == kOpAccumOrAssign,
                 "the routed form exists for the three operations the sharded table routes");
   __shared__ uint8_t* sm_values[kMaxPeers];
-  __shared__ const bool* sm_flags[kMaxPeers];
   __shared__ uint32_t sm_requests[kMaxRequests][kMutateBlock];
   // a copy in shared memory: the warps reach the arguments through a pointer,
   // which would otherwise put the whole parameter block into local memory
   __shared__ RoutedArgs sm_r;
   if (threadIdx.x < kMaxPeers) {
     sm_values[threadIdx.x] = static_cast<uint8_t*>(r.values_of.p[threadIdx.x]);
-    sm_flags[threadIdx.x] = static_cast<const bool*>(r.flags_of.p[threadIdx.x]);
   }
   if (threadIdx.x == 0) {
     sm_r.world = r.world;
@@ -903,15 +950,16 @@ __global__ void __launch_bounds__(kMutateBlock, kRoutedMinBlocks)
     sm_r.inbox_keys = r.inbox_keys;
     sm_r.inbox_origin = r.inbox_origin;
     sm_r.inbox_counts = r.inbox_counts;
+    sm_r.plan = r.plan;
+    sm_r.lists = r.lists;
     sm_r.set_keys = r.set_keys;
     sm_r.set_head = r.set_head;
-    sm_r.next = r.next;
     sm_r.set_slot = r.set_slot;
-    sm_r.set_bits = r.set_bits;
+    if (blockIdx.x == 0) *r.list_cursor = 0;  // the resolving pass is over
   }
   __syncthreads();
   const uint64_t tiles = routed_tiles(r);
-  RoutedWarp rw{&sm_r, 0, sm_values, sm_flags, sm_requests};
+  RoutedWarp rw{&sm_r, 0, sm_values, sm_requests};
   for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
     rw.segment = segment_of(r, uint32_t(tile % r.world));
     const uint64_t base = (tile / r.world) * kMutateBlock + (threadIdx.x & ~31u);
@@ -1517,15 +1565,13 @@ void launch_routed_op(const TableView& t, const MutateArgs& args, const RoutedAr
   cudaGetDevice(&device);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   const uint64_t tiles = ((r.segment_capacity + kMutateBlock - 1) / kMutateBlock) * r.world;
-  const uint64_t resident = uint64_t(sms) * kRoutedMinBlocks;
+  const uint64_t resident = uint64_t(sms) * routed_min_blocks(OP);
   const unsigned blocks = static_cast<unsigned>(tiles < resident ? tiles : resident);
   const unsigned scan_blocks = static_cast<unsigned>(tiles < uint64_t(sms) * 16 ? tiles : sms * 16);
   routed_group_kernel<<<scan_blocks, kMutateBlock, 0, stream>>>(t, r);
+  routed_resolve_kernel<<<scan_blocks, kMutateBlock, 0, stream>>>(t, r, OP == kOpAccumOrAssign);
   auto kernel = fast_rows(t) ? mutate_routed_kernel<OP, 16> : mutate_routed_kernel<OP, 0>;
-#ifndef HKV_EXP_SKIP_B
   kernel<<<blocks, kMutateBlock, 0, stream>>>(t, args, r);
-#endif
-  routed_ungroup_kernel<<<scan_blocks, kMutateBlock, 0, stream>>>(t, r);
 }
 
 size_t routed_workspace_bytes(uint32_t world, uint64_t segment_capacity) {
@@ -1533,7 +1579,8 @@ size_t routed_workspace_bytes(uint32_t world, uint64_t segment_capacity) {
   uint32_t bits = 10;
   while (bits < 31 && (1ull << bits) < 2 * entries) ++bits;
   const uint64_t places = 1ull << bits;
-  return places * sizeof(uint64_t) + places * sizeof(uint32_t) + 2 * entries * sizeof(uint32_t) + 1024;
+  return places * sizeof(uint64_t) + entries * sizeof(uint64_t) + places * sizeof(uint32_t) +
+         3 * entries * sizeof(uint32_t) + 1024;
 }
 
 void prepare_routed_workspace(const TableView& t, RoutedArgs& r, void* work, bool fresh,
@@ -1545,14 +1592,21 @@ void prepare_routed_workspace(const TableView& t, RoutedArgs& r, void* work, boo
   uint8_t* at = static_cast<uint8_t*>(work);
   r.set_keys = reinterpret_cast<uint64_t*>(at);
   at += places * sizeof(uint64_t);
+  r.plan = reinterpret_cast<uint64_t*>(at);
+  at += entries * sizeof(uint64_t);
   r.set_head = reinterpret_cast<uint32_t*>(at);
   at += places * sizeof(uint32_t);
   r.next = reinterpret_cast<uint32_t*>(at);
   at += entries * sizeof(uint32_t);
   r.set_slot = reinterpret_cast<uint32_t*>(at);
+  at += entries * sizeof(uint32_t);
+  r.lists = reinterpret_cast<uint32_t*>(at);
+  at += entries * sizeof(uint32_t);
+  r.list_cursor = reinterpret_cast<uint32_t*>(at);
   r.set_bits = bits;
   if (fresh) {
     routed_fill_kernel<<<1184, 256, 0, stream>>>(r.set_keys, r.set_head, places, t.empty_key);
+    cudaMemsetAsync(r.list_cursor, 0, sizeof(uint32_t), stream);
   }
 }
 
