@@ -487,10 +487,6 @@ __device__ __forceinline__ void warp_accumulate_row(uint8_t* row, const uint8_t*
 // MODE 0: table -> batch (gather)   MODE 1: batch -> table (scatter)
 // MODE 2: table += batch, float32 elements (needs VEC % 4 == 0); the other
 //         element types go through warp_accumulate_rows
-// MODE 3: either way in one pass: row r goes batch -> table when bit r of the
-//         warp-uniform mask `to_table` is set, table -> batch otherwise
-//         (find_or_insert: the rows of new keys go in while those of the keys
-//         that were found come out)
 //
 // INDEXED (the routed form of the sharded table): the batch rows are not the
 // warp's 32 consecutive rows.  Lane r holds in `row_index` a row tag: bits
@@ -504,8 +500,7 @@ template <int VEC, int MODE, bool INDEXED = false, bool PURE = false>
 __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* batch_rows,
                                                    uint32_t slot, uint32_t lane,
                                                    uint32_t row_index = 0,
-                                                   uint8_t* const* bases = nullptr,
-                                                   uint32_t to_table = 0) {
+                                                   uint8_t* const* bases = nullptr) {
   using T = typename VecType<VEC>::type;
   // Chunks in flight per lane.  Accumulation holds two values per chunk (the
   // delta and the stored chunk: both are loaded before anything is written, so
@@ -513,10 +508,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
   // other) and the routed form keeps a second address per chunk: four instead
   // of eight for those, two where both apply (the routed accumulation then
   // runs six blocks per SM instead of five: 208 -> 184 us for 2 x 156 k keys).
-#ifndef HKV_U_ACC_INDEXED
-#define HKV_U_ACC_INDEXED 2
-#endif
-  constexpr int U = (VEC == 16 && MODE != 2 && !INDEXED) ? 8 : (MODE == 2 && INDEXED) ? HKV_U_ACC_INDEXED : 4;
+  constexpr int U = (VEC == 16 && MODE != 2 && !INDEXED) ? 8 : (MODE == 2 && INDEXED) ? 2 : 4;
   const uint32_t cpr = t.chunks_per_row;
   const uint32_t total = cpr * 32u;
   for (uint32_t base = 0; base < total; base += 32u * U) {
@@ -525,15 +517,12 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
     uint8_t* tab[U];
     uint8_t* bat[U];
     bool ok[U];
-    bool in[MODE == 3 ? U : 1];  // MODE 3: this chunk goes into the table
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t c = base + u * 32u + lane;
       const uint32_t r = row_of_chunk(t, c);
       const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r & 31u);
       ok[u] = (c < total) && (s != kNoSlot);
-      if (MODE == 3) in[MODE == 3 ? u : 0] = (to_table >> (r & 31u)) & 1u;
-      const bool from_table = MODE == 0 || (MODE == 3 && !in[MODE == 3 ? u : 0]);
       const uint32_t off = (c - r * cpr) * VEC;
       const uint64_t rs = (ok[u] && !PURE) ? row_slot(t, s) : s;
       tab[u] = !ok[u] ? nullptr
@@ -544,7 +533,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
         bat[u] = bases[at >> kRowTagShift] + uint64_t(at & kRowTagMask) * t.row_bytes + off;
       }
       if (ok[u]) {
-        if (from_table) {
+        if (MODE == 0) {
           regs[u] = ld_table_row<T>(tab[u], !PURE && rs >= t.hbm_slots);
         } else if (INDEXED) {
           regs[u] = *reinterpret_cast<const T*>(bat[u]);
@@ -558,13 +547,13 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
     for (int u = 0; u < U; ++u) {
       const uint32_t c = base + u * 32u + lane;
       if (ok[u]) {
-        if (MODE == 0 || (MODE == 3 && !in[MODE == 3 ? u : 0])) {
+        if (MODE == 0) {
           if (INDEXED) {
             *reinterpret_cast<T*>(bat[u]) = regs[u];
           } else {
             st_stream(reinterpret_cast<T*>(batch_rows + size_t(c) * VEC), regs[u]);
           }
-        } else if (MODE == 1 || MODE == 3) {
+        } else if (MODE == 1) {
           st_stream(reinterpret_cast<T*>(tab[u]), regs[u]);
         } else {
           if constexpr (VEC % 4 == 0) {
@@ -648,8 +637,7 @@ template <int MODE, int VEC = 0, bool INDEXED = false>
 __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batch_rows,
                                                uint32_t slot, uint32_t lane,
                                                uint32_t row_index = 0,
-                                               uint8_t* const* bases = nullptr,
-                                               uint32_t to_table = 0) {
+                                               uint8_t* const* bases = nullptr) {
   if constexpr (MODE == 2) {
     if (t.value_kind > kValueF32) {
       // the rarer element types: one row after the other, all lanes on one row
@@ -669,18 +657,17 @@ __device__ __forceinline__ void warp_move_rows(const TableView& t, uint8_t* batc
   }
   if constexpr (VEC != 0) {
     // the fixed-width instantiations serve pure-HBM tables only
-    warp_move_rows_vec<VEC, MODE, INDEXED, true>(t, batch_rows, slot, lane, row_index, bases,
-                                                 to_table);
+    warp_move_rows_vec<VEC, MODE, INDEXED, true>(t, batch_rows, slot, lane, row_index, bases);
     return;
   }
   // vec_bytes is warp-uniform; the host lowers it when a batch pointer is
   // less aligned than the rows.
   switch (t.vec_bytes) {
-    case 16: warp_move_rows_vec<16, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases, to_table); break;
-    case 8: warp_move_rows_vec<8, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases, to_table); break;
-    case 4: warp_move_rows_vec<4, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases, to_table); break;
-    case 2: warp_move_rows_vec<2, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases, to_table); break;
-    default: warp_move_rows_vec<1, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases, to_table); break;
+    case 16: warp_move_rows_vec<16, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    case 8: warp_move_rows_vec<8, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    case 4: warp_move_rows_vec<4, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    case 2: warp_move_rows_vec<2, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
+    default: warp_move_rows_vec<1, MODE, INDEXED>(t, batch_rows, slot, lane, row_index, bases); break;
   }
 }
 

@@ -281,26 +281,112 @@ __device__ __forceinline__ uint32_t segment_of(const RoutedArgs& r, uint32_t tur
   return s >= r.world ? s - r.world : s;
 }
 
-// Requests `from` .. `count - 1` of each lane's key that are selected by
-// `which` (bit r: request r), one after the other: MODE 0 copies the slot's row
-// into the requesting rank's buffer, MODE 2 adds that rank's row to the slot's.
-// All lanes call it; a lane without a slot passes kNoSlot.
-#ifdef HKV_SERVE_NOINLINE
-#define HKV_SERVE_INLINE __noinline__
-#else
-#define HKV_SERVE_INLINE __forceinline__
-#endif
-template <int MODE, int VEC>
-__device__ HKV_SERVE_INLINE void serve_requests(const TableView& t, const RoutedWarp* rw,
-                                               uint32_t slot, uint32_t from, uint32_t count,
-                                               uint32_t which, uint32_t lane) {
+// accum_or_assign for the requests of each lane's key: requests `from` ..
+// `count - 1` that `which` selects (bit q: request q) add their rank's row to
+// the slot's, one after the other, in request order.  All lanes call it; a
+// lane without a slot passes kNoSlot.  (One pass over the row with all
+// requests' chunks in flight, as find_or_insert has it below, was built for
+// the accumulation as well: it needs more registers than this kernel has and
+// measured slower, 226 against 184 us for 2 x 156 k keys nobody shares, 309
+// against 269 us for eight ranks sharing most keys.)
+template <int VEC>
+__device__ __forceinline__ void serve_accumulate(const TableView& t, const RoutedWarp* rw,
+                                                 uint32_t slot, uint32_t from, uint32_t count,
+                                                 uint32_t which, uint32_t lane) {
   const uint32_t most = __reduce_max_sync(0xFFFFFFFFu, slot != kNoSlot ? count : 0u);
   for (uint32_t q = 0; q < most; ++q) {
     const bool mine = slot != kNoSlot && q >= from && q < count && ((which >> q) & 1u);
     if (__ballot_sync(0xFFFFFFFFu, mine) == 0) continue;
     const uint32_t tag = mine ? rw->requests[q][threadIdx.x] : 0u;
-    warp_move_rows<MODE, VEC, true>(t, nullptr, mine ? slot : kNoSlot, lane, tag, rw->values_of);
+    warp_move_rows<2, VEC, true>(t, nullptr, mine ? slot : kNoSlot, lane, tag, rw->values_of);
     __syncwarp();  // request q + 1 of a key sees what request q did to its row
+  }
+}
+
+// find_or_insert for the requests of each lane's key, in ONE pass over the
+// key's row, chunk by chunk, instead of one pass per request: a key that all
+// ranks ask for costs one read of its row, not one per rank.  Per lane (key):
+// `slot` (kNoSlot: nothing to do), `todo` (bit q: request q gets the row) and
+// `first` (the request whose row is the source -- a new key, the row also goes
+// into the table; kMaxRequests: the row stored in the table).  Requests are
+// read from the warp's columns of rw->requests, rows are addressed as
+// values_of[rank] + row * row_bytes with plain loads and stores (other GPUs'
+// memory).
+constexpr uint32_t kServeNothing = 0xFFFFFFFFu;
+template <int V, bool PURE>
+__device__ __forceinline__ void serve_gather_vec(const TableView& t, const RoutedWarp* rw,
+                                                 uint32_t slot, uint32_t todo, uint32_t first,
+                                                 uint32_t lane) {
+  using T = typename VecType<V>::type;
+  constexpr int U = 4;  // chunks in flight per lane
+  const uint32_t cpr = t.chunks_per_row;
+  const uint32_t total = cpr * 32u;
+  const uint32_t column0 = threadIdx.x & ~31u;
+  const bool idle = slot == kNoSlot || (todo == 0 && first == kMaxRequests);
+  const uint32_t packed = idle ? kServeNothing : (todo & 0xFFFFu) | (first << 16);
+  // the row of request `tag` (rank << 28 | row) at byte `off`
+  auto request_row = [&](uint32_t tag, uint32_t off) -> uint8_t* {
+    return rw->values_of[tag >> kRowTagShift] + uint64_t(tag & kRowTagMask) * t.row_bytes + off;
+  };
+  __syncwarp();  // the lanes read each other's columns of rw->requests
+  for (uint32_t base = 0; base < total; base += 32u * U) {
+    T cur[U];
+    uint8_t* tab[U];
+    uint32_t work[U], off[U], column[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t c = base + u * 32u + lane;
+      const uint32_t r = row_of_chunk(t, c);
+      const uint32_t s = __shfl_sync(0xFFFFFFFFu, slot, r & 31u);
+      const uint32_t w = __shfl_sync(0xFFFFFFFFu, packed, r & 31u);
+      work[u] = (c < total) ? w : kServeNothing;
+      column[u] = column0 + (r & 31u);
+      off[u] = (c - r * cpr) * V;
+      const bool ok = work[u] != kServeNothing;
+      const uint64_t rs = (ok && !PURE) ? row_slot(t, s) : s;
+      tab[u] = !ok ? nullptr
+                   : (PURE ? t.values_hbm + uint64_t(s) * t.row_bytes
+                           : row_ptr_of_row_slot(t, rs)) + off[u];
+      if (ok) {
+        const uint32_t f = work[u] >> 16;
+        if (f == kMaxRequests) {
+          cur[u] = ld_table_row<T>(tab[u], !PURE && rs >= t.hbm_slots);
+        } else {
+          cur[u] = *reinterpret_cast<const T*>(request_row(rw->requests[f][column[u]], off[u]));
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (work[u] == kServeNothing) continue;
+      if ((work[u] >> 16) != kMaxRequests) st_stream(reinterpret_cast<T*>(tab[u]), cur[u]);
+      uint32_t m = work[u] & 0xFFFFu;
+      while (m != 0) {
+        const uint32_t q = __ffs(m) - 1;
+        m &= m - 1;
+        *reinterpret_cast<T*>(request_row(rw->requests[q][column[u]], off[u])) = cur[u];
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// VEC != 0: the access width is fixed at compile time and every row is in HBM
+// at its slot's own place (the launcher picks the instantiation).
+template <int VEC>
+__device__ __forceinline__ void serve_gather(const TableView& t, const RoutedWarp* rw,
+                                             uint32_t slot, uint32_t todo, uint32_t first,
+                                             uint32_t lane) {
+  if constexpr (VEC != 0) {
+    serve_gather_vec<VEC, true>(t, rw, slot, todo, first, lane);
+    return;
+  }
+  switch (t.vec_bytes) {
+    case 16: serve_gather_vec<16, false>(t, rw, slot, todo, first, lane); break;
+    case 8: serve_gather_vec<8, false>(t, rw, slot, todo, first, lane); break;
+    case 4: serve_gather_vec<4, false>(t, rw, slot, todo, first, lane); break;
+    case 2: serve_gather_vec<2, false>(t, rw, slot, todo, first, lane); break;
+    default: serve_gather_vec<1, false>(t, rw, slot, todo, first, lane); break;
   }
 }
 
@@ -591,21 +677,17 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
                                       my_row, bases);
     } else if (OP == kOpFindOrInsert) {
       if constexpr (INDEXED) {
-        // found rows come out, the rows of new keys go in: one pass (the routed
-        // form is short of registers; the local form is faster with two)
-        warp_move_rows<3, VEC, true>(
-            t, batch_rows,
-            (my_result == kDuplicate || my_result == kOccupiedEmpty) ? my_slot : kNoSlot, pl.lane,
-            my_row, bases, __ballot_sync(full, my_result == kOccupiedEmpty));
+        // a key that was there: its row goes to every rank that asked; a new key:
+        // the first rank's row goes in and to the ranks whose turn comes later
+        const bool fresh = my_result == kOccupiedEmpty;
+        const uint32_t everyone = (1u << n_requests) - 1u;
+        serve_gather<VEC>(t, rw, holds_lock ? my_slot : kNoSlot,
+                               fresh ? (everyone & ~1u) : everyone, fresh ? 0u : kMaxRequests,
+                               pl.lane);
       } else {
         warp_move_rows<0, VEC>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot, pl.lane);
         warp_move_rows<1, VEC>(t, batch_rows, my_result == kOccupiedEmpty ? my_slot : kNoSlot,
                                pl.lane);
-      }
-      if constexpr (INDEXED) {
-        // the ranks whose turn comes later find the key: they get the row
-        __syncwarp();
-        serve_requests<0, VEC>(t, rw, holds_lock ? my_slot : kNoSlot, 1u, n_requests, ~0u, pl.lane);
       }
     } else if (OP == kOpAccumOrAssign && !INDEXED) {
       warp_move_rows<2, VEC, false>(t, batch_rows, my_result == kDuplicate ? my_slot : kNoSlot,
@@ -615,14 +697,14 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
                                     my_row);
     } else if constexpr (OP == kOpAccumOrAssign && INDEXED) {
       // a key that was there: every accumulating request adds, in turn order; a
-      // new key: the first assigning request's row went in (my_row), the
+      // new key: the first assigning request's row goes in (my_row), the
       // accumulating requests behind it add
       warp_move_rows<1, VEC, true>(t, batch_rows, my_result == kOccupiedEmpty ? my_slot : kNoSlot,
                                    pl.lane, my_row, bases);
       __syncwarp();
-      serve_requests<2, VEC>(t, rw, holds_lock ? my_slot : kNoSlot,
-                             my_result == kDuplicate ? 0u : first_assign + 1u, n_requests,
-                             accumulating, pl.lane);
+      serve_accumulate<VEC>(t, rw, holds_lock ? my_slot : kNoSlot,
+                            my_result == kDuplicate ? 0u : first_assign + 1u, n_requests,
+                            accumulating, pl.lane);
     }
     __syncwarp();
     if (OP == kOpErase) {
@@ -754,18 +836,19 @@ __device__ __forceinline__ void mutate_warp(const TableView& t, const MutateArgs
           }
         }
       }
-      if (op_writes_row_on_insert(OP)) {
+      if constexpr (INDEXED && OP == kOpFindOrInsert) {
+        // the first rank's row goes in and to the ranks whose turn comes later
+        serve_gather<VEC>(t, rw, placed ? my_slot : kNoSlot, ((1u << n_requests) - 1u) & ~1u,
+                               0u, pl.lane);
+      } else if (op_writes_row_on_insert(OP)) {
         warp_move_rows<1, VEC, INDEXED>(t, batch_rows, placed ? my_slot : kNoSlot, pl.lane,
                                         my_row, bases);
       }
-      if constexpr (INDEXED && OP == kOpFindOrInsert) {
-        __syncwarp();
-        serve_requests<0, VEC>(t, rw, placed ? my_slot : kNoSlot, 1u, n_requests, ~0u, pl.lane);
-      }
       if constexpr (INDEXED && OP == kOpAccumOrAssign) {
+        // the first assigning request's row went in; the accumulating ones behind it add
         __syncwarp();
-        serve_requests<2, VEC>(t, rw, placed ? my_slot : kNoSlot, first_assign + 1u, n_requests,
-                               accumulating, pl.lane);
+        serve_accumulate<VEC>(t, rw, placed ? my_slot : kNoSlot, first_assign + 1u, n_requests,
+                              accumulating, pl.lane);
       }
       __syncwarp();
       if (placed && !(OP == kOpFindOrInsertPtr && keep_locked)) st_release(key_ptr(t, my_slot), key);
@@ -919,14 +1002,15 @@ __global__ void __launch_bounds__(256)
 // registers the local form does not need: fewer resident blocks per SM than
 // its eight keep the routed form free of large spills (its pace is set by the
 // peer-memory accesses anyway).  Measured per operation with both source
-// ranks' buffers local, 2 x 156 k keys: find_or_insert 151 / 176 / 184 us at
-// 4 / 5 / 6 blocks, accum_or_assign 211 / 223 / 207 us, insert_or_assign
-// 140 / 132 / 142 us.
+// ranks' buffers local, 2 x 156 k keys: find_or_insert 144 / 145 / 141 / 174 us
+// at 4 / 5 / 6 / 8 blocks (eight ranks sharing most keys: 165 us at 4, 143 us
+// at 6), accum_or_assign 211 / 223 / 184 us at 4 / 5 / 6, insert_or_assign
+// 140 / 132 / 142 / 166 us at 4 / 5 / 6 / 8.
 #ifdef HKV_ROUTED_MIN_BLOCKS
 __host__ __device__ constexpr int routed_min_blocks(int) { return HKV_ROUTED_MIN_BLOCKS; }
 #else
 __host__ __device__ constexpr int routed_min_blocks(int op) {
-  return op == kOpFindOrInsert ? 4 : op == kOpAccumOrAssign ? 6 : 5;
+  return op == kOpInsertOrAssign ? 5 : 6;
 }
 #endif
 
