@@ -1168,6 +1168,10 @@ def main():
     ap.add_argument("--staged-e2e", action="store_true",
                     help="end-to-end loop with the caller staging the batch (copy keys in, find, copy "
                          "rows out) instead of the host-buffer entry point")
+    ap.add_argument("--peer-memory", choices=["auto", "symmetric", "ipc"], default="auto",
+                    help="where the sharded table's peer workspaces come from: torch symmetric "
+                         "memory handed to the library, the library's own cudaMalloc memory "
+                         "shared over CUDA IPC, or the former with the latter as fallback")
     ap.add_argument("--lanes", type=int, default=2,
                     help="N > 1: peer workspaces the fused find rotates through (1: no overlap of "
                          "one batch's routing with the previous batch's lookup)")
@@ -1267,7 +1271,7 @@ def main():
     fused = False
     if sharded is not None and not args.nccl_routing:
         try:
-            ws = sharded.enable_fused_find(batch, dim, lanes=args.lanes)
+            ws = sharded.enable_fused_find(batch, dim, lanes=args.lanes, memory=args.peer_memory)
             out_vals, founds = ws.out_values, ws.out_founds     # results land in peer-visible buffers
             fused = True
         except Exception as e:  # no peer mappings on this box: route with NCCL instead
@@ -1470,6 +1474,9 @@ def main():
                             "hit rows stored by the lookup kernel into the requester's buffer (NVLink)"
                             + ("; %d workspaces in rotation, batch k + 1 routed while batch k is served"
                                % args.lanes if pipelined else "")
+                            + ("; workspaces in torch symmetric memory"
+                               if getattr(sharded, "_symmetric", None) is not None else
+                               "; workspaces in cudaMalloc memory shared over CUDA IPC")
                             if fused else
                             "every batch routed by NCCL all-to-all: keys out, rows and flags back"))
             if world > 1 else ("single table" if launched_world == 1 else

@@ -38,7 +38,8 @@ uint64_t up256(uint64_t x) { return (x + 255) / 256 * 256; }
 // One workspace.  All ranks lay theirs out the same way, so a peer's arrays are
 // its base address plus the same offsets.
 struct Lane {
-  uint8_t* local = nullptr;             // this rank's workspace (cudaMalloc)
+  uint8_t* local = nullptr;             // this rank's workspace
+  bool owns_local = false;              // ... from cudaMalloc here (else the caller's memory)
   void* base[kMaxRanks] = {};           // every rank's workspace as this process sees it
   bool opened[kMaxRanks] = {};          // base[r] came from cudaIpcOpenMemHandle
   uint64_t* scratch = nullptr;          // [0,16): routing cursors; [16]: barrier status
@@ -80,6 +81,24 @@ struct DeviceScope {
     if (prev >= 0) cudaSetDevice(prev);
   }
 };
+
+// Offsets of the arrays inside a workspace (needs world, max_batch, row_bytes).
+void lay_out(hkv_sharded* s) {
+  uint64_t at = 0;
+  s->off_keys = at;
+  at = up256(at + uint64_t(s->world) * s->max_batch * 8);
+  s->off_origin = at;
+  at = up256(at + uint64_t(s->world) * s->max_batch * 4);
+  s->off_counts = at;
+  at = up256(at + kMaxRanks * 8);
+  s->off_flags = at;
+  at = up256(at + kMaxRanks * 4);
+  s->off_founds = at;
+  at = up256(at + s->max_batch);
+  s->off_values = at;
+  at = up256(at + s->max_batch * s->row_bytes);
+  s->bytes = at;
+}
 
 int check_lane(const hkv_sharded* s, uint32_t lane, bool connected) {
   if (s == nullptr) return fail(HKV_ERR_INVALID_ARG, "null sharded table");
@@ -133,6 +152,29 @@ const char* hkv_sharded_last_error(void) { return g_sharded_error.c_str(); }
 
 int hkv_sharded_create(hkv_table* table, uint32_t world, uint32_t rank, uint64_t max_batch,
                        uint32_t lanes, hkv_sharded** out) {
+  return hkv_sharded_create_external(table, world, rank, max_batch, lanes, nullptr, out);
+}
+
+int hkv_sharded_workspace_bytes(hkv_table* table, uint32_t world, uint64_t max_batch,
+                                uint64_t* bytes) {
+  if (table == nullptr || bytes == nullptr) return fail(HKV_ERR_INVALID_ARG, "null argument");
+  if (world == 0 || world > kMaxRanks) {
+    return fail(HKV_ERR_INVALID_ARG, "world size must be between 1 and 16");
+  }
+  hkv_table_view view{};
+  if (hkv_get_view(table, &view) != HKV_OK) return fail(HKV_ERR_RUNTIME, hkv_last_error());
+  hkv_sharded layout;
+  layout.world = world;
+  layout.max_batch = (max_batch + 31) / 32 * 32;
+  layout.row_bytes = view.row_bytes;
+  lay_out(&layout);
+  *bytes = layout.bytes;
+  return HKV_OK;
+}
+
+int hkv_sharded_create_external(hkv_table* table, uint32_t world, uint32_t rank,
+                                uint64_t max_batch, uint32_t lanes, void* const* workspaces,
+                                hkv_sharded** out) {
   if (table == nullptr || out == nullptr) {
     return fail(HKV_ERR_INVALID_ARG, "table and out must not be null");
   }
@@ -155,26 +197,25 @@ int hkv_sharded_create(hkv_table* table, uint32_t world, uint32_t rank, uint64_t
   s->device = attr.device;
   s->max_batch = (max_batch + 31) / 32 * 32;  // inbox segments hold whole warps of keys
   s->row_bytes = view.row_bytes;
-  uint64_t at = 0;
-  s->off_keys = at;
-  at = up256(at + uint64_t(world) * s->max_batch * 8);
-  s->off_origin = at;
-  at = up256(at + uint64_t(world) * s->max_batch * 4);
-  s->off_counts = at;
-  at = up256(at + kMaxRanks * 8);
-  s->off_flags = at;
-  at = up256(at + kMaxRanks * 4);
-  s->off_founds = at;
-  at = up256(at + s->max_batch);
-  s->off_values = at;
-  at = up256(at + s->max_batch * s->row_bytes);
-  s->bytes = at;
+  lay_out(s);
   DeviceScope scope(s->device);
   s->lanes.resize(lanes);
-  for (Lane& l : s->lanes) {
+  for (uint32_t i = 0; i < lanes; ++i) {
+    Lane& l = s->lanes[i];
     int least = 0, greatest = 0;
     cudaDeviceGetStreamPriorityRange(&least, &greatest);
-    if (cudaMalloc(reinterpret_cast<void**>(&l.local), s->bytes) != cudaSuccess ||
+    if (workspaces != nullptr) {
+      if (workspaces[i] == nullptr) {
+        hkv_sharded_destroy(s);
+        return fail(HKV_ERR_INVALID_ARG, "null workspace");
+      }
+      l.local = static_cast<uint8_t*>(workspaces[i]);
+    } else if (cudaMalloc(reinterpret_cast<void**>(&l.local), s->bytes) == cudaSuccess) {
+      l.owns_local = true;
+    } else {
+      l.local = nullptr;
+    }
+    if (l.local == nullptr ||
         cudaMalloc(reinterpret_cast<void**>(&l.scratch), 32 * sizeof(uint64_t)) != cudaSuccess ||
         cudaMemset(l.local, 0, s->bytes) != cudaSuccess ||
         cudaMemset(l.scratch, 0, 32 * sizeof(uint64_t)) != cudaSuccess ||
@@ -210,7 +251,7 @@ int hkv_sharded_destroy(hkv_sharded* s) {
     for (uint32_t r = 0; r < s->world; ++r) {
       if (l.opened[r]) cudaIpcCloseMemHandle(l.base[r]);
     }
-    if (l.local) cudaFree(l.local);
+    if (l.local && l.owns_local) cudaFree(l.local);
     if (l.scratch) cudaFree(l.scratch);
     if (l.hi) cudaStreamDestroy(l.hi);
     if (l.lo) cudaStreamDestroy(l.lo);
@@ -229,6 +270,9 @@ uint64_t hkv_sharded_max_batch(const hkv_sharded* s) { return s ? s->max_batch :
 int hkv_sharded_ipc_handle(hkv_sharded* s, uint32_t lane, hkv_ipc_handle* handle) {
   if (int rc = check_lane(s, lane, false)) return rc;
   static_assert(sizeof(cudaIpcMemHandle_t) <= sizeof(hkv_ipc_handle), "handle size");
+  if (!s->lanes[lane].owns_local) {
+    return fail(HKV_ERR_RUNTIME, "the caller supplied this workspace and shares it by its own means");
+  }
   DeviceScope scope(s->device);
   cudaIpcMemHandle_t h;
   if (cudaIpcGetMemHandle(&h, s->lanes[lane].local) != cudaSuccess) {

@@ -240,39 +240,90 @@ class ShardedHashTable:
             self.ops.scatter_rows(sc_back, where, scores)
 
     def enable_fused_find(self, max_batch: int, dim: int, dtype: torch.dtype = torch.float32,
-                          lanes: int = 1):
-        """Creates the C++ host of the fused paths for this rank's sub-table
-        (hkv_sharded_create), lets the ranks exchange the CUDA IPC handles of
-        their workspaces and maps them.  With ``lanes`` > 1 there are that many
-        independent workspaces (own inbox, flags, epochs and streams) for
-        find_fused_async, which rotates through them so the routing of one
-        batch overlaps the lookup of the previous one.  A collective call."""
+                          lanes: int = 1, memory: str = "auto"):
+        """Creates the C++ host of the fused paths for this rank's sub-table and
+        connects the ranks' workspaces.  ``memory``: "symmetric" takes the
+        workspaces from torch symmetric memory (CUDA virtual-memory allocations
+        that every rank maps) and hands them to hkv_sharded_create_external;
+        "ipc" lets the library allocate them and exchanges their CUDA IPC
+        handles; "auto" tries the former and falls back to the latter.  Peer
+        stores into IPC-mapped cudaMalloc memory measured much slower at eight
+        GPUs (find 13.5 against 20.0 B-KV/s), level at two and four.  With
+        ``lanes`` > 1 there are that many independent workspaces (own inbox,
+        flags, epochs and streams) for find_fused_async, which rotates through
+        them so the routing of one batch overlaps the lookup of the previous
+        one.  A collective call: every rank passes the same arguments."""
         lib = self.ops.lib
+        lanes = max(1, lanes)
         host = ctypes.c_void_p()
-        self._chk_host(lib.hkv_sharded_create(self.local.handle, self.world, self.rank, max_batch,
-                                              max(1, lanes), ctypes.byref(host)))
-        self._host = host
-        n_lanes = lib.hkv_sharded_lanes(host)
-        if self.world > 1:
-            mine = []
-            for lane in range(n_lanes):
-                h = _IpcHandle()
-                self._chk_host(lib.hkv_sharded_ipc_handle(host, lane, ctypes.byref(h)))
-                mine.append(bytes(h.bytes))
-            everyone = [None] * self.world
-            self.dist.all_gather_object(everyone, mine, group=self.group)
-            for lane in range(n_lanes):
-                handles = (_IpcHandle * self.world)()
-                for r in range(self.world):
-                    ctypes.memmove(handles[r].bytes, everyone[r][lane], 64)
-                self._chk_host(lib.hkv_sharded_connect_ipc(host, lane, handles))
+        self._symmetric = None
+        if self.world > 1 and memory in ("auto", "symmetric"):
+            try:
+                self._symmetric = self._symmetric_workspaces(max_batch, lanes)
+            except Exception:
+                if memory == "symmetric":
+                    raise
+                self._symmetric = None
+            if memory == "auto":
+                # all ranks take the same path
+                ok = torch.tensor([1 if self._symmetric is not None else 0], device="cuda")
+                self.dist.all_reduce(ok, op=self.dist.ReduceOp.MIN, group=self.group)
+                if int(ok.item()) == 0:
+                    self._symmetric = None
+        if self._symmetric is not None:
+            bufs, peer_ptrs = self._symmetric
+            mine = (ctypes.c_void_p * lanes)(*[peer_ptrs[lane][self.rank] for lane in range(lanes)])
+            self._chk_host(lib.hkv_sharded_create_external(self.local.handle, self.world, self.rank,
+                                                           max_batch, lanes, mine, ctypes.byref(host)))
+            self._host = host
+            for lane in range(lanes):
+                bases = (ctypes.c_void_p * self.world)(*peer_ptrs[lane])
+                self._chk_host(lib.hkv_sharded_connect_pointers(host, lane, bases))
             torch.cuda.synchronize()
-            self.dist.barrier(self.group)     # every rank's workspace is mapped, its flags still zero
+            self.dist.barrier(self.group)     # every rank's workspace is cleared and connected
+        else:
+            self._chk_host(lib.hkv_sharded_create(self.local.handle, self.world, self.rank, max_batch,
+                                                  lanes, ctypes.byref(host)))
+            self._host = host
+            if self.world > 1:
+                mine = []
+                for lane in range(lanes):
+                    h = _IpcHandle()
+                    self._chk_host(lib.hkv_sharded_ipc_handle(host, lane, ctypes.byref(h)))
+                    mine.append(bytes(h.bytes))
+                everyone = [None] * self.world
+                self.dist.all_gather_object(everyone, mine, group=self.group)
+                for lane in range(lanes):
+                    handles = (_IpcHandle * self.world)()
+                    for r in range(self.world):
+                        ctypes.memmove(handles[r].bytes, everyone[r][lane], 64)
+                    self._chk_host(lib.hkv_sharded_connect_ipc(host, lane, handles))
+                torch.cuda.synchronize()
+                self.dist.barrier(self.group)     # every rank's workspace is mapped, its flags still zero
+        n_lanes = lib.hkv_sharded_lanes(host)
         cap = lib.hkv_sharded_max_batch(host)
         self.lanes = [PeerWorkspace(lib, host, lane, cap, dim, dtype) for lane in range(n_lanes)]
         self._pending = [None for _ in self.lanes]
         self.peer = self.lanes[0]
         return self.peer
+
+    def _symmetric_workspaces(self, max_batch: int, lanes: int):
+        """One symmetric-memory buffer per lane, sized by the library, and every
+        rank's address of it: ([buffers], [[address per rank] per lane])."""
+        import torch.distributed._symmetric_memory as symm
+
+        size = ctypes.c_uint64(0)
+        self._chk_host(self.ops.lib.hkv_sharded_workspace_bytes(self.local.handle, self.world,
+                                                                max_batch, ctypes.byref(size)))
+        group = self.group if self.group is not None else self.dist.group.WORLD
+        bufs, ptrs = [], []
+        for _ in range(lanes):
+            buf = symm.empty(size.value, dtype=torch.uint8,
+                             device=torch.device("cuda", torch.cuda.current_device()))
+            handle = symm.rendezvous(buf, group)
+            bufs.append((buf, handle))
+            ptrs.append([int(p) for p in handle.buffer_ptrs])
+        return bufs, ptrs
 
     def share_workspace(self, other: "ShardedHashTable") -> None:
         """Gives this table fused paths shaped like `other`'s (a collective call:
@@ -286,6 +337,7 @@ class ShardedHashTable:
         if host:
             self.ops.lib.hkv_sharded_destroy(host)
             self._host = None
+        self._symmetric = None
 
     # -- fused paths: routing, lookup / update and transfer without NCCL ----------
     def _chk_host(self, rc: int) -> None:

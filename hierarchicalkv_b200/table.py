@@ -186,6 +186,8 @@ _SIGNATURES = {
     "hkv_sharded_ipc_handle": [_P, ctypes.c_uint32, _P],
     "hkv_sharded_connect_ipc": [_P, ctypes.c_uint32, _P],
     "hkv_sharded_workspace": [_P, ctypes.c_uint32],
+    "hkv_sharded_workspace_bytes": [_P, ctypes.c_uint32, _U64, _P],
+    "hkv_sharded_create_external": [_P, ctypes.c_uint32, ctypes.c_uint32, _U64, ctypes.c_uint32, _P, _P],
     "hkv_sharded_connect_pointers": [_P, ctypes.c_uint32, _P],
     "hkv_sharded_buffers": [_P, ctypes.c_uint32, ctypes.POINTER(_P), ctypes.POINTER(_P)],
     "hkv_sharded_find": [_P, ctypes.c_uint32, _U64, _P, ctypes.c_uint32, _P],

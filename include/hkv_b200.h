@@ -455,6 +455,18 @@ typedef struct hkv_ipc_handle {
 
 HKV_API int hkv_sharded_create(hkv_table* table, uint32_t world, uint32_t rank,
                                uint64_t max_batch, uint32_t lanes, hkv_sharded** out);
+/* The same with workspaces the caller supplies: workspaces[lanes], each
+ * hkv_sharded_workspace_bytes of device memory on the table's GPU that every
+ * rank can map (CUDA virtual-memory allocations shared through file
+ * descriptors or fabric handles, a framework's symmetric memory, ...).  The
+ * library clears them, never frees them and cannot export them
+ * (hkv_sharded_ipc_handle fails): the caller maps its peers' workspaces itself
+ * and passes the addresses to hkv_sharded_connect_pointers. */
+HKV_API int hkv_sharded_workspace_bytes(hkv_table* table, uint32_t world, uint64_t max_batch,
+                                        uint64_t* bytes);
+HKV_API int hkv_sharded_create_external(hkv_table* table, uint32_t world, uint32_t rank,
+                                        uint64_t max_batch, uint32_t lanes,
+                                        void* const* workspaces, hkv_sharded** out);
 HKV_API int hkv_sharded_destroy(hkv_sharded* sharded);
 HKV_API uint32_t hkv_sharded_lanes(const hkv_sharded* sharded);
 HKV_API uint64_t hkv_sharded_max_batch(const hkv_sharded* sharded);

@@ -41,10 +41,31 @@ class ShardedHashTable {
       throw MerlinException(hkv_sharded_last_error());
     }
   }
+  // The same over workspaces the caller allocated (one per lane, each
+  // workspace_bytes() of device memory every rank can map: CUDA virtual-memory
+  // allocations shared through file descriptors or fabric handles, a
+  // framework's symmetric memory); connect them with connect(lane, pointers).
+  ShardedHashTable(Local* local, uint32_t world, uint32_t rank, uint64_t max_batch,
+                   const std::vector<void*>& workspaces, uint32_t max_polls = 50000000u)
+      : local_(local), max_polls_(max_polls) {
+    if (hkv_sharded_create_external(local->native_handle(), world, rank, max_batch,
+                                    static_cast<uint32_t>(workspaces.size()), workspaces.data(),
+                                    &s_) != HKV_OK) {
+      throw MerlinException(hkv_sharded_last_error());
+    }
+  }
+  static uint64_t workspace_bytes(Local* local, uint32_t world, uint64_t max_batch) {
+    uint64_t bytes = 0;
+    if (hkv_sharded_workspace_bytes(local->native_handle(), world, max_batch, &bytes) != HKV_OK) {
+      throw MerlinException(hkv_sharded_last_error());
+    }
+    return bytes;
+  }
   ShardedHashTable(const ShardedHashTable&) = delete;
   ShardedHashTable& operator=(const ShardedHashTable&) = delete;
   ~ShardedHashTable() { hkv_sharded_destroy(s_); }
 
+  hkv_sharded* native_handle() { return s_; }
   uint32_t lanes() const { return hkv_sharded_lanes(s_); }
   uint64_t max_batch() const { return hkv_sharded_max_batch(s_); }
 

@@ -20,6 +20,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -83,10 +84,32 @@ int main(int argc, char** argv) {
   Table local;
   local.init(o);
   const uint64_t per = 4000, shared = 1500, max_batch = per * world + shared;
-  Sharded table(&local, world, rank, max_batch, 2);
+  // "external" (one rank): the caller allocates the workspaces and the
+  // library adopts them instead of allocating and exporting its own
+  const bool external = argc > 4 && std::string(argv[4]) == "external";
+  std::vector<void*> own_workspaces;
+  if (external) {
+    REQUIRE(world == 1);
+    const uint64_t bytes = Sharded::workspace_bytes(&local, world, max_batch);
+    REQUIRE(bytes > max_batch * kDim * sizeof(V));
+    for (int lane = 0; lane < 2; ++lane) {
+      void* w = nullptr;
+      CUDA_CHECK(cudaMalloc(&w, bytes));
+      own_workspaces.push_back(w);
+    }
+  }
+  std::unique_ptr<Sharded> table_owner(external
+                                           ? new Sharded(&local, world, rank, max_batch, own_workspaces)
+                                           : new Sharded(&local, world, rank, max_batch, 2));
+  Sharded& table = *table_owner;
+  if (external) {
+    hkv_ipc_handle none;
+    REQUIRE(hkv_sharded_ipc_handle(table.native_handle(), 0, &none) != HKV_OK);  // not the library's to export
+    REQUIRE(table.rows(0) != nullptr && table.lanes() == 2);
+  }
 
   // exchange the workspaces' IPC handles through files
-  for (uint32_t lane = 0; lane < table.lanes(); ++lane) {
+  for (uint32_t lane = 0; !external && lane < table.lanes(); ++lane) {
     const hkv_ipc_handle h = table.ipc_handle(lane);
     std::ofstream f(dir + "/handle." + std::to_string(lane) + "." + std::to_string(rank) + ".tmp", std::ios::binary);
     f.write(reinterpret_cast<const char*>(&h), sizeof(h));
@@ -95,7 +118,7 @@ int main(int argc, char** argv) {
            (dir + "/handle." + std::to_string(lane) + "." + std::to_string(rank)).c_str());
   }
   file_barrier(dir, "handles", rank, world);
-  for (uint32_t lane = 0; lane < table.lanes(); ++lane) {
+  for (uint32_t lane = 0; !external && lane < table.lanes(); ++lane) {
     std::vector<hkv_ipc_handle> all(world);
     for (int r = 0; r < world; ++r) {
       std::ifstream f(dir + "/handle." + std::to_string(lane) + "." + std::to_string(r), std::ios::binary);
@@ -206,6 +229,8 @@ int main(int argc, char** argv) {
   }
   REQUIRE(table.status(0) == 0 && table.status(1) == 0);
   file_barrier(dir, "done", rank, world);
+  table_owner.reset();  // the library never frees workspaces it did not allocate
+  for (void* w : own_workspaces) CUDA_CHECK(cudaFree(w));
   printf("rank %d PASS\n", rank);
   return 0;
 }

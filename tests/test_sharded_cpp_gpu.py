@@ -16,11 +16,12 @@ BINARY = os.path.join(ROOT, "tests", "cpp", "build", "sharded_test")
 pytestmark = pytest.mark.gpu
 
 
-def _run(world, tmp_path):
+def _run(world, tmp_path, *extra):
     if not os.path.exists(BINARY):
         subprocess.run(["make", "-C", os.path.join(ROOT, "tests", "cpp")], check=True)
-    procs = [subprocess.Popen([BINARY, str(r), str(world), str(tmp_path)], stdout=subprocess.PIPE,
-                              stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    procs = [subprocess.Popen([BINARY, str(r), str(world), str(tmp_path), *extra],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for r in range(world)]
     outs = []
     for p in procs:
         try:
@@ -37,6 +38,12 @@ def _run(world, tmp_path):
 
 def test_one_rank_is_the_local_table(tmp_path, product_lib):
     _run(1, tmp_path)
+
+
+def test_workspaces_supplied_by_the_caller(tmp_path, product_lib):
+    """hkv_sharded_create_external: the library adopts memory it did not
+    allocate, cannot export it and does not free it."""
+    _run(1, tmp_path, "external")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
