@@ -373,6 +373,13 @@ template <class T>
 __device__ __forceinline__ void st_stream(T* p, const T& v) {
   __stcs(p, v);
 }
+// A load from a buffer that may be another GPU's memory and that its owner
+// rewrites between this GPU's launches: never served from L1 (ld.global.cv
+// fetches again whatever the cache holds).
+template <class T>
+__device__ __forceinline__ T ld_peer(const T* p) {
+  return __ldcv(p);
+}
 // __ldcs/__stcs have no 1- and 2-byte unsigned overloads for every toolkit;
 // narrow rows are rare, plain accesses are enough for them.
 template <>
@@ -536,7 +543,7 @@ __device__ __forceinline__ void warp_move_rows_vec(const TableView& t, uint8_t* 
         if (MODE == 0) {
           regs[u] = ld_table_row<T>(tab[u], !PURE && rs >= t.hbm_slots);
         } else if (INDEXED) {
-          regs[u] = *reinterpret_cast<const T*>(bat[u]);
+          regs[u] = ld_peer(reinterpret_cast<const T*>(bat[u]));
         } else {
           regs[u] = ld_stream(reinterpret_cast<const T*>(batch_rows + size_t(c) * VEC));
         }

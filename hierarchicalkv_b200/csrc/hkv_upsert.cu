@@ -352,7 +352,7 @@ __device__ __forceinline__ void serve_gather_vec(const TableView& t, const Route
         if (f == kMaxRequests) {
           cur[u] = ld_table_row<T>(tab[u], !PURE && rs >= t.hbm_slots);
         } else {
-          cur[u] = *reinterpret_cast<const T*>(request_row(rw->requests[f][column[u]], off[u]));
+          cur[u] = ld_peer(reinterpret_cast<const T*>(request_row(rw->requests[f][column[u]], off[u])));
         }
       }
     }
@@ -972,7 +972,7 @@ __global__ void __launch_bounds__(kMutateBlock)
           const uint32_t row = words[q] & kRowTagMask;
           words[q] = (rank << kRowTagShift) | row;
           if (with_flags) {
-            if (static_cast<const bool*>(r.flags_of.p[rank])[row]) accumulating |= 1u << q;
+            if (ld_peer(static_cast<const uint8_t*>(r.flags_of.p[rank]) + row)) accumulating |= 1u << q;
             else if (first_assign == kMaxRequests) first_assign = q;
           }
         }
@@ -1051,6 +1051,14 @@ __global__ void __launch_bounds__(kMutateBlock, routed_min_blocks(OP))
     if (base < n) mutate_warp<OP, VEC, true>(t, args, base, n, &rw);
     __syncwarp();  // the warp's columns of the parked results and requests are reused
   }
+  // Rows found by find_or_insert went to other GPUs, and the requesters overwrite
+  // those buffers (the next operation's rows) as soon as the barrier that
+  // follows lets them.  That barrier's own system-scope fence orders the stores
+  // before its flags; this one, by the writers themselves, costs a few per
+  // cent of the step and stays as a second line until the replay check of the
+  // step, which failed at eight ranks on symmetric-memory workspaces, is
+  // understood.
+  __threadfence_system();
 }
 
 // ---- serialising kernel for batches that may repeat a key -------------------
