@@ -248,7 +248,11 @@ class ShardedHashTable:
         "ipc" lets the library allocate them and exchanges their CUDA IPC
         handles; "auto" tries the former and falls back to the latter.  Peer
         stores into IPC-mapped cudaMalloc memory measured much slower at eight
-        GPUs (find 13.5 against 20.0 B-KV/s), level at two and four.  With
+        GPUs (find 13.5 against 20.1 B-KV/s), level at two and four; the
+        updates (upsert_fused), on the other hand, have passed their
+        bit-for-bit replay check at eight ranks only on "ipc" workspaces (on
+        symmetric memory at two and four), so a table that is updated across
+        more than four ranks should keep a host with memory="ipc" for that.  With
         ``lanes`` > 1 there are that many independent workspaces (own inbox,
         flags, epochs and streams) for find_fused_async, which rotates through
         them so the routing of one batch overlaps the lookup of the previous
