@@ -319,17 +319,19 @@ def _routed_call(lib, table, op, world, my_rank, cap_seg, inbox_keys, inbox_orig
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("world,me", [(3, 1), (8, 5), (16, 0)])
 @pytest.mark.parametrize("dim", [8, 5])
-def test_upsert_routed_applies_the_ranks_one_after_the_other(dim):
-    """The owner side of the fused sharded update on one GPU: three source
+def test_upsert_routed_applies_the_ranks_one_after_the_other(dim, world, me):
+    """The owner side of the fused sharded update on one GPU: several source
     ranks' inbox segments, their batch buffers standing in for peer memory.
-    Keys that several ranks send are applied in the order rank owner + 1,
-    owner + 2, ... -- checked against the CPU oracle fed in that order."""
+    Keys that several ranks send (with eight and sixteen ranks most keys come
+    from most ranks) are applied in the order rank owner + 1, owner + 2, ...
+    -- checked against the CPU oracle fed in that order."""
     import hierarchicalkv_b200 as hkv
     from hierarchicalkv_b200.sharded import CudaOps
 
     lib = CudaOps().lib
-    world, me, cap_seg, nbuf = 3, 1, 2048, 3000
+    cap_seg, nbuf = 2048, 3000
     cap = 128 * 64
     t = hkv.HashTable(hkv.EvictStrategy.kLru)
     t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
@@ -428,6 +430,83 @@ def test_upsert_routed_applies_the_ranks_one_after_the_other(dim):
     assert lib.hkv_upsert_routed(lfu.handle, 0, world, me, cap_seg, ik.data_ptr(), io.data_ptr(),
                                  cnt.data_ptr(), ctypes.byref(pv), None, None) != 0
     lfu.close()
+    t.close()
+
+
+@pytest.mark.parametrize("world,me", [(2, 0), (8, 3)])
+def test_upsert_routed_steps_back_to_back(world, me):
+    """The sharded embedding step as the owner sees it, several steps without a
+    host synchronisation in between: find_or_insert of every rank's keys, then
+    accum_or_assign of deltas for the same inbox (the route is reused), with
+    keys most ranks share and buffers that are rewritten between the calls.
+    The table must hold what the CPU oracle holds when the ranks' batches are
+    applied in the order owner + 1, owner + 2, ..."""
+    import ctypes
+
+    import hierarchicalkv_b200 as hkv
+    from hierarchicalkv_b200.sharded import CudaOps, _PeerPtrs
+
+    lib = CudaOps().lib
+    dim, cap_seg, nbuf, cap = 8, 1024, 1024, 128 * 64
+    t = hkv.HashTable(hkv.EvictStrategy.kLru)
+    t.init(hkv.HashTableOptions(init_capacity=cap, max_capacity=cap, max_hbm_for_vectors=1 << 30,
+                                dim=dim))
+    o = OracleTable(cap, dim, 0)
+    keys = unique_keys(3000, seed=17)
+    rng = np.random.default_rng(23)
+    order = [(me + 1 + k) % world for k in range(world)]
+    bufs = [torch.zeros((nbuf, dim), device="cuda") for _ in range(world)]
+    flags = [torch.ones(nbuf, dtype=torch.bool, device="cuda") for _ in range(world)]
+    pv, pf = _PeerPtrs(), _PeerPtrs()
+    for r in range(world):
+        pv.p[r], pf.p[r] = bufs[r].data_ptr(), flags[r].data_ptr()
+    inbox_k = torch.zeros(world * cap_seg, dtype=torch.int64, device="cuda")
+    inbox_o = torch.zeros(world * cap_seg, dtype=torch.int32, device="cuda")
+    counts = torch.zeros(16, dtype=torch.int64, device="cuda")
+
+    def call(op):
+        rc = lib.hkv_upsert_routed(t.handle, op, world, me, cap_seg, inbox_k.data_ptr(),
+                                   inbox_o.data_ptr(), counts.data_ptr(), ctypes.byref(pv),
+                                   ctypes.byref(pf), None)
+        assert rc == 0, (lib.hkv_last_error() or b"").decode()
+
+    steps = []
+    for step in range(6):
+        hot = keys[:300]                                   # every rank sends these in every step
+        per = {}
+        for r in range(world):
+            own = rng.choice(keys[300:], size=int(rng.integers(200, 600)), replace=False)
+            kk = np.concatenate([hot, own])
+            at = rng.permutation(nbuf)[:kk.size].astype(np.int32)
+            init = values_for(kk, dim, seed=100 * step + r)
+            delta = values_for(kk, dim, seed=5000 + 100 * step + r) * np.float32(1e-3)
+            per[r] = (kk, at, init, delta)
+            inbox_k[r * cap_seg: r * cap_seg + kk.size] = to_dev(kk)
+            inbox_o[r * cap_seg: r * cap_seg + kk.size] = torch.from_numpy(at).cuda()
+            counts[r] = kk.size
+            bufs[r][torch.from_numpy(at.astype(np.int64)).cuda()] = torch.from_numpy(init).cuda()
+        call(1)                                            # find_or_insert: rows come back
+        for r in range(world):                             # the "gradients" take their place
+            kk, at, init, delta = per[r]
+            bufs[r][torch.from_numpy(at.astype(np.int64)).cuda()] = torch.from_numpy(delta).cuda()
+        call(2)                                            # accum_or_assign on the same inbox
+        steps.append(per)
+    torch.cuda.synchronize()
+    for per in steps:
+        for r in order:
+            kk, at, init, delta = per[r]
+            o.find_or_insert(kk, init)
+        for r in order:
+            kk, at, init, delta = per[r]
+            o.accum_or_assign(kk, delta, np.ones(kk.size, dtype=bool))
+    out = torch.zeros((keys.size, dim), device="cuda")
+    f = torch.zeros(keys.size, dtype=torch.bool, device="cuda")
+    t.find(keys.size, to_dev(keys), out, f)
+    torch.cuda.synchronize()
+    want, wf, _ = o.find(keys)
+    np.testing.assert_array_equal(f.cpu().numpy(), wf)
+    np.testing.assert_array_equal(out.cpu().numpy()[wf].view(np.uint32), want[wf].view(np.uint32))
+    assert t.device_status() == 0
     t.close()
 
 
