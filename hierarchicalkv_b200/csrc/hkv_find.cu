@@ -10,6 +10,8 @@
 // warp-cooperative streaming gather of the hit rows.
 #include <cub/device/device_radix_sort.cuh>
 
+#include <cstdlib>
+
 #include "hkv_device.cuh"
 #include "hkv_internal.h"
 
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(kFindBlock)
                        const uint32_t first_segment, const uint64_t segment_capacity, const uint64_t* __restrict__ inbox_keys,
                        const uint32_t* __restrict__ inbox_origin,
                        const uint64_t* __restrict__ inbox_counts, const PeerPtrs out_values,
-                       const PeerPtrs out_founds) {
+                       const PeerPtrs out_founds, const bool writers_fence) {
   // The key counts are only known on the device, so the grid covers every
   // segment's full capacity and blocks beyond a segment's count leave at once.
   const ProbeLane pl = probe_lane();
@@ -213,6 +215,11 @@ __global__ void __launch_bounds__(kFindBlock)
   const uint32_t slot = warp_probe_readonly(t, pl, key, valid, a);
   if (present) founds_of[origin] = slot != kNoSlot ? 1 : 0;
   warp_gather_rows_to<VEC>(t, values_of, origin, slot, pl.lane);
+  // Rows and flags went to other GPUs; the barrier kernel that follows orders
+  // them before its flags with a system-scope fence of its own.  The strict
+  // form, in which every storing thread also fences its own stores before it
+  // leaves, costs 14 % of the two-GPU lookup and is off unless asked for.
+  if (writers_fence) __threadfence_system();
 }
 
 // find on a dual-bucket table (include/merlin/core_kernels/dual_bucket_lookup.cuh):
@@ -438,12 +445,18 @@ void launch_find_routed(const TableView& t, uint32_t world, uint32_t my_rank,
                         const uint64_t* inbox_counts, const PeerPtrs& out_values,
                         const PeerPtrs& out_founds, cudaStream_t stream) {
   if (segment_capacity == 0) return;
+  // HKV_STRICT_PEER_ORDER=1 in the environment: every thread that stored rows
+  // into a peer's buffer fences them at system scope before it exits
+  static const bool writers_fence = [] {
+    const char* e = std::getenv("HKV_STRICT_PEER_ORDER");
+    return e != nullptr && e[0] == '1';
+  }();
   const uint64_t per_segment = (segment_capacity + kFindBlock - 1) / kFindBlock;
   auto kernel = fast_rows(t) ? find_routed_kernel<16> : find_routed_kernel<0>;
   kernel<<<static_cast<unsigned>(per_segment * world), kFindBlock, 0, stream>>>(
       t, world, (my_rank + 1) % world, segment_capacity,
       inbox_keys, inbox_origin,
-      inbox_counts, out_values, out_founds);
+      inbox_counts, out_values, out_founds, writers_fence);
 }
 
 void launch_contains(const TableView& t, uint64_t n, const uint64_t* keys, bool* founds,
