@@ -434,8 +434,9 @@ HKV_API int hkv_upsert_routed(hkv_table* table, int op, uint32_t world, uint32_t
 /* ---- the sharded table's host side -----------------------------------------
  * No counterpart in the reference.  One hkv_sharded per rank (one rank per GPU;
  * ranks are processes, or threads of one process) wraps that rank's sub-table
- * and owns its peer workspaces ("lanes": inbox of routed keys, barrier flags,
- * batch / result buffers, allocated with cudaMalloc so that they can be shared).
+ * and its peer workspaces ("lanes": inbox of routed keys, barrier flags, batch /
+ * result buffers; allocated here with cudaMalloc and shared over CUDA IPC, or
+ * supplied by the caller -- hkv_sharded_create_external).
  * Set-up, once:
  *   1. every rank: hkv_sharded_create;
  *   2. ranks in different processes exchange hkv_sharded_ipc_handle of every
